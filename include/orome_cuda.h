@@ -1,0 +1,223 @@
+/*
+ * orome_cuda.h -- C ABI of the B200 (sm_100a) implementation of Orome's
+ * quantized dequant-matvec path.
+ *
+ * The library replaces, for an NVIDIA B200, the part of Orome's "format" layer
+ * through which the engine issues every weight-bound product of a decode step:
+ * the GGUF block-quantized matvec (Q8_0 / Q4_K / Q5_K / Q6_K), the fused
+ * gate/up + SwiGLU forms, the batched (prefill) form and the MoE top-k expert
+ * gather-matvec.  Each declaration cites the reference interface it replaces
+ * (paths are relative to the Orome source tree).
+ *
+ * Conventions
+ *   - Plain C types only: pointers, sizes, enums.  `stream` arguments are a
+ *     cudaStream_t passed as void* (NULL = the legacy default stream).
+ *   - Every compute entry point only ENQUEUES work on the given stream and never
+ *     synchronises, like the reference's encoder-style dispatch
+ *     (format.m:240-303 returns after dispatchThreadgroups).  Ordering between
+ *     dependent calls is stream order; that replaces the reference's explicit
+ *     memoryBarrierWithScope calls (engine.m:564, 594, 624, ...).
+ *   - Return value: 0 on success, a negative errno-style code on a rejected
+ *     call (OROME_EINVAL, OROME_ENOTSUP, OROME_ECUDA ...), and
+ *     orome_cuda_last_error() gives the message.  The reference returns void and
+ *     prints to stderr (format.m:260-264); a NULL weight buffer is a silent
+ *     no-op returning 0, which keeps the reference's optional-tensor convention
+ *     (format.m:247-250).
+ *   - A context is not thread-safe (neither is the reference's MetalCtx).
+ *   - All device pointers must belong to the context's device.  Weight tensors
+ *     must start on a 16-byte boundary (GGUF aligns tensor data to 32 bytes,
+ *     gguf.m:323) and activations / outputs on a 16-byte boundary.
+ */
+#ifndef OROME_CUDA_H
+#define OROME_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------- */
+#define OROME_OK        0
+#define OROME_EINVAL   (-22)   /* bad dimensions, NULL where not allowed, misaligned pointer */
+#define OROME_ENOTSUP  (-95)   /* format / variant combination without a kernel               */
+#define OROME_ENOMEM   (-12)   /* device allocation failed                                   */
+#define OROME_ECUDA    (-5)    /* a CUDA runtime call failed (message has the CUDA error)     */
+#define OROME_ETIMEOUT (-110)  /* a bounded device-side wait gave up (see orome_cuda_status)   */
+
+/* ---- types mirrored from inference/include/orome.h ---------------------- */
+
+/* QuantFormat, orome.h:227-235 -- same enumerators in the same order. */
+typedef enum {
+    OROME_QFMT_GGUF_Q4_K = 0,   /* 256 weights in a 144-byte superblock */
+    OROME_QFMT_GGUF_Q5_K = 1,   /* 256 weights in a 176-byte superblock */
+    OROME_QFMT_GGUF_Q6_K = 2,   /* 256 weights in a 210-byte superblock */
+    OROME_QFMT_GGUF_Q8_0 = 3,   /* 32 int8 weights + fp16 scale, 34 bytes */
+    OROME_QFMT_F16       = 4,
+    OROME_QFMT_BF16      = 5,
+    OROME_QFMT_F32       = 6
+} OromeQuantFormat;
+
+/* Kernel family, the role `pipeline` plays in the reference's TensorRef.
+ * DEFAULT reads the six-bit K-quant scales the way the reference's CPU decode
+ * and default kernels do (format.m:41-64, shaders.metal:1413-1436).  LLAMA reads
+ * them the way the reference's `_llama` kernels do (shaders.metal:1575-1578,
+ * 2053-2056), which is what engine_qwen35_hybrid.m:86-148 selects for the 27B
+ * model.  The two differ on sub-blocks 4..7; all other arithmetic is shared. */
+typedef enum {
+    OROME_VARIANT_DEFAULT = 0,
+    OROME_VARIANT_LLAMA   = 1
+} OromeKernelVariant;
+
+/* TensorRef, orome.h:239-246.  `buffer` is a device pointer instead of an
+ * id<MTLBuffer>; `variant` stands where the reference keeps the pipeline. */
+typedef struct {
+    void            *buffer;     /* device allocation holding the tensor (NULL = absent tensor) */
+    size_t           offset;     /* byte offset of the tensor inside `buffer`                   */
+    uint32_t         variant;    /* OromeKernelVariant                                          */
+    OromeQuantFormat format;
+    uint32_t         out_dim;    /* rows                                                        */
+    uint32_t         in_dim;     /* columns (weights per row)                                   */
+} OromeTensorRef;
+
+/* ExpertProjRef / ExpertLayerRef, orome.h:249-259: expert e of a projection
+ * starts at buffer + offset + e * expert_stride (format.m:381-406). */
+typedef struct {
+    size_t           offset;
+    size_t           expert_stride;
+    OromeQuantFormat format;
+} OromeExpertProjRef;
+
+typedef struct {
+    void              *buffer;
+    OromeExpertProjRef gate, up, down;
+} OromeExpertLayerRef;
+
+typedef struct orome_cuda_ctx orome_cuda_ctx;
+
+/* ---- context, memory, errors ------------------------------------------- */
+
+/* Replaces metal_setup / metal_free (orome.h:219-221, metal.m:41) for this path:
+ * binds a CUDA device, allocates the context's status word.  No scratch is sized
+ * from a model config; the path's kernels need none beyond their outputs. */
+int  orome_cuda_ctx_create(int device, orome_cuda_ctx **out);
+void orome_cuda_ctx_destroy(orome_cuda_ctx *ctx);
+
+/* Message of the last failed call on this thread ("" if none). */
+const char *orome_cuda_last_error(void);
+
+/* Device-side status word: 0, or the code left by a kernel whose bounded wait
+ * on its own copy pipeline ran out.  Synchronises the context's device. */
+int  orome_cuda_status(orome_cuda_ctx *ctx, int *status_out);
+
+/* Replaces format_provider_open_gguf (format.m:343-363).  The reference wraps
+ * the mmap'd file as one no-copy buffer (unified memory); a discrete GPU needs
+ * the bytes in HBM, so this copies `bytes` bytes to a new 256-byte aligned
+ * device allocation.  Offsets relative to `host` stay valid relative to
+ * `*dev_base`, so TensorRef.offset = data_offset + tensor offset is unchanged
+ * (format.m:422). */
+int  orome_cuda_upload(orome_cuda_ctx *ctx, const void *host, size_t bytes, void **dev_base);
+int  orome_cuda_free(orome_cuda_ctx *ctx, void *dev_base);
+
+/* ---- format helpers ------------------------------------------------------ */
+
+/* format_from_ggml_type, format.m:326-337 (unknown ids map to Q4_K, line 335). */
+OromeQuantFormat orome_format_from_ggml_type(uint32_t ggml_type);
+
+/* Bytes of one row; 0 if in_dim is not a whole number of blocks
+ * (row strides of format.m:198, 203, 208, 213). */
+size_t orome_format_row_bytes(OromeQuantFormat format, uint32_t in_dim);
+
+/* ---- the hot path -------------------------------------------------------- */
+
+/* format_dispatch_matvec, format.m:240-303 / orome.h:319-322.
+ * y[out_dim] = W[out_dim][in_dim] . x[in_dim], x and y fp32.  in_buf/in_off and
+ * out_buf/out_off are a device buffer and a byte offset, exactly the reference's
+ * (buffer, offset) pairs. */
+int  orome_format_dispatch_matvec(orome_cuda_ctx *ctx, const OromeTensorRef *ref,
+                                  const void *in_buf, size_t in_off,
+                                  void *out_buf, size_t out_off, void *stream);
+
+/* Batched form of the same product: y[b][r] = sum_c W[r][c] x[b][c] for
+ * b < batch, x row stride ldx, y row stride ldy (in floats).  batch == 1 is the
+ * decode matvec; larger batches are the prefill form, which the reference runs
+ * as one matvec per token (main.m:745-747). */
+int  orome_cuda_matvec(orome_cuda_ctx *ctx, const OromeTensorRef *ref,
+                       const float *x_dev, float *y_dev, int batch, int ldx, int ldy, void *stream);
+
+/* Several tensors that share one input vector in a single launch (the
+ * reference encodes q/k/v projections back to back with no barrier between
+ * them, engine.m:554-563, 777-784, so they run concurrently).  y_dev[i] receives
+ * refs[i].out_dim floats.  All refs must share format, variant and in_dim. */
+int  orome_cuda_matvec_group(orome_cuda_ctx *ctx, const OromeTensorRef *refs, int n_refs,
+                             const float *x_dev, float *const *y_dev, void *stream);
+
+/* Fused gate/up + SwiGLU: out[b][r] = silu(Wg x_b)[r] * (Wu x_b)[r], silu(g) = g / (1 + exp(-g)).
+ * Replaces shared_gate_up_swiglu_q4k / _q8_0 and fused_gate_up_swiglu_q4k_llama
+ * (shaders.metal:2316-2445, 2451-2584) as dispatched by encode_dense_ffn
+ * (engine.m:342-392).  gate and up must have identical shape and format. */
+int  orome_cuda_gate_up_swiglu(orome_cuda_ctx *ctx, const OromeTensorRef *gate, const OromeTensorRef *up,
+                               const float *x_dev, float *out_dev, int batch, int ldx, int ldo, void *stream);
+
+/* Device counterpart of format_decode_row_f32 (format.m:176-218, orome.h:325):
+ * decodes rows [row0, row0 + nrows) to out_dev[nrows][in_dim], bit-identical to
+ * the reference's CPU decode (also the embedding lookup of engine.m:122-141). */
+int  orome_cuda_dequant_rows(orome_cuda_ctx *ctx, const OromeTensorRef *ref,
+                             uint32_t row0, uint32_t nrows, float *out_dev, void *stream);
+
+/* MoE routing: logits = Wr x per token (matvec_f32 / matvec_f32_pair,
+ * shaders.metal:1342-1392, engine.m:656-684) followed by softmax_topk_route
+ * (shaders.metal:1141-1234): K rounds of arg-max, ties to the lowest index,
+ * softmax over the selected logits only, K capped at 8, n_experts <= 256.
+ * idx_dev[t][8] and w_dev[t][8] (slots >= K zero-filled) per token t.
+ * `router` must be an F32 tensor [n_experts][hidden]. */
+int  orome_cuda_moe_route(orome_cuda_ctx *ctx, const OromeTensorRef *router,
+                          const float *x_dev, int n_tokens, int ldx, uint32_t K,
+                          uint32_t *idx_dev, float *w_dev, float *logits_dev /* optional [t][n_experts] */,
+                          void *stream);
+
+/* Routed-expert FFN with the weighted combine, replacing
+ * batch_expert_gate_up_swiglu_q4k_dyn, batch_expert_down_q4k_dyn / _q5k_dyn and
+ * the expert term of moe_combine_copy_sq (shaders.metal:2232-2310, 2590-2760,
+ * 1049-1055) as sequenced by encode_experts_gguf (engine.m:158-340):
+ *   out[t][h] = sum_{k<K} w[t][k] * ( Wd[e] ( silu(Wg[e] x_t) * (Wu[e] x_t) ) )[h],  e = idx[t][k].
+ * idx/w use the [t][8] layout written by orome_cuda_moe_route.  act_dev is
+ * caller-provided scratch of n_tokens * K * inter floats (the reference's
+ * buf_batch_expert_act, orome.h:189).  The shared-expert term and the residual
+ * add of the reference's combine kernel are outside this entry point. */
+int  orome_cuda_moe_ffn(orome_cuda_ctx *ctx, const OromeExpertLayerRef *layer, uint32_t variant,
+                        const float *x_dev, int n_tokens, int ldx,
+                        const uint32_t *idx_dev, const float *w_dev, uint32_t K,
+                        uint32_t hidden, uint32_t inter, float *act_dev, float *out_dev, int ldo,
+                        void *stream);
+
+/* ---- host-buffer convenience (end-to-end form) --------------------------- */
+
+/* Same product as orome_cuda_matvec with HOST x and y: copies x to the device,
+ * runs the kernel, copies y back and waits.  Staging buffers are owned by the
+ * context and grow on demand. */
+int  orome_cuda_matvec_host(orome_cuda_ctx *ctx, const OromeTensorRef *ref,
+                            const float *x_host, float *y_host, int batch);
+
+/* ---- tuning knobs -------------------------------------------------------- */
+
+/* Integer options; unknown keys return OROME_EINVAL.
+ *   OROME_OPT_X_BITS      16 or 24: fixed-point width used for x inside the
+ *                         quantized matvec kernels (default 24).
+ *   OROME_OPT_FORCE_GENERIC  1 = always use the plain (non-pipelined) kernels. */
+#define OROME_OPT_X_BITS         1
+#define OROME_OPT_FORCE_GENERIC  2
+#define OROME_OPT_STAGE_KB       3
+#define OROME_OPT_CTAS_PER_SM    4
+#define OROME_OPT_PDL            5
+int  orome_cuda_set_option(orome_cuda_ctx *ctx, int key, int value);
+int  orome_cuda_get_option(orome_cuda_ctx *ctx, int key, int *value);
+
+/* Number of kernel launches issued through this context since creation. */
+uint64_t orome_cuda_launch_count(orome_cuda_ctx *ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OROME_CUDA_H */

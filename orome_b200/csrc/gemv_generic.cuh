@@ -1,0 +1,92 @@
+// gemv_generic.cuh -- shape-agnostic kernels: row decode, warp-per-row matvec for
+// any format / batch, SwiGLU epilogue.  They take every shape the formats allow;
+// the pipelined kernels in gemv_pipe.cuh take over for the decode-sized ones.
+#pragma once
+#include "decode.cuh"
+
+namespace orome {
+
+// One thread per 32-weight group: out[(r - row0) * in_dim + 32*b .. +32].
+// Device counterpart of format_decode_row_f32 (format.m:176-218).
+template <int FMT>
+__global__ void dequant_rows_kernel(const uint8_t *__restrict__ data, size_t row_bytes, uint32_t row0, uint32_t nrows,
+                                    uint32_t in_dim, int layout, float *__restrict__ out)
+{
+    uint32_t groups = in_dim / 32;
+    size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (gid >= (size_t)nrows * groups) return;
+    uint32_t r = (uint32_t)(gid / groups), b = (uint32_t)(gid % groups);
+    float w[32];
+    decode32<FMT>(data + (size_t)(row0 + r) * row_bytes, b, layout, w);
+    float4 *o = reinterpret_cast<float4 *>(out + (size_t)r * in_dim + (size_t)b * 32);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = make_float4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+}
+
+// Tail of an unquantized row whose length is not a multiple of 32 (F32/F16/BF16 only).
+template <int FMT>
+__device__ __forceinline__ float plain_elem(const uint8_t *row, uint32_t c)
+{
+    if constexpr (FMT == FMT_F32) return reinterpret_cast<const float *>(row)[c];
+    else if constexpr (FMT == FMT_F16) return half_bits_to_float(ld16(row + 2 * (size_t)c));
+    else return __uint_as_float(ld16(row + 2 * (size_t)c) << 16);
+}
+
+// y[b][r] = sum_c W[r][c] x[b][c]; one warp per row, lanes stride over 32-weight
+// groups, NB batch columns per pass (the weights are decoded once per pass).
+template <int FMT, int NB>
+__global__ void __launch_bounds__(256)
+gemv_generic_kernel(const uint8_t *__restrict__ data, size_t row_bytes, uint32_t out_dim, uint32_t in_dim, int layout,
+                    const float *__restrict__ x, int batch, int ldx, float *__restrict__ y, int ldy)
+{
+    uint32_t row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    uint32_t lane = threadIdx.x & 31;
+    if (row >= out_dim) return;
+    const uint8_t *rp = data + (size_t)row * row_bytes;
+    uint32_t groups = in_dim / 32;
+    for (int b0 = 0; b0 < batch; b0 += NB) {
+        float acc[NB];
+#pragma unroll
+        for (int i = 0; i < NB; ++i) acc[i] = 0.0f;
+        for (uint32_t g = lane; g < groups; g += 32) {
+            float w[32];
+            decode32<FMT>(rp, g, layout, w);
+#pragma unroll
+            for (int i = 0; i < NB; ++i) {
+                if (b0 + i < batch) {
+                    const float *xb = x + (size_t)(b0 + i) * ldx + (size_t)g * 32;
+                    float a = 0.0f;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) a = fmaf(w[j], xb[j], a);
+                    acc[i] += a;
+                }
+            }
+        }
+        if constexpr (FMT == FMT_F32 || FMT == FMT_F16 || FMT == FMT_BF16) {
+            for (uint32_t c = groups * 32 + lane; c < in_dim; c += 32) {
+                float wv = plain_elem<FMT>(rp, c);
+#pragma unroll
+                for (int i = 0; i < NB; ++i)
+                    if (b0 + i < batch) acc[i] = fmaf(wv, x[(size_t)(b0 + i) * ldx + c], acc[i]);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < NB; ++i) {
+            float s = warp_sum(acc[i]);
+            if (lane == 0 && b0 + i < batch) y[(size_t)(b0 + i) * ldy + row] = s;
+        }
+    }
+}
+
+// out = silu(gate) * up, elementwise (shaders.metal:1018-1030); used after two
+// generic matvecs when the fused kernel does not take the shape.
+__global__ void swiglu_kernel(const float *__restrict__ gate, const float *__restrict__ up, float *__restrict__ out,
+                              uint32_t n, int batch, int ldg, int ldo)
+{
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)n * batch) return;
+    uint32_t b = (uint32_t)(i / n), c = (uint32_t)(i % n);
+    out[(size_t)b * ldo + c] = silu_mul(gate[(size_t)b * ldg + c], up[(size_t)b * ldg + c]);
+}
+
+}  // namespace orome

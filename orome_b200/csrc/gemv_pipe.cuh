@@ -1,0 +1,532 @@
+// gemv_pipe.cuh -- the decode matvec kernel for sm_100a.
+//
+// Design (HBM-bound byte work, no tensor cores):
+//   * The packed rows a CTA owns are one contiguous byte range of the tensor.
+//     One elected thread streams that range into a ring of shared-memory stages
+//     with 1-D bulk async copies (cp.async.bulk ... mbarrier::complete_tx), several
+//     stages deep, so tens of KB per SM are in flight without spending registers.
+//   * Every thread owns a fixed 64-weight column slot of the row ("unit" x
+//     "part") and keeps its slice of x in registers for the whole kernel, as
+//     per-group fixed point: x_i ~= s * X_i with X_i a 16- or 24-bit integer
+//     split into bytes (top byte signed, lower bytes unsigned).  The packed
+//     weights are multiplied against those bytes with dp4a, so the integer dot
+//     products are exact and the only approximation is the fixed-point
+//     rounding of x (2^-23 or 2^-15 of the group's max).
+//   * Per-row partial sums go through shared memory; one warp per row adds
+//     them and writes y (or silu(g)*u for the fused gate/up form).
+//   * The kernel starts its weight copies before griddepcontrol.wait, so under
+//     programmatic dependent launch they overlap the previous kernel's tail;
+//     only x (the previous kernel's output) is read after the wait.
+//   * Every wait on a copy barrier is bounded by a timer; on expiry the kernel
+//     records a code in the status word, stops waiting and runs to completion.
+#pragma once
+#include "decode.cuh"
+
+namespace orome {
+
+constexpr int PIPE_MAX_SEG = 8;
+constexpr int PIPE_MAX_STAGES = 16;
+constexpr int PIPE_MAX_THREADS = 512;
+constexpr uint32_t PIPE_WAIT_NS = 1000000000u;   // 1 s per wait
+
+struct PipeSeg {
+    const uint8_t *w;     // tensor (gate tensor in the fused form)
+    const uint8_t *w2;    // up tensor in the fused form, else unused
+    float *y;             // output rows of this segment
+    uint32_t rows;
+    uint32_t vstart;      // first virtual row (segments are concatenated)
+};
+
+struct PipeArgs {
+    PipeSeg seg[PIPE_MAX_SEG];
+    int nseg;
+    const float *x;
+    uint32_t in_dim, row_bytes;
+    uint32_t units;            // column units per row (64 weights for Q8_0, one superblock for K-quants)
+    uint32_t rows_par;         // rows processed side by side
+    uint32_t rows_per_stage;   // multiple of rows_par
+    uint32_t nstages;
+    uint32_t stage_stride;     // bytes between stages
+    uint32_t half_stride;      // offset of the second tensor's rows inside a stage (fused form)
+    uint32_t stage_base;       // offset of stage 0 in dynamic shared memory
+    uint32_t red_floats;       // floats per reduction buffer (per tensor)
+    uint32_t total_rows;
+    int layout;
+    int *status;
+};
+
+// ---- PTX wrappers ---------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ uint64_t global_ns()
+{
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Wait for a phase of a copy barrier, at most PIPE_WAIT_NS.  Returns false on expiry.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    uint64_t t0 = global_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (global_ns() - t0 > PIPE_WAIT_NS) return false;
+    }
+}
+
+__device__ __forceinline__ int dp4a_ss(uint32_t a, uint32_t b, int c)
+{
+    int d; asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c)); return d;
+}
+__device__ __forceinline__ int dp4a_su(uint32_t a, uint32_t b, int c)
+{
+    int d; asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c)); return d;
+}
+__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c)
+{
+    int d; asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c)); return d;
+}
+__device__ __forceinline__ int dp4a_uu(uint32_t a, uint32_t b, int c)
+{
+    uint32_t d; asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"((uint32_t)c)); return (int)d;
+}
+
+// ---- x as per-group fixed point -------------------------------------------
+// pc[p][k]: byte p of X_{4k..4k+3}, packed little-endian; piece NP-1 is the signed top byte.
+template <int NP, int N>
+struct XGroup {
+    uint32_t pc[NP][N / 4];
+    float scale;
+};
+
+template <int NP, int N>
+__device__ __forceinline__ void quantize_group(const float (&xv)[N], XGroup<NP, N> &g)
+{
+    constexpr float QMAX = NP == 3 ? 8388607.0f : 32767.0f;
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < N; ++i) amax = fmaxf(amax, fabsf(xv[i]));
+    float inv = amax > 0.0f ? QMAX / amax : 0.0f;
+    g.scale = amax / QMAX;
+#pragma unroll
+    for (int k = 0; k < N / 4; ++k) {
+        int X[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            int v = __float2int_rn(xv[4 * k + j] * inv);
+            X[j] = max(-(int)QMAX, min((int)QMAX, v));
+        }
+#pragma unroll
+        for (int p = 0; p < NP; ++p) {
+            uint32_t sel = (uint32_t)p | ((uint32_t)(4 + p) << 4);
+            uint32_t lo = __byte_perm((uint32_t)X[0], (uint32_t)X[1], sel);
+            uint32_t hi = __byte_perm((uint32_t)X[2], (uint32_t)X[3], sel);
+            g.pc[p][k] = __byte_perm(lo, hi, 0x5410);
+        }
+    }
+}
+
+// sum_i q_i X_i from per-byte partial dot products I[p] = sum_i q_i * byte_p(X_i)
+template <int NP>
+__device__ __forceinline__ float combine(const int (&I)[NP])
+{
+    if constexpr (NP == 3) return fmaf((float)I[2], 65536.0f, (float)(I[1] * 256 + I[0]));
+    else return (float)(I[1] * 256 + I[0]);
+}
+
+// unsigned weight bytes against the pieces of one word of x
+template <int NP, int N>
+__device__ __forceinline__ void dot_u(uint32_t q, const XGroup<NP, N> &g, int k, int (&I)[NP])
+{
+#pragma unroll
+    for (int p = 0; p < NP; ++p) I[p] = (p == NP - 1) ? dp4a_us(q, g.pc[p][k], I[p]) : dp4a_uu(q, g.pc[p][k], I[p]);
+}
+// signed weight bytes
+template <int NP, int N>
+__device__ __forceinline__ void dot_s(uint32_t q, const XGroup<NP, N> &g, int k, int (&I)[NP])
+{
+#pragma unroll
+    for (int p = 0; p < NP; ++p) I[p] = (p == NP - 1) ? dp4a_ss(q, g.pc[p][k], I[p]) : dp4a_su(q, g.pc[p][k], I[p]);
+}
+
+__device__ __forceinline__ void load_x(const float *__restrict__ x, float *dst, int n)
+{
+    const float4 *p = reinterpret_cast<const float4 *>(x);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        if (i * 4 < n) {
+            float4 v = __ldg(p + i);
+            dst[4 * i] = v.x; dst[4 * i + 1] = v.y; dst[4 * i + 2] = v.z; dst[4 * i + 3] = v.w;
+        }
+    }
+}
+
+// 16 bytes from a shared address that is only 2-byte aligned (reads 20 aligned bytes).
+__device__ __forceinline__ void lds16_a2(const uint8_t *p, uint32_t (&o)[4])
+{
+    uintptr_t a = reinterpret_cast<uintptr_t>(p);
+    const uint32_t *q = reinterpret_cast<const uint32_t *>(a & ~(uintptr_t)3);
+    uint32_t sel = (a & 2) ? 0x5432u : 0x3210u;
+    uint32_t v0 = q[0], v1 = q[1], v2 = q[2], v3 = q[3], v4 = q[4];
+    o[0] = __byte_perm(v0, v1, sel); o[1] = __byte_perm(v1, v2, sel);
+    o[2] = __byte_perm(v2, v3, sel); o[3] = __byte_perm(v3, v4, sel);
+}
+
+// 8 bytes from a shared address that is only 2-byte aligned (reads 12 aligned bytes).
+__device__ __forceinline__ void lds8_a2(const uint8_t *p, uint32_t (&o)[2])
+{
+    uintptr_t a = reinterpret_cast<uintptr_t>(p);
+    const uint32_t *q = reinterpret_cast<const uint32_t *>(a & ~(uintptr_t)3);
+    uint32_t sel = (a & 2) ? 0x5432u : 0x3210u;
+    uint32_t v0 = q[0], v1 = q[1], v2 = q[2];
+    o[0] = __byte_perm(v0, v1, sel); o[1] = __byte_perm(v1, v2, sel);
+}
+
+// Six-bit scales/mins of the sub-block pair (2g, 2g+1) from the three packed words
+// (bytes 0-3, 4-7, 8-11).  Layout A: format.m:41-64; layout B: shaders.metal:1575-1578.
+__device__ __forceinline__ void pair_scales(uint32_t w0, uint32_t w1, uint32_t w2, int layout, int g,
+                                            uint32_t &scA, uint32_t &scB, uint32_t &mnA, uint32_t &mnB)
+{
+    int u = g & 1, sh = 16 * u;
+    if (g < 2) {
+        scA = (w0 >> sh) & 63u; scB = (w0 >> (sh + 8)) & 63u;
+        mnA = (w1 >> sh) & 63u; mnB = (w1 >> (sh + 8)) & 63u;
+    } else {
+        uint32_t tA = ((w0 >> (sh + 6)) & 3u) << 4, tB = ((w0 >> (sh + 14)) & 3u) << 4;
+        uint32_t uA = ((w1 >> (sh + 6)) & 3u) << 4, uB = ((w1 >> (sh + 14)) & 3u) << 4;
+        if (layout == LAYOUT_A) {
+            uint32_t sp = (w2 >> (8 * u)) & 255u, mp = (w2 >> (16 + 8 * u)) & 255u;
+            scA = (sp & 15u) | tA; scB = (sp >> 4) | tB;
+            mnA = (mp & 15u) | uA; mnB = (mp >> 4) | uB;
+        } else {
+            scA = ((w2 >> sh) & 15u) | tA;        mnA = ((w2 >> (sh + 4)) & 15u) | uA;
+            scB = ((w2 >> (sh + 8)) & 15u) | tB;  mnB = ((w2 >> (sh + 12)) & 15u) | uB;
+        }
+    }
+}
+
+// ---- per-format column slots ----------------------------------------------
+template <int FMT, int NP> struct Slot;
+
+// Q8_0: unit = two blocks (68 bytes, 4-byte aligned), one part.
+template <int NP>
+struct Slot<FMT_Q8_0, NP> {
+    static constexpr int PARTS = 1, UNIT_ELEMS = 64;
+    XGroup<NP, 32> g[2];
+    __device__ __forceinline__ void load(const float *__restrict__ x, uint32_t unit, int)
+    {
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+            float xv[32];
+            load_x(x + (size_t)unit * 64 + 32 * b, xv, 32);
+            quantize_group<NP, 32>(xv, g[b]);
+        }
+    }
+    __device__ __forceinline__ float dot(const uint8_t *row, uint32_t unit, int, int) const
+    {
+        const uint32_t *w = reinterpret_cast<const uint32_t *>(row + (size_t)unit * 68);
+        uint32_t v[17];
+#pragma unroll
+        for (int i = 0; i < 17; ++i) v[i] = w[i];
+        int I0[NP], I1[NP];
+#pragma unroll
+        for (int p = 0; p < NP; ++p) { I0[p] = 0; I1[p] = 0; }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            dot_s<NP, 32>(__byte_perm(v[j], v[j + 1], 0x5432), g[0], j, I0);
+            dot_s<NP, 32>(v[9 + j], g[1], j, I1);
+        }
+        float d0 = __half2float(__ushort_as_half((unsigned short)(v[0] & 0xffffu)));
+        float d1 = __half2float(__ushort_as_half((unsigned short)(v[8] >> 16)));
+        return fmaf(d0 * g[0].scale, combine<NP>(I0), d1 * g[1].scale * combine<NP>(I1));
+    }
+};
+
+// Q4_K / Q5_K: unit = superblock, part g = the 64 weights of sub-blocks 2g, 2g+1.
+template <int FMT, int NP>
+struct SlotK45 {
+    static constexpr int PARTS = 4, UNIT_ELEMS = 256;
+    XGroup<NP, 32> a, b;
+    float sumA, sumB;
+    __device__ __forceinline__ void load(const float *__restrict__ x, uint32_t unit, int g)
+    {
+        float xv[32];
+        load_x(x + (size_t)unit * 256 + 64 * g, xv, 32);
+        quantize_group<NP, 32>(xv, a);
+        float s = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) s += xv[i];
+        sumA = s;
+        load_x(x + (size_t)unit * 256 + 64 * g + 32, xv, 32);
+        quantize_group<NP, 32>(xv, b);
+        s = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) s += xv[i];
+        sumB = s;
+    }
+    __device__ __forceinline__ float dot(const uint8_t *row, uint32_t unit, int g, int layout) const
+    {
+        constexpr int BB = FMT == FMT_Q4_K ? 144 : 176;
+        const uint8_t *sb = row + (size_t)unit * BB;
+        uint4 h = *reinterpret_cast<const uint4 *>(sb);
+        const uint4 *qp = reinterpret_cast<const uint4 *>(sb + (FMT == FMT_Q4_K ? 16 : 48) + 32 * g);
+        uint4 q0 = qp[0], q1 = qp[1];
+        uint32_t ql[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+        uint32_t qh[8];
+        if constexpr (FMT == FMT_Q5_K) {
+            uint4 h0 = *reinterpret_cast<const uint4 *>(sb + 16), h1 = *reinterpret_cast<const uint4 *>(sb + 32);
+            qh[0] = h0.x; qh[1] = h0.y; qh[2] = h0.z; qh[3] = h0.w;
+            qh[4] = h1.x; qh[5] = h1.y; qh[6] = h1.z; qh[7] = h1.w;
+        }
+        int IA[NP], IB[NP];
+#pragma unroll
+        for (int p = 0; p < NP; ++p) { IA[p] = 0; IB[p] = 0; }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            uint32_t lo = ql[k] & 0x0F0F0F0Fu, hi = (ql[k] >> 4) & 0x0F0F0F0Fu;
+            if constexpr (FMT == FMT_Q5_K) {
+                uint32_t t = qh[k] >> (2 * g);
+                lo |= (t & 0x01010101u) << 4;
+                hi |= (t & 0x02020202u) << 3;
+            }
+            dot_u<NP, 32>(lo, a, k, IA);
+            dot_u<NP, 32>(hi, b, k, IB);
+        }
+        uint32_t scA, scB, mnA, mnB;
+        pair_scales(h.y, h.z, h.w, layout, g, scA, scB, mnA, mnB);
+        float d = __half2float(__ushort_as_half((unsigned short)(h.x & 0xffffu)));
+        float dmin = __half2float(__ushort_as_half((unsigned short)(h.x >> 16)));
+        float pos = fmaf((float)scA * a.scale, combine<NP>(IA), (float)scB * b.scale * combine<NP>(IB));
+        float neg = fmaf((float)mnA, sumA, (float)mnB * sumB);
+        return fmaf(d, pos, -dmin * neg);
+    }
+};
+template <int NP> struct Slot<FMT_Q4_K, NP> : SlotK45<FMT_Q4_K, NP> {};
+template <int NP> struct Slot<FMT_Q5_K, NP> : SlotK45<FMT_Q5_K, NP> {};
+
+// Q6_K: unit = superblock (210 bytes, 2-byte aligned), part = (half, lh): the 64 weights
+// at positions 128*half + 32*t + 16*lh + (0..15), t = 0..3, each 16-group with its own scale.
+template <int NP>
+struct Slot<FMT_Q6_K, NP> {
+    static constexpr int PARTS = 4, UNIT_ELEMS = 256;
+    XGroup<NP, 16> g[4];
+    int sx[4][NP];   // sum of the piece bytes, for the -32 offset of the 6-bit quants
+    __device__ __forceinline__ void load(const float *__restrict__ x, uint32_t unit, int part)
+    {
+        int half = part >> 1, lh = part & 1;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            float xv[16];
+            load_x(x + (size_t)unit * 256 + 128 * half + 32 * t + 16 * lh, xv, 16);
+            quantize_group<NP, 16>(xv, g[t]);
+#pragma unroll
+            for (int p = 0; p < NP; ++p) {
+                int s = 0;
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    s = (p == NP - 1) ? dp4a_us(0x01010101u, g[t].pc[p][k], s) : dp4a_uu(0x01010101u, g[t].pc[p][k], s);
+                sx[t][p] = s;
+            }
+        }
+    }
+    __device__ __forceinline__ float dot(const uint8_t *row, uint32_t unit, int part, int) const
+    {
+        int half = part >> 1, lh = part & 1;
+        const uint8_t *sb = row + (size_t)unit * 210;
+        uint32_t qa[4], qb[4], qh[4], scw[2];
+        lds16_a2(sb + 64 * half + 16 * lh, qa);
+        lds16_a2(sb + 64 * half + 32 + 16 * lh, qb);
+        lds16_a2(sb + 128 + 32 * half + 16 * lh, qh);
+        lds8_a2(sb + 192 + 8 * half, scw);   // this half's 8 sub-scales; group t uses byte lh + 2t
+        int I[4][NP];
+#pragma unroll
+        for (int t = 0; t < 4; ++t)
+#pragma unroll
+            for (int p = 0; p < NP; ++p) I[t][p] = 0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            uint32_t h = qh[k];
+            dot_u<NP, 16>((qa[k] & 0x0F0F0F0Fu) | ((h << 4) & 0x30303030u), g[0], k, I[0]);
+            dot_u<NP, 16>((qb[k] & 0x0F0F0F0Fu) | ((h << 2) & 0x30303030u), g[1], k, I[1]);
+            dot_u<NP, 16>(((qa[k] >> 4) & 0x0F0F0F0Fu) | (h & 0x30303030u), g[2], k, I[2]);
+            dot_u<NP, 16>(((qb[k] >> 4) & 0x0F0F0F0Fu) | ((h >> 2) & 0x30303030u), g[3], k, I[3]);
+        }
+        float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(sb + 208)));
+        float acc = 0.0f;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            int J[NP];
+#pragma unroll
+            for (int p = 0; p < NP; ++p) J[p] = I[t][p] - 32 * sx[t][p];
+            int sc = (int)(scw[t >> 1] << (24 - 8 * (lh + 2 * (t & 1)))) >> 24;   // sign-extended int8
+            acc = fmaf((float)sc * g[t].scale, combine<NP>(J), acc);
+        }
+        return d * acc;
+    }
+};
+
+// ---- tile walk -------------------------------------------------------------
+struct PipeTile { int seg; uint32_t row0, n; };
+
+__device__ __forceinline__ bool next_tile(const PipeArgs &a, uint32_t &cur, uint32_t vend, PipeTile &t)
+{
+    if (cur >= vend) return false;
+    int s = 0;
+    while (s + 1 < a.nseg && cur >= a.seg[s + 1].vstart) ++s;
+    uint32_t seg_end = a.seg[s].vstart + a.seg[s].rows;
+    uint32_t lim = vend < seg_end ? vend : seg_end;
+    uint32_t n = lim - cur;
+    if (n > a.rows_per_stage) n = a.rows_per_stage;
+    t.seg = s; t.row0 = cur - a.seg[s].vstart; t.n = n;
+    cur += n;
+    return true;
+}
+
+template <bool SWIGLU>
+__device__ __forceinline__ void issue_tile(const PipeArgs &a, const PipeTile &t, uint8_t *stage, uint32_t bar)
+{
+    uint32_t tx = 0;
+    uintptr_t a0[2], e1[2];
+#pragma unroll
+    for (int h = 0; h < (SWIGLU ? 2 : 1); ++h) {
+        const uint8_t *base = h ? a.seg[t.seg].w2 : a.seg[t.seg].w;
+        uintptr_t src = reinterpret_cast<uintptr_t>(base) + (size_t)t.row0 * a.row_bytes;
+        uintptr_t end = src + (size_t)t.n * a.row_bytes;
+        a0[h] = src & ~(uintptr_t)15;
+        e1[h] = end & ~(uintptr_t)15;
+        uint8_t *dst = stage + h * a.half_stride;
+        // bytes past the last 16-byte boundary are fetched with plain loads so no copy reads beyond the tensor
+        for (uintptr_t p = e1[h]; p < end; p += 2)
+            *reinterpret_cast<uint16_t *>(dst + (p - a0[h])) = *reinterpret_cast<const uint16_t *>(p);
+        tx += (uint32_t)(e1[h] - a0[h]);
+    }
+    mbar_expect_tx(bar, tx);
+#pragma unroll
+    for (int h = 0; h < (SWIGLU ? 2 : 1); ++h)
+        bulk_g2s(smem_u32(stage + h * a.half_stride), reinterpret_cast<const void *>(a0[h]), (uint32_t)(e1[h] - a0[h]), bar);
+}
+
+template <int FMT, int NP, bool SWIGLU>
+__global__ void __launch_bounds__(PIPE_MAX_THREADS, 1)
+gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
+{
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem);
+    float *red = reinterpret_cast<float *>(smem + 8 * PIPE_MAX_STAGES);
+    uint8_t *stages = smem + a.stage_base;
+    __shared__ volatile int s_abort;
+
+    using SlotT = Slot<FMT, NP>;
+    constexpr int P = SlotT::PARTS;
+    const uint32_t tid = threadIdx.x, nthr = blockDim.x;
+    const uint32_t U = a.units, W = U * a.rows_par, PU = P * U;
+    const bool active = tid < P * W;
+    const int part = (int)(tid / W);
+    const uint32_t rem = tid % W, rp = rem / U, unit = rem % U;
+
+    const uint32_t v0 = (uint32_t)((uint64_t)blockIdx.x * a.total_rows / gridDim.x);
+    const uint32_t v1 = (uint32_t)((uint64_t)(blockIdx.x + 1) * a.total_rows / gridDim.x);
+
+    if (tid == 0) {
+        s_abort = 0;
+        for (uint32_t s = 0; s < a.nstages; ++s) mbar_init(smem_u32(bars + s), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+
+    // producer cursor: the weight copies do not depend on the previous kernel
+    uint32_t pcur = v0, issued = 0;
+    if (tid == 0) {
+        PipeTile t;
+        while (issued < a.nstages && next_tile(a, pcur, v1, t)) {
+            issue_tile<SWIGLU>(a, t, stages + (size_t)issued * a.stage_stride, smem_u32(bars + issued));
+            ++issued;
+        }
+    }
+    pdl_launch_dependents();
+    pdl_wait();   // x is the previous kernel's output
+
+    SlotT slot;
+    if (active) slot.load(a.x, unit, part);
+
+    uint32_t ccur = v0, i = 0;
+    PipeTile t;
+    while (next_tile(a, ccur, v1, t)) {
+        const uint32_t s = i % a.nstages, parity = (i / a.nstages) & 1u;
+        if (!s_abort && !mbar_wait_bounded(smem_u32(bars + s), parity)) {
+            s_abort = 1;
+            atomicExch(a.status, 1);
+        }
+        const uint8_t *stage = stages + (size_t)s * a.stage_stride;
+        const uint32_t delta = (uint32_t)((reinterpret_cast<uintptr_t>(a.seg[t.seg].w) + (size_t)t.row0 * a.row_bytes) & 15u);
+        float *rbuf = red + (size_t)(i & 1u) * a.red_floats * (SWIGLU ? 2 : 1);
+        if (active) {
+            for (uint32_t r = rp; r < t.n; r += a.rows_par) {
+                const uint8_t *row = stage + delta + (size_t)r * a.row_bytes;
+                rbuf[r * PU + part * U + unit] = slot.dot(row, unit, part, a.layout);
+                if constexpr (SWIGLU) {
+                    const uint32_t delta2 =
+                        (uint32_t)((reinterpret_cast<uintptr_t>(a.seg[t.seg].w2) + (size_t)t.row0 * a.row_bytes) & 15u);
+                    const uint8_t *row2 = stage + a.half_stride + delta2 + (size_t)r * a.row_bytes;
+                    rbuf[a.red_floats + r * PU + part * U + unit] = slot.dot(row2, unit, part, a.layout);
+                }
+            }
+        }
+        __syncthreads();
+        if (tid == 0) {
+            PipeTile nt;
+            if (next_tile(a, pcur, v1, nt)) {
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                issue_tile<SWIGLU>(a, nt, stages + (size_t)s * a.stage_stride, smem_u32(bars + s));
+                ++issued;
+            }
+        }
+        // one warp per row adds the partial sums
+        float *y = a.seg[t.seg].y + t.row0;
+        for (uint32_t r = tid >> 5; r < t.n; r += nthr >> 5) {
+            float acc = 0.0f, acc2 = 0.0f;
+            for (uint32_t j = tid & 31u; j < PU; j += 32) {
+                acc += rbuf[r * PU + j];
+                if constexpr (SWIGLU) acc2 += rbuf[a.red_floats + r * PU + j];
+            }
+            acc = warp_sum(acc);
+            if constexpr (SWIGLU) acc2 = warp_sum(acc2);
+            if ((tid & 31u) == 0) y[r] = SWIGLU ? silu_mul(acc, acc2) : acc;
+        }
+        ++i;
+    }
+    // after an expired wait: give copies still in flight a bounded time to land before the CTA exits
+    if (s_abort && tid == 0) {
+        for (uint32_t k = i; k < issued; ++k) mbar_wait_bounded(smem_u32(bars + k % a.nstages), (k / a.nstages) & 1u);
+    }
+}
+
+}  // namespace orome

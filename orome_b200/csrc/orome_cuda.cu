@@ -1,0 +1,628 @@
+// orome_cuda.cu -- C ABI (include/orome_cuda.h) and host-side dispatch for the
+// B200 quantized dequant-matvec path.  The host logic here is the counterpart
+// of the reference's format layer (inference/src/format.m:224-337): validate the
+// TensorRef, pick the kernel from its format/variant, size the launch.
+#include "../../include/orome_cuda.h"
+
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <string>
+
+#include "decode.cuh"
+#include "gemv_generic.cuh"
+#include "gemv_pipe.cuh"
+#include "moe.cuh"
+
+using namespace orome;
+
+struct orome_cuda_ctx {
+    int device = 0;
+    int sm_count = 0;
+    int smem_optin = 0;
+    int *status_dev = nullptr;
+    uint64_t launches = 0;
+    // options
+    int x_bits = 24;
+    int force_generic = 0;
+    int stage_kb = 0;        // 0 = automatic
+    int ctas_per_sm = 1;
+    int pdl = 1;
+    // staging for the host-buffer entry point
+    float *stage_x_host = nullptr, *stage_y_host = nullptr, *stage_x_dev = nullptr, *stage_y_dev = nullptr;
+    size_t stage_x_cap = 0, stage_y_cap = 0;
+    cudaStream_t own_stream = nullptr;
+    // scratch for routing logits when the caller passes none
+    float *logits_dev = nullptr;
+    size_t logits_cap = 0;
+    // scratch for the unfused gate/up fallback
+    float *gu_dev = nullptr;
+    size_t gu_cap = 0;
+};
+
+static thread_local std::string g_err;
+
+static int fail(int code, const char *fmt, ...)
+{
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    g_err = buf;
+    return code;
+}
+
+#define CU(call)                                                                                         \
+    do {                                                                                                 \
+        cudaError_t e_ = (call);                                                                         \
+        if (e_ != cudaSuccess) return fail(OROME_ECUDA, "%s: %s", #call, cudaGetErrorString(e_));        \
+    } while (0)
+
+extern "C" const char *orome_cuda_last_error(void) { return g_err.c_str(); }
+
+extern "C" int orome_cuda_ctx_create(int device, orome_cuda_ctx **out)
+{
+    if (!out) return fail(OROME_EINVAL, "ctx_create: out is NULL");
+    int n = 0;
+    CU(cudaGetDeviceCount(&n));
+    if (device < 0 || device >= n) return fail(OROME_EINVAL, "ctx_create: device %d of %d", device, n);
+    CU(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    CU(cudaGetDeviceProperties(&prop, device));
+    if (prop.major < 10) return fail(OROME_ENOTSUP, "ctx_create: device is sm_%d%d, the kernels are built for sm_100a", prop.major, prop.minor);
+    auto *c = new orome_cuda_ctx;
+    c->device = device;
+    c->sm_count = prop.multiProcessorCount;
+    c->smem_optin = (int)prop.sharedMemPerBlockOptin;
+    CU(cudaMalloc(&c->status_dev, sizeof(int)));
+    CU(cudaMemset(c->status_dev, 0, sizeof(int)));
+    CU(cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking));
+    *out = c;
+    return OROME_OK;
+}
+
+extern "C" void orome_cuda_ctx_destroy(orome_cuda_ctx *c)
+{
+    if (!c) return;
+    cudaSetDevice(c->device);
+    cudaFree(c->status_dev);
+    cudaFree(c->stage_x_dev);
+    cudaFree(c->stage_y_dev);
+    cudaFree(c->logits_dev);
+    cudaFree(c->gu_dev);
+    cudaFreeHost(c->stage_x_host);
+    cudaFreeHost(c->stage_y_host);
+    if (c->own_stream) cudaStreamDestroy(c->own_stream);
+    delete c;
+}
+
+extern "C" int orome_cuda_status(orome_cuda_ctx *c, int *status_out)
+{
+    if (!c || !status_out) return fail(OROME_EINVAL, "status: NULL argument");
+    CU(cudaSetDevice(c->device));
+    CU(cudaDeviceSynchronize());
+    CU(cudaMemcpy(status_out, c->status_dev, sizeof(int), cudaMemcpyDeviceToHost));
+    return *status_out ? fail(OROME_ETIMEOUT, "a kernel's bounded wait expired (status %d)", *status_out) : OROME_OK;
+}
+
+extern "C" int orome_cuda_upload(orome_cuda_ctx *c, const void *host, size_t bytes, void **dev_base)
+{
+    if (!c || !dev_base || (!host && bytes)) return fail(OROME_EINVAL, "upload: NULL argument");
+    CU(cudaSetDevice(c->device));
+    void *p = nullptr;
+    // 256 bytes of zeroed slack after the data keep 16-byte granular reads of a ragged tensor end inside the allocation
+    cudaError_t e = cudaMalloc(&p, bytes + 256);
+    if (e != cudaSuccess) return fail(OROME_ENOMEM, "upload: cudaMalloc(%zu): %s", bytes + 256, cudaGetErrorString(e));
+    CU(cudaMemset(static_cast<uint8_t *>(p) + bytes, 0, 256));
+    if (bytes) CU(cudaMemcpy(p, host, bytes, cudaMemcpyHostToDevice));
+    *dev_base = p;
+    return OROME_OK;
+}
+
+extern "C" int orome_cuda_free(orome_cuda_ctx *c, void *dev_base)
+{
+    if (!c) return fail(OROME_EINVAL, "free: NULL ctx");
+    CU(cudaSetDevice(c->device));
+    CU(cudaFree(dev_base));
+    return OROME_OK;
+}
+
+extern "C" OromeQuantFormat orome_format_from_ggml_type(uint32_t t)
+{
+    switch (t) {
+    case 8: return OROME_QFMT_GGUF_Q8_0;
+    case 12: return OROME_QFMT_GGUF_Q4_K;
+    case 13: return OROME_QFMT_GGUF_Q5_K;
+    case 14: return OROME_QFMT_GGUF_Q6_K;
+    case 1: return OROME_QFMT_F16;
+    case 30: return OROME_QFMT_BF16;
+    case 0: return OROME_QFMT_F32;
+    default: return OROME_QFMT_GGUF_Q4_K;   // the reference's fallback (format.m:335)
+    }
+}
+
+extern "C" size_t orome_format_row_bytes(OromeQuantFormat f, uint32_t in_dim)
+{
+    int fmt = (int)f;
+    if (fmt < 0 || fmt > FMT_F32) return 0;
+    if (fmt <= FMT_Q8_0 && in_dim % block_elems(fmt)) return 0;
+    return row_bytes_of(fmt, in_dim);
+}
+
+extern "C" int orome_cuda_set_option(orome_cuda_ctx *c, int key, int value)
+{
+    if (!c) return fail(OROME_EINVAL, "set_option: NULL ctx");
+    switch (key) {
+    case OROME_OPT_X_BITS:
+        if (value != 16 && value != 24) return fail(OROME_EINVAL, "X_BITS must be 16 or 24");
+        c->x_bits = value; return OROME_OK;
+    case OROME_OPT_FORCE_GENERIC: c->force_generic = value != 0; return OROME_OK;
+    case OROME_OPT_STAGE_KB:
+        if (value < 0 || value > 200) return fail(OROME_EINVAL, "STAGE_KB out of range");
+        c->stage_kb = value; return OROME_OK;
+    case OROME_OPT_CTAS_PER_SM:
+        if (value < 1 || value > 4) return fail(OROME_EINVAL, "CTAS_PER_SM must be 1..4");
+        c->ctas_per_sm = value; return OROME_OK;
+    case OROME_OPT_PDL: c->pdl = value != 0; return OROME_OK;
+    }
+    return fail(OROME_EINVAL, "set_option: unknown key %d", key);
+}
+
+extern "C" int orome_cuda_get_option(orome_cuda_ctx *c, int key, int *value)
+{
+    if (!c || !value) return fail(OROME_EINVAL, "get_option: NULL argument");
+    switch (key) {
+    case OROME_OPT_X_BITS: *value = c->x_bits; return OROME_OK;
+    case OROME_OPT_FORCE_GENERIC: *value = c->force_generic; return OROME_OK;
+    case OROME_OPT_STAGE_KB: *value = c->stage_kb; return OROME_OK;
+    case OROME_OPT_CTAS_PER_SM: *value = c->ctas_per_sm; return OROME_OK;
+    case OROME_OPT_PDL: *value = c->pdl; return OROME_OK;
+    }
+    return fail(OROME_EINVAL, "get_option: unknown key %d", key);
+}
+
+extern "C" uint64_t orome_cuda_launch_count(orome_cuda_ctx *c) { return c ? c->launches : 0; }
+
+// ---------------------------------------------------------------------------
+// validation shared by the entry points
+// ---------------------------------------------------------------------------
+static int check_ref(const char *who, const OromeTensorRef *r, const uint8_t **data)
+{
+    if (!r) return fail(OROME_EINVAL, "%s: NULL TensorRef", who);
+    int fmt = (int)r->format;
+    if (fmt < 0 || fmt > FMT_F32) return fail(OROME_ENOTSUP, "%s: unknown format %d", who, fmt);
+    if (r->variant > OROME_VARIANT_LLAMA) return fail(OROME_ENOTSUP, "%s: unknown kernel variant %u", who, r->variant);
+    if (r->out_dim == 0 || r->in_dim == 0) return fail(OROME_EINVAL, "%s: empty tensor (%u x %u)", who, r->out_dim, r->in_dim);
+    if (fmt <= FMT_Q8_0 && r->in_dim % block_elems(fmt))
+        return fail(OROME_EINVAL, "%s: in_dim %u is not a multiple of %d", who, r->in_dim, block_elems(fmt));
+    const uint8_t *p = static_cast<const uint8_t *>(r->buffer) + r->offset;
+    if (reinterpret_cast<uintptr_t>(p) & 15) return fail(OROME_EINVAL, "%s: tensor data is not 16-byte aligned", who);
+    *data = p;
+    return OROME_OK;
+}
+
+static int post_launch(orome_cuda_ctx *c, const char *what)
+{
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(OROME_ECUDA, "%s launch: %s", what, cudaGetErrorString(e));
+    ++c->launches;
+    return OROME_OK;
+}
+
+// ---------------------------------------------------------------------------
+// generic kernels
+// ---------------------------------------------------------------------------
+template <int FMT>
+static int launch_generic_fmt(orome_cuda_ctx *c, const uint8_t *data, uint32_t out_dim, uint32_t in_dim, int layout,
+                              const float *x, int batch, int ldx, float *y, int ldy, cudaStream_t st)
+{
+    size_t rb = row_bytes_of(FMT, in_dim);
+    dim3 grid((out_dim + 7) / 8), block(256);
+    if (batch == 1) gemv_generic_kernel<FMT, 1><<<grid, block, 0, st>>>(data, rb, out_dim, in_dim, layout, x, batch, ldx, y, ldy);
+    else if (batch <= 4) gemv_generic_kernel<FMT, 4><<<grid, block, 0, st>>>(data, rb, out_dim, in_dim, layout, x, batch, ldx, y, ldy);
+    else gemv_generic_kernel<FMT, 8><<<grid, block, 0, st>>>(data, rb, out_dim, in_dim, layout, x, batch, ldx, y, ldy);
+    return post_launch(c, "gemv_generic");
+}
+
+static int launch_generic(orome_cuda_ctx *c, int fmt, const uint8_t *data, uint32_t out_dim, uint32_t in_dim, int layout,
+                          const float *x, int batch, int ldx, float *y, int ldy, cudaStream_t st)
+{
+    switch (fmt) {
+    case FMT_Q4_K: return launch_generic_fmt<FMT_Q4_K>(c, data, out_dim, in_dim, layout, x, batch, ldx, y, ldy, st);
+    case FMT_Q5_K: return launch_generic_fmt<FMT_Q5_K>(c, data, out_dim, in_dim, layout, x, batch, ldx, y, ldy, st);
+    case FMT_Q6_K: return launch_generic_fmt<FMT_Q6_K>(c, data, out_dim, in_dim, layout, x, batch, ldx, y, ldy, st);
+    case FMT_Q8_0: return launch_generic_fmt<FMT_Q8_0>(c, data, out_dim, in_dim, layout, x, batch, ldx, y, ldy, st);
+    case FMT_F16: return launch_generic_fmt<FMT_F16>(c, data, out_dim, in_dim, layout, x, batch, ldx, y, ldy, st);
+    case FMT_BF16: return launch_generic_fmt<FMT_BF16>(c, data, out_dim, in_dim, layout, x, batch, ldx, y, ldy, st);
+    case FMT_F32: return launch_generic_fmt<FMT_F32>(c, data, out_dim, in_dim, layout, x, batch, ldx, y, ldy, st);
+    }
+    return fail(OROME_ENOTSUP, "no kernel for format %d", fmt);
+}
+
+// ---------------------------------------------------------------------------
+// pipelined decode kernel: planning and launch
+// ---------------------------------------------------------------------------
+struct PipePlan {
+    PipeArgs args;
+    int threads;
+    int grid;
+    size_t smem;
+};
+
+static bool pipe_supported(int fmt, uint32_t in_dim)
+{
+    if (fmt == FMT_Q8_0) return in_dim % 64 == 0 && in_dim / 64 <= PIPE_MAX_THREADS;
+    if (fmt == FMT_Q4_K || fmt == FMT_Q5_K || fmt == FMT_Q6_K) return in_dim % 256 == 0 && in_dim / 256 * 4 <= PIPE_MAX_THREADS;
+    return false;
+}
+
+// Fill everything of the plan except the segments' pointers.
+static int plan_pipe(orome_cuda_ctx *c, int fmt, uint32_t in_dim, uint32_t total_rows, bool swiglu, PipePlan &p)
+{
+    PipeArgs &a = p.args;
+    const int parts = fmt == FMT_Q8_0 ? 1 : 4;
+    a.in_dim = in_dim;
+    a.row_bytes = (uint32_t)row_bytes_of(fmt, in_dim);
+    a.units = fmt == FMT_Q8_0 ? in_dim / 64 : in_dim / 256;
+    const uint32_t slots = a.units * parts;                 // threads one row keeps busy
+    a.rows_par = std::max(1u, std::min(16u, (uint32_t)PIPE_MAX_THREADS / slots));
+    a.rows_par = std::min(a.rows_par, std::max(1u, total_rows));
+    p.threads = (int)((slots * a.rows_par + 31) / 32 * 32);
+    a.total_rows = total_rows;
+
+    const uint32_t per_row = a.row_bytes * (swiglu ? 2 : 1);
+    // stage size: a multiple of rows_par rows, about 32 KiB unless overridden
+    const uint32_t want = (c->stage_kb ? (uint32_t)c->stage_kb : 32u) * 1024u;
+    uint32_t iters = std::max(1u, want / (per_row * a.rows_par));
+    a.rows_per_stage = a.rows_par * iters;
+
+    const int ctas = c->ctas_per_sm;
+    p.grid = (int)std::min<uint64_t>((uint64_t)c->sm_count * ctas, (total_rows + a.rows_par - 1) / a.rows_par);
+    p.grid = std::max(p.grid, 1);
+    // do not make stages larger than a CTA's whole share
+    const uint32_t share = (total_rows + p.grid - 1) / p.grid;
+    const uint32_t share_rows = (share + a.rows_par - 1) / a.rows_par * a.rows_par;
+    a.rows_per_stage = std::min(a.rows_per_stage, share_rows);
+
+    const size_t budget = (size_t)(c->smem_optin - 1024) / ctas;
+    for (;;) {
+        a.half_stride = (a.rows_per_stage * a.row_bytes + 48 + 127) / 128 * 128;
+        a.stage_stride = a.half_stride * (swiglu ? 2 : 1);
+        a.red_floats = a.rows_per_stage * slots;
+        size_t red_bytes = (size_t)a.red_floats * 4 * 2 * (swiglu ? 2 : 1);
+        a.stage_base = (uint32_t)((8 * PIPE_MAX_STAGES + red_bytes + 127) / 128 * 128);
+        if (a.stage_base + (size_t)a.stage_stride * 2 <= budget || a.rows_per_stage == a.rows_par) {
+            size_t room = budget > a.stage_base ? budget - a.stage_base : 0;
+            uint32_t ns = (uint32_t)std::min<size_t>(PIPE_MAX_STAGES, room / a.stage_stride);
+            const uint32_t tiles = (share + a.rows_per_stage - 1) / a.rows_per_stage + 1;
+            ns = std::min(ns, tiles);
+            if (ns < 1) return fail(OROME_ENOTSUP, "pipe plan: a stage of %u bytes does not fit shared memory", a.stage_stride);
+            a.nstages = ns;
+            break;
+        }
+        a.rows_per_stage -= a.rows_par;
+    }
+    p.smem = a.stage_base + (size_t)a.stage_stride * a.nstages;
+    a.status = c->status_dev;
+    return OROME_OK;
+}
+
+template <int FMT, int NP, bool SW>
+static int launch_pipe_inst(orome_cuda_ctx *c, const PipePlan &p, cudaStream_t st)
+{
+    auto kern = gemv_pipe_kernel<FMT, NP, SW>;
+    static size_t configured[64] = {0};   // per device: largest dynamic smem opted in so far
+    if (configured[c->device] < p.smem) {
+        CU(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, c->smem_optin));
+        configured[c->device] = (size_t)c->smem_optin;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.grid);
+    cfg.blockDim = dim3(p.threads);
+    cfg.dynamicSmemBytes = p.smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = c->pdl ? 1 : 0;
+    CU(cudaLaunchKernelEx(&cfg, kern, p.args));
+    ++c->launches;
+    return OROME_OK;
+}
+
+template <int FMT>
+static int launch_pipe_fmt(orome_cuda_ctx *c, const PipePlan &p, bool swiglu, cudaStream_t st)
+{
+    if (c->x_bits == 24) return swiglu ? launch_pipe_inst<FMT, 3, true>(c, p, st) : launch_pipe_inst<FMT, 3, false>(c, p, st);
+    return swiglu ? launch_pipe_inst<FMT, 2, true>(c, p, st) : launch_pipe_inst<FMT, 2, false>(c, p, st);
+}
+
+static int launch_pipe(orome_cuda_ctx *c, int fmt, const PipePlan &p, bool swiglu, cudaStream_t st)
+{
+    switch (fmt) {
+    case FMT_Q4_K: return launch_pipe_fmt<FMT_Q4_K>(c, p, swiglu, st);
+    case FMT_Q5_K: return launch_pipe_fmt<FMT_Q5_K>(c, p, swiglu, st);
+    case FMT_Q6_K: return launch_pipe_fmt<FMT_Q6_K>(c, p, swiglu, st);
+    case FMT_Q8_0: return launch_pipe_fmt<FMT_Q8_0>(c, p, swiglu, st);
+    }
+    return fail(OROME_ENOTSUP, "no pipelined kernel for format %d", fmt);
+}
+
+// ---------------------------------------------------------------------------
+// matvec entry points
+// ---------------------------------------------------------------------------
+extern "C" int orome_cuda_matvec_group(orome_cuda_ctx *c, const OromeTensorRef *refs, int n_refs, const float *x_dev,
+                                       float *const *y_dev, void *stream)
+{
+    if (!c || !refs || !y_dev || n_refs < 1) return fail(OROME_EINVAL, "matvec_group: NULL or empty argument");
+    if (n_refs > PIPE_MAX_SEG) return fail(OROME_EINVAL, "matvec_group: at most %d tensors per launch", PIPE_MAX_SEG);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    CU(cudaSetDevice(c->device));
+    const uint8_t *data[PIPE_MAX_SEG];
+    for (int i = 0; i < n_refs; ++i) {
+        if (!refs[i].buffer) return fail(OROME_EINVAL, "matvec_group: tensor %d is absent", i);
+        int rc = check_ref("matvec_group", &refs[i], &data[i]);
+        if (rc) return rc;
+        if (refs[i].format != refs[0].format || refs[i].variant != refs[0].variant || refs[i].in_dim != refs[0].in_dim)
+            return fail(OROME_EINVAL, "matvec_group: tensors must share format, variant and in_dim");
+        if (!y_dev[i]) return fail(OROME_EINVAL, "matvec_group: y_dev[%d] is NULL", i);
+    }
+    if (!x_dev || (reinterpret_cast<uintptr_t>(x_dev) & 15)) return fail(OROME_EINVAL, "matvec_group: x must be a 16-byte aligned device pointer");
+    const int fmt = (int)refs[0].format, layout = (int)refs[0].variant;
+    if (c->force_generic || !pipe_supported(fmt, refs[0].in_dim)) {
+        for (int i = 0; i < n_refs; ++i) {
+            int rc = launch_generic(c, fmt, data[i], refs[i].out_dim, refs[i].in_dim, layout, x_dev, 1, 0, y_dev[i], 0, st);
+            if (rc) return rc;
+        }
+        return OROME_OK;
+    }
+    PipePlan p;
+    memset(&p, 0, sizeof p);
+    uint32_t total = 0;
+    for (int i = 0; i < n_refs; ++i) {
+        p.args.seg[i].w = data[i];
+        p.args.seg[i].w2 = nullptr;
+        p.args.seg[i].y = y_dev[i];
+        p.args.seg[i].rows = refs[i].out_dim;
+        p.args.seg[i].vstart = total;
+        total += refs[i].out_dim;
+    }
+    p.args.nseg = n_refs;
+    p.args.x = x_dev;
+    p.args.layout = layout;
+    int rc = plan_pipe(c, fmt, refs[0].in_dim, total, false, p);
+    if (rc) return rc;
+    return launch_pipe(c, fmt, p, false, st);
+}
+
+extern "C" int orome_cuda_matvec(orome_cuda_ctx *c, const OromeTensorRef *ref, const float *x_dev, float *y_dev, int batch,
+                                 int ldx, int ldy, void *stream)
+{
+    if (!c || !ref) return fail(OROME_EINVAL, "matvec: NULL argument");
+    if (!ref->buffer) return OROME_OK;   // absent optional tensor: silent no-op (format.m:247-250)
+    if (batch < 1) return fail(OROME_EINVAL, "matvec: batch %d", batch);
+    if (!x_dev || !y_dev) return fail(OROME_EINVAL, "matvec: NULL x or y");
+    if (batch == 1 && (int)ref->format <= FMT_Q8_0) {
+        float *ys[1] = {y_dev};
+        return orome_cuda_matvec_group(c, ref, 1, x_dev, ys, stream);
+    }
+    if (batch > 1 && (ldx < (int)ref->in_dim || ldy < (int)ref->out_dim))
+        return fail(OROME_EINVAL, "matvec: ldx/ldy smaller than the row length");
+    const uint8_t *data;
+    int rc = check_ref("matvec", ref, &data);
+    if (rc) return rc;
+    CU(cudaSetDevice(c->device));
+    return launch_generic(c, (int)ref->format, data, ref->out_dim, ref->in_dim, (int)ref->variant, x_dev, batch, ldx, y_dev, ldy,
+                          static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int orome_format_dispatch_matvec(orome_cuda_ctx *c, const OromeTensorRef *ref, const void *in_buf, size_t in_off,
+                                            void *out_buf, size_t out_off, void *stream)
+{
+    if (!c || !ref) return fail(OROME_EINVAL, "format_dispatch_matvec: NULL argument");
+    if (!ref->buffer) return OROME_OK;
+    if (!in_buf || !out_buf) return fail(OROME_EINVAL, "format_dispatch_matvec: NULL buffer");
+    if ((in_off | out_off) & 3) return fail(OROME_EINVAL, "format_dispatch_matvec: offsets must be multiples of 4");
+    const float *x = reinterpret_cast<const float *>(static_cast<const uint8_t *>(in_buf) + in_off);
+    float *y = reinterpret_cast<float *>(static_cast<uint8_t *>(out_buf) + out_off);
+    return orome_cuda_matvec(c, ref, x, y, 1, 0, 0, stream);
+}
+
+static int ensure(float **p, size_t *cap, size_t floats)
+{
+    if (*cap >= floats) return OROME_OK;
+    if (*p) cudaFree(*p);
+    *p = nullptr;
+    *cap = 0;
+    cudaError_t e = cudaMalloc(p, floats * sizeof(float));
+    if (e != cudaSuccess) return fail(OROME_ENOMEM, "scratch of %zu floats: %s", floats, cudaGetErrorString(e));
+    *cap = floats;
+    return OROME_OK;
+}
+
+extern "C" int orome_cuda_gate_up_swiglu(orome_cuda_ctx *c, const OromeTensorRef *gate, const OromeTensorRef *up,
+                                         const float *x_dev, float *out_dev, int batch, int ldx, int ldo, void *stream)
+{
+    if (!c || !gate || !up) return fail(OROME_EINVAL, "gate_up_swiglu: NULL argument");
+    if (!gate->buffer || !up->buffer) return OROME_OK;
+    if (batch < 1 || !x_dev || !out_dev) return fail(OROME_EINVAL, "gate_up_swiglu: bad x/out/batch");
+    const uint8_t *gd, *ud;
+    int rc = check_ref("gate_up_swiglu(gate)", gate, &gd);
+    if (rc) return rc;
+    rc = check_ref("gate_up_swiglu(up)", up, &ud);
+    if (rc) return rc;
+    if (gate->format != up->format || gate->variant != up->variant || gate->out_dim != up->out_dim || gate->in_dim != up->in_dim)
+        return fail(OROME_EINVAL, "gate_up_swiglu: gate and up must have the same shape, format and variant");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    CU(cudaSetDevice(c->device));
+    const int fmt = (int)gate->format, layout = (int)gate->variant;
+    if (batch == 1 && !c->force_generic && pipe_supported(fmt, gate->in_dim)) {
+        if (reinterpret_cast<uintptr_t>(x_dev) & 15) return fail(OROME_EINVAL, "gate_up_swiglu: x must be 16-byte aligned");
+        PipePlan p;
+        memset(&p, 0, sizeof p);
+        p.args.seg[0] = PipeSeg{gd, ud, out_dev, gate->out_dim, 0};
+        p.args.nseg = 1;
+        p.args.x = x_dev;
+        p.args.layout = layout;
+        rc = plan_pipe(c, fmt, gate->in_dim, gate->out_dim, true, p);
+        if (rc) return rc;
+        return launch_pipe(c, fmt, p, true, st);
+    }
+    // two matvecs into context scratch, then the elementwise epilogue (the reference's unfused branch, engine.m:388-404)
+    if (batch > 1 && (ldx < (int)gate->in_dim || ldo < (int)gate->out_dim))
+        return fail(OROME_EINVAL, "gate_up_swiglu: ldx/ldo smaller than the row length");
+    const size_t n = (size_t)gate->out_dim;
+    rc = ensure(&c->gu_dev, &c->gu_cap, 2 * n * batch);
+    if (rc) return rc;
+    float *g = c->gu_dev, *u = c->gu_dev + n * batch;
+    rc = launch_generic(c, fmt, gd, gate->out_dim, gate->in_dim, layout, x_dev, batch, ldx, g, (int)n, st);
+    if (rc) return rc;
+    rc = launch_generic(c, fmt, ud, up->out_dim, up->in_dim, layout, x_dev, batch, ldx, u, (int)n, st);
+    if (rc) return rc;
+    size_t tot = n * batch;
+    swiglu_kernel<<<(unsigned)((tot + 255) / 256), 256, 0, st>>>(g, u, out_dev, (uint32_t)n, batch, (int)n, batch == 1 ? (int)n : ldo);
+    return post_launch(c, "swiglu");
+}
+
+extern "C" int orome_cuda_dequant_rows(orome_cuda_ctx *c, const OromeTensorRef *ref, uint32_t row0, uint32_t nrows,
+                                       float *out_dev, void *stream)
+{
+    if (!c || !ref || !out_dev) return fail(OROME_EINVAL, "dequant_rows: NULL argument");
+    if (!ref->buffer) return fail(OROME_EINVAL, "dequant_rows: tensor is absent");   // the reference returns false (format.m:177)
+    const uint8_t *data;
+    int rc = check_ref("dequant_rows", ref, &data);
+    if (rc) return rc;
+    if (row0 >= ref->out_dim || nrows > ref->out_dim - row0) return fail(OROME_EINVAL, "dequant_rows: rows [%u, %u) of %u", row0, row0 + nrows, ref->out_dim);
+    if (nrows == 0) return OROME_OK;
+    if (ref->in_dim % 32) return fail(OROME_EINVAL, "dequant_rows: in_dim %u is not a multiple of 32", ref->in_dim);
+    if (reinterpret_cast<uintptr_t>(out_dev) & 15) return fail(OROME_EINVAL, "dequant_rows: out must be 16-byte aligned");
+    CU(cudaSetDevice(c->device));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int fmt = (int)ref->format, layout = (int)ref->variant;
+    size_t rb = row_bytes_of(fmt, ref->in_dim);
+    size_t groups = (size_t)nrows * (ref->in_dim / 32);
+    unsigned grid = (unsigned)((groups + 127) / 128);
+#define DQ(F) dequant_rows_kernel<F><<<grid, 128, 0, st>>>(data, rb, row0, nrows, ref->in_dim, layout, out_dev)
+    switch (fmt) {
+    case FMT_Q4_K: DQ(FMT_Q4_K); break;
+    case FMT_Q5_K: DQ(FMT_Q5_K); break;
+    case FMT_Q6_K: DQ(FMT_Q6_K); break;
+    case FMT_Q8_0: DQ(FMT_Q8_0); break;
+    case FMT_F16: DQ(FMT_F16); break;
+    case FMT_BF16: DQ(FMT_BF16); break;
+    case FMT_F32: DQ(FMT_F32); break;
+    }
+#undef DQ
+    return post_launch(c, "dequant_rows");
+}
+
+// ---------------------------------------------------------------------------
+// MoE
+// ---------------------------------------------------------------------------
+extern "C" int orome_cuda_moe_route(orome_cuda_ctx *c, const OromeTensorRef *router, const float *x_dev, int n_tokens, int ldx,
+                                    uint32_t K, uint32_t *idx_dev, float *w_dev, float *logits_dev, void *stream)
+{
+    if (!c || !router || !x_dev || !idx_dev || !w_dev) return fail(OROME_EINVAL, "moe_route: NULL argument");
+    if (!router->buffer) return fail(OROME_EINVAL, "moe_route: router tensor is absent");
+    const uint8_t *data;
+    int rc = check_ref("moe_route", router, &data);
+    if (rc) return rc;
+    if (router->format != OROME_QFMT_F32) return fail(OROME_ENOTSUP, "moe_route: the router must be an F32 tensor");
+    if (router->out_dim > 256) return fail(OROME_EINVAL, "moe_route: %u experts (the routing kernel takes at most 256)", router->out_dim);
+    if (n_tokens < 1 || (n_tokens > 1 && ldx < (int)router->in_dim)) return fail(OROME_EINVAL, "moe_route: bad n_tokens/ldx");
+    if (K < 1) return fail(OROME_EINVAL, "moe_route: K must be at least 1");
+    CU(cudaSetDevice(c->device));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const uint32_t ne = router->out_dim;
+    if (!logits_dev) {
+        rc = ensure(&c->logits_dev, &c->logits_cap, (size_t)ne * n_tokens);
+        if (rc) return rc;
+        logits_dev = c->logits_dev;
+    }
+    rc = launch_generic(c, FMT_F32, data, ne, router->in_dim, 0, x_dev, n_tokens, ldx, logits_dev, (int)ne, st);
+    if (rc) return rc;
+    route_topk_kernel<<<n_tokens, 256, 0, st>>>(logits_dev, (int)ne, ne, K, idx_dev, w_dev);
+    return post_launch(c, "route_topk");
+}
+
+extern "C" int orome_cuda_moe_ffn(orome_cuda_ctx *c, const OromeExpertLayerRef *L, uint32_t variant, const float *x_dev,
+                                  int n_tokens, int ldx, const uint32_t *idx_dev, const float *w_dev, uint32_t K, uint32_t hidden,
+                                  uint32_t inter, float *act_dev, float *out_dev, int ldo, void *stream)
+{
+    if (!c || !L || !x_dev || !idx_dev || !w_dev || !act_dev || !out_dev) return fail(OROME_EINVAL, "moe_ffn: NULL argument");
+    if (!L->buffer) return OROME_OK;
+    if (K < 1 || K > 8) return fail(OROME_EINVAL, "moe_ffn: K = %u (1..8; the reference's routing caps K at 8)", K);
+    if (variant > OROME_VARIANT_LLAMA) return fail(OROME_ENOTSUP, "moe_ffn: unknown kernel variant %u", variant);
+    if (n_tokens < 1 || (n_tokens > 1 && (ldx < (int)hidden || ldo < (int)hidden))) return fail(OROME_EINVAL, "moe_ffn: bad n_tokens/ldx/ldo");
+    if (L->gate.format != L->up.format) return fail(OROME_ENOTSUP, "moe_ffn: gate and up must share a format");
+    const int gfmt = (int)L->gate.format, dfmt = (int)L->down.format;
+    if (gfmt < 0 || gfmt > FMT_Q8_0 || dfmt < 0 || dfmt > FMT_Q8_0) return fail(OROME_ENOTSUP, "moe_ffn: expert tensors must be quantized (Q4_K/Q5_K/Q6_K/Q8_0)");
+    if (hidden % block_elems(gfmt) || inter % block_elems(dfmt)) return fail(OROME_EINVAL, "moe_ffn: hidden/inter not a whole number of blocks");
+    const uint8_t *base = static_cast<const uint8_t *>(L->buffer);
+    const uint8_t *gate = base + L->gate.offset, *up = base + L->up.offset, *down = base + L->down.offset;
+    if ((reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(up) | reinterpret_cast<uintptr_t>(down) | L->gate.expert_stride |
+         L->up.expert_stride | L->down.expert_stride) & 15)
+        return fail(OROME_EINVAL, "moe_ffn: expert tensors and strides must be 16-byte aligned");
+    CU(cudaSetDevice(c->device));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t grb = row_bytes_of(gfmt, hidden), drb = row_bytes_of(dfmt, inter);
+    dim3 g1((inter + 7) / 8, (unsigned)n_tokens * K), g2((hidden + 7) / 8, (unsigned)n_tokens);
+#define GU(F) moe_gate_up_kernel<F><<<g1, 256, 0, st>>>(gate, L->gate.expert_stride, up, L->up.expert_stride, grb, inter, hidden, (int)variant, x_dev, ldx, idx_dev, K, act_dev)
+    switch (gfmt) {
+    case FMT_Q4_K: GU(FMT_Q4_K); break;
+    case FMT_Q5_K: GU(FMT_Q5_K); break;
+    case FMT_Q6_K: GU(FMT_Q6_K); break;
+    case FMT_Q8_0: GU(FMT_Q8_0); break;
+    }
+#undef GU
+    int rc = post_launch(c, "moe_gate_up");
+    if (rc) return rc;
+#define DN(F) moe_down_kernel<F><<<g2, 256, 0, st>>>(down, L->down.expert_stride, drb, hidden, inter, (int)variant, act_dev, idx_dev, w_dev, K, out_dev, n_tokens == 1 ? (int)hidden : ldo)
+    switch (dfmt) {
+    case FMT_Q4_K: DN(FMT_Q4_K); break;
+    case FMT_Q5_K: DN(FMT_Q5_K); break;
+    case FMT_Q6_K: DN(FMT_Q6_K); break;
+    case FMT_Q8_0: DN(FMT_Q8_0); break;
+    }
+#undef DN
+    return post_launch(c, "moe_down");
+}
+
+// ---------------------------------------------------------------------------
+// host-buffer form
+// ---------------------------------------------------------------------------
+extern "C" int orome_cuda_matvec_host(orome_cuda_ctx *c, const OromeTensorRef *ref, const float *x_host, float *y_host, int batch)
+{
+    if (!c || !ref || !x_host || !y_host) return fail(OROME_EINVAL, "matvec_host: NULL argument");
+    if (!ref->buffer) return OROME_OK;
+    if (batch < 1) return fail(OROME_EINVAL, "matvec_host: batch %d", batch);
+    CU(cudaSetDevice(c->device));
+    const size_t nx = (size_t)ref->in_dim * batch, ny = (size_t)ref->out_dim * batch;
+    if (c->stage_x_cap < nx) {
+        cudaFreeHost(c->stage_x_host); cudaFree(c->stage_x_dev);
+        c->stage_x_host = c->stage_x_dev = nullptr; c->stage_x_cap = 0;
+        CU(cudaMallocHost(&c->stage_x_host, nx * sizeof(float)));
+        CU(cudaMalloc(&c->stage_x_dev, nx * sizeof(float)));
+        c->stage_x_cap = nx;
+    }
+    if (c->stage_y_cap < ny) {
+        cudaFreeHost(c->stage_y_host); cudaFree(c->stage_y_dev);
+        c->stage_y_host = c->stage_y_dev = nullptr; c->stage_y_cap = 0;
+        CU(cudaMallocHost(&c->stage_y_host, ny * sizeof(float)));
+        CU(cudaMalloc(&c->stage_y_dev, ny * sizeof(float)));
+        c->stage_y_cap = ny;
+    }
+    memcpy(c->stage_x_host, x_host, nx * sizeof(float));
+    CU(cudaMemcpyAsync(c->stage_x_dev, c->stage_x_host, nx * sizeof(float), cudaMemcpyHostToDevice, c->own_stream));
+    int rc = orome_cuda_matvec(c, ref, c->stage_x_dev, c->stage_y_dev, batch, (int)ref->in_dim, (int)ref->out_dim, c->own_stream);
+    if (rc) return rc;
+    CU(cudaMemcpyAsync(c->stage_y_host, c->stage_y_dev, ny * sizeof(float), cudaMemcpyDeviceToHost, c->own_stream));
+    CU(cudaStreamSynchronize(c->own_stream));
+    memcpy(y_host, c->stage_y_host, ny * sizeof(float));
+    return OROME_OK;
+}

@@ -1,0 +1,188 @@
+"""ctypes binding of ``liborome_cuda.so`` mirroring the reference's format layer.
+
+Names follow inference/include/orome.h: ``TensorRef`` (239-246), ``ExpertProjRef`` /
+``ExpertLayerRef`` (249-259), ``format_dispatch_matvec`` (319-322),
+``format_from_ggml_type`` (324), ``format_decode_row_f32`` (325, here
+``dequant_rows`` on the device).  Device memory is passed as integer addresses
+(``tensor.data_ptr()``), streams as ``torch.cuda.current_stream().cuda_stream``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "liborome_cuda.so")
+
+VARIANT_DEFAULT, VARIANT_LLAMA = 0, 1
+OPT_X_BITS, OPT_FORCE_GENERIC, OPT_STAGE_KB, OPT_CTAS_PER_SM, OPT_PDL = 1, 2, 3, 4, 5
+
+OK, EINVAL, ENOTSUP, ENOMEM, ECUDA, ETIMEOUT = 0, -22, -95, -12, -5, -110
+
+
+class OromeError(RuntimeError):
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"[{code}] {msg}")
+        self.code = code
+
+
+class TensorRef(C.Structure):
+    """orome.h:239-246 with the Metal buffer replaced by a device pointer."""
+    _fields_ = [("buffer", C.c_void_p), ("offset", C.c_size_t), ("variant", C.c_uint32), ("format", C.c_int),
+                ("out_dim", C.c_uint32), ("in_dim", C.c_uint32)]
+
+
+class ExpertProjRef(C.Structure):
+    _fields_ = [("offset", C.c_size_t), ("expert_stride", C.c_size_t), ("format", C.c_int)]
+
+
+class ExpertLayerRef(C.Structure):
+    _fields_ = [("buffer", C.c_void_p), ("gate", ExpertProjRef), ("up", ExpertProjRef), ("down", ExpertProjRef)]
+
+
+EXPORTS = [
+    "orome_cuda_ctx_create", "orome_cuda_ctx_destroy", "orome_cuda_last_error", "orome_cuda_status", "orome_cuda_upload",
+    "orome_cuda_free", "orome_format_from_ggml_type", "orome_format_row_bytes", "orome_format_dispatch_matvec",
+    "orome_cuda_matvec", "orome_cuda_matvec_group", "orome_cuda_gate_up_swiglu", "orome_cuda_dequant_rows",
+    "orome_cuda_moe_route", "orome_cuda_moe_ffn", "orome_cuda_matvec_host", "orome_cuda_set_option",
+    "orome_cuda_get_option", "orome_cuda_launch_count",
+]
+
+_lib = None
+
+
+def lib():
+    """Load the CUDA library; fails loudly when it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(f"{LIB_PATH} is missing: build it with `python -m orome_b200.build` "
+                          "(there is no CPU fallback for this path)")
+    L = C.CDLL(LIB_PATH)
+    vp, sz, u32, i32 = C.c_void_p, C.c_size_t, C.c_uint32, C.c_int
+    TR, EL = C.POINTER(TensorRef), C.POINTER(ExpertLayerRef)
+    L.orome_cuda_ctx_create.argtypes = [i32, C.POINTER(vp)]
+    L.orome_cuda_ctx_destroy.argtypes = [vp]
+    L.orome_cuda_ctx_destroy.restype = None
+    L.orome_cuda_last_error.restype = C.c_char_p
+    L.orome_cuda_status.argtypes = [vp, C.POINTER(i32)]
+    L.orome_cuda_upload.argtypes = [vp, vp, sz, C.POINTER(vp)]
+    L.orome_cuda_free.argtypes = [vp, vp]
+    L.orome_format_from_ggml_type.argtypes = [u32]
+    L.orome_format_row_bytes.argtypes = [i32, u32]
+    L.orome_format_row_bytes.restype = sz
+    L.orome_format_dispatch_matvec.argtypes = [vp, TR, vp, sz, vp, sz, vp]
+    L.orome_cuda_matvec.argtypes = [vp, TR, vp, vp, i32, i32, i32, vp]
+    L.orome_cuda_matvec_group.argtypes = [vp, TR, i32, vp, C.POINTER(vp), vp]
+    L.orome_cuda_gate_up_swiglu.argtypes = [vp, TR, TR, vp, vp, i32, i32, i32, vp]
+    L.orome_cuda_dequant_rows.argtypes = [vp, TR, u32, u32, vp, vp]
+    L.orome_cuda_moe_route.argtypes = [vp, TR, vp, i32, i32, u32, vp, vp, vp, vp]
+    L.orome_cuda_moe_ffn.argtypes = [vp, EL, u32, vp, i32, i32, vp, vp, u32, u32, u32, vp, vp, i32, vp]
+    L.orome_cuda_matvec_host.argtypes = [vp, TR, vp, vp, i32]
+    L.orome_cuda_set_option.argtypes = [vp, i32, i32]
+    L.orome_cuda_get_option.argtypes = [vp, i32, C.POINTER(i32)]
+    L.orome_cuda_launch_count.argtypes = [vp]
+    L.orome_cuda_launch_count.restype = C.c_uint64
+    _lib = L
+    return L
+
+
+def _chk(rc: int):
+    if rc != 0:
+        raise OromeError(rc, lib().orome_cuda_last_error().decode())
+
+
+def format_from_ggml_type(ggml_type: int) -> int:
+    return int(lib().orome_format_from_ggml_type(ggml_type))
+
+
+def format_row_bytes(fmt: int, in_dim: int) -> int:
+    return int(lib().orome_format_row_bytes(fmt, in_dim))
+
+
+class Context:
+    """One CUDA device bound to the library (the role MetalCtx plays for this path)."""
+
+    def __init__(self, device: int = 0):
+        self._h = C.c_void_p()
+        _chk(lib().orome_cuda_ctx_create(device, C.byref(self._h)))
+        self.device = device
+
+    def close(self):
+        if self._h:
+            lib().orome_cuda_ctx_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- memory ---------------------------------------------------------------
+    def upload(self, host_bytes) -> int:
+        """Copy a bytes-like / numpy uint8 array to a new device allocation; returns the device address."""
+        import numpy as np
+        a = np.ascontiguousarray(np.frombuffer(host_bytes, dtype=np.uint8) if not hasattr(host_bytes, "ctypes") else host_bytes)
+        out = C.c_void_p()
+        _chk(lib().orome_cuda_upload(self._h, a.ctypes.data_as(C.c_void_p), a.nbytes, C.byref(out)))
+        return int(out.value)
+
+    def free(self, dev_base: int):
+        _chk(lib().orome_cuda_free(self._h, C.c_void_p(dev_base)))
+
+    # -- options ----------------------------------------------------------------
+    def set_option(self, key: int, value: int):
+        _chk(lib().orome_cuda_set_option(self._h, key, value))
+
+    def get_option(self, key: int) -> int:
+        v = C.c_int()
+        _chk(lib().orome_cuda_get_option(self._h, key, C.byref(v)))
+        return v.value
+
+    def status(self) -> int:
+        v = C.c_int()
+        _chk(lib().orome_cuda_status(self._h, C.byref(v)))
+        return v.value
+
+    @property
+    def launch_count(self) -> int:
+        return int(lib().orome_cuda_launch_count(self._h))
+
+    # -- the path ---------------------------------------------------------------
+    def format_dispatch_matvec(self, ref: TensorRef, in_buf: int, in_off: int, out_buf: int, out_off: int, stream: int = 0):
+        _chk(lib().orome_format_dispatch_matvec(self._h, C.byref(ref), in_buf, in_off, out_buf, out_off, stream))
+
+    def matvec(self, ref: TensorRef, x: int, y: int, batch: int = 1, ldx: int = 0, ldy: int = 0, stream: int = 0):
+        _chk(lib().orome_cuda_matvec(self._h, C.byref(ref), x, y, batch, ldx, ldy, stream))
+
+    def matvec_group(self, refs, x: int, ys, stream: int = 0):
+        arr = (TensorRef * len(refs))(*refs)
+        yp = (C.c_void_p * len(ys))(*ys)
+        _chk(lib().orome_cuda_matvec_group(self._h, arr, len(refs), x, yp, stream))
+
+    def gate_up_swiglu(self, gate: TensorRef, up: TensorRef, x: int, out: int, batch: int = 1, ldx: int = 0, ldo: int = 0,
+                       stream: int = 0):
+        _chk(lib().orome_cuda_gate_up_swiglu(self._h, C.byref(gate), C.byref(up), x, out, batch, ldx, ldo, stream))
+
+    def dequant_rows(self, ref: TensorRef, row0: int, nrows: int, out: int, stream: int = 0):
+        _chk(lib().orome_cuda_dequant_rows(self._h, C.byref(ref), row0, nrows, out, stream))
+
+    def moe_route(self, router: TensorRef, x: int, n_tokens: int, ldx: int, K: int, idx: int, w: int, logits: int = 0,
+                  stream: int = 0):
+        _chk(lib().orome_cuda_moe_route(self._h, C.byref(router), x, n_tokens, ldx, K, idx, w, logits or None, stream))
+
+    def moe_ffn(self, layer: ExpertLayerRef, variant: int, x: int, n_tokens: int, ldx: int, idx: int, w: int, K: int,
+                hidden: int, inter: int, act: int, out: int, ldo: int, stream: int = 0):
+        _chk(lib().orome_cuda_moe_ffn(self._h, C.byref(layer), variant, x, n_tokens, ldx, idx, w, K, hidden, inter, act, out,
+                                      ldo, stream))
+
+    def matvec_host(self, ref: TensorRef, x_host, y_host, batch: int = 1):
+        """x_host / y_host: contiguous float32 numpy arrays (host memory)."""
+        _chk(lib().orome_cuda_matvec_host(self._h, C.byref(ref), x_host.ctypes.data_as(C.c_void_p),
+                                          y_host.ctypes.data_as(C.c_void_p), batch))
+
+
+def tensor_ref(buffer: int, offset: int, fmt: int, out_dim: int, in_dim: int, variant: int = VARIANT_DEFAULT) -> TensorRef:
+    return TensorRef(buffer, offset, variant, fmt, out_dim, in_dim)

@@ -1,0 +1,342 @@
+"""GPU parity tests: the CUDA path (through the C ABI) against the CPU oracle and the
+committed golden vectors.  Bit-exact for dequantized weights and routing indices;
+rel-L2 <= 1e-4 against the fp64-accumulated oracle for matvec outputs."""
+import os
+
+import numpy as np
+import pytest
+
+import oracle
+from orome_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+REL_L2_TOL = 1e-4          # the tolerance the path states for fp32 accumulation
+GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "decode_golden.npz"))
+FMTS = {"Q8_0": synth.Q8_0, "Q4_K": synth.Q4_K, "Q5_K": synth.Q5_K, "Q6_K": synth.Q6_K}
+QUANT = list(FMTS.values())
+
+
+@pytest.fixture(scope="module")
+def env():
+    import torch
+    from orome_b200 import format as F
+    ctx = F.Context(0)
+    yield torch, F, ctx
+    assert ctx.status() == 0
+    ctx.close()
+
+
+def bits(a):
+    return np.ascontiguousarray(a, np.float32).view(np.uint32)
+
+
+def rel_l2(got, want):
+    want = np.asarray(want, np.float64)
+    return float(np.linalg.norm(np.asarray(got, np.float64) - want) / max(np.linalg.norm(want), 1e-300))
+
+
+def dev_bytes(torch, arr):
+    return torch.from_numpy(np.ascontiguousarray(arr)).cuda()
+
+
+def make_ref(F, wt, fmt, out_dim, in_dim, variant=0, offset=0):
+    return F.tensor_ref(wt.data_ptr(), offset, fmt, out_dim, in_dim, variant)
+
+
+def gpu_matvec(env, fmt, data, out_dim, in_dim, x, variant=0):
+    torch, F, ctx = env
+    wt = dev_bytes(torch, data)
+    xm = np.atleast_2d(x)
+    xt = dev_bytes(torch, xm)
+    y = torch.full((xm.shape[0], out_dim), float("nan"), device="cuda", dtype=torch.float32)
+    ref = make_ref(F, wt, fmt, out_dim, in_dim, variant)
+    ctx.matvec(ref, xt.data_ptr(), y.data_ptr(), xm.shape[0], in_dim, out_dim, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    out = y.cpu().numpy()
+    return out[0] if np.ndim(x) == 1 else out
+
+
+# ---------------------------------------------------------------- dequant ----
+@pytest.mark.parametrize("name", list(FMTS))
+def test_dequant_bit_exact_vs_golden(env, name):
+    torch, F, ctx = env
+    fmt = FMTS[name]
+    rows, in_dim = (int(v) for v in GOLD[f"{name}_shape"])
+    for key, nrows in ((name, rows), (f"{name}_edge", 4)):
+        wt = dev_bytes(torch, GOLD[f"{key}_data"])
+        out = torch.empty((nrows, in_dim), device="cuda", dtype=torch.float32)
+        ctx.dequant_rows(make_ref(F, wt, fmt, nrows, in_dim), 0, nrows, out.data_ptr())
+        torch.cuda.synchronize()
+        assert np.array_equal(bits(out.cpu().numpy()), bits(GOLD[f"{key}_out"]))
+
+
+@pytest.mark.parametrize("fmt", QUANT)
+def test_dequant_bit_exact_vs_oracle_random_bytes(env, fmt):
+    """Every byte pattern, including NaN / inf / subnormal fp16 scales."""
+    torch, F, ctx = env
+    rows, in_dim = 37, 1024
+    data = np.random.default_rng(fmt).integers(0, 256, synth.tensor_bytes(fmt, rows, in_dim), dtype=np.uint8)
+    wt = dev_bytes(torch, data)
+    for variant in (0, 1):
+        out = torch.empty((rows - 5, in_dim), device="cuda", dtype=torch.float32)
+        ctx.dequant_rows(make_ref(F, wt, fmt, rows, in_dim, variant), 5, rows - 5, out.data_ptr())
+        torch.cuda.synchronize()
+        want = oracle.decode_rows(fmt, data, rows, in_dim, row0=5, layout=variant)
+        assert np.array_equal(bits(out.cpu().numpy()), bits(want))
+
+
+def test_dequant_unquantized_formats(env):
+    torch, F, ctx = env
+    rng = np.random.default_rng(1)
+    raw = rng.integers(0, 65536, (3, 64), dtype=np.uint16)
+    for fmt in (synth.F16, synth.BF16):
+        wt = dev_bytes(torch, raw.view(np.uint8).reshape(-1))
+        out = torch.empty((3, 64), device="cuda", dtype=torch.float32)
+        ctx.dequant_rows(make_ref(F, wt, fmt, 3, 64), 0, 3, out.data_ptr())
+        torch.cuda.synchronize()
+        want = oracle.decode_rows(fmt, raw.view(np.uint8).reshape(-1), 3, 64)
+        assert np.array_equal(bits(out.cpu().numpy()), bits(want))
+
+
+# ----------------------------------------------------------------- matvec ----
+def test_known_answer_vectors(env):
+    from test_oracle import kat_f32, kat_q4_k, kat_q8_0
+    data, x, expected, od, idim = kat_q8_0()
+    y = gpu_matvec(env, synth.Q8_0, data, od, idim, x)
+    assert np.max(np.abs(y - expected)) < 0.01                       # tests/test_q8_0.m:106
+    data, x, expected, od, idim = kat_q4_k()
+    y = gpu_matvec(env, synth.Q4_K, data, od, idim, x)
+    assert np.all(np.abs(y - expected) / np.abs(expected) < 0.1)     # tests/test_q4k.m:93
+    data, x, expected, od, idim = kat_f32()
+    y = gpu_matvec(env, synth.F32, data, od, idim, x)
+    assert np.max(np.abs(y - expected)) < 0.01                       # tests/test_f32.m:56
+
+
+SHAPES = [(1, 256), (3, 512), (33, 1024), (64, 4096), (100, 5120), (257, 2048), (31, 768), (40, 12288), (18, 17408)]
+
+
+@pytest.mark.parametrize("fmt", QUANT)
+@pytest.mark.parametrize("x_bits", [24, 16])
+def test_matvec_matches_oracle(env, fmt, x_bits):
+    torch, F, ctx = env
+    ctx.set_option(F.OPT_X_BITS, x_bits)
+    try:
+        for out_dim, in_dim in SHAPES:
+            data = synth.host_tensor(fmt, out_dim, in_dim, seed=synth.seed_for("mv", fmt, out_dim, in_dim))
+            x = synth.host_x(in_dim, seed=out_dim)
+            for variant in ((0, 1) if fmt in (synth.Q4_K, synth.Q5_K) else (0,)):
+                y = gpu_matvec(env, fmt, data, out_dim, in_dim, x, variant)
+                want = oracle.matvec_f64(fmt, data, out_dim, in_dim, x, layout=variant)
+                err = rel_l2(y, want)
+                assert err <= REL_L2_TOL, (fmt, out_dim, in_dim, variant, err)
+                if x_bits == 24:
+                    assert err <= 2e-6, (fmt, out_dim, in_dim, variant, err)
+    finally:
+        ctx.set_option(F.OPT_X_BITS, 24)
+
+
+@pytest.mark.parametrize("fmt", QUANT)
+def test_generic_and_pipelined_kernels_agree(env, fmt):
+    torch, F, ctx = env
+    out_dim, in_dim = 129, 4096
+    data = synth.host_tensor(fmt, out_dim, in_dim, seed=77)
+    x = synth.host_x(in_dim, seed=78)
+    y_pipe = gpu_matvec(env, fmt, data, out_dim, in_dim, x)
+    ctx.set_option(F.OPT_FORCE_GENERIC, 1)
+    try:
+        y_gen = gpu_matvec(env, fmt, data, out_dim, in_dim, x)
+    finally:
+        ctx.set_option(F.OPT_FORCE_GENERIC, 0)
+    want = oracle.matvec_f64(fmt, data, out_dim, in_dim, x)
+    assert rel_l2(y_gen, want) <= 2e-6 and rel_l2(y_pipe, want) <= 2e-6
+
+
+def test_matvec_x_edge_cases(env):
+    """Zero vector, one huge element among tiny ones, denormal-sized inputs."""
+    fmt, out_dim, in_dim = synth.Q8_0, 64, 1024
+    data = synth.host_tensor(fmt, out_dim, in_dim, seed=5)
+    y = gpu_matvec(env, fmt, data, out_dim, in_dim, np.zeros(in_dim, np.float32))
+    assert np.all(y == 0)
+    x = synth.host_x(in_dim, seed=6) * np.float32(1e-3)
+    x[17] = 1e4
+    want = oracle.matvec_f64(fmt, data, out_dim, in_dim, x)
+    assert rel_l2(gpu_matvec(env, fmt, data, out_dim, in_dim, x), want) <= REL_L2_TOL
+    x = synth.host_x(in_dim, seed=7) * np.float32(1e-30)
+    want = oracle.matvec_f64(fmt, data, out_dim, in_dim, x)
+    assert rel_l2(gpu_matvec(env, fmt, data, out_dim, in_dim, x), want) <= REL_L2_TOL
+
+
+@pytest.mark.parametrize("fmt", QUANT + [synth.F32])
+@pytest.mark.parametrize("batch", [2, 8, 13])
+def test_batched_matvec(env, fmt, batch):
+    out_dim, in_dim = 70, 1024
+    data = synth.host_tensor(fmt, out_dim, in_dim, seed=batch)
+    x = synth.host_x(in_dim, batch, seed=3)
+    y = gpu_matvec(env, fmt, data, out_dim, in_dim, x)
+    want = oracle.matvec_f64(fmt, data, out_dim, in_dim, x)
+    assert y.shape == want.shape and rel_l2(y, want) <= REL_L2_TOL
+
+
+def test_format_dispatch_matvec_offsets_and_absent_tensor(env):
+    torch, F, ctx = env
+    fmt, out_dim, in_dim = synth.Q4_K, 48, 512
+    data = synth.host_tensor(fmt, out_dim, in_dim, seed=1)
+    blob = np.concatenate([np.zeros(64, np.uint8), data])           # tensor at byte offset 64 of its buffer
+    wt = dev_bytes(torch, blob)
+    x = synth.host_x(in_dim, seed=2)
+    inbuf = dev_bytes(torch, np.concatenate([np.zeros(8, np.float32), x]))
+    outbuf = torch.zeros(out_dim + 4, device="cuda", dtype=torch.float32)
+    ref = make_ref(F, wt, fmt, out_dim, in_dim, offset=64)
+    ctx.format_dispatch_matvec(ref, inbuf.data_ptr(), 32, outbuf.data_ptr(), 16)
+    torch.cuda.synchronize()
+    got = outbuf.cpu().numpy()
+    assert np.all(got[:4] == 0)
+    assert rel_l2(got[4:], oracle.matvec_f64(fmt, data, out_dim, in_dim, x)) <= 2e-6
+    # a NULL buffer is a silent no-op (format.m:247-250)
+    outbuf.fill_(7.0)
+    ctx.format_dispatch_matvec(F.tensor_ref(0, 0, fmt, out_dim, in_dim), inbuf.data_ptr(), 32, outbuf.data_ptr(), 16)
+    torch.cuda.synchronize()
+    assert torch.all(outbuf == 7.0)
+
+
+def test_rejected_calls_return_codes(env):
+    torch, F, ctx = env
+    wt = torch.zeros(4096, device="cuda", dtype=torch.uint8)
+    x = torch.zeros(4096, device="cuda")
+    y = torch.zeros(4096, device="cuda")
+    with pytest.raises(F.OromeError) as e:
+        ctx.matvec(make_ref(F, wt, synth.Q8_0, 4, 48), x.data_ptr(), y.data_ptr())
+    assert e.value.code == F.EINVAL
+    with pytest.raises(F.OromeError) as e:
+        ctx.matvec(make_ref(F, wt, 9, 4, 256), x.data_ptr(), y.data_ptr())
+    assert e.value.code == F.ENOTSUP
+    with pytest.raises(F.OromeError) as e:
+        ctx.matvec(make_ref(F, wt, synth.Q4_K, 4, 256, offset=2), x.data_ptr(), y.data_ptr())
+    assert e.value.code == F.EINVAL
+    with pytest.raises(F.OromeError):
+        ctx.dequant_rows(make_ref(F, wt, synth.Q8_0, 4, 256), 3, 2, y.data_ptr())
+
+
+def test_matvec_group_shares_x(env):
+    torch, F, ctx = env
+    fmt, in_dim = synth.Q8_0, 4096
+    dims = [96, 24, 24]
+    datas = [synth.host_tensor(fmt, d, in_dim, seed=10 + i) for i, d in enumerate(dims)]
+    wts = [dev_bytes(torch, d) for d in datas]
+    x = synth.host_x(in_dim, seed=4)
+    xt = dev_bytes(torch, x)
+    ys = [torch.full((d,), float("nan"), device="cuda") for d in dims]
+    ctx.matvec_group([make_ref(F, w, fmt, d, in_dim) for w, d in zip(wts, dims)], xt.data_ptr(), [y.data_ptr() for y in ys])
+    torch.cuda.synchronize()
+    for d, data, y in zip(dims, datas, ys):
+        assert rel_l2(y.cpu().numpy(), oracle.matvec_f64(fmt, data, d, in_dim, x)) <= 2e-6
+
+
+@pytest.mark.parametrize("fmt", [synth.Q8_0, synth.Q4_K, synth.Q6_K])
+@pytest.mark.parametrize("batch", [1, 3])
+def test_gate_up_swiglu(env, fmt, batch):
+    torch, F, ctx = env
+    out_dim, in_dim = 200, 2048
+    gd = synth.host_tensor(fmt, out_dim, in_dim, seed=31)
+    ud = synth.host_tensor(fmt, out_dim, in_dim, seed=32)
+    x = synth.host_x(in_dim, batch, seed=33) * np.float32(8.0)      # large enough that silu is not in its linear range
+    xm = np.atleast_2d(x)
+    gt, ut, xt = dev_bytes(torch, gd), dev_bytes(torch, ud), dev_bytes(torch, xm)
+    out = torch.full((batch, out_dim), float("nan"), device="cuda")
+    for variant in ((0, 1) if fmt == synth.Q4_K else (0,)):
+        ctx.gate_up_swiglu(make_ref(F, gt, fmt, out_dim, in_dim, variant), make_ref(F, ut, fmt, out_dim, in_dim, variant),
+                           xt.data_ptr(), out.data_ptr(), batch, in_dim, out_dim)
+        torch.cuda.synchronize()
+        g = oracle.matvec_f64(fmt, gd, out_dim, in_dim, xm, layout=variant)
+        u = oracle.matvec_f64(fmt, ud, out_dim, in_dim, xm, layout=variant)
+        want = oracle.swiglu_f64(g, u)
+        assert rel_l2(out.cpu().numpy(), want) <= REL_L2_TOL
+
+
+def test_matvec_host_roundtrip(env):
+    torch, F, ctx = env
+    fmt, out_dim, in_dim = synth.Q6_K, 96, 1024
+    data = synth.host_tensor(fmt, out_dim, in_dim, seed=8)
+    wt = dev_bytes(torch, data)
+    x = synth.host_x(in_dim, seed=9)
+    y = np.empty(out_dim, np.float32)
+    ctx.matvec_host(make_ref(F, wt, fmt, out_dim, in_dim), x, y)
+    assert rel_l2(y, oracle.matvec_f64(fmt, data, out_dim, in_dim, x)) <= 2e-6
+
+
+def test_upload_keeps_offsets(env):
+    torch, F, ctx = env
+    fmt, out_dim, in_dim = synth.Q5_K, 16, 512
+    data = synth.host_tensor(fmt, out_dim, in_dim, seed=12)
+    blob = np.concatenate([np.arange(96, dtype=np.uint8), data])
+    base = ctx.upload(blob)
+    try:
+        x = synth.host_x(in_dim, seed=13)
+        xt = dev_bytes(torch, x)
+        y = torch.empty(out_dim, device="cuda")
+        ctx.matvec(F.tensor_ref(base, 96, fmt, out_dim, in_dim), xt.data_ptr(), y.data_ptr())
+        torch.cuda.synchronize()
+        assert rel_l2(y.cpu().numpy(), oracle.matvec_f64(fmt, data, out_dim, in_dim, x)) <= 2e-6
+    finally:
+        ctx.free(base)
+
+
+# -------------------------------------------------------------------- MoE ----
+def test_route_matches_oracle_including_ties(env):
+    torch, F, ctx = env
+    n_experts, hidden, T, K = 128, 2048, 9, 8
+    W = synth.host_router(n_experts, hidden, seed=2)
+    W[7] = W[3]                                                      # identical rows give exact ties
+    W[90] = W[3]
+    x = synth.host_x(hidden, T, seed=5)
+    wt, xt = dev_bytes(torch, W.view(np.uint8).reshape(-1)), dev_bytes(torch, x)
+    idx = torch.zeros((T, 8), device="cuda", dtype=torch.int32)
+    w = torch.zeros((T, 8), device="cuda")
+    logits = torch.zeros((T, n_experts), device="cuda")
+    ctx.moe_route(make_ref(F, wt, synth.F32, n_experts, hidden), xt.data_ptr(), T, hidden, K, idx.data_ptr(), w.data_ptr(),
+                  logits.data_ptr())
+    torch.cuda.synchronize()
+    lg = logits.cpu().numpy()
+    assert rel_l2(lg, oracle.matvec_f64(synth.F32, W.view(np.uint8).reshape(-1), n_experts, hidden, x)) <= 1e-5
+    for t in range(T):
+        oi, ow = oracle.route(lg[t], K)                              # the oracle routes the SAME logits
+        assert np.array_equal(idx[t].cpu().numpy().astype(np.uint32), oi)
+        assert np.max(np.abs(w[t].cpu().numpy() - ow)) <= 1e-6
+    # K < 8 zero-fills, K > 8 is capped
+    for K2 in (3, 12):
+        ctx.moe_route(make_ref(F, wt, synth.F32, n_experts, hidden), xt.data_ptr(), 1, hidden, K2, idx.data_ptr(), w.data_ptr())
+        torch.cuda.synchronize()
+        oi, ow = oracle.route(lg[0], K2)
+        assert np.array_equal(idx[0].cpu().numpy().astype(np.uint32), oi)
+        assert np.max(np.abs(w[0].cpu().numpy() - ow)) <= 1e-6
+
+
+@pytest.mark.parametrize("T", [1, 5])
+@pytest.mark.parametrize("down_fmt", [synth.Q5_K, synth.Q4_K])
+def test_moe_ffn_matches_oracle(env, T, down_fmt):
+    torch, F, ctx = env
+    H, M, E, K = 512, 256, 16, 8
+    gate = synth.host_tensor(synth.Q4_K, E * M, H, seed=21)
+    up = synth.host_tensor(synth.Q4_K, E * M, H, seed=22)
+    down = synth.host_tensor(down_fmt, E * H, M, seed=23)
+    sg, sd = synth.tensor_bytes(synth.Q4_K, M, H), synth.tensor_bytes(down_fmt, H, M)
+    blob = np.concatenate([gate, up, down])
+    wt = dev_bytes(torch, blob)
+    x = synth.host_x(H, T, seed=24)
+    xm = np.atleast_2d(x)
+    rng = np.random.default_rng(25)
+    idx = np.stack([rng.permutation(E)[:8] for _ in range(T)]).astype(np.uint32)
+    w = rng.random((T, 8)).astype(np.float32)
+    w /= w.sum(1, keepdims=True)
+    layer = F.ExpertLayerRef(wt.data_ptr(), F.ExpertProjRef(0, sg, synth.Q4_K), F.ExpertProjRef(gate.size, sg, synth.Q4_K),
+                             F.ExpertProjRef(gate.size + up.size, sd, down_fmt))
+    xt, it, wtt = dev_bytes(torch, xm), dev_bytes(torch, idx.view(np.int32)), dev_bytes(torch, w)
+    act = torch.empty((T, K, M), device="cuda")
+    out = torch.full((T, H), float("nan"), device="cuda")
+    ctx.moe_ffn(layer, 0, xt.data_ptr(), T, H, it.data_ptr(), wtt.data_ptr(), K, H, M, act.data_ptr(), out.data_ptr(), H)
+    torch.cuda.synchronize()
+    got = out.cpu().numpy()
+    for t in range(T):
+        want = oracle.moe_ffn_f64(gate, up, down, (synth.Q4_K, synth.Q4_K, down_fmt), (sg, sg, sd), xm[t], H, M, idx[t], w[t])
+        assert rel_l2(got[t], want) <= REL_L2_TOL
