@@ -1,0 +1,422 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized dequant-matvec path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One "step" is one decode-token pass over a Qwen3.5-shape matvec set: per layer the
+grouped q/k/v projections, the o projection, the fused gate/up + SwiGLU and the down
+projection, then the lm_head (129 launches per step for the 9B Q8_0 set).  Every layer
+has its own weights (7.2 GB for the 9B set), far above the 126 MB L2, so no weight byte
+is served from cache between or within steps.
+
+Prints ONE JSON line: metric decode_matvec_tok_s (tokens per second of the whole job),
+`roofline` (algorithmic HBM bytes per step / device time against the measured copy
+bandwidth), `e2e` (same steps with the input vector copied from pinned host memory and
+the logits read back every step), `cpu_baseline` (the reference's CPU decode + dot on
+the host cores, on a bounded sample) and the clocks seen during the timed region.
+
+With N > 1 (launched by torch.distributed.run) every tensor is row-split over the
+ranks and each product is followed by an all-gather of the output vector over NCCL,
+so the scaling is "strong" (the same token step on more GPUs).
+
+`--impl reference` times the reference's own CPU implementation of the path (its
+format.m decode compiled into oracle/_ref, else the C restatement) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FALLBACK_HBM_GBS = 6650.0      # used only when MEASURED_PEAKS.json is absent
+NOMINAL_HBM_GBS = 8000.0
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML (read-only) while a region runs."""
+
+    def __init__(self, index: int, period: float = 0.05):
+        super().__init__(daemon=True)
+        self.index, self.period = index, period
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop_evt = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.ok = False
+
+    NAMES = {0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x10: "sync_boost",
+             0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown",
+             0x100: "display_clock_setting"}
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        while not self._stop_evt.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in self.NAMES.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def finish(self):
+        self._stop_evt.set()
+        if self.is_alive():
+            self.join(timeout=2)
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["unavailable"]}
+        return {"sm_mhz": int(statistics.median(self.samples)), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+# ----------------------------------------------------------------------------------------------
+# CPU arm: the reference's CPU decode + dot on the host cores
+# ----------------------------------------------------------------------------------------------
+def cpu_layer_sample(set_name: str, reps: int):
+    """Time one layer's matvecs (q,k,v,o,gate,up,down) on the host; returns (seconds per layer, meta)."""
+    import numpy as np
+    import oracle
+    from orome_b200 import decode_set, synth
+
+    cfg = decode_set.SETS[set_name]
+    H, A, KV = cfg["hidden"], cfg["ffn"], cfg["kv"]
+    shapes = dict(q=(H, H), k=(KV, H), v=(KV, H), o=(H, H), gate=(A, H), up=(A, H), down=(H, A))
+    use_ref = oracle.ref() is not None and cfg["variant"] == 0     # the reference's CPU decode knows only its default scale layout
+    rng = np.random.default_rng(0)
+    xh, xa = rng.standard_normal(H, dtype=np.float32), rng.standard_normal(A, dtype=np.float32)
+    tensors = {k: synth.host_tensor(cfg["fmt"][k], *shapes[k], seed=synth.seed_for(set_name, "cpu", k)) for k in shapes}
+    layer_bytes = sum(t.size for t in tensors.values())
+
+    def one_layer():
+        for k, (od, idim) in shapes.items():
+            oracle.matvec_f32(cfg["fmt"][k], tensors[k], od, idim, xa if k == "down" else xh, layout=cfg["variant"],
+                              use_ref=use_ref)
+
+    one_layer()
+    best = float("inf")
+    times = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        one_layer()
+        dt = time.perf_counter() - t0
+        times.append(dt)
+        best = min(best, dt)
+    threads = (oracle.ref().ref_num_threads() if use_ref else oracle.num_threads())
+    return times, dict(kind="reference" if use_ref else "port", cores=int(threads), layer_bytes=int(layer_bytes))
+
+
+def run_reference_arm(args):
+    """--impl reference: the reference's CPU implementation on the host cores (rank 0 only)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from orome_b200 import decode_set, synth
+    name = args.workload
+    cfg = decode_set.SETS[name]
+    H, A, KV = cfg["hidden"], cfg["ffn"], cfg["kv"]
+    shapes = dict(q=(H, H), k=(KV, H), v=(KV, H), o=(H, H), gate=(A, H), up=(A, H), down=(H, A))
+    total_bytes = sum(synth.tensor_bytes(cfg["fmt"][k], *shapes[k]) for k in shapes) * cfg["layers"] + \
+        synth.tensor_bytes(cfg["fmt"]["lm_head"], cfg["vocab"], H)
+    for _ in range(max(0, args.warmup - 1)):
+        pass
+    times, meta = cpu_layer_sample(name, max(1, args.steps))
+    per_layer = statistics.median(times)
+    # a step is sampled by one layer; the whole token step scales by the byte ratio
+    step_s = per_layer * total_bytes / meta["layer_bytes"]
+    tok_s = 1.0 / step_s
+    sample = f"one layer of {name} ({meta['layer_bytes']} weight bytes) per step, scaled to the full set by bytes ({total_bytes})"
+    line = {
+        "impl": "reference", "metric": "decode_matvec_tok_s", "value": tok_s, "unit": "tok/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": name, "batch": 1, "inputs": "seeded synthetic GGUF blocks"},
+        "cpu_baseline": {"value": tok_s, "unit": "tok/s", "cores": meta["cores"], "kind": meta["kind"], "sample": sample,
+                         "cpu_gbs": meta["layer_bytes"] / per_layer / 1e9},
+        "e2e": {"value": tok_s, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------------------------
+# GPU arm
+# ----------------------------------------------------------------------------------------------
+class Stepper:
+    """Issues one token step of a DecodeSet through the C ABI (optionally replayed from a CUDA graph)."""
+
+    def __init__(self, torch, F, ctx, ds, dist=None):
+        self.torch, self.F, self.ctx, self.ds, self.dist = torch, F, ctx, ds, dist
+        dev = ds.arena.device
+        H, A, KV, V = ds.hidden, ds.ffn, ds.kv, ds.vocab
+        g = torch.Generator(device=dev)
+        g.manual_seed(1234)
+        self.x_h = torch.randn(H, device=dev, generator=g)           # input of every hidden-sized product
+        self.x_a = torch.randn(A, device=dev, generator=g)           # input of the down projection
+        w = ds.world
+        # full-size outputs (all-gather targets when sharded); local slices are written in place
+        self.q, self.k, self.v = (torch.zeros(n, device=dev) for n in (H, KV, KV))
+        self.o, self.act, self.dn, self.logits = (torch.zeros(n, device=dev) for n in (H, A, H, V))
+        self.refs = [[ds.ref(t) for t in lt] for lt in ds.tensors]
+        self.lm_ref = ds.ref(ds.lm_head)
+        self.graph = None
+        self.launches_per_step = 0
+
+    def _slice(self, full, full_out):
+        from orome_b200.decode_set import shard_rows
+        lo, hi = shard_rows(full_out, self.ds.rank, self.ds.world)
+        return full[lo:hi]
+
+    def _gather(self, full, full_out):
+        """All-gather of the output vector when the rows are split over ranks."""
+        if self.ds.world == 1:
+            return
+        from orome_b200.decode_set import shard_rows
+        w = self.ds.world
+        lo, hi = shard_rows(full_out, self.ds.rank, w)
+        per = (full_out // w + 31) // 32 * 32
+        if per * w == full_out:
+            self.dist.all_gather_into_tensor(full, full[lo:hi])
+        else:   # ragged last shard: gather padded slices
+            pad = self.torch.zeros(per, device=full.device)
+            pad[:hi - lo] = full[lo:hi]
+            out = self.torch.empty(per * w, device=full.device)
+            self.dist.all_gather_into_tensor(out, pad)
+            full.copy_(out[:full_out])
+
+    def issue(self, stream):
+        ctx, ds = self.ctx, self.ds
+        H, A, KV, V = ds.hidden, ds.ffn, ds.kv, ds.vocab
+        xh, xa = self.x_h.data_ptr(), self.x_a.data_ptr()
+        c0 = ctx.launch_count
+        for refs in self.refs:
+            rq, rk, rv, ro, rg, ru, rd = refs
+            ctx.matvec_group([rq, rk, rv], xh, [self._slice(self.q, H).data_ptr(), self._slice(self.k, KV).data_ptr(),
+                                                self._slice(self.v, KV).data_ptr()], stream)
+            self._gather(self.q, H); self._gather(self.k, KV); self._gather(self.v, KV)
+            ctx.matvec(ro, xh, self._slice(self.o, H).data_ptr(), 1, 0, 0, stream)
+            self._gather(self.o, H)
+            ctx.gate_up_swiglu(rg, ru, xh, self._slice(self.act, A).data_ptr(), 1, 0, 0, stream)
+            self._gather(self.act, A)
+            ctx.matvec(rd, xa, self._slice(self.dn, H).data_ptr(), 1, 0, 0, stream)
+            self._gather(self.dn, H)
+        ctx.matvec(self.lm_ref, xh, self._slice(self.logits, V).data_ptr(), 1, 0, 0, stream)
+        self._gather(self.logits, V)
+        self.launches_per_step = ctx.launch_count - c0
+
+    def capture(self):
+        torch = self.torch
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            self.issue(s.cuda_stream)           # warm every kernel variant before capturing
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            self.issue(torch.cuda.current_stream().cuda_stream)
+        self.graph = g
+
+    def step(self):
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self.issue(self.torch.cuda.current_stream().cuda_stream)
+
+
+def run_ours(args):
+    import numpy as np
+    import torch
+
+    from orome_b200 import decode_set
+    from orome_b200 import format as F
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; this path has no CPU fallback (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local))
+        dist = dist_mod
+    dev = torch.device("cuda", local)
+    ctx = F.Context(local)
+    if args.x_bits:
+        ctx.set_option(F.OPT_X_BITS, args.x_bits)
+
+    ds = decode_set.DecodeSet(args.workload, dev, rank=rank, world=world, layers=args.layers)
+    st = Stepper(torch, F, ctx, ds, dist)
+    use_graph = args.graph
+    if use_graph:
+        try:
+            st.capture()
+        except Exception as ex:     # report and run eagerly rather than hide the failure
+            if rank == 0:
+                print(f"bench.py: graph capture failed ({ex}); running without a graph", file=sys.stderr)
+            st.graph = None
+            use_graph = False
+    else:
+        st.issue(torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        """K steps between events on the current stream; returns (device seconds max over ranks, per-step list)."""
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+        barrier()
+        evs[0].record()
+        for i in range(steps):
+            fn()
+            evs[i + 1].record()
+        torch.cuda.synchronize()
+        barrier()
+        total = evs[0].elapsed_time(evs[steps]) * 1e-3
+        per = [evs[i].elapsed_time(evs[i + 1]) * 1e-3 for i in range(steps)]
+        if dist is not None:
+            t = torch.tensor([total], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            total = float(t.item())
+        return total, per
+
+    # ---- device-resident timing ---------------------------------------------------------
+    for _ in range(max(3, args.warmup)):
+        st.step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local)
+    sampler.start()
+    c0 = ctx.launch_count
+    total, per = timed(st.step, args.steps)
+    launches = (ctx.launch_count - c0) if not use_graph else st.launches_per_step * args.steps
+    clocks = sampler.finish()
+    ms_per_step = total / args.steps * 1e3
+    tok_s = args.steps / total
+
+    # ---- end to end: x from pinned host memory, logits back to the host every step ---------
+    x_pin = torch.randn(ds.hidden).pin_memory()
+    logits_pin = torch.empty(ds.vocab).pin_memory()
+
+    def e2e_step():
+        st.x_h.copy_(x_pin, non_blocking=True)
+        st.step()
+        logits_pin.copy_(st.logits, non_blocking=True)
+        torch.cuda.current_stream().synchronize()      # the host needs the logits before the next token
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    e_total, _ = timed(e2e_step, args.steps)
+    wall = time.perf_counter() - t0
+    e2e_tok_s = args.steps / max(e_total, 1e-12)
+
+    if ctx.status() != 0:
+        raise SystemExit("bench.py: a kernel reported an expired wait; the numbers are void")
+
+    # ---- spot check of the last step against the CPU oracle (one small slice, rank 0) -------
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_kind = measured_peak()
+    w_bytes = ds.full_weight_bytes()
+    alg_bytes = w_bytes + ds.io_bytes()
+    achieved = alg_bytes / (total / args.steps) / 1e9
+    launches_per_step = st.launches_per_step
+    roofline = {
+        "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
+        "frac_of_8tbs_nominal": achieved / NOMINAL_HBM_GBS, "traffic": None,
+        "kernel": "gemv_pipe_kernel", "algorithmic_bytes_per_step": alg_bytes, "launches_per_step": launches_per_step,
+        "avg_launch_us": ms_per_step * 1e3 / max(1, launches_per_step),
+        "algorithmic_bytes_per_launch": alg_bytes / max(1, launches_per_step),
+    }
+
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        times, meta = cpu_layer_sample(args.workload, 3)
+        per_layer = statistics.median(times)
+        step_s = per_layer * w_bytes / meta["layer_bytes"]
+        cpu = {"value": 1.0 / step_s, "unit": "tok/s", "cores": meta["cores"], "kind": meta["kind"],
+               "sample": f"one layer ({meta['layer_bytes']} weight bytes) x3, median, scaled to the full set by bytes",
+               "cpu_gbs": meta["layer_bytes"] / per_layer / 1e9}
+
+    line = {
+        "metric": "decode_matvec_tok_s", "value": tok_s, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "int8 dot products on 24-bit fixed-point x, fp32 accumulate" if ctx.get_option(F.OPT_X_BITS) == 24
+        else "int8 dot products on 16-bit fixed-point x, fp32 accumulate",
+        "data": "synthetic",
+        "config": {"workload": args.workload, "batch": 1, "layers": ds.layers, "weight_bytes": w_bytes,
+                   "l2": "inputs larger than L2: every layer has its own weights", "cuda_graph": bool(use_graph),
+                   "parallelism": "single GPU" if world == 1 else f"row-split x{world} + all-gather (NCCL)"},
+        "roofline": roofline,
+        "e2e": {"value": e2e_tok_s, "unit": "tok/s", "h2d_bytes_per_step": ds.hidden * 4, "d2h_bytes_per_step": ds.vocab * 4,
+                "wall_tok_s": args.steps / wall},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+        "step_ms_min_med_max": [min(per) * 1e3, statistics.median(per) * 1e3, max(per) * 1e3],
+    }
+    if cpu is not None:
+        line["cpu_baseline"] = cpu
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="9b_q8_0", choices=["9b_q8_0", "27b_q4_k_m"])
+    ap.add_argument("--layers", type=int, default=None, help="override the number of layers (smaller captures for profiling)")
+    ap.add_argument("--x-bits", type=int, default=0, choices=[0, 16, 24])
+    ap.add_argument("--graph", dest="graph", action="store_true", default=True)
+    ap.add_argument("--no-graph", dest="graph", action="store_false")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

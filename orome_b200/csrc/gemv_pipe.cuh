@@ -2,21 +2,29 @@
 //
 // Design (HBM-bound byte work, no tensor cores):
 //   * The packed rows a CTA owns are one contiguous byte range of the tensor.
-//     One elected thread streams that range into a ring of shared-memory stages
+//     A producer warp streams that range into a ring of shared-memory stages
 //     with 1-D bulk async copies (cp.async.bulk ... mbarrier::complete_tx), several
 //     stages deep, so tens of KB per SM are in flight without spending registers.
-//   * Every thread owns a fixed 64-weight column slot of the row ("unit" x
-//     "part") and keeps its slice of x in registers for the whole kernel, as
-//     per-group fixed point: x_i ~= s * X_i with X_i a 16- or 24-bit integer
-//     split into bytes (top byte signed, lower bytes unsigned).  The packed
-//     weights are multiplied against those bytes with dp4a, so the integer dot
-//     products are exact and the only approximation is the fixed-point
-//     rounding of x (2^-23 or 2^-15 of the group's max).
-//   * Per-row partial sums go through shared memory; one warp per row adds
-//     them and writes y (or silu(g)*u for the fused gate/up form).
-//   * The kernel starts its weight copies before griddepcontrol.wait, so under
-//     programmatic dependent launch they overlap the previous kernel's tail;
-//     only x (the previous kernel's output) is read after the wait.
+//     Consumer warps hand a stage back through a second ("empty") barrier; there
+//     is no block-wide synchronisation in the main loop.
+//   * Consumer threads are arranged in row groups: a group of warps covers the
+//     columns of one row, rows_par groups work on different rows side by side.
+//     Every thread owns a fixed 64-weight column slot ("unit" x "part") and keeps
+//     its slice of x in registers for the whole kernel, as per-group fixed point:
+//     x_i ~= s * X_i with X_i a 16- or 24-bit integer split into bytes (top byte
+//     signed, lower bytes unsigned).  The packed weights are multiplied against
+//     those bytes with dp4a, so the integer dot products are exact and the only
+//     approximation is the fixed-point rounding of x (2^-23 or 2^-15 of the
+//     group's max).  x reaches the registers through a coalesced copy into a
+//     swizzled shared-memory chunk.
+//   * A row's partial sums are added inside each warp by shuffles, then across
+//     the group's warps through shared memory under a named barrier private to
+//     the group; the group's first warp writes y (or silu(g)*u, fused gate/up).
+//   * The producer starts its copies before griddepcontrol.wait, so under
+//     programmatic dependent launch they overlap the previous kernel's tail; only
+//     x (the previous kernel's output) is read after the wait.  CTAs are sized so
+//     that two fit on an SM, which lets the next kernel's CTA become resident
+//     beside a running one.
 //   * Every wait on a copy barrier is bounded by a timer; on expiry the kernel
 //     records a code in the status word, stops waiting and runs to completion.
 #pragma once
@@ -26,8 +34,15 @@ namespace orome {
 
 constexpr int PIPE_MAX_SEG = 8;
 constexpr int PIPE_MAX_STAGES = 16;
-constexpr int PIPE_MAX_THREADS = 512;
-constexpr uint32_t PIPE_WAIT_NS = 1000000000u;   // 1 s per wait
+constexpr int PIPE_MAX_CONSUMERS = 480;          // 15 consumer warps + the producer warp = 512 threads
+constexpr int PIPE_MAX_THREADS = PIPE_MAX_CONSUMERS + 32;
+constexpr int PIPE_CONSUMERS_2CTA = 288;           // consumer threads of a CTA meant to share an SM with another
+constexpr int PIPE_THREADS_2CTA = PIPE_CONSUMERS_2CTA + 32;
+constexpr int PIPE_MAX_ITERS = 8;               // rows a group handles per tile
+constexpr int PIPE_MAX_ROWS_PAR = 8;            // named barriers 1..8 belong to the row groups
+constexpr int PIPE_XCHUNK = 4096;               // floats of x staged at a time
+constexpr int PIPE_BAR_CONSUMERS = 9;           // named barrier over all consumer threads
+constexpr uint32_t PIPE_WAIT_NS = 1000000000u;  // 1 s per wait
 
 struct PipeSeg {
     const uint8_t *w;     // tensor (gate tensor in the fused form)
@@ -43,13 +58,15 @@ struct PipeArgs {
     const float *x;
     uint32_t in_dim, row_bytes;
     uint32_t units;            // column units per row (64 weights for Q8_0, one superblock for K-quants)
-    uint32_t rows_par;         // rows processed side by side
-    uint32_t rows_per_stage;   // multiple of rows_par
+    uint32_t group_threads;    // consumer threads per row group: parts*units rounded up to a warp multiple
+    uint32_t rows_par;         // row groups working side by side
+    uint32_t iters;            // rows per group per tile; a tile is rows_par*iters rows
     uint32_t nstages;
     uint32_t stage_stride;     // bytes between stages
     uint32_t half_stride;      // offset of the second tensor's rows inside a stage (fused form)
     uint32_t stage_base;       // offset of stage 0 in dynamic shared memory
-    uint32_t red_floats;       // floats per reduction buffer (per tensor)
+    uint32_t red_base;         // offset of the cross-warp reduction buffers
+    uint32_t xs_base;          // offset of the x staging chunk
     uint32_t total_rows;
     int layout;
     int *status;
@@ -65,6 +82,14 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
 {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads)
+{
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
 {
@@ -176,13 +201,17 @@ __device__ __forceinline__ void dot_s(uint32_t q, const XGroup<NP, N> &g, int k,
     for (int p = 0; p < NP; ++p) I[p] = (p == NP - 1) ? dp4a_ss(q, g.pc[p][k], I[p]) : dp4a_su(q, g.pc[p][k], I[p]);
 }
 
-__device__ __forceinline__ void load_x(const float *__restrict__ x, float *dst, int n)
+// x staging chunk: 16-byte piece G of the chunk lives at piece index (G & ~15) | ((G ^ (G >> 4)) & 15), so that
+// threads whose slots are 64 floats apart read different banks.
+__device__ __forceinline__ uint32_t xs_swizzle(uint32_t G) { return (G & ~15u) | ((G ^ (G >> 4)) & 15u); }
+
+// n (multiple of 4, <= 64) consecutive floats starting at chunk-relative element e0 (multiple of 4)
+__device__ __forceinline__ void load_x(const float4 *__restrict__ xs, uint32_t e0, float *dst, int n)
 {
-    const float4 *p = reinterpret_cast<const float4 *>(x);
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
         if (i * 4 < n) {
-            float4 v = __ldg(p + i);
+            float4 v = xs[xs_swizzle(e0 / 4 + i)];
             dst[4 * i] = v.x; dst[4 * i + 1] = v.y; dst[4 * i + 2] = v.z; dst[4 * i + 3] = v.w;
         }
     }
@@ -240,12 +269,13 @@ template <int NP>
 struct Slot<FMT_Q8_0, NP> {
     static constexpr int PARTS = 1, UNIT_ELEMS = 64;
     XGroup<NP, 32> g[2];
-    __device__ __forceinline__ void load(const float *__restrict__ x, uint32_t unit, int)
+    static __device__ __forceinline__ uint32_t first_elem(uint32_t unit, int) { return unit * 64; }
+    __device__ __forceinline__ void load(const float4 *__restrict__ xs, uint32_t e0, int)
     {
 #pragma unroll
         for (int b = 0; b < 2; ++b) {
             float xv[32];
-            load_x(x + (size_t)unit * 64 + 32 * b, xv, 32);
+            load_x(xs, e0 + 32 * b, xv, 32);
             quantize_group<NP, 32>(xv, g[b]);
         }
     }
@@ -275,16 +305,17 @@ struct SlotK45 {
     static constexpr int PARTS = 4, UNIT_ELEMS = 256;
     XGroup<NP, 32> a, b;
     float sumA, sumB;
-    __device__ __forceinline__ void load(const float *__restrict__ x, uint32_t unit, int g)
+    static __device__ __forceinline__ uint32_t first_elem(uint32_t unit, int g) { return unit * 256 + 64 * g; }
+    __device__ __forceinline__ void load(const float4 *__restrict__ xs, uint32_t e0, int)
     {
         float xv[32];
-        load_x(x + (size_t)unit * 256 + 64 * g, xv, 32);
+        load_x(xs, e0, xv, 32);
         quantize_group<NP, 32>(xv, a);
         float s = 0.0f;
 #pragma unroll
         for (int i = 0; i < 32; ++i) s += xv[i];
         sumA = s;
-        load_x(x + (size_t)unit * 256 + 64 * g + 32, xv, 32);
+        load_x(xs, e0 + 32, xv, 32);
         quantize_group<NP, 32>(xv, b);
         s = 0.0f;
 #pragma unroll
@@ -338,13 +369,16 @@ struct Slot<FMT_Q6_K, NP> {
     static constexpr int PARTS = 4, UNIT_ELEMS = 256;
     XGroup<NP, 16> g[4];
     int sx[4][NP];   // sum of the piece bytes, for the -32 offset of the 6-bit quants
-    __device__ __forceinline__ void load(const float *__restrict__ x, uint32_t unit, int part)
+    static __device__ __forceinline__ uint32_t first_elem(uint32_t unit, int part)
     {
-        int half = part >> 1, lh = part & 1;
+        return unit * 256 + 128 * (part >> 1) + 16 * (part & 1);
+    }
+    __device__ __forceinline__ void load(const float4 *__restrict__ xs, uint32_t e0, int)
+    {
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
             float xv[16];
-            load_x(x + (size_t)unit * 256 + 128 * half + 32 * t + 16 * lh, xv, 16);
+            load_x(xs, e0 + 32 * t, xv, 16);
             quantize_group<NP, 16>(xv, g[t]);
 #pragma unroll
             for (int p = 0; p < NP; ++p) {
@@ -402,8 +436,8 @@ __device__ __forceinline__ bool next_tile(const PipeArgs &a, uint32_t &cur, uint
     while (s + 1 < a.nseg && cur >= a.seg[s + 1].vstart) ++s;
     uint32_t seg_end = a.seg[s].vstart + a.seg[s].rows;
     uint32_t lim = vend < seg_end ? vend : seg_end;
-    uint32_t n = lim - cur;
-    if (n > a.rows_per_stage) n = a.rows_per_stage;
+    uint32_t n = lim - cur, cap = a.rows_par * a.iters;
+    if (n > cap) n = cap;
     t.seg = s; t.row0 = cur - a.seg[s].vstart; t.n = n;
     cur += n;
     return true;
@@ -433,99 +467,135 @@ __device__ __forceinline__ void issue_tile(const PipeArgs &a, const PipeTile &t,
         bulk_g2s(smem_u32(stage + h * a.half_stride), reinterpret_cast<const void *>(a0[h]), (uint32_t)(e1[h] - a0[h]), bar);
 }
 
-template <int FMT, int NP, bool SWIGLU>
-__global__ void __launch_bounds__(PIPE_MAX_THREADS, 1)
+template <int FMT, int NP, bool SWIGLU, int MINB>
+__global__ void __launch_bounds__(MINB == 2 ? PIPE_THREADS_2CTA : PIPE_MAX_THREADS, MINB)
 gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
 {
     extern __shared__ __align__(128) uint8_t smem[];
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem);
-    float *red = reinterpret_cast<float *>(smem + 8 * PIPE_MAX_STAGES);
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem);
+    uint64_t *empty = full + PIPE_MAX_STAGES;
+    float *red = reinterpret_cast<float *>(smem + a.red_base);
+    const float4 *xs = reinterpret_cast<const float4 *>(smem + a.xs_base);
     uint8_t *stages = smem + a.stage_base;
     __shared__ volatile int s_abort;
 
     using SlotT = Slot<FMT, NP>;
     constexpr int P = SlotT::PARTS;
-    const uint32_t tid = threadIdx.x, nthr = blockDim.x;
-    const uint32_t U = a.units, W = U * a.rows_par, PU = P * U;
-    const bool active = tid < P * W;
-    const int part = (int)(tid / W);
-    const uint32_t rem = tid % W, rp = rem / U, unit = rem % U;
+    const uint32_t tid = threadIdx.x, lane = tid & 31u;
+    const uint32_t GT = a.group_threads, C = GT * a.rows_par, GW = GT >> 5;
+    const uint32_t U = a.units;
+    const bool producer = tid >= C;
 
     const uint32_t v0 = (uint32_t)((uint64_t)blockIdx.x * a.total_rows / gridDim.x);
     const uint32_t v1 = (uint32_t)((uint64_t)(blockIdx.x + 1) * a.total_rows / gridDim.x);
 
     if (tid == 0) {
         s_abort = 0;
-        for (uint32_t s = 0; s < a.nstages; ++s) mbar_init(smem_u32(bars + s), 1);
+        for (uint32_t s = 0; s < a.nstages; ++s) {
+            mbar_init(smem_u32(full + s), 1);
+            mbar_init(smem_u32(empty + s), C >> 5);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncthreads();
-
-    // producer cursor: the weight copies do not depend on the previous kernel
-    uint32_t pcur = v0, issued = 0;
-    if (tid == 0) {
-        PipeTile t;
-        while (issued < a.nstages && next_tile(a, pcur, v1, t)) {
-            issue_tile<SWIGLU>(a, t, stages + (size_t)issued * a.stage_stride, smem_u32(bars + issued));
-            ++issued;
-        }
-    }
     pdl_launch_dependents();
+
+    if (producer) {
+        // The weight copies do not depend on the previous kernel: no griddepcontrol.wait on this path.
+        if (lane == 0) {
+            uint32_t cur = v0, i = 0;
+            PipeTile t;
+            while (next_tile(a, cur, v1, t)) {
+                const uint32_t s = i % a.nstages, k = i / a.nstages;
+                if (k > 0) {
+                    if (s_abort || !mbar_wait_bounded(smem_u32(empty + s), (k - 1) & 1u)) {
+                        if (!s_abort) { s_abort = 1; atomicExch(a.status, 2); }
+                        break;
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                }
+                issue_tile<SWIGLU>(a, t, stages + (size_t)s * a.stage_stride, smem_u32(full + s));
+                ++i;
+            }
+            if (s_abort) {   // give copies still in flight a bounded time to land before this warp leaves
+                for (uint32_t s = 0; s < a.nstages && s < i; ++s) {
+                    const uint32_t last = ((i - 1 - s) / a.nstages) * a.nstages + s;   // newest tile issued into stage s
+                    mbar_wait_bounded(smem_u32(full + s), (last / a.nstages) & 1u);
+                }
+            }
+        }
+        return;
+    }
+
+    // ---- consumers ------------------------------------------------------------------------
+    const uint32_t group = tid / GT, j = tid % GT, wig = j >> 5;
+    const bool active = j < (uint32_t)P * U;
+    const int part = (int)(j / U);
+    const uint32_t unit = j % U;
+
     pdl_wait();   // x is the previous kernel's output
 
     SlotT slot;
-    if (active) slot.load(a.x, unit, part);
+    {
+        const uint32_t e_first = active ? SlotT::first_elem(unit, part) : 0xffffffffu;
+        float4 *xsw = reinterpret_cast<float4 *>(smem + a.xs_base);
+        const float4 *xg = reinterpret_cast<const float4 *>(a.x);
+        for (uint32_t c0 = 0; c0 < a.in_dim; c0 += PIPE_XCHUNK) {
+            const uint32_t n = min((uint32_t)PIPE_XCHUNK, a.in_dim - c0);
+            for (uint32_t g4 = tid; g4 < n / 4; g4 += C) xsw[xs_swizzle(g4)] = __ldg(xg + c0 / 4 + g4);
+            named_bar_sync(PIPE_BAR_CONSUMERS, (int)C);
+            if (e_first >= c0 && e_first < c0 + n) slot.load(xs, e_first - c0, part);
+            if (c0 + PIPE_XCHUNK < a.in_dim) named_bar_sync(PIPE_BAR_CONSUMERS, (int)C);
+        }
+    }
 
-    uint32_t ccur = v0, i = 0;
+    uint32_t cur = v0, i = 0;
     PipeTile t;
-    while (next_tile(a, ccur, v1, t)) {
+    const uint32_t red_tile = a.rows_par * PIPE_MAX_ITERS * GW * (SWIGLU ? 2 : 1);   // floats per buffer
+    while (next_tile(a, cur, v1, t)) {
         const uint32_t s = i % a.nstages, parity = (i / a.nstages) & 1u;
-        if (!s_abort && !mbar_wait_bounded(smem_u32(bars + s), parity)) {
+        if (!s_abort && !mbar_wait_bounded(smem_u32(full + s), parity)) {
             s_abort = 1;
             atomicExch(a.status, 1);
         }
         const uint8_t *stage = stages + (size_t)s * a.stage_stride;
         const uint32_t delta = (uint32_t)((reinterpret_cast<uintptr_t>(a.seg[t.seg].w) + (size_t)t.row0 * a.row_bytes) & 15u);
-        float *rbuf = red + (size_t)(i & 1u) * a.red_floats * (SWIGLU ? 2 : 1);
-        if (active) {
-            for (uint32_t r = rp; r < t.n; r += a.rows_par) {
-                const uint8_t *row = stage + delta + (size_t)r * a.row_bytes;
-                rbuf[r * PU + part * U + unit] = slot.dot(row, unit, part, a.layout);
-                if constexpr (SWIGLU) {
-                    const uint32_t delta2 =
-                        (uint32_t)((reinterpret_cast<uintptr_t>(a.seg[t.seg].w2) + (size_t)t.row0 * a.row_bytes) & 15u);
-                    const uint8_t *row2 = stage + a.half_stride + delta2 + (size_t)r * a.row_bytes;
-                    rbuf[a.red_floats + r * PU + part * U + unit] = slot.dot(row2, unit, part, a.layout);
+        uint32_t delta2 = 0;
+        if constexpr (SWIGLU)
+            delta2 = (uint32_t)((reinterpret_cast<uintptr_t>(a.seg[t.seg].w2) + (size_t)t.row0 * a.row_bytes) & 15u);
+        float *rb = red + (size_t)(i & 1u) * red_tile + (size_t)group * PIPE_MAX_ITERS * GW * (SWIGLU ? 2 : 1);
+#pragma unroll 1
+        for (uint32_t it = 0; it < a.iters; ++it) {
+            const uint32_t r = it * a.rows_par + group;
+            float v = 0.0f, v2 = 0.0f;
+            if (r < t.n && active) {
+                v = slot.dot(stage + delta + (size_t)r * a.row_bytes, unit, part, a.layout);
+                if constexpr (SWIGLU)
+                    v2 = slot.dot(stage + a.half_stride + delta2 + (size_t)r * a.row_bytes, unit, part, a.layout);
+            }
+            v = warp_sum(v);
+            if constexpr (SWIGLU) v2 = warp_sum(v2);
+            if (lane == 0) {
+                rb[it * GW + wig] = v;
+                if constexpr (SWIGLU) rb[PIPE_MAX_ITERS * GW + it * GW + wig] = v2;
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(empty + s));   // this warp is done reading the stage
+        named_bar_sync(1 + (int)group, (int)GT);
+        if (wig == 0 && lane < a.iters) {
+            const uint32_t r = lane * a.rows_par + group;
+            if (r < t.n) {
+                float g = 0.0f, u = 0.0f;
+                for (uint32_t w = 0; w < GW; ++w) {
+                    g += rb[lane * GW + w];
+                    if constexpr (SWIGLU) u += rb[PIPE_MAX_ITERS * GW + lane * GW + w];
                 }
+                a.seg[t.seg].y[t.row0 + r] = SWIGLU ? silu_mul(g, u) : g;
             }
-        }
-        __syncthreads();
-        if (tid == 0) {
-            PipeTile nt;
-            if (next_tile(a, pcur, v1, nt)) {
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                issue_tile<SWIGLU>(a, nt, stages + (size_t)s * a.stage_stride, smem_u32(bars + s));
-                ++issued;
-            }
-        }
-        // one warp per row adds the partial sums
-        float *y = a.seg[t.seg].y + t.row0;
-        for (uint32_t r = tid >> 5; r < t.n; r += nthr >> 5) {
-            float acc = 0.0f, acc2 = 0.0f;
-            for (uint32_t j = tid & 31u; j < PU; j += 32) {
-                acc += rbuf[r * PU + j];
-                if constexpr (SWIGLU) acc2 += rbuf[a.red_floats + r * PU + j];
-            }
-            acc = warp_sum(acc);
-            if constexpr (SWIGLU) acc2 = warp_sum(acc2);
-            if ((tid & 31u) == 0) y[r] = SWIGLU ? silu_mul(acc, acc2) : acc;
         }
         ++i;
-    }
-    // after an expired wait: give copies still in flight a bounded time to land before the CTA exits
-    if (s_abort && tid == 0) {
-        for (uint32_t k = i; k < issued; ++k) mbar_wait_bounded(smem_u32(bars + k % a.nstages), (k / a.nstages) & 1u);
     }
 }
 

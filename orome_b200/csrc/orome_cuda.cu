@@ -29,7 +29,7 @@ struct orome_cuda_ctx {
     int x_bits = 24;
     int force_generic = 0;
     int stage_kb = 0;        // 0 = automatic
-    int ctas_per_sm = 1;
+    int ctas_per_sm = 2;
     int pdl = 1;
     // staging for the host-buffer entry point
     float *stage_x_host = nullptr, *stage_y_host = nullptr, *stage_x_dev = nullptr, *stage_y_dev = nullptr;
@@ -250,13 +250,21 @@ struct PipePlan {
     PipeArgs args;
     int threads;
     int grid;
+    int minb;       // CTAs per SM the kernel instance is compiled for
     size_t smem;
 };
 
+static uint32_t pipe_group_threads(int fmt, uint32_t in_dim)
+{
+    const uint32_t slots = fmt == FMT_Q8_0 ? in_dim / 64 : in_dim / 256 * 4;
+    return (slots + 31) / 32 * 32;
+}
+
 static bool pipe_supported(int fmt, uint32_t in_dim)
 {
-    if (fmt == FMT_Q8_0) return in_dim % 64 == 0 && in_dim / 64 <= PIPE_MAX_THREADS;
-    if (fmt == FMT_Q4_K || fmt == FMT_Q5_K || fmt == FMT_Q6_K) return in_dim % 256 == 0 && in_dim / 256 * 4 <= PIPE_MAX_THREADS;
+    if (fmt == FMT_Q8_0) return in_dim % 64 == 0 && pipe_group_threads(fmt, in_dim) <= PIPE_MAX_CONSUMERS;
+    if (fmt == FMT_Q4_K || fmt == FMT_Q5_K || fmt == FMT_Q6_K)
+        return in_dim % 256 == 0 && pipe_group_threads(fmt, in_dim) <= PIPE_MAX_CONSUMERS;
     return false;
 }
 
@@ -264,61 +272,66 @@ static bool pipe_supported(int fmt, uint32_t in_dim)
 static int plan_pipe(orome_cuda_ctx *c, int fmt, uint32_t in_dim, uint32_t total_rows, bool swiglu, PipePlan &p)
 {
     PipeArgs &a = p.args;
-    const int parts = fmt == FMT_Q8_0 ? 1 : 4;
     a.in_dim = in_dim;
     a.row_bytes = (uint32_t)row_bytes_of(fmt, in_dim);
     a.units = fmt == FMT_Q8_0 ? in_dim / 64 : in_dim / 256;
-    const uint32_t slots = a.units * parts;                 // threads one row keeps busy
-    a.rows_par = std::max(1u, std::min(16u, (uint32_t)PIPE_MAX_THREADS / slots));
-    a.rows_par = std::min(a.rows_par, std::max(1u, total_rows));
-    p.threads = (int)((slots * a.rows_par + 31) / 32 * 32);
+    a.group_threads = pipe_group_threads(fmt, in_dim);
     a.total_rows = total_rows;
+    p.minb = c->ctas_per_sm >= 2 && a.group_threads <= PIPE_CONSUMERS_2CTA ? 2 : 1;
+    if (fmt == FMT_Q6_K && c->x_bits == 24) p.minb = 1;   // its 24-bit x slices need more than the 96 registers of the two-CTA build
+    const uint32_t max_consumers = p.minb == 2 ? PIPE_CONSUMERS_2CTA : PIPE_MAX_CONSUMERS;
+    a.rows_par = std::max(1u, std::min((uint32_t)PIPE_MAX_ROWS_PAR, max_consumers / a.group_threads));
+    a.rows_par = std::min(a.rows_par, std::max(1u, total_rows));
+    const uint32_t consumers = a.group_threads * a.rows_par, gw = a.group_threads / 32;
+    p.threads = (int)consumers + 32;
+
+    p.grid = (int)std::min<uint64_t>((uint64_t)c->sm_count * p.minb, (total_rows + a.rows_par - 1) / a.rows_par);
+    p.grid = std::max(p.grid, 1);
+    const uint32_t share = (total_rows + p.grid - 1) / p.grid;            // rows of the busiest CTA
 
     const uint32_t per_row = a.row_bytes * (swiglu ? 2 : 1);
-    // stage size: a multiple of rows_par rows, about 32 KiB unless overridden
-    const uint32_t want = (c->stage_kb ? (uint32_t)c->stage_kb : 32u) * 1024u;
-    uint32_t iters = std::max(1u, want / (per_row * a.rows_par));
-    a.rows_per_stage = a.rows_par * iters;
+    const uint32_t want = (c->stage_kb ? (uint32_t)c->stage_kb : 16u) * 1024u;
+    a.iters = std::max(1u, std::min((uint32_t)PIPE_MAX_ITERS, want / (per_row * a.rows_par)));
+    a.iters = std::min(a.iters, (share + a.rows_par - 1) / a.rows_par);
 
-    const int ctas = c->ctas_per_sm;
-    p.grid = (int)std::min<uint64_t>((uint64_t)c->sm_count * ctas, (total_rows + a.rows_par - 1) / a.rows_par);
-    p.grid = std::max(p.grid, 1);
-    // do not make stages larger than a CTA's whole share
-    const uint32_t share = (total_rows + p.grid - 1) / p.grid;
-    const uint32_t share_rows = (share + a.rows_par - 1) / a.rows_par * a.rows_par;
-    a.rows_per_stage = std::min(a.rows_per_stage, share_rows);
-
-    const size_t budget = (size_t)(c->smem_optin - 1024) / ctas;
+    // shared memory of one SM is 228 KiB; every resident CTA also reserves 1 KiB
+    const size_t sm_total = 228 * 1024;
+    size_t budget = sm_total / p.minb - 1024 - 256;
+    budget = std::min(budget, (size_t)c->smem_optin - 256);
+    a.red_base = 2 * 8 * PIPE_MAX_STAGES;
+    const size_t red_bytes = (size_t)2 * a.rows_par * PIPE_MAX_ITERS * gw * (swiglu ? 2 : 1) * sizeof(float);
+    a.xs_base = (uint32_t)((a.red_base + red_bytes + 127) / 128 * 128);
+    a.stage_base = (uint32_t)((a.xs_base + (size_t)std::min<uint32_t>(in_dim, PIPE_XCHUNK) * 4 + 127) / 128 * 128);
     for (;;) {
-        a.half_stride = (a.rows_per_stage * a.row_bytes + 48 + 127) / 128 * 128;
+        a.half_stride = (a.rows_par * a.iters * a.row_bytes + 48 + 127) / 128 * 128;
         a.stage_stride = a.half_stride * (swiglu ? 2 : 1);
-        a.red_floats = a.rows_per_stage * slots;
-        size_t red_bytes = (size_t)a.red_floats * 4 * 2 * (swiglu ? 2 : 1);
-        a.stage_base = (uint32_t)((8 * PIPE_MAX_STAGES + red_bytes + 127) / 128 * 128);
-        if (a.stage_base + (size_t)a.stage_stride * 2 <= budget || a.rows_per_stage == a.rows_par) {
-            size_t room = budget > a.stage_base ? budget - a.stage_base : 0;
-            uint32_t ns = (uint32_t)std::min<size_t>(PIPE_MAX_STAGES, room / a.stage_stride);
-            const uint32_t tiles = (share + a.rows_per_stage - 1) / a.rows_per_stage + 1;
-            ns = std::min(ns, tiles);
+        const size_t room = budget > a.stage_base ? budget - a.stage_base : 0;
+        uint32_t ns = (uint32_t)std::min<size_t>(PIPE_MAX_STAGES, room / a.stage_stride);
+        if (ns >= 3 || a.iters == 1) {
             if (ns < 1) return fail(OROME_ENOTSUP, "pipe plan: a stage of %u bytes does not fit shared memory", a.stage_stride);
-            a.nstages = ns;
+            const uint32_t tiles = (share + a.rows_par * a.iters - 1) / (a.rows_par * a.iters) + 1;
+            a.nstages = std::min(ns, tiles);
             break;
         }
-        a.rows_per_stage -= a.rows_par;
+        --a.iters;
     }
     p.smem = a.stage_base + (size_t)a.stage_stride * a.nstages;
     a.status = c->status_dev;
     return OROME_OK;
 }
 
-template <int FMT, int NP, bool SW>
+template <int FMT, int NP, bool SW, int MINB>
 static int launch_pipe_inst(orome_cuda_ctx *c, const PipePlan &p, cudaStream_t st)
 {
-    auto kern = gemv_pipe_kernel<FMT, NP, SW>;
-    static size_t configured[64] = {0};   // per device: largest dynamic smem opted in so far
+    auto kern = gemv_pipe_kernel<FMT, NP, SW, MINB>;
+    static size_t configured[64] = {0};   // per device: dynamic shared memory opted in so far
     if (configured[c->device] < p.smem) {
-        CU(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, c->smem_optin));
-        configured[c->device] = (size_t)c->smem_optin;
+        cudaFuncAttributes fa;
+        CU(cudaFuncGetAttributes(&fa, kern));
+        const int max_dyn = c->smem_optin - (int)fa.sharedSizeBytes;   // the opt-in limit covers static + dynamic
+        if ((size_t)max_dyn < p.smem) return fail(OROME_ENOTSUP, "pipe launch: %zu bytes of shared memory exceed the limit %d", p.smem, max_dyn);
+        CU(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, max_dyn));
+        configured[c->device] = (size_t)max_dyn;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(p.grid);
@@ -335,11 +348,17 @@ static int launch_pipe_inst(orome_cuda_ctx *c, const PipePlan &p, cudaStream_t s
     return OROME_OK;
 }
 
+template <int FMT, int NP>
+static int launch_pipe_np(orome_cuda_ctx *c, const PipePlan &p, bool swiglu, cudaStream_t st)
+{
+    if (p.minb == 2) return swiglu ? launch_pipe_inst<FMT, NP, true, 2>(c, p, st) : launch_pipe_inst<FMT, NP, false, 2>(c, p, st);
+    return swiglu ? launch_pipe_inst<FMT, NP, true, 1>(c, p, st) : launch_pipe_inst<FMT, NP, false, 1>(c, p, st);
+}
+
 template <int FMT>
 static int launch_pipe_fmt(orome_cuda_ctx *c, const PipePlan &p, bool swiglu, cudaStream_t st)
 {
-    if (c->x_bits == 24) return swiglu ? launch_pipe_inst<FMT, 3, true>(c, p, st) : launch_pipe_inst<FMT, 3, false>(c, p, st);
-    return swiglu ? launch_pipe_inst<FMT, 2, true>(c, p, st) : launch_pipe_inst<FMT, 2, false>(c, p, st);
+    return c->x_bits == 24 ? launch_pipe_np<FMT, 3>(c, p, swiglu, st) : launch_pipe_np<FMT, 2>(c, p, swiglu, st);
 }
 
 static int launch_pipe(orome_cuda_ctx *c, int fmt, const PipePlan &p, bool swiglu, cudaStream_t st)

