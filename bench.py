@@ -103,7 +103,7 @@ class ClockSampler(threading.Thread):
 # ----------------------------------------------------------------------------------------------
 # CPU arm: the reference's CPU decode + dot on the host cores
 # ----------------------------------------------------------------------------------------------
-def cpu_layer_sample(set_name: str, reps: int):
+def cpu_layer_sample(set_name: str, reps: int, budget_s: float = 0.0):
     """Time one layer's matvecs (q,k,v,o,gate,up,down) on the host; returns (seconds per layer, meta)."""
     import numpy as np
     import oracle
@@ -124,14 +124,14 @@ def cpu_layer_sample(set_name: str, reps: int):
                               use_ref=use_ref)
 
     one_layer()
-    best = float("inf")
     times = []
+    t_all = time.perf_counter()
     for _ in range(reps):
         t0 = time.perf_counter()
         one_layer()
-        dt = time.perf_counter() - t0
-        times.append(dt)
-        best = min(best, dt)
+        times.append(time.perf_counter() - t0)
+        if budget_s and time.perf_counter() - t_all > budget_s:
+            break
     threads = (oracle.ref().ref_num_threads() if use_ref else oracle.num_threads())
     return times, dict(kind="reference" if use_ref else "port", cores=int(threads), layer_bytes=int(layer_bytes))
 
@@ -369,11 +369,11 @@ def run_ours(args):
 
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
-        times, meta = cpu_layer_sample(args.workload, 3)
+        times, meta = cpu_layer_sample(args.workload, 400, budget_s=12.0)    # about 12 s of CPU work
         per_layer = statistics.median(times)
         step_s = per_layer * w_bytes / meta["layer_bytes"]
         cpu = {"value": 1.0 / step_s, "unit": "tok/s", "cores": meta["cores"], "kind": meta["kind"],
-               "sample": f"one layer ({meta['layer_bytes']} weight bytes) x3, median, scaled to the full set by bytes",
+               "sample": f"one layer ({meta['layer_bytes']} weight bytes) x{len(times)}, median, scaled to the full set by bytes",
                "cpu_gbs": meta["layer_bytes"] / per_layer / 1e9}
 
     line = {

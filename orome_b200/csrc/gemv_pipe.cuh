@@ -15,8 +15,8 @@
 //     signed, lower bytes unsigned).  The packed weights are multiplied against
 //     those bytes with dp4a, so the integer dot products are exact and the only
 //     approximation is the fixed-point rounding of x (2^-23 or 2^-15 of the
-//     group's max).  x reaches the registers through a coalesced copy into a
-//     swizzled shared-memory chunk.
+//     group's max).  x is quantized once per CTA, cooperatively and with
+//     coalesced loads, into shared memory; each thread then picks up its slice.
 //   * A row's partial sums are added inside each warp by shuffles, then across
 //     the group's warps through shared memory under a named barrier private to
 //     the group; the group's first warp writes y (or silu(g)*u, fused gate/up).
@@ -40,7 +40,6 @@ constexpr int PIPE_CONSUMERS_2CTA = 288;           // consumer threads of a CTA 
 constexpr int PIPE_THREADS_2CTA = PIPE_CONSUMERS_2CTA + 32;
 constexpr int PIPE_MAX_ITERS = 8;               // rows a group handles per tile
 constexpr int PIPE_MAX_ROWS_PAR = 8;            // named barriers 1..8 belong to the row groups
-constexpr int PIPE_XCHUNK = 4096;               // floats of x staged at a time
 constexpr int PIPE_BAR_CONSUMERS = 9;           // named barrier over all consumer threads
 constexpr uint32_t PIPE_WAIT_NS = 1000000000u;  // 1 s per wait
 
@@ -66,7 +65,7 @@ struct PipeArgs {
     uint32_t half_stride;      // offset of the second tensor's rows inside a stage (fused form)
     uint32_t stage_base;       // offset of stage 0 in dynamic shared memory
     uint32_t red_base;         // offset of the cross-warp reduction buffers
-    uint32_t xs_base;          // offset of the x staging chunk
+    uint32_t xs_base;          // offset of the quantized copy of x (byte planes, scales, sums)
     uint32_t total_rows;
     int layout;
     int *status;
@@ -143,6 +142,15 @@ __device__ __forceinline__ int dp4a_uu(uint32_t a, uint32_t b, int c)
     uint32_t d; asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"((uint32_t)c)); return (int)d;
 }
 
+// Quantized x in shared memory: NP byte planes of in_dim bytes (plane p holds byte p of every X_i), then one
+// fp32 scale per group of G elements, then (Q4_K/Q5_K) one fp32 sum of x per 32 elements.
+struct XqView {
+    const uint8_t *planes;   // plane p at planes + p * in_dim
+    const float *scales;     // [in_dim / G]
+    const float *sums;       // [in_dim / 32] (K-quants with a min term)
+    uint32_t in_dim;
+};
+
 // ---- x as per-group fixed point -------------------------------------------
 // pc[p][k]: byte p of X_{4k..4k+3}, packed little-endian; piece NP-1 is the signed top byte.
 template <int NP, int N>
@@ -151,31 +159,20 @@ struct XGroup {
     float scale;
 };
 
+// N/4 words of every plane for N consecutive elements starting at element e0 (multiple of 16)
 template <int NP, int N>
-__device__ __forceinline__ void quantize_group(const float (&xv)[N], XGroup<NP, N> &g)
+__device__ __forceinline__ void load_group(const XqView &xv, uint32_t e0, uint32_t scale_idx, XGroup<NP, N> &g)
 {
-    constexpr float QMAX = NP == 3 ? 8388607.0f : 32767.0f;
-    float amax = 0.0f;
 #pragma unroll
-    for (int i = 0; i < N; ++i) amax = fmaxf(amax, fabsf(xv[i]));
-    float inv = amax > 0.0f ? QMAX / amax : 0.0f;
-    g.scale = amax / QMAX;
+    for (int p = 0; p < NP; ++p) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(xv.planes + (size_t)p * xv.in_dim + e0);
 #pragma unroll
-    for (int k = 0; k < N / 4; ++k) {
-        int X[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            int v = __float2int_rn(xv[4 * k + j] * inv);
-            X[j] = max(-(int)QMAX, min((int)QMAX, v));
-        }
-#pragma unroll
-        for (int p = 0; p < NP; ++p) {
-            uint32_t sel = (uint32_t)p | ((uint32_t)(4 + p) << 4);
-            uint32_t lo = __byte_perm((uint32_t)X[0], (uint32_t)X[1], sel);
-            uint32_t hi = __byte_perm((uint32_t)X[2], (uint32_t)X[3], sel);
-            g.pc[p][k] = __byte_perm(lo, hi, 0x5410);
+        for (int k = 0; k < N / 16; ++k) {
+            const uint4 w = src[k];
+            g.pc[p][4 * k] = w.x; g.pc[p][4 * k + 1] = w.y; g.pc[p][4 * k + 2] = w.z; g.pc[p][4 * k + 3] = w.w;
         }
     }
+    g.scale = xv.scales[scale_idx];
 }
 
 // sum_i q_i X_i from per-byte partial dot products I[p] = sum_i q_i * byte_p(X_i)
@@ -201,18 +198,62 @@ __device__ __forceinline__ void dot_s(uint32_t q, const XGroup<NP, N> &g, int k,
     for (int p = 0; p < NP; ++p) I[p] = (p == NP - 1) ? dp4a_ss(q, g.pc[p][k], I[p]) : dp4a_su(q, g.pc[p][k], I[p]);
 }
 
-// x staging chunk: 16-byte piece G of the chunk lives at piece index (G & ~15) | ((G ^ (G >> 4)) & 15), so that
-// threads whose slots are 64 floats apart read different banks.
-__device__ __forceinline__ uint32_t xs_swizzle(uint32_t G) { return (G & ~15u) | ((G ^ (G >> 4)) & 15u); }
+// ---- x in shared memory, quantized once per CTA --------------------------------------------
+// Layout at xq: NP byte planes of in_dim bytes (plane p holds byte p of every X_i), then one fp32
+// scale per group of G elements, then (Q4_K/Q5_K only) one fp32 sum of x per 32 elements.
 
-// n (multiple of 4, <= 64) consecutive floats starting at chunk-relative element e0 (multiple of 4)
-__device__ __forceinline__ void load_x(const float4 *__restrict__ xs, uint32_t e0, float *dst, int n)
+// Cooperative pass over x by `nthreads` consumer threads (whole warps): every lane owns 4
+// consecutive floats, a group of G elements is G/4 adjacent lanes.
+template <int NP, int G, bool SUMS>
+__device__ __forceinline__ void quantize_x_to_smem(const float *__restrict__ x, uint32_t in_dim, uint8_t *xq,
+                                                   uint32_t tid, uint32_t nthreads)
 {
+    constexpr float QMAX = NP == 3 ? 8388607.0f : 32767.0f;
+    constexpr int BATCH = 8;
+    const uint32_t n4 = in_dim / 4, lane = tid & 31u;
+    uint32_t *planes = reinterpret_cast<uint32_t *>(xq);
+    float *scales = reinterpret_cast<float *>(xq + (size_t)NP * in_dim);
+    float *sums = scales + in_dim / G;
+    const float4 *x4 = reinterpret_cast<const float4 *>(x);
+    for (uint32_t base = tid - lane; base < n4; base += nthreads * BATCH) {
+        float4 v[BATCH];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        if (i * 4 < n) {
-            float4 v = xs[xs_swizzle(e0 / 4 + i)];
-            dst[4 * i] = v.x; dst[4 * i + 1] = v.y; dst[4 * i + 2] = v.z; dst[4 * i + 3] = v.w;
+        for (int b = 0; b < BATCH; ++b) {
+            const uint32_t f = base + b * nthreads + lane;
+            v[b] = f < n4 ? __ldg(x4 + f) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int b = 0; b < BATCH; ++b) {
+            const uint32_t fb = base + b * nthreads;       // warp-uniform
+            if (fb >= n4) break;
+            const uint32_t f = fb + lane;
+            float amax = fmaxf(fmaxf(fabsf(v[b].x), fabsf(v[b].y)), fmaxf(fabsf(v[b].z), fabsf(v[b].w)));
+#pragma unroll
+            for (int o = 1; o < G / 4; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            const float inv = amax > 0.0f ? QMAX / amax : 0.0f;
+            int X[4];
+            X[0] = __float2int_rn(v[b].x * inv); X[1] = __float2int_rn(v[b].y * inv);
+            X[2] = __float2int_rn(v[b].z * inv); X[3] = __float2int_rn(v[b].w * inv);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) X[j] = max(-(int)QMAX, min((int)QMAX, X[j]));
+            float sum = 0.0f;
+            if constexpr (SUMS) {
+                sum = (v[b].x + v[b].y) + (v[b].z + v[b].w);
+#pragma unroll
+                for (int o = 1; o < 8; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            }
+            if (f < n4) {
+#pragma unroll
+                for (int p = 0; p < NP; ++p) {
+                    const uint32_t sel = (uint32_t)p | ((uint32_t)(4 + p) << 4);
+                    const uint32_t lo = __byte_perm((uint32_t)X[0], (uint32_t)X[1], sel);
+                    const uint32_t hi = __byte_perm((uint32_t)X[2], (uint32_t)X[3], sel);
+                    planes[(size_t)p * n4 + f] = __byte_perm(lo, hi, 0x5410);
+                }
+                if ((lane & (G / 4 - 1)) == 0) scales[f / (G / 4)] = amax / QMAX;
+                if constexpr (SUMS)
+                    if ((lane & 7u) == 0) sums[f / 8] = sum;
+            }
         }
     }
 }
@@ -269,15 +310,12 @@ template <int NP>
 struct Slot<FMT_Q8_0, NP> {
     static constexpr int PARTS = 1, UNIT_ELEMS = 64;
     XGroup<NP, 32> g[2];
-    static __device__ __forceinline__ uint32_t first_elem(uint32_t unit, int) { return unit * 64; }
-    __device__ __forceinline__ void load(const float4 *__restrict__ xs, uint32_t e0, int)
+    static constexpr int GROUP = 32;
+    static constexpr bool SUMS = false;
+    __device__ __forceinline__ void load(const XqView &xv, uint32_t unit, int)
     {
 #pragma unroll
-        for (int b = 0; b < 2; ++b) {
-            float xv[32];
-            load_x(xs, e0 + 32 * b, xv, 32);
-            quantize_group<NP, 32>(xv, g[b]);
-        }
+        for (int b = 0; b < 2; ++b) load_group<NP, 32>(xv, unit * 64 + 32 * b, unit * 2 + b, g[b]);
     }
     __device__ __forceinline__ float dot(const uint8_t *row, uint32_t unit, int, int) const
     {
@@ -305,22 +343,15 @@ struct SlotK45 {
     static constexpr int PARTS = 4, UNIT_ELEMS = 256;
     XGroup<NP, 32> a, b;
     float sumA, sumB;
-    static __device__ __forceinline__ uint32_t first_elem(uint32_t unit, int g) { return unit * 256 + 64 * g; }
-    __device__ __forceinline__ void load(const float4 *__restrict__ xs, uint32_t e0, int)
+    static constexpr int GROUP = 32;
+    static constexpr bool SUMS = true;
+    __device__ __forceinline__ void load(const XqView &xv, uint32_t unit, int g)
     {
-        float xv[32];
-        load_x(xs, e0, xv, 32);
-        quantize_group<NP, 32>(xv, a);
-        float s = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 32; ++i) s += xv[i];
-        sumA = s;
-        load_x(xs, e0 + 32, xv, 32);
-        quantize_group<NP, 32>(xv, b);
-        s = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 32; ++i) s += xv[i];
-        sumB = s;
+        const uint32_t e0 = unit * 256 + 64 * g;
+        load_group<NP, 32>(xv, e0, e0 / 32, a);
+        load_group<NP, 32>(xv, e0 + 32, e0 / 32 + 1, b);
+        sumA = xv.sums[e0 / 32];
+        sumB = xv.sums[e0 / 32 + 1];
     }
     __device__ __forceinline__ float dot(const uint8_t *row, uint32_t unit, int g, int layout) const
     {
@@ -369,17 +400,14 @@ struct Slot<FMT_Q6_K, NP> {
     static constexpr int PARTS = 4, UNIT_ELEMS = 256;
     XGroup<NP, 16> g[4];
     int sx[4][NP];   // sum of the piece bytes, for the -32 offset of the 6-bit quants
-    static __device__ __forceinline__ uint32_t first_elem(uint32_t unit, int part)
+    static constexpr int GROUP = 16;
+    static constexpr bool SUMS = false;
+    __device__ __forceinline__ void load(const XqView &xv, uint32_t unit, int part)
     {
-        return unit * 256 + 128 * (part >> 1) + 16 * (part & 1);
-    }
-    __device__ __forceinline__ void load(const float4 *__restrict__ xs, uint32_t e0, int)
-    {
+        const uint32_t e0 = unit * 256 + 128 * (part >> 1) + 16 * (part & 1);
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
-            float xv[16];
-            load_x(xs, e0 + 32 * t, xv, 16);
-            quantize_group<NP, 16>(xv, g[t]);
+            load_group<NP, 16>(xv, e0 + 32 * t, (e0 + 32 * t) / 16, g[t]);
 #pragma unroll
             for (int p = 0; p < NP; ++p) {
                 int s = 0;
@@ -475,7 +503,6 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);
     uint64_t *empty = full + PIPE_MAX_STAGES;
     float *red = reinterpret_cast<float *>(smem + a.red_base);
-    const float4 *xs = reinterpret_cast<const float4 *>(smem + a.xs_base);
     uint8_t *stages = smem + a.stage_base;
     __shared__ volatile int s_abort;
 
@@ -538,16 +565,15 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
 
     SlotT slot;
     {
-        const uint32_t e_first = active ? SlotT::first_elem(unit, part) : 0xffffffffu;
-        float4 *xsw = reinterpret_cast<float4 *>(smem + a.xs_base);
-        const float4 *xg = reinterpret_cast<const float4 *>(a.x);
-        for (uint32_t c0 = 0; c0 < a.in_dim; c0 += PIPE_XCHUNK) {
-            const uint32_t n = min((uint32_t)PIPE_XCHUNK, a.in_dim - c0);
-            for (uint32_t g4 = tid; g4 < n / 4; g4 += C) xsw[xs_swizzle(g4)] = __ldg(xg + c0 / 4 + g4);
-            named_bar_sync(PIPE_BAR_CONSUMERS, (int)C);
-            if (e_first >= c0 && e_first < c0 + n) slot.load(xs, e_first - c0, part);
-            if (c0 + PIPE_XCHUNK < a.in_dim) named_bar_sync(PIPE_BAR_CONSUMERS, (int)C);
-        }
+        uint8_t *xq = smem + a.xs_base;
+        quantize_x_to_smem<NP, SlotT::GROUP, SlotT::SUMS>(a.x, a.in_dim, xq, tid, C);
+        named_bar_sync(PIPE_BAR_CONSUMERS, (int)C);
+        XqView xv;
+        xv.planes = xq;
+        xv.scales = reinterpret_cast<const float *>(xq + (size_t)NP * a.in_dim);
+        xv.sums = xv.scales + a.in_dim / SlotT::GROUP;
+        xv.in_dim = a.in_dim;
+        if (active) slot.load(xv, unit, part);
     }
 
     uint32_t cur = v0, i = 0;

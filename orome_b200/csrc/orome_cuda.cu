@@ -278,7 +278,7 @@ static int plan_pipe(orome_cuda_ctx *c, int fmt, uint32_t in_dim, uint32_t total
     a.group_threads = pipe_group_threads(fmt, in_dim);
     a.total_rows = total_rows;
     p.minb = c->ctas_per_sm >= 2 && a.group_threads <= PIPE_CONSUMERS_2CTA ? 2 : 1;
-    if (fmt == FMT_Q6_K && c->x_bits == 24) p.minb = 1;   // its 24-bit x slices need more than the 96 registers of the two-CTA build
+    if (fmt == FMT_Q6_K && c->x_bits == 24 && swiglu) p.minb = 1;   // needs more than the 96 registers of the two-CTA build
     const uint32_t max_consumers = p.minb == 2 ? PIPE_CONSUMERS_2CTA : PIPE_MAX_CONSUMERS;
     a.rows_par = std::max(1u, std::min((uint32_t)PIPE_MAX_ROWS_PAR, max_consumers / a.group_threads));
     a.rows_par = std::min(a.rows_par, std::max(1u, total_rows));
@@ -301,7 +301,10 @@ static int plan_pipe(orome_cuda_ctx *c, int fmt, uint32_t in_dim, uint32_t total
     a.red_base = 2 * 8 * PIPE_MAX_STAGES;
     const size_t red_bytes = (size_t)2 * a.rows_par * PIPE_MAX_ITERS * gw * (swiglu ? 2 : 1) * sizeof(float);
     a.xs_base = (uint32_t)((a.red_base + red_bytes + 127) / 128 * 128);
-    a.stage_base = (uint32_t)((a.xs_base + (size_t)std::min<uint32_t>(in_dim, PIPE_XCHUNK) * 4 + 127) / 128 * 128);
+    // quantized x: one byte plane per 8 bits of x, a scale per group (16 for Q6_K, else 32), a sum per 32 elements
+    const size_t np = c->x_bits == 24 ? 3 : 2;
+    const size_t xq_bytes = np * in_dim + (size_t)in_dim / (fmt == FMT_Q6_K ? 16 : 32) * 4 + (size_t)in_dim / 32 * 4;
+    a.stage_base = (uint32_t)((a.xs_base + xq_bytes + 127) / 128 * 128);
     for (;;) {
         a.half_stride = (a.rows_par * a.iters * a.row_bytes + 48 + 127) / 128 * 128;
         a.stage_stride = a.half_stride * (swiglu ? 2 : 1);
