@@ -51,7 +51,7 @@ def measured_peak():
 class ClockSampler(threading.Thread):
     """Samples SM clock and throttle reasons through NVML (read-only) while a region runs."""
 
-    def __init__(self, index: int, period: float = 0.05):
+    def __init__(self, index: int, period: float = 0.004):
         super().__init__(daemon=True)
         self.index, self.period = index, period
         self.samples, self.reasons = [], set()

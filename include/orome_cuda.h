@@ -211,6 +211,7 @@ int  orome_cuda_matvec_host(orome_cuda_ctx *ctx, const OromeTensorRef *ref,
 #define OROME_OPT_STAGE_KB       3
 #define OROME_OPT_CTAS_PER_SM    4
 #define OROME_OPT_PDL            5
+#define OROME_OPT_GRID_PER_SM    6
 int  orome_cuda_set_option(orome_cuda_ctx *ctx, int key, int value);
 int  orome_cuda_get_option(orome_cuda_ctx *ctx, int key, int *value);
 

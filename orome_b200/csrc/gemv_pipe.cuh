@@ -305,17 +305,31 @@ __device__ __forceinline__ void pair_scales(uint32_t w0, uint32_t w1, uint32_t w
 // ---- per-format column slots ----------------------------------------------
 template <int FMT, int NP> struct Slot;
 
-// Q8_0: unit = two blocks (68 bytes, 4-byte aligned), one part.
+// Q8_0: unit = two blocks (68 bytes, 4-byte aligned), one part.  The first block's quants sit
+// two bytes into their words (after the fp16 scale), so the thread keeps that block's x bytes
+// shifted the same way, with zero bytes facing the scale bytes: nine dp4a per byte plane cover
+// the unit's first nine words as they are, no realignment of the weights needed.
 template <int NP>
 struct Slot<FMT_Q8_0, NP> {
     static constexpr int PARTS = 1, UNIT_ELEMS = 64;
-    XGroup<NP, 32> g[2];
     static constexpr int GROUP = 32;
     static constexpr bool SUMS = false;
+    uint32_t x0[NP][9];       // block 0, shifted by two bytes
+    XGroup<NP, 32> g1;        // block 1, word aligned
+    float s0;
     __device__ __forceinline__ void load(const XqView &xv, uint32_t unit, int)
     {
+        XGroup<NP, 32> g0;
+        load_group<NP, 32>(xv, unit * 64, unit * 2, g0);
+        load_group<NP, 32>(xv, unit * 64 + 32, unit * 2 + 1, g1);
+        s0 = g0.scale;
 #pragma unroll
-        for (int b = 0; b < 2; ++b) load_group<NP, 32>(xv, unit * 64 + 32 * b, unit * 2 + b, g[b]);
+        for (int p = 0; p < NP; ++p) {
+            x0[p][0] = g0.pc[p][0] << 16;
+#pragma unroll
+            for (int j = 1; j < 8; ++j) x0[p][j] = __byte_perm(g0.pc[p][j - 1], g0.pc[p][j], 0x5432);
+            x0[p][8] = g0.pc[p][7] >> 16;
+        }
     }
     __device__ __forceinline__ float dot(const uint8_t *row, uint32_t unit, int, int) const
     {
@@ -327,13 +341,16 @@ struct Slot<FMT_Q8_0, NP> {
 #pragma unroll
         for (int p = 0; p < NP; ++p) { I0[p] = 0; I1[p] = 0; }
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            dot_s<NP, 32>(__byte_perm(v[j], v[j + 1], 0x5432), g[0], j, I0);
-            dot_s<NP, 32>(v[9 + j], g[1], j, I1);
+        for (int j = 0; j < 9; ++j) {
+#pragma unroll
+            for (int p = 0; p < NP; ++p)
+                I0[p] = (p == NP - 1) ? dp4a_ss(v[j], x0[p][j], I0[p]) : dp4a_su(v[j], x0[p][j], I0[p]);
         }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) dot_s<NP, 32>(v[9 + j], g1, j, I1);
         float d0 = __half2float(__ushort_as_half((unsigned short)(v[0] & 0xffffu)));
         float d1 = __half2float(__ushort_as_half((unsigned short)(v[8] >> 16)));
-        return fmaf(d0 * g[0].scale, combine<NP>(I0), d1 * g[1].scale * combine<NP>(I1));
+        return fmaf(d0 * s0, combine<NP>(I0), d1 * g1.scale * combine<NP>(I1));
     }
 };
 

@@ -29,7 +29,8 @@ struct orome_cuda_ctx {
     int x_bits = 24;
     int force_generic = 0;
     int stage_kb = 0;        // 0 = automatic
-    int ctas_per_sm = 2;
+    int ctas_per_sm = 1;     // CTAs an SM is sized to hold (1 or 2); measured best with one large CTA
+    int grid_per_sm = 1;     // CTAs per SM a launch creates; 1 with ctas_per_sm 2 leaves room for the next kernel's CTA
     int pdl = 1;
     // staging for the host-buffer entry point
     float *stage_x_host = nullptr, *stage_y_host = nullptr, *stage_x_dev = nullptr, *stage_y_dev = nullptr;
@@ -168,6 +169,9 @@ extern "C" int orome_cuda_set_option(orome_cuda_ctx *c, int key, int value)
         if (value < 1 || value > 4) return fail(OROME_EINVAL, "CTAS_PER_SM must be 1..4");
         c->ctas_per_sm = value; return OROME_OK;
     case OROME_OPT_PDL: c->pdl = value != 0; return OROME_OK;
+    case OROME_OPT_GRID_PER_SM:
+        if (value < 1 || value > 2) return fail(OROME_EINVAL, "GRID_PER_SM must be 1 or 2");
+        c->grid_per_sm = value; return OROME_OK;
     }
     return fail(OROME_EINVAL, "set_option: unknown key %d", key);
 }
@@ -181,6 +185,7 @@ extern "C" int orome_cuda_get_option(orome_cuda_ctx *c, int key, int *value)
     case OROME_OPT_STAGE_KB: *value = c->stage_kb; return OROME_OK;
     case OROME_OPT_CTAS_PER_SM: *value = c->ctas_per_sm; return OROME_OK;
     case OROME_OPT_PDL: *value = c->pdl; return OROME_OK;
+    case OROME_OPT_GRID_PER_SM: *value = c->grid_per_sm; return OROME_OK;
     }
     return fail(OROME_EINVAL, "get_option: unknown key %d", key);
 }
@@ -285,7 +290,7 @@ static int plan_pipe(orome_cuda_ctx *c, int fmt, uint32_t in_dim, uint32_t total
     const uint32_t consumers = a.group_threads * a.rows_par, gw = a.group_threads / 32;
     p.threads = (int)consumers + 32;
 
-    p.grid = (int)std::min<uint64_t>((uint64_t)c->sm_count * p.minb, (total_rows + a.rows_par - 1) / a.rows_par);
+    p.grid = (int)std::min<uint64_t>((uint64_t)c->sm_count * std::min(p.minb, c->grid_per_sm), (total_rows + a.rows_par - 1) / a.rows_par);
     p.grid = std::max(p.grid, 1);
     const uint32_t share = (total_rows + p.grid - 1) / p.grid;            // rows of the busiest CTA
 
