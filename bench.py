@@ -182,36 +182,25 @@ class Stepper:
         g.manual_seed(1234)
         self.x_h = torch.randn(H, device=dev, generator=g)           # input of every hidden-sized product
         self.x_a = torch.randn(A, device=dev, generator=g)           # input of the down projection
+        from orome_b200.rowsplit import padded_rows
         w = ds.world
-        # full-size outputs (all-gather targets when sharded); local slices are written in place
-        self.q, self.k, self.v = (torch.zeros(n, device=dev) for n in (H, KV, KV))
-        self.o, self.act, self.dn, self.logits = (torch.zeros(n, device=dev) for n in (H, A, H, V))
+        # gather buffers (padded to equal slices per rank when sharded); local slices are written in place
+        self.q, self.k, self.v = (torch.zeros(padded_rows(n, w), device=dev) for n in (H, KV, KV))
+        self.o, self.act, self.dn, self.logits = (torch.zeros(padded_rows(n, w), device=dev) for n in (H, A, H, V))
         self.refs = [[ds.ref(t) for t in lt] for lt in ds.tensors]
         self.lm_ref = ds.ref(ds.lm_head)
         self.graph = None
         self.launches_per_step = 0
 
     def _slice(self, full, full_out):
-        from orome_b200.decode_set import shard_rows
+        from orome_b200.rowsplit import shard_rows
         lo, hi = shard_rows(full_out, self.ds.rank, self.ds.world)
         return full[lo:hi]
 
     def _gather(self, full, full_out):
         """All-gather of the output vector when the rows are split over ranks."""
-        if self.ds.world == 1:
-            return
-        from orome_b200.decode_set import shard_rows
-        w = self.ds.world
-        lo, hi = shard_rows(full_out, self.ds.rank, w)
-        per = (full_out // w + 31) // 32 * 32
-        if per * w == full_out:
-            self.dist.all_gather_into_tensor(full, full[lo:hi])
-        else:   # ragged last shard: gather padded slices
-            pad = self.torch.zeros(per, device=full.device)
-            pad[:hi - lo] = full[lo:hi]
-            out = self.torch.empty(per * w, device=full.device)
-            self.dist.all_gather_into_tensor(out, pad)
-            full.copy_(out[:full_out])
+        from orome_b200.rowsplit import all_gather_rows
+        all_gather_rows(self.dist, full, full_out, self.ds.rank, self.ds.world)
 
     def issue(self, stream):
         ctx, ds = self.ctx, self.ds
@@ -220,16 +209,25 @@ class Stepper:
         c0 = ctx.launch_count
         for refs in self.refs:
             rq, rk, rv, ro, rg, ru, rd = refs
-            ctx.matvec_group([rq, rk, rv], xh, [self._slice(self.q, H).data_ptr(), self._slice(self.k, KV).data_ptr(),
-                                                self._slice(self.v, KV).data_ptr()], stream)
+            if rq.out_dim and rk.out_dim and rv.out_dim:
+                ctx.matvec_group([rq, rk, rv], xh, [self._slice(self.q, H).data_ptr(), self._slice(self.k, KV).data_ptr(),
+                                                    self._slice(self.v, KV).data_ptr()], stream)
+            else:   # some rank holds no rows of a small tensor
+                for r, buf, n in ((rq, self.q, H), (rk, self.k, KV), (rv, self.v, KV)):
+                    if r.out_dim:
+                        ctx.matvec(r, xh, self._slice(buf, n).data_ptr(), 1, 0, 0, stream)
             self._gather(self.q, H); self._gather(self.k, KV); self._gather(self.v, KV)
-            ctx.matvec(ro, xh, self._slice(self.o, H).data_ptr(), 1, 0, 0, stream)
+            if ro.out_dim:
+                ctx.matvec(ro, xh, self._slice(self.o, H).data_ptr(), 1, 0, 0, stream)
             self._gather(self.o, H)
-            ctx.gate_up_swiglu(rg, ru, xh, self._slice(self.act, A).data_ptr(), 1, 0, 0, stream)
+            if rg.out_dim:
+                ctx.gate_up_swiglu(rg, ru, xh, self._slice(self.act, A).data_ptr(), 1, 0, 0, stream)
             self._gather(self.act, A)
-            ctx.matvec(rd, xa, self._slice(self.dn, H).data_ptr(), 1, 0, 0, stream)
+            if rd.out_dim:
+                ctx.matvec(rd, xa, self._slice(self.dn, H).data_ptr(), 1, 0, 0, stream)
             self._gather(self.dn, H)
-        ctx.matvec(self.lm_ref, xh, self._slice(self.logits, V).data_ptr(), 1, 0, 0, stream)
+        if self.lm_ref.out_dim:
+            ctx.matvec(self.lm_ref, xh, self._slice(self.logits, V).data_ptr(), 1, 0, 0, stream)
         self._gather(self.logits, V)
         self.launches_per_step = ctx.launch_count - c0
 
@@ -334,7 +332,7 @@ def run_ours(args):
     def e2e_step():
         st.x_h.copy_(x_pin, non_blocking=True)
         st.step()
-        logits_pin.copy_(st.logits, non_blocking=True)
+        logits_pin.copy_(st.logits[:ds.vocab], non_blocking=True)
         torch.cuda.current_stream().synchronize()      # the host needs the logits before the next token
 
     for _ in range(3):
@@ -348,10 +346,20 @@ def run_ours(args):
     if ctx.status() != 0:
         raise SystemExit("bench.py: a kernel reported an expired wait; the numbers are void")
 
-    # ---- spot check of the last step against the CPU oracle (one small slice, rank 0) -------
+    def leave():
+        """Multi-rank exit: agree that every rank is done, then leave without tearing NCCL down
+        (destroying a communicator that a captured graph still references can block)."""
+        if dist is None:
+            return
+        sys.stdout.flush()
+        sys.stderr.flush()
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        os._exit(0)
+
     if rank != 0:
-        if dist is not None:
-            dist.destroy_process_group()
+        leave()
         return
 
     peak, peak_kind = measured_peak()
@@ -395,8 +403,7 @@ def run_ours(args):
     if cpu is not None:
         line["cpu_baseline"] = cpu
     print(json.dumps(line), flush=True)
-    if dist is not None:
-        dist.destroy_process_group()
+    leave()
 
 
 def main():

@@ -14,6 +14,7 @@ from dataclasses import dataclass
 
 from . import format as F
 from . import synth
+from .rowsplit import shard_rows
 
 # name -> (format, out_dim, in_dim); "h" = hidden-sized input, "a" = ffn-sized input
 SETS = {
@@ -40,15 +41,6 @@ class Tensor:
     offset: int       # byte offset inside the arena
     nbytes: int
     full_out: int     # rows of the whole tensor
-
-
-def shard_rows(n: int, rank: int, world: int) -> tuple[int, int]:
-    """Row range of `rank`; boundaries are multiples of 32 rows like the reference's 32-row tiles
-    (format.m:228-238) except for the last shard, which takes the remainder."""
-    per = (n // world + 31) // 32 * 32
-    lo = min(n, rank * per)
-    hi = n if rank == world - 1 else min(n, lo + per)
-    return lo, hi
 
 
 class DecodeSet:
