@@ -177,6 +177,31 @@ int  orome_cuda_moe_route(orome_cuda_ctx *ctx, const OromeTensorRef *router,
                           uint32_t *idx_dev, float *w_dev, float *logits_dev /* optional [t][n_experts] */,
                           void *stream);
 
+/* Routing for callers that must not allocate.  No counterpart in the reference (its
+ * Metal context sizes every scratch buffer once, at start-up, metal.m:155-251).
+ *
+ * Same result as orome_cuda_moe_route called without a logits buffer, but the router
+ * logits go to a fixed array that is part of the library image (device memory of
+ * OROME_ROUTE_STATIC_MAX_LOGITS floats, 64 KiB, held by every GPU that loads the library
+ * until the process exits) instead of context scratch obtained with cudaMalloc.  It is
+ * meant for the per-token loop of an engine that, like the reference, reserves all device
+ * memory up front and then forbids allocation - cudaMalloc synchronises the whole device
+ * and can fail once the model has filled HBM - and for hosts whose device memory belongs
+ * entirely to another allocator.  The call itself performs no cudaMalloc / cudaFree and
+ * calls no allocating library routine.
+ *
+ *   - n_tokens * n_experts must not exceed OROME_ROUTE_STATIC_MAX_LOGITS, else OROME_EINVAL.
+ *   - The first call on a device looks up the array's device address (once per device,
+ *     with that device current); make that first call before any stream capture.
+ *   - All calls on a device share the one array and it keeps the previous call's logits.
+ *     Nothing in it has to start at zero (every entry that is read is written first by the
+ *     same call), but two calls whose kernels overlap on the GPU - different streams, or
+ *     different contexts on the same device - race on it: keep them in one stream. */
+#define OROME_ROUTE_STATIC_MAX_LOGITS (64 * 256)
+int  orome_cuda_moe_route_static(orome_cuda_ctx *ctx, const OromeTensorRef *router,
+                                 const float *x_dev, int n_tokens, int ldx, uint32_t K,
+                                 uint32_t *idx_dev, float *w_dev, void *stream);
+
 /* Routed-expert FFN with the weighted combine, replacing
  * batch_expert_gate_up_swiglu_q4k_dyn, batch_expert_down_q4k_dyn / _q5k_dyn and
  * the expert term of moe_combine_copy_sq (shaders.metal:2232-2310, 2590-2760,

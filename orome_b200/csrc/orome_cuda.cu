@@ -577,6 +577,48 @@ extern "C" int orome_cuda_moe_route(orome_cuda_ctx *c, const OromeTensorRef *rou
     return post_launch(c, "route_topk");
 }
 
+// ---------------------------------------------------------------------------
+// routing without any allocation
+// ---------------------------------------------------------------------------
+// Scratch for the router logits of orome_cuda_moe_route_static.  The array lives in the library image: every
+// device that loads the library holds its 64 KiB until the process exits.  In host code this name is only a
+// stand-in for the symbol, not a device address; the address a kernel may use comes from cudaGetSymbolAddress,
+// looked up once per device with that device current.
+static __device__ __align__(256) float g_route_logits_static[OROME_ROUTE_STATIC_MAX_LOGITS];
+static float *g_route_logits_addr[64];   // per device ordinal, filled on first use
+
+extern "C" int orome_cuda_moe_route_static(orome_cuda_ctx *c, const OromeTensorRef *router, const float *x_dev, int n_tokens,
+                                           int ldx, uint32_t K, uint32_t *idx_dev, float *w_dev, void *stream)
+{
+    if (!c || !router || !x_dev || !idx_dev || !w_dev) return fail(OROME_EINVAL, "moe_route_static: NULL argument");
+    if (!router->buffer) return fail(OROME_EINVAL, "moe_route_static: router tensor is absent");
+    const uint8_t *data;
+    int rc = check_ref("moe_route_static", router, &data);
+    if (rc) return rc;
+    if (router->format != OROME_QFMT_F32) return fail(OROME_ENOTSUP, "moe_route_static: the router must be an F32 tensor");
+    if (router->out_dim > 256) return fail(OROME_EINVAL, "moe_route_static: %u experts (the routing kernel takes at most 256)", router->out_dim);
+    if (n_tokens < 1 || (n_tokens > 1 && ldx < (int)router->in_dim)) return fail(OROME_EINVAL, "moe_route_static: bad n_tokens/ldx");
+    if (K < 1) return fail(OROME_EINVAL, "moe_route_static: K must be at least 1");
+    const uint32_t ne = router->out_dim;
+    if ((size_t)n_tokens * ne > (size_t)OROME_ROUTE_STATIC_MAX_LOGITS)
+        return fail(OROME_EINVAL, "moe_route_static: %d tokens x %u experts = %zu logits exceed the fixed scratch of %d floats; "
+                    "use orome_cuda_moe_route with a caller buffer", n_tokens, ne, (size_t)n_tokens * ne, OROME_ROUTE_STATIC_MAX_LOGITS);
+    if (c->device < 0 || c->device >= 64) return fail(OROME_EINVAL, "moe_route_static: device ordinal %d out of range", c->device);
+    CU(cudaSetDevice(c->device));
+    if (!g_route_logits_addr[c->device]) {   // set-up: once per device, with that device current
+        void *p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_route_logits_static);
+        if (e != cudaSuccess || !p) return fail(OROME_ECUDA, "moe_route_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        g_route_logits_addr[c->device] = static_cast<float *>(p);
+    }
+    float *logits = g_route_logits_addr[c->device];
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    rc = launch_generic(c, FMT_F32, data, ne, router->in_dim, 0, x_dev, n_tokens, ldx, logits, (int)ne, st);
+    if (rc) return rc;
+    route_topk_kernel<<<n_tokens, 256, 0, st>>>(logits, (int)ne, ne, K, idx_dev, w_dev);
+    return post_launch(c, "route_topk");
+}
+
 extern "C" int orome_cuda_moe_ffn(orome_cuda_ctx *c, const OromeExpertLayerRef *L, uint32_t variant, const float *x_dev,
                                   int n_tokens, int ldx, const uint32_t *idx_dev, const float *w_dev, uint32_t K, uint32_t hidden,
                                   uint32_t inter, float *act_dev, float *out_dev, int ldo, void *stream)

@@ -18,6 +18,7 @@ VARIANT_DEFAULT, VARIANT_LLAMA = 0, 1
 OPT_X_BITS, OPT_FORCE_GENERIC, OPT_STAGE_KB, OPT_CTAS_PER_SM, OPT_PDL, OPT_GRID_PER_SM = 1, 2, 3, 4, 5, 6
 
 OK, EINVAL, ENOTSUP, ENOMEM, ECUDA, ETIMEOUT = 0, -22, -95, -12, -5, -110
+ROUTE_STATIC_MAX_LOGITS = 64 * 256
 
 
 class OromeError(RuntimeError):
@@ -44,7 +45,7 @@ EXPORTS = [
     "orome_cuda_ctx_create", "orome_cuda_ctx_destroy", "orome_cuda_last_error", "orome_cuda_status", "orome_cuda_upload",
     "orome_cuda_free", "orome_format_from_ggml_type", "orome_format_row_bytes", "orome_format_dispatch_matvec",
     "orome_cuda_matvec", "orome_cuda_matvec_group", "orome_cuda_gate_up_swiglu", "orome_cuda_dequant_rows",
-    "orome_cuda_moe_route", "orome_cuda_moe_ffn", "orome_cuda_matvec_host", "orome_cuda_set_option",
+    "orome_cuda_moe_route", "orome_cuda_moe_route_static", "orome_cuda_moe_ffn", "orome_cuda_matvec_host", "orome_cuda_set_option",
     "orome_cuda_get_option", "orome_cuda_launch_count",
 ]
 
@@ -78,6 +79,7 @@ def lib():
     L.orome_cuda_gate_up_swiglu.argtypes = [vp, TR, TR, vp, vp, i32, i32, i32, vp]
     L.orome_cuda_dequant_rows.argtypes = [vp, TR, u32, u32, vp, vp]
     L.orome_cuda_moe_route.argtypes = [vp, TR, vp, i32, i32, u32, vp, vp, vp, vp]
+    L.orome_cuda_moe_route_static.argtypes = [vp, TR, vp, i32, i32, u32, vp, vp, vp]
     L.orome_cuda_moe_ffn.argtypes = [vp, EL, u32, vp, i32, i32, vp, vp, u32, u32, u32, vp, vp, i32, vp]
     L.orome_cuda_matvec_host.argtypes = [vp, TR, vp, vp, i32]
     L.orome_cuda_set_option.argtypes = [vp, i32, i32]
@@ -172,6 +174,10 @@ class Context:
     def moe_route(self, router: TensorRef, x: int, n_tokens: int, ldx: int, K: int, idx: int, w: int, logits: int = 0,
                   stream: int = 0):
         _chk(lib().orome_cuda_moe_route(self._h, C.byref(router), x, n_tokens, ldx, K, idx, w, logits or None, stream))
+
+    def moe_route_static(self, router: TensorRef, x: int, n_tokens: int, ldx: int, K: int, idx: int, w: int, stream: int = 0):
+        """Routing with the logits in the library's fixed scratch array: no allocation (see include/orome_cuda.h)."""
+        _chk(lib().orome_cuda_moe_route_static(self._h, C.byref(router), x, n_tokens, ldx, K, idx, w, stream))
 
     def moe_ffn(self, layer: ExpertLayerRef, variant: int, x: int, n_tokens: int, ldx: int, idx: int, w: int, K: int,
                 hidden: int, inter: int, act: int, out: int, ldo: int, stream: int = 0):
