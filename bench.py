@@ -191,6 +191,7 @@ class Stepper:
         self.lm_ref = ds.ref(ds.lm_head)
         self.graph = None
         self.launches_per_step = 0
+        self.hints = True
 
     def _slice(self, full, full_out):
         from orome_b200.rowsplit import shard_rows
@@ -207,8 +208,12 @@ class Stepper:
         H, A, KV, V = ds.hidden, ds.ffn, ds.kv, ds.vocab
         xh, xa = self.x_h.data_ptr(), self.x_a.data_ptr()
         c0 = ctx.launch_count
-        for refs in self.refs:
+        hint = ctx.hint_next if self.hints else (lambda r: None)
+        nl = len(self.refs)
+        for li, refs in enumerate(self.refs):
             rq, rk, rv, ro, rg, ru, rd = refs
+            nxt_q = self.refs[li + 1][0] if li + 1 < nl else self.lm_ref      # first tensor the step reads after this layer
+            hint(ro if ro.out_dim else None)
             if rq.out_dim and rk.out_dim and rv.out_dim:
                 ctx.matvec_group([rq, rk, rv], xh, [self._slice(self.q, H).data_ptr(), self._slice(self.k, KV).data_ptr(),
                                                     self._slice(self.v, KV).data_ptr()], stream)
@@ -218,15 +223,19 @@ class Stepper:
                         ctx.matvec(r, xh, self._slice(buf, n).data_ptr(), 1, 0, 0, stream)
             self._gather(self.q, H); self._gather(self.k, KV); self._gather(self.v, KV)
             if ro.out_dim:
+                hint(rg)
                 ctx.matvec(ro, xh, self._slice(self.o, H).data_ptr(), 1, 0, 0, stream)
             self._gather(self.o, H)
             if rg.out_dim:
+                hint(rd)
                 ctx.gate_up_swiglu(rg, ru, xh, self._slice(self.act, A).data_ptr(), 1, 0, 0, stream)
             self._gather(self.act, A)
             if rd.out_dim:
+                hint(nxt_q if nxt_q.out_dim else None)
                 ctx.matvec(rd, xa, self._slice(self.dn, H).data_ptr(), 1, 0, 0, stream)
             self._gather(self.dn, H)
         if self.lm_ref.out_dim:
+            hint(self.refs[0][0] if nl and self.refs[0][0].out_dim else None)   # the next token starts at layer 0 again
             ctx.matvec(self.lm_ref, xh, self._slice(self.logits, V).data_ptr(), 1, 0, 0, stream)
         self._gather(self.logits, V)
         self.launches_per_step = ctx.launch_count - c0
@@ -273,6 +282,8 @@ def run_ours(args):
     ctx = F.Context(local)
     if args.x_bits:
         ctx.set_option(F.OPT_X_BITS, args.x_bits)
+    if args.prefetch_mb >= 0:
+        ctx.set_option(F.OPT_PREFETCH_MB, args.prefetch_mb)
 
     ds = decode_set.DecodeSet(args.workload, dev, rank=rank, world=world, layers=args.layers)
     st = Stepper(torch, F, ctx, ds, dist)
@@ -418,6 +429,7 @@ def main():
     ap.add_argument("--graph", dest="graph", action="store_true", default=True)
     ap.add_argument("--no-graph", dest="graph", action="store_false")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--prefetch-mb", type=int, default=-1, help="cap of the next-tensor L2 prefetch in MiB (0 = off, -1 = library default)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

@@ -217,6 +217,14 @@ int  orome_cuda_moe_ffn(orome_cuda_ctx *ctx, const OromeExpertLayerRef *layer, u
                         uint32_t hidden, uint32_t inter, float *act_dev, float *out_dev, int ldo,
                         void *stream);
 
+/* Optional hint: the tensor the NEXT matvec / group / gate-up call on this context will read.
+ * The launch issued in between pulls the first bytes of that tensor into L2 once its own rows
+ * are requested, so HBM keeps streaming across the launch boundary (a decode step is a fixed
+ * sequence of products, engine.m:481-1046, so the caller always knows the next tensor).  The hint
+ * is consumed by the next launch and then cleared; passing NULL clears it.  Purely a
+ * performance hint: results do not depend on it. */
+int  orome_cuda_hint_next(orome_cuda_ctx *ctx, const OromeTensorRef *next);
+
 /* ---- host-buffer convenience (end-to-end form) --------------------------- */
 
 /* Same product as orome_cuda_matvec with HOST x and y: copies x to the device,
@@ -237,6 +245,7 @@ int  orome_cuda_matvec_host(orome_cuda_ctx *ctx, const OromeTensorRef *ref,
 #define OROME_OPT_CTAS_PER_SM    4
 #define OROME_OPT_PDL            5
 #define OROME_OPT_GRID_PER_SM    6
+#define OROME_OPT_PREFETCH_MB     7   /* cap on the L2 prefetch of orome_cuda_hint_next, MiB (0 = off) */
 int  orome_cuda_set_option(orome_cuda_ctx *ctx, int key, int value);
 int  orome_cuda_get_option(orome_cuda_ctx *ctx, int key, int *value);
 

@@ -17,9 +17,10 @@
 //     approximation is the fixed-point rounding of x (2^-23 or 2^-15 of the
 //     group's max).  x is quantized once per CTA, cooperatively and with
 //     coalesced loads, into shared memory; each thread then picks up its slice.
-//   * A row's partial sums are added inside each warp by shuffles, then across
-//     the group's warps through shared memory under a named barrier private to
-//     the group; the group's first warp writes y (or silu(g)*u, fused gate/up).
+//   * A row's partial sums are added inside each warp by shuffles; the per-warp
+//     sums of a batch of rows wait in shared memory and all consumer threads add
+//     them up together, one barrier per batch, writing y (or silu(g)*u for the
+//     fused gate/up form) with coalesced stores.
 //   * The producer starts its copies before griddepcontrol.wait, so under
 //     programmatic dependent launch they overlap the previous kernel's tail; only
 //     x (the previous kernel's output) is read after the wait.  CTAs are sized so
@@ -64,11 +65,14 @@ struct PipeArgs {
     uint32_t stage_stride;     // bytes between stages
     uint32_t half_stride;      // offset of the second tensor's rows inside a stage (fused form)
     uint32_t stage_base;       // offset of stage 0 in dynamic shared memory
-    uint32_t red_base;         // offset of the cross-warp reduction buffers
+    uint32_t red_base;         // offset of the per-row partial-sum buffers
+    uint32_t red_rows;         // rows one partial-sum buffer holds before it is flushed
     uint32_t xs_base;          // offset of the quantized copy of x (byte planes, scales, sums)
     uint32_t total_rows;
     int layout;
     int *status;
+    const uint8_t *pf_ptr;     // weights of the launch that follows (16-byte aligned), or NULL
+    uint64_t pf_bytes;         // how many of its leading bytes to pull into L2
 };
 
 // ---- PTX wrappers ---------------------------------------------------------
@@ -102,6 +106,10 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
 {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void bulk_prefetch_l2(const void *src, uint32_t bytes)
+{
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ uint64_t global_ns()
 {
@@ -142,6 +150,30 @@ __device__ __forceinline__ int dp4a_uu(uint32_t a, uint32_t b, int c)
     uint32_t d; asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"((uint32_t)c)); return (int)d;
 }
 
+// Shared-memory loads by 32-bit shared-space address with a compile-time byte offset: one instruction each,
+// no generic-address arithmetic.  volatile keeps them behind the barrier wait that publishes the stage.
+template <int OFF>
+__device__ __forceinline__ uint32_t lds32(uint32_t a)
+{
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(a), "n"(OFF));
+    return v;
+}
+template <int OFF>
+__device__ __forceinline__ uint32_t lds16(uint32_t a)
+{
+    uint32_t v;
+    asm volatile("{\n .reg .u16 t;\n ld.shared.u16 t, [%1+%2];\n cvt.u32.u16 %0, t;\n}\n" : "=r"(v) : "r"(a), "n"(OFF));
+    return v;
+}
+template <int OFF>
+__device__ __forceinline__ uint4 lds128(uint32_t a)
+{
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a), "n"(OFF));
+    return v;
+}
+
 // Quantized x in shared memory: NP byte planes of in_dim bytes (plane p holds byte p of every X_i), then one
 // fp32 scale per group of G elements, then (Q4_K/Q5_K) one fp32 sum of x per 32 elements.
 struct XqView {
@@ -150,6 +182,10 @@ struct XqView {
     const float *sums;       // [in_dim / 32] (K-quants with a min term)
     uint32_t in_dim;
 };
+
+// 16-byte pieces of a plane are permuted inside each aligned group of eight (128 bytes) so that threads
+// whose slices start 64 or 256 bytes apart read different banks: piece c lives at plane_swz(c).
+__device__ __forceinline__ uint32_t plane_swz(uint32_t c) { return (c & ~7u) | ((c ^ (c >> 3) ^ (c >> 4)) & 7u); }
 
 // ---- x as per-group fixed point -------------------------------------------
 // pc[p][k]: byte p of X_{4k..4k+3}, packed little-endian; piece NP-1 is the signed top byte.
@@ -165,10 +201,10 @@ __device__ __forceinline__ void load_group(const XqView &xv, uint32_t e0, uint32
 {
 #pragma unroll
     for (int p = 0; p < NP; ++p) {
-        const uint4 *src = reinterpret_cast<const uint4 *>(xv.planes + (size_t)p * xv.in_dim + e0);
+        const uint4 *plane = reinterpret_cast<const uint4 *>(xv.planes + (size_t)p * xv.in_dim);
 #pragma unroll
         for (int k = 0; k < N / 16; ++k) {
-            const uint4 w = src[k];
+            const uint4 w = plane[plane_swz(e0 / 16 + k)];
             g.pc[p][4 * k] = w.x; g.pc[p][4 * k + 1] = w.y; g.pc[p][4 * k + 2] = w.z; g.pc[p][4 * k + 3] = w.w;
         }
     }
@@ -248,7 +284,7 @@ __device__ __forceinline__ void quantize_x_to_smem(const float *__restrict__ x, 
                     const uint32_t sel = (uint32_t)p | ((uint32_t)(4 + p) << 4);
                     const uint32_t lo = __byte_perm((uint32_t)X[0], (uint32_t)X[1], sel);
                     const uint32_t hi = __byte_perm((uint32_t)X[2], (uint32_t)X[3], sel);
-                    planes[(size_t)p * n4 + f] = __byte_perm(lo, hi, 0x5410);
+                    planes[(size_t)p * n4 + 4 * plane_swz(f >> 2) + (f & 3u)] = __byte_perm(lo, hi, 0x5410);
                 }
                 if ((lane & (G / 4 - 1)) == 0) scales[f / (G / 4)] = amax / QMAX;
                 if constexpr (SUMS)
@@ -258,24 +294,18 @@ __device__ __forceinline__ void quantize_x_to_smem(const float *__restrict__ x, 
     }
 }
 
-// 16 bytes from a shared address that is only 2-byte aligned (reads 20 aligned bytes).
-__device__ __forceinline__ void lds16_a2(const uint8_t *p, uint32_t (&o)[4])
+// 16 (8) bytes from a shared address that is only 2-byte aligned: aligned words around it, fixed up with prmt.
+__device__ __forceinline__ void lds16_a2(uint32_t a, uint32_t (&o)[4])
 {
-    uintptr_t a = reinterpret_cast<uintptr_t>(p);
-    const uint32_t *q = reinterpret_cast<const uint32_t *>(a & ~(uintptr_t)3);
-    uint32_t sel = (a & 2) ? 0x5432u : 0x3210u;
-    uint32_t v0 = q[0], v1 = q[1], v2 = q[2], v3 = q[3], v4 = q[4];
+    const uint32_t q = a & ~3u, sel = (a & 2u) ? 0x5432u : 0x3210u;
+    const uint32_t v0 = lds32<0>(q), v1 = lds32<4>(q), v2 = lds32<8>(q), v3 = lds32<12>(q), v4 = lds32<16>(q);
     o[0] = __byte_perm(v0, v1, sel); o[1] = __byte_perm(v1, v2, sel);
     o[2] = __byte_perm(v2, v3, sel); o[3] = __byte_perm(v3, v4, sel);
 }
-
-// 8 bytes from a shared address that is only 2-byte aligned (reads 12 aligned bytes).
-__device__ __forceinline__ void lds8_a2(const uint8_t *p, uint32_t (&o)[2])
+__device__ __forceinline__ void lds8_a2(uint32_t a, uint32_t (&o)[2])
 {
-    uintptr_t a = reinterpret_cast<uintptr_t>(p);
-    const uint32_t *q = reinterpret_cast<const uint32_t *>(a & ~(uintptr_t)3);
-    uint32_t sel = (a & 2) ? 0x5432u : 0x3210u;
-    uint32_t v0 = q[0], v1 = q[1], v2 = q[2];
+    const uint32_t q = a & ~3u, sel = (a & 2u) ? 0x5432u : 0x3210u;
+    const uint32_t v0 = lds32<0>(q), v1 = lds32<4>(q), v2 = lds32<8>(q);
     o[0] = __byte_perm(v0, v1, sel); o[1] = __byte_perm(v1, v2, sel);
 }
 
@@ -331,12 +361,15 @@ struct Slot<FMT_Q8_0, NP> {
             x0[p][8] = g0.pc[p][7] >> 16;
         }
     }
-    __device__ __forceinline__ float dot(const uint8_t *row, uint32_t unit, int, int) const
+    static constexpr uint32_t UNIT_BYTES = 68;
+    // `u` = shared-space address of this thread's unit inside the row
+    __device__ __forceinline__ float dot(uint32_t u, int, int) const
     {
-        const uint32_t *w = reinterpret_cast<const uint32_t *>(row + (size_t)unit * 68);
         uint32_t v[17];
-#pragma unroll
-        for (int i = 0; i < 17; ++i) v[i] = w[i];
+        v[0] = lds32<0>(u);   v[1] = lds32<4>(u);   v[2] = lds32<8>(u);   v[3] = lds32<12>(u);  v[4] = lds32<16>(u);
+        v[5] = lds32<20>(u);  v[6] = lds32<24>(u);  v[7] = lds32<28>(u);  v[8] = lds32<32>(u);  v[9] = lds32<36>(u);
+        v[10] = lds32<40>(u); v[11] = lds32<44>(u); v[12] = lds32<48>(u); v[13] = lds32<52>(u); v[14] = lds32<56>(u);
+        v[15] = lds32<60>(u); v[16] = lds32<64>(u);
         int I0[NP], I1[NP];
 #pragma unroll
         for (int p = 0; p < NP; ++p) { I0[p] = 0; I1[p] = 0; }
@@ -370,17 +403,18 @@ struct SlotK45 {
         sumA = xv.sums[e0 / 32];
         sumB = xv.sums[e0 / 32 + 1];
     }
-    __device__ __forceinline__ float dot(const uint8_t *row, uint32_t unit, int g, int layout) const
+    static constexpr uint32_t UNIT_BYTES = FMT == FMT_Q4_K ? 144 : 176;
+    // `sb` = shared-space address of this thread's superblock inside the row
+    __device__ __forceinline__ float dot(uint32_t sb, int g, int layout) const
     {
-        constexpr int BB = FMT == FMT_Q4_K ? 144 : 176;
-        const uint8_t *sb = row + (size_t)unit * BB;
-        uint4 h = *reinterpret_cast<const uint4 *>(sb);
-        const uint4 *qp = reinterpret_cast<const uint4 *>(sb + (FMT == FMT_Q4_K ? 16 : 48) + 32 * g);
-        uint4 q0 = qp[0], q1 = qp[1];
+        constexpr int QOFF = FMT == FMT_Q4_K ? 16 : 48;
+        const uint4 h = lds128<0>(sb);
+        const uint32_t qa = sb + 32u * (uint32_t)g;
+        const uint4 q0 = lds128<QOFF>(qa), q1 = lds128<QOFF + 16>(qa);
         uint32_t ql[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
         uint32_t qh[8];
         if constexpr (FMT == FMT_Q5_K) {
-            uint4 h0 = *reinterpret_cast<const uint4 *>(sb + 16), h1 = *reinterpret_cast<const uint4 *>(sb + 32);
+            const uint4 h0 = lds128<16>(sb), h1 = lds128<32>(sb);
             qh[0] = h0.x; qh[1] = h0.y; qh[2] = h0.z; qh[3] = h0.w;
             qh[4] = h1.x; qh[5] = h1.y; qh[6] = h1.z; qh[7] = h1.w;
         }
@@ -435,10 +469,10 @@ struct Slot<FMT_Q6_K, NP> {
             }
         }
     }
-    __device__ __forceinline__ float dot(const uint8_t *row, uint32_t unit, int part, int) const
+    static constexpr uint32_t UNIT_BYTES = 210;
+    __device__ __forceinline__ float dot(uint32_t sb, int part, int) const
     {
         int half = part >> 1, lh = part & 1;
-        const uint8_t *sb = row + (size_t)unit * 210;
         uint32_t qa[4], qb[4], qh[4], scw[2];
         lds16_a2(sb + 64 * half + 16 * lh, qa);
         lds16_a2(sb + 64 * half + 32 + 16 * lh, qb);
@@ -457,7 +491,7 @@ struct Slot<FMT_Q6_K, NP> {
             dot_u<NP, 16>(((qa[k] >> 4) & 0x0F0F0F0Fu) | (h & 0x30303030u), g[2], k, I[2]);
             dot_u<NP, 16>(((qb[k] >> 4) & 0x0F0F0F0Fu) | ((h >> 2) & 0x30303030u), g[3], k, I[3]);
         }
-        float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(sb + 208)));
+        float d = __half2float(__ushort_as_half((unsigned short)lds16<208>(sb)));
         float acc = 0.0f;
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
@@ -562,6 +596,16 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
                 issue_tile<SWIGLU>(a, t, stages + (size_t)s * a.stage_stride, smem_u32(full + s));
                 ++i;
             }
+            // All of this CTA's rows are requested.  Pull the head of the next launch's weights into L2 so that HBM
+            // keeps streaming while this grid drains and the next one starts.
+            if (a.pf_ptr && !s_abort) {
+                const uint64_t per = (a.pf_bytes / gridDim.x) & ~(uint64_t)15;
+                const uint8_t *p = a.pf_ptr + (uint64_t)blockIdx.x * per;
+                for (uint64_t off = 0; off < per; off += 32768) {
+                    const uint64_t n = per - off < 32768 ? per - off : 32768;
+                    bulk_prefetch_l2(p + off, (uint32_t)n);
+                }
+            }
             if (s_abort) {   // give copies still in flight a bounded time to land before this warp leaves
                 for (uint32_t s = 0; s < a.nstages && s < i; ++s) {
                     const uint32_t last = ((i - 1 - s) / a.nstages) * a.nstages + s;   // newest tile issued into stage s
@@ -593,53 +637,68 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
         if (active) slot.load(xv, unit, part);
     }
 
+    // Per-row partial sums (one per warp of the row's group) collect in shared memory and are added up, a whole
+    // batch of rows at a time, by all consumer threads: one consumer-wide barrier per batch, coalesced stores of y.
+    // Two buffers alternate, so the barrier that opens a flush also protects the buffer written two flushes ago.
+    const uint32_t CAP = a.red_rows, PLANE = CAP * GW;                 // floats per buffer (per tensor)
+    float *pbuf = red;
+    uint32_t which = 0, buf_n = 0, buf_row0 = 0;
+    int buf_seg = 0;
+    auto flush = [&]() {
+        named_bar_sync(PIPE_BAR_CONSUMERS, (int)C);
+        const float *src = pbuf + (size_t)which * PLANE * (SWIGLU ? 2 : 1);
+        float *y = a.seg[buf_seg].y + buf_row0;
+        for (uint32_t r = tid; r < buf_n; r += C) {
+            float g = 0.0f, u = 0.0f;
+            for (uint32_t w = 0; w < GW; ++w) {
+                g += src[r * GW + w];
+                if constexpr (SWIGLU) u += src[PLANE + r * GW + w];
+            }
+            y[r] = SWIGLU ? silu_mul(g, u) : g;
+        }
+        which ^= 1u;
+        buf_n = 0;
+    };
+
+    const uint32_t stages_s = smem_u32(stages);
+    const uint32_t unit_off = unit * SlotT::UNIT_BYTES;
     uint32_t cur = v0, i = 0;
     PipeTile t;
-    const uint32_t red_tile = a.rows_par * PIPE_MAX_ITERS * GW * (SWIGLU ? 2 : 1);   // floats per buffer
     while (next_tile(a, cur, v1, t)) {
+        if (buf_n && (t.seg != buf_seg || buf_n + t.n > CAP)) flush();
+        if (buf_n == 0) { buf_seg = t.seg; buf_row0 = t.row0; }
         const uint32_t s = i % a.nstages, parity = (i / a.nstages) & 1u;
         if (!s_abort && !mbar_wait_bounded(smem_u32(full + s), parity)) {
             s_abort = 1;
             atomicExch(a.status, 1);
         }
-        const uint8_t *stage = stages + (size_t)s * a.stage_stride;
         const uint32_t delta = (uint32_t)((reinterpret_cast<uintptr_t>(a.seg[t.seg].w) + (size_t)t.row0 * a.row_bytes) & 15u);
-        uint32_t delta2 = 0;
+        const uint32_t base = stages_s + s * a.stage_stride + delta + unit_off;
+        uint32_t base2 = 0;
         if constexpr (SWIGLU)
-            delta2 = (uint32_t)((reinterpret_cast<uintptr_t>(a.seg[t.seg].w2) + (size_t)t.row0 * a.row_bytes) & 15u);
-        float *rb = red + (size_t)(i & 1u) * red_tile + (size_t)group * PIPE_MAX_ITERS * GW * (SWIGLU ? 2 : 1);
+            base2 = stages_s + s * a.stage_stride + a.half_stride + unit_off +
+                    (uint32_t)((reinterpret_cast<uintptr_t>(a.seg[t.seg].w2) + (size_t)t.row0 * a.row_bytes) & 15u);
+        float *dst = pbuf + (size_t)which * PLANE * (SWIGLU ? 2 : 1) + (size_t)buf_n * GW + wig;
 #pragma unroll 1
-        for (uint32_t it = 0; it < a.iters; ++it) {
-            const uint32_t r = it * a.rows_par + group;
+        for (uint32_t r = group; r < t.n; r += a.rows_par) {
             float v = 0.0f, v2 = 0.0f;
-            if (r < t.n && active) {
-                v = slot.dot(stage + delta + (size_t)r * a.row_bytes, unit, part, a.layout);
-                if constexpr (SWIGLU)
-                    v2 = slot.dot(stage + a.half_stride + delta2 + (size_t)r * a.row_bytes, unit, part, a.layout);
+            if (active) {
+                v = slot.dot(base + r * a.row_bytes, part, a.layout);
+                if constexpr (SWIGLU) v2 = slot.dot(base2 + r * a.row_bytes, part, a.layout);
             }
             v = warp_sum(v);
             if constexpr (SWIGLU) v2 = warp_sum(v2);
             if (lane == 0) {
-                rb[it * GW + wig] = v;
-                if constexpr (SWIGLU) rb[PIPE_MAX_ITERS * GW + it * GW + wig] = v2;
+                dst[r * GW] = v;
+                if constexpr (SWIGLU) dst[PLANE + r * GW] = v2;
             }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(empty + s));   // this warp is done reading the stage
-        named_bar_sync(1 + (int)group, (int)GT);
-        if (wig == 0 && lane < a.iters) {
-            const uint32_t r = lane * a.rows_par + group;
-            if (r < t.n) {
-                float g = 0.0f, u = 0.0f;
-                for (uint32_t w = 0; w < GW; ++w) {
-                    g += rb[lane * GW + w];
-                    if constexpr (SWIGLU) u += rb[PIPE_MAX_ITERS * GW + lane * GW + w];
-                }
-                a.seg[t.seg].y[t.row0 + r] = SWIGLU ? silu_mul(g, u) : g;
-            }
-        }
+        buf_n += t.n;
         ++i;
     }
+    if (buf_n) flush();
 }
 
 }  // namespace orome

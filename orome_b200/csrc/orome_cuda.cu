@@ -32,6 +32,9 @@ struct orome_cuda_ctx {
     int ctas_per_sm = 1;     // CTAs an SM is sized to hold (1 or 2); measured best with one large CTA
     int grid_per_sm = 1;     // CTAs per SM a launch creates; 1 with ctas_per_sm 2 leaves room for the next kernel's CTA
     int pdl = 1;
+    int prefetch_mb = 24;    // at most this many MiB of the next tensor are pulled into L2 by the current launch
+    const uint8_t *hint_ptr = nullptr;   // set by orome_cuda_hint_next, consumed by the next pipelined launch
+    uint64_t hint_bytes = 0;
     // staging for the host-buffer entry point
     float *stage_x_host = nullptr, *stage_y_host = nullptr, *stage_x_dev = nullptr, *stage_y_dev = nullptr;
     size_t stage_x_cap = 0, stage_y_cap = 0;
@@ -172,6 +175,9 @@ extern "C" int orome_cuda_set_option(orome_cuda_ctx *c, int key, int value)
     case OROME_OPT_GRID_PER_SM:
         if (value < 1 || value > 2) return fail(OROME_EINVAL, "GRID_PER_SM must be 1 or 2");
         c->grid_per_sm = value; return OROME_OK;
+    case OROME_OPT_PREFETCH_MB:
+        if (value < 0 || value > 96) return fail(OROME_EINVAL, "PREFETCH_MB must be 0..96");
+        c->prefetch_mb = value; return OROME_OK;
     }
     return fail(OROME_EINVAL, "set_option: unknown key %d", key);
 }
@@ -186,6 +192,7 @@ extern "C" int orome_cuda_get_option(orome_cuda_ctx *c, int key, int *value)
     case OROME_OPT_CTAS_PER_SM: *value = c->ctas_per_sm; return OROME_OK;
     case OROME_OPT_PDL: *value = c->pdl; return OROME_OK;
     case OROME_OPT_GRID_PER_SM: *value = c->grid_per_sm; return OROME_OK;
+    case OROME_OPT_PREFETCH_MB: *value = c->prefetch_mb; return OROME_OK;
     }
     return fail(OROME_EINVAL, "get_option: unknown key %d", key);
 }
@@ -304,7 +311,10 @@ static int plan_pipe(orome_cuda_ctx *c, int fmt, uint32_t in_dim, uint32_t total
     size_t budget = sm_total / p.minb - 1024 - 256;
     budget = std::min(budget, (size_t)c->smem_optin - 256);
     a.red_base = 2 * 8 * PIPE_MAX_STAGES;
-    const size_t red_bytes = (size_t)2 * a.rows_par * PIPE_MAX_ITERS * gw * (swiglu ? 2 : 1) * sizeof(float);
+    // partial-sum buffers: a whole CTA share when it is small, else batches of 256 rows (at most 16 KiB per buffer)
+    a.red_rows = std::min<uint32_t>(std::max<uint32_t>(share, a.rows_par * PIPE_MAX_ITERS), 256u);
+    a.red_rows = std::max<uint32_t>(std::min<uint32_t>(a.red_rows, 4096u / gw), a.rows_par * PIPE_MAX_ITERS);
+    const size_t red_bytes = (size_t)2 * a.red_rows * gw * (swiglu ? 2 : 1) * sizeof(float);
     a.xs_base = (uint32_t)((a.red_base + red_bytes + 127) / 128 * 128);
     // quantized x: one byte plane per 8 bits of x, a scale per group (16 for Q6_K, else 32), a sum per 32 elements
     const size_t np = c->x_bits == 24 ? 3 : 2;
@@ -325,6 +335,10 @@ static int plan_pipe(orome_cuda_ctx *c, int fmt, uint32_t in_dim, uint32_t total
     }
     p.smem = a.stage_base + (size_t)a.stage_stride * a.nstages;
     a.status = c->status_dev;
+    a.pf_ptr = c->hint_ptr;
+    a.pf_bytes = c->hint_bytes;
+    c->hint_ptr = nullptr;
+    c->hint_bytes = 0;
     return OROME_OK;
 }
 
@@ -378,6 +392,23 @@ static int launch_pipe(orome_cuda_ctx *c, int fmt, const PipePlan &p, bool swigl
     case FMT_Q8_0: return launch_pipe_fmt<FMT_Q8_0>(c, p, swiglu, st);
     }
     return fail(OROME_ENOTSUP, "no pipelined kernel for format %d", fmt);
+}
+
+extern "C" int orome_cuda_hint_next(orome_cuda_ctx *c, const OromeTensorRef *next)
+{
+    if (!c) return fail(OROME_EINVAL, "hint_next: NULL ctx");
+    c->hint_ptr = nullptr;
+    c->hint_bytes = 0;
+    if (!next || !next->buffer || c->prefetch_mb <= 0) return OROME_OK;
+    const int fmt = (int)next->format;
+    if (fmt < 0 || fmt > FMT_F32) return OROME_OK;
+    if (fmt <= FMT_Q8_0 && next->in_dim % block_elems(fmt)) return OROME_OK;
+    const uint8_t *p = static_cast<const uint8_t *>(next->buffer) + next->offset;
+    if (reinterpret_cast<uintptr_t>(p) & 15) return OROME_OK;
+    const uint64_t total = (uint64_t)row_bytes_of(fmt, next->in_dim) * next->out_dim;
+    c->hint_ptr = p;
+    c->hint_bytes = std::min<uint64_t>(total, (uint64_t)c->prefetch_mb << 20) & ~(uint64_t)15;
+    return OROME_OK;
 }
 
 // ---------------------------------------------------------------------------

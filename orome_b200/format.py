@@ -15,7 +15,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "liborome_cuda.so")
 
 VARIANT_DEFAULT, VARIANT_LLAMA = 0, 1
-OPT_X_BITS, OPT_FORCE_GENERIC, OPT_STAGE_KB, OPT_CTAS_PER_SM, OPT_PDL, OPT_GRID_PER_SM = 1, 2, 3, 4, 5, 6
+OPT_X_BITS, OPT_FORCE_GENERIC, OPT_STAGE_KB, OPT_CTAS_PER_SM, OPT_PDL, OPT_GRID_PER_SM, OPT_PREFETCH_MB = 1, 2, 3, 4, 5, 6, 7
 
 OK, EINVAL, ENOTSUP, ENOMEM, ECUDA, ETIMEOUT = 0, -22, -95, -12, -5, -110
 ROUTE_STATIC_MAX_LOGITS = 64 * 256
@@ -46,7 +46,7 @@ EXPORTS = [
     "orome_cuda_free", "orome_format_from_ggml_type", "orome_format_row_bytes", "orome_format_dispatch_matvec",
     "orome_cuda_matvec", "orome_cuda_matvec_group", "orome_cuda_gate_up_swiglu", "orome_cuda_dequant_rows",
     "orome_cuda_moe_route", "orome_cuda_moe_route_static", "orome_cuda_moe_ffn", "orome_cuda_matvec_host", "orome_cuda_set_option",
-    "orome_cuda_get_option", "orome_cuda_launch_count",
+    "orome_cuda_get_option", "orome_cuda_launch_count", "orome_cuda_hint_next",
 ]
 
 _lib = None
@@ -84,6 +84,7 @@ def lib():
     L.orome_cuda_matvec_host.argtypes = [vp, TR, vp, vp, i32]
     L.orome_cuda_set_option.argtypes = [vp, i32, i32]
     L.orome_cuda_get_option.argtypes = [vp, i32, C.POINTER(i32)]
+    L.orome_cuda_hint_next.argtypes = [vp, TR]
     L.orome_cuda_launch_count.argtypes = [vp]
     L.orome_cuda_launch_count.restype = C.c_uint64
     _lib = L
@@ -151,6 +152,9 @@ class Context:
     @property
     def launch_count(self) -> int:
         return int(lib().orome_cuda_launch_count(self._h))
+
+    def hint_next(self, ref: TensorRef | None):
+        _chk(lib().orome_cuda_hint_next(self._h, C.byref(ref) if ref is not None else None))
 
     # -- the path ---------------------------------------------------------------
     def format_dispatch_matvec(self, ref: TensorRef, in_buf: int, in_off: int, out_buf: int, out_off: int, stream: int = 0):
