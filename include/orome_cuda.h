@@ -249,6 +249,13 @@ int  orome_cuda_matvec_host(orome_cuda_ctx *ctx, const OromeTensorRef *ref,
 int  orome_cuda_set_option(orome_cuda_ctx *ctx, int key, int value);
 int  orome_cuda_get_option(orome_cuda_ctx *ctx, int key, int *value);
 
+/* Diagnostics.  orome_cuda_trace_begin makes the next `launches` pipelined launches record eight
+ * %globaltimer stamps per CTA (entry, copies issued, dependency wait over, x quantized, x slice
+ * loaded, first tile landed, last tile done, exit); orome_cuda_trace_read synchronises and copies
+ * launches * 148 * 8 values out.  Tracing allocates; it is off unless begun. */
+int  orome_cuda_trace_begin(orome_cuda_ctx *ctx, int launches);
+int  orome_cuda_trace_read(orome_cuda_ctx *ctx, unsigned long long *out, size_t n_values);
+
 /* Number of kernel launches issued through this context since creation. */
 uint64_t orome_cuda_launch_count(orome_cuda_ctx *ctx);
 

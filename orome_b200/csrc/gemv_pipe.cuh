@@ -73,6 +73,7 @@ struct PipeArgs {
     int *status;
     const uint8_t *pf_ptr;     // weights of the launch that follows (16-byte aligned), or NULL
     uint64_t pf_bytes;         // how many of its leading bytes to pull into L2
+    unsigned long long *trace; // diagnostics: 8 %globaltimer stamps per CTA, or NULL
 };
 
 // ---- PTX wrappers ---------------------------------------------------------
@@ -116,6 +117,10 @@ __device__ __forceinline__ uint64_t global_ns()
     uint64_t t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
+}
+__device__ __forceinline__ void stamp(unsigned long long *trace, int k)
+{
+    if (trace) trace[(size_t)blockIdx.x * 8 + k] = global_ns();
 }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
@@ -578,6 +583,7 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
     }
     __syncthreads();
     pdl_launch_dependents();
+    if (tid == 0) stamp(a.trace, 0);
 
     if (producer) {
         // The weight copies do not depend on the previous kernel: no griddepcontrol.wait on this path.
@@ -596,6 +602,7 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
                 issue_tile<SWIGLU>(a, t, stages + (size_t)s * a.stage_stride, smem_u32(full + s));
                 ++i;
             }
+            stamp(a.trace, 1);
             // All of this CTA's rows are requested.  Pull the head of the next launch's weights into L2 so that HBM
             // keeps streaming while this grid drains and the next one starts.
             if (a.pf_ptr && !s_abort) {
@@ -623,18 +630,21 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
     const uint32_t unit = j % U;
 
     pdl_wait();   // x is the previous kernel's output
+    if (tid == 0) stamp(a.trace, 2);
 
     SlotT slot;
     {
         uint8_t *xq = smem + a.xs_base;
         quantize_x_to_smem<NP, SlotT::GROUP, SlotT::SUMS>(a.x, a.in_dim, xq, tid, C);
         named_bar_sync(PIPE_BAR_CONSUMERS, (int)C);
+        if (tid == 0) stamp(a.trace, 3);
         XqView xv;
         xv.planes = xq;
         xv.scales = reinterpret_cast<const float *>(xq + (size_t)NP * a.in_dim);
         xv.sums = xv.scales + a.in_dim / SlotT::GROUP;
         xv.in_dim = a.in_dim;
         if (active) slot.load(xv, unit, part);
+        if (tid == 0) stamp(a.trace, 4);
     }
 
     // Per-row partial sums (one per warp of the row's group) collect in shared memory and are added up, a whole
@@ -672,6 +682,7 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
             s_abort = 1;
             atomicExch(a.status, 1);
         }
+        if (i == 0 && tid == 0) stamp(a.trace, 5);
         const uint32_t delta = (uint32_t)((reinterpret_cast<uintptr_t>(a.seg[t.seg].w) + (size_t)t.row0 * a.row_bytes) & 15u);
         const uint32_t base = stages_s + s * a.stage_stride + delta + unit_off;
         uint32_t base2 = 0;
@@ -698,7 +709,9 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
         buf_n += t.n;
         ++i;
     }
+    if (tid == 0) stamp(a.trace, 6);
     if (buf_n) flush();
+    if (tid == 0) stamp(a.trace, 7);
 }
 
 }  // namespace orome

@@ -35,6 +35,8 @@ struct orome_cuda_ctx {
     int prefetch_mb = 24;    // at most this many MiB of the next tensor are pulled into L2 by the current launch
     const uint8_t *hint_ptr = nullptr;   // set by orome_cuda_hint_next, consumed by the next pipelined launch
     uint64_t hint_bytes = 0;
+    unsigned long long *trace_dev = nullptr;   // diagnostics buffer [trace_cap][sm_count][8]
+    int trace_cap = 0, trace_next = 0;
     // staging for the host-buffer entry point
     float *stage_x_host = nullptr, *stage_y_host = nullptr, *stage_x_dev = nullptr, *stage_y_dev = nullptr;
     size_t stage_x_cap = 0, stage_y_cap = 0;
@@ -98,6 +100,7 @@ extern "C" void orome_cuda_ctx_destroy(orome_cuda_ctx *c)
     cudaFree(c->stage_y_dev);
     cudaFree(c->logits_dev);
     cudaFree(c->gu_dev);
+    cudaFree(c->trace_dev);
     cudaFreeHost(c->stage_x_host);
     cudaFreeHost(c->stage_y_host);
     if (c->own_stream) cudaStreamDestroy(c->own_stream);
@@ -195,6 +198,31 @@ extern "C" int orome_cuda_get_option(orome_cuda_ctx *c, int key, int *value)
     case OROME_OPT_PREFETCH_MB: *value = c->prefetch_mb; return OROME_OK;
     }
     return fail(OROME_EINVAL, "get_option: unknown key %d", key);
+}
+
+extern "C" int orome_cuda_trace_begin(orome_cuda_ctx *c, int launches)
+{
+    if (!c || launches < 0) return fail(OROME_EINVAL, "trace_begin: bad argument");
+    CU(cudaSetDevice(c->device));
+    if (c->trace_dev) cudaFree(c->trace_dev);
+    c->trace_dev = nullptr;
+    c->trace_cap = c->trace_next = 0;
+    if (launches == 0) return OROME_OK;
+    size_t bytes = (size_t)launches * c->sm_count * 8 * sizeof(unsigned long long);
+    CU(cudaMalloc(&c->trace_dev, bytes));
+    CU(cudaMemset(c->trace_dev, 0, bytes));
+    c->trace_cap = launches;
+    return OROME_OK;
+}
+
+extern "C" int orome_cuda_trace_read(orome_cuda_ctx *c, unsigned long long *out, size_t n_values)
+{
+    if (!c || !out || !c->trace_dev) return fail(OROME_EINVAL, "trace_read: no trace");
+    CU(cudaSetDevice(c->device));
+    CU(cudaDeviceSynchronize());
+    size_t have = (size_t)c->trace_cap * c->sm_count * 8;
+    CU(cudaMemcpy(out, c->trace_dev, std::min(have, n_values) * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+    return OROME_OK;
 }
 
 extern "C" uint64_t orome_cuda_launch_count(orome_cuda_ctx *c) { return c ? c->launches : 0; }
@@ -335,6 +363,8 @@ static int plan_pipe(orome_cuda_ctx *c, int fmt, uint32_t in_dim, uint32_t total
     }
     p.smem = a.stage_base + (size_t)a.stage_stride * a.nstages;
     a.status = c->status_dev;
+    a.trace = nullptr;
+    if (c->trace_dev && c->trace_next < c->trace_cap) a.trace = c->trace_dev + (size_t)(c->trace_next++) * c->sm_count * 8;
     a.pf_ptr = c->hint_ptr;
     a.pf_bytes = c->hint_bytes;
     c->hint_ptr = nullptr;

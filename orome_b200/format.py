@@ -46,7 +46,7 @@ EXPORTS = [
     "orome_cuda_free", "orome_format_from_ggml_type", "orome_format_row_bytes", "orome_format_dispatch_matvec",
     "orome_cuda_matvec", "orome_cuda_matvec_group", "orome_cuda_gate_up_swiglu", "orome_cuda_dequant_rows",
     "orome_cuda_moe_route", "orome_cuda_moe_route_static", "orome_cuda_moe_ffn", "orome_cuda_matvec_host", "orome_cuda_set_option",
-    "orome_cuda_get_option", "orome_cuda_launch_count", "orome_cuda_hint_next",
+    "orome_cuda_get_option", "orome_cuda_launch_count", "orome_cuda_hint_next", "orome_cuda_trace_begin", "orome_cuda_trace_read",
 ]
 
 _lib = None
@@ -85,6 +85,8 @@ def lib():
     L.orome_cuda_set_option.argtypes = [vp, i32, i32]
     L.orome_cuda_get_option.argtypes = [vp, i32, C.POINTER(i32)]
     L.orome_cuda_hint_next.argtypes = [vp, TR]
+    L.orome_cuda_trace_begin.argtypes = [vp, i32]
+    L.orome_cuda_trace_read.argtypes = [vp, vp, sz]
     L.orome_cuda_launch_count.argtypes = [vp]
     L.orome_cuda_launch_count.restype = C.c_uint64
     _lib = L
@@ -152,6 +154,15 @@ class Context:
     @property
     def launch_count(self) -> int:
         return int(lib().orome_cuda_launch_count(self._h))
+
+    def trace_begin(self, launches: int):
+        _chk(lib().orome_cuda_trace_begin(self._h, launches))
+
+    def trace_read(self, launches: int, sm_count: int = 148):
+        import numpy as np
+        out = np.zeros((launches, sm_count, 8), np.uint64)
+        _chk(lib().orome_cuda_trace_read(self._h, out.ctypes.data_as(C.c_void_p), out.size))
+        return out
 
     def hint_next(self, ref: TensorRef | None):
         _chk(lib().orome_cuda_hint_next(self._h, C.byref(ref) if ref is not None else None))
