@@ -174,8 +174,12 @@ def run_reference_arm(args):
 class Stepper:
     """Issues one token step of a DecodeSet through the C ABI (optionally replayed from a CUDA graph)."""
 
-    def __init__(self, torch, F, ctx, ds, dist=None):
+    # arrival counters of the fused all-gather, one per gathered vector
+    FLAG_QKV, FLAG_O, FLAG_ACT, FLAG_DN, FLAG_LOGITS = range(5)
+
+    def __init__(self, torch, F, ctx, ds, dist=None, fused=False):
         self.torch, self.F, self.ctx, self.ds, self.dist = torch, F, ctx, ds, dist
+        self.fused = fused and ds.world > 1
         dev = ds.arena.device
         H, A, KV, V = ds.hidden, ds.ffn, ds.kv, ds.vocab
         g = torch.Generator(device=dev)
@@ -185,8 +189,14 @@ class Stepper:
         from orome_b200.rowsplit import padded_rows
         w = ds.world
         # gather buffers (padded to equal slices per rank when sharded); local slices are written in place
-        self.q, self.k, self.v = (torch.zeros(padded_rows(n, w), device=dev) for n in (H, KV, KV))
-        self.o, self.act, self.dn, self.logits = (torch.zeros(padded_rows(n, w), device=dev) for n in (H, A, H, V))
+        sizes = [padded_rows(n, w) for n in (H, KV, KV, H, A, H, V)]
+        if self.fused:
+            from orome_b200.rowsplit import PeerArena
+            self.arena = PeerArena(ctx, dist, ds.rank, w, sum((n * 4 + 255) // 256 * 256 for n in sizes), 5)
+            bufs = [self.arena.floats(n) for n in sizes]
+        else:
+            bufs = [torch.zeros(n, device=dev) for n in sizes]
+        self.q, self.k, self.v, self.o, self.act, self.dn, self.logits = bufs
         self.refs = [[ds.ref(t) for t in lt] for lt in ds.tensors]
         self.lm_ref = ds.ref(ds.lm_head)
         self.graph = None
@@ -200,6 +210,8 @@ class Stepper:
 
     def _gather(self, full, full_out):
         """All-gather of the output vector when the rows are split over ranks."""
+        if self.fused:
+            return      # the producing kernel already stored this rank's rows into every peer's arena
         from orome_b200.rowsplit import all_gather_rows
         all_gather_rows(self.dist, full, full_out, self.ds.rank, self.ds.world)
 
@@ -209,12 +221,14 @@ class Stepper:
         xh, xa = self.x_h.data_ptr(), self.x_a.data_ptr()
         c0 = ctx.launch_count
         hint = ctx.hint_next if self.hints else (lambda r: None)
+        gn = ctx.gather_next if self.fused else (lambda w, p: None)     # (counter to wait on, counter to publish)
         nl = len(self.refs)
         for li, refs in enumerate(self.refs):
             rq, rk, rv, ro, rg, ru, rd = refs
             nxt_q = self.refs[li + 1][0] if li + 1 < nl else self.lm_ref      # first tensor the step reads after this layer
             hint(ro if ro.out_dim else None)
             if rq.out_dim and rk.out_dim and rv.out_dim:
+                gn(self.FLAG_DN if li else -1, self.FLAG_QKV)
                 ctx.matvec_group([rq, rk, rv], xh, [self._slice(self.q, H).data_ptr(), self._slice(self.k, KV).data_ptr(),
                                                     self._slice(self.v, KV).data_ptr()], stream)
             else:   # some rank holds no rows of a small tensor
@@ -224,20 +238,26 @@ class Stepper:
             self._gather(self.q, H); self._gather(self.k, KV); self._gather(self.v, KV)
             if ro.out_dim:
                 hint(rg)
+                gn(self.FLAG_QKV, self.FLAG_O)
                 ctx.matvec(ro, xh, self._slice(self.o, H).data_ptr(), 1, 0, 0, stream)
             self._gather(self.o, H)
             if rg.out_dim:
                 hint(rd)
+                gn(self.FLAG_O, self.FLAG_ACT)
                 ctx.gate_up_swiglu(rg, ru, xh, self._slice(self.act, A).data_ptr(), 1, 0, 0, stream)
             self._gather(self.act, A)
             if rd.out_dim:
                 hint(nxt_q if nxt_q.out_dim else None)
+                gn(self.FLAG_ACT, self.FLAG_DN)
                 ctx.matvec(rd, xa, self._slice(self.dn, H).data_ptr(), 1, 0, 0, stream)
             self._gather(self.dn, H)
         if self.lm_ref.out_dim:
             hint(self.refs[0][0] if nl and self.refs[0][0].out_dim else None)   # the next token starts at layer 0 again
+            gn(self.FLAG_DN if nl else -1, self.FLAG_LOGITS)
             ctx.matvec(self.lm_ref, xh, self._slice(self.logits, V).data_ptr(), 1, 0, 0, stream)
         self._gather(self.logits, V)
+        if self.fused:
+            ctx.gather_wait(self.FLAG_LOGITS, stream)     # the logits are complete on this rank from here on
         self.launches_per_step = ctx.launch_count - c0
 
     def capture(self):
@@ -286,7 +306,7 @@ def run_ours(args):
         ctx.set_option(F.OPT_PREFETCH_MB, args.prefetch_mb)
 
     ds = decode_set.DecodeSet(args.workload, dev, rank=rank, world=world, layers=args.layers)
-    st = Stepper(torch, F, ctx, ds, dist)
+    st = Stepper(torch, F, ctx, ds, dist, fused=args.gather == "fused")
     use_graph = args.graph
     if use_graph:
         try:
@@ -403,7 +423,9 @@ def run_ours(args):
         "data": "synthetic",
         "config": {"workload": args.workload, "batch": 1, "layers": ds.layers, "weight_bytes": w_bytes,
                    "l2": "inputs larger than L2: every layer has its own weights", "cuda_graph": bool(use_graph),
-                   "parallelism": "single GPU" if world == 1 else f"row-split x{world} + all-gather (NCCL)"},
+                   "parallelism": "single GPU" if world == 1 else
+                   (f"row-split x{world}, y completed by peer stores from the kernel epilogue (NVLink) + arrival counters" if st.fused
+                    else f"row-split x{world} + all-gather (NCCL)")},
         "roofline": roofline,
         "e2e": {"value": e2e_tok_s, "unit": "tok/s", "h2d_bytes_per_step": ds.hidden * 4, "d2h_bytes_per_step": ds.vocab * 4,
                 "wall_tok_s": args.steps / wall},
@@ -429,6 +451,8 @@ def main():
     ap.add_argument("--graph", dest="graph", action="store_true", default=True)
     ap.add_argument("--no-graph", dest="graph", action="store_false")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+                    help="N > 1: complete y by peer stores from the kernel epilogue (fused) or by an NCCL all-gather per product")
     ap.add_argument("--prefetch-mb", type=int, default=-1, help="cap of the next-tensor L2 prefetch in MiB (0 = off, -1 = library default)")
     args = ap.parse_args()
     if args.impl == "reference":

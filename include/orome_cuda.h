@@ -225,6 +225,35 @@ int  orome_cuda_moe_ffn(orome_cuda_ctx *ctx, const OromeExpertLayerRef *layer, u
  * performance hint: results do not depend on it. */
 int  orome_cuda_hint_next(orome_cuda_ctx *ctx, const OromeTensorRef *next);
 
+/* ---- multi-GPU: row-split products, output vector completed on every GPU ---------------
+ *
+ * No counterpart in the reference (single GPU, unified memory).  Output rows of a matvec are
+ * independent, so rank r of `world` GPUs in one box keeps a slice of the rows of every tensor
+ * and the full y must reach every GPU before the next product.  Instead of a collective after
+ * the kernel, the kernel that produces a slice also stores every value into the same offset of
+ * each peer's "gather arena" over NVLink (plain peer stores), and when its grid is done bumps
+ * an arrival counter on each peer; the launch that consumes the vector waits on its own
+ * counter (bounded: after 1 s it records status 3, see orome_cuda_status, and carries on).
+ *
+ * Set-up: every process allocates an arena with orome_cuda_peer_alloc, exchanges the 64-byte
+ * handles by any host channel, opens the others with orome_cuda_peer_open and passes all
+ * `world` pointers (its own included, at index rank) to orome_cuda_gather_setup.  The arena
+ * holds data_bytes of buffers followed by n_flags counters.  Then, before a matvec / group /
+ * gate-up launch, orome_cuda_gather_next(ctx, wait_flag, publish_flag) says which counter the
+ * launch waits on before reading x (-1: none) and which one it bumps on the peers after
+ * mirroring its y rows (-1: y stays local); it applies to the next launch only.  A published
+ * launch must write y inside the local arena.  Each published round of a counter must be
+ * consumed by exactly one later launch (or orome_cuda_gather_wait) on every rank. */
+int  orome_cuda_peer_alloc(orome_cuda_ctx *ctx, size_t bytes, void **dev_ptr, unsigned char handle_out[64]);
+int  orome_cuda_peer_open(orome_cuda_ctx *ctx, const unsigned char handle[64], void **dev_ptr);
+int  orome_cuda_peer_close(orome_cuda_ctx *ctx, void *dev_ptr);
+int  orome_cuda_gather_setup(orome_cuda_ctx *ctx, int rank, int world, void *const *arenas, size_t data_bytes, int n_flags);
+size_t orome_cuda_gather_arena_bytes(size_t data_bytes, int n_flags);
+int  orome_cuda_gather_next(orome_cuda_ctx *ctx, int wait_flag, int publish_flag);
+/* Enqueue a wait for one round of `flag` with nothing else attached (e.g. before copying the
+ * gathered logits to the host). */
+int  orome_cuda_gather_wait(orome_cuda_ctx *ctx, int flag, void *stream);
+
 /* ---- host-buffer convenience (end-to-end form) --------------------------- */
 
 /* Same product as orome_cuda_matvec with HOST x and y: copies x to the device,

@@ -78,6 +78,37 @@ gemv_generic_kernel(const uint8_t *__restrict__ data, size_t row_bytes, uint32_t
     }
 }
 
+// fp32 weights (the MoE router, shaders.metal:1342-1366): one warp per row, lanes take consecutive float4s so every
+// load is coalesced; up to 4 input vectors per pass.  Waits for the previous kernel first (it may produce x).
+__global__ void __launch_bounds__(256)
+gemv_f32_kernel(const float *__restrict__ W, uint32_t out_dim, uint32_t in_dim, const float *__restrict__ x, int batch, int ldx,
+                float *__restrict__ y, int ldy)
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint32_t row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= out_dim) return;
+    const float4 *w4 = reinterpret_cast<const float4 *>(W + (size_t)row * in_dim);
+    const uint32_t n4 = in_dim / 4;
+    for (int b0 = 0; b0 < batch; b0 += 4) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        for (uint32_t c = lane; c < n4; c += 32) {
+            const float4 w = __ldg(w4 + c);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if (b0 + i < batch) {
+                    const float4 xv = *(reinterpret_cast<const float4 *>(x + (size_t)(b0 + i) * ldx) + c);
+                    acc[i] = fmaf(w.x, xv.x, fmaf(w.y, xv.y, fmaf(w.z, xv.z, fmaf(w.w, xv.w, acc[i]))));
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float s = warp_sum(acc[i]);
+            if (lane == 0 && b0 + i < batch) y[(size_t)(b0 + i) * ldy + row] = s;
+        }
+    }
+}
+
 // out = silu(gate) * up, elementwise (shaders.metal:1018-1030); used after two
 // generic matvecs when the fused kernel does not take the shape.
 __global__ void swiglu_kernel(const float *__restrict__ gate, const float *__restrict__ up, float *__restrict__ out,

@@ -34,6 +34,7 @@
 namespace orome {
 
 constexpr int PIPE_MAX_SEG = 8;
+constexpr int PIPE_MAX_PEERS = 7;
 constexpr int PIPE_MAX_STAGES = 16;
 constexpr int PIPE_MAX_CONSUMERS = 480;          // 15 consumer warps + the producer warp = 512 threads
 constexpr int PIPE_MAX_THREADS = PIPE_MAX_CONSUMERS + 32;
@@ -74,6 +75,29 @@ struct PipeArgs {
     const uint8_t *pf_ptr;     // weights of the launch that follows (16-byte aligned), or NULL
     uint64_t pf_bytes;         // how many of its leading bytes to pull into L2
     unsigned long long *trace; // diagnostics: 8 %globaltimer stamps per CTA, or NULL
+    // MoE forms.  seg_expert: segment s reads expert seg_expert[s] of a 3-D expert tensor, i.e. its weights start
+    // at seg[s].w + seg_expert[s] * w_stride (w2_stride for the second tensor); NULL = plain tensors.
+    const uint32_t *seg_expert;
+    uint64_t w_stride, w2_stride;
+    // Combine form (expert down projection): every segment has its own input vector x + s * x_stride, every CTA
+    // owns the same row range of all segments and writes y[r] = sum_s seg_weight[s] * (W_s x_s)[r] to seg[0].y.
+    uint32_t x_stride;         // floats between the segments' input vectors
+    const float *seg_weight;   // [nseg]
+    uint32_t acc_base;         // offset of the fp32 accumulators of the CTA's rows
+    uint32_t xq_vec_bytes;     // bytes of one quantized input vector in shared memory
+    // Multi-GPU (row-split) forms.  Publishing: every y value is also stored at the same offset of each peer's
+    // gather arena (peer address = local address + peer_delta[p]); when the whole grid is done, the last CTA adds 1
+    // to pub_flag[p] on every peer.  Waiting: before x is read, the launch waits until wait_flag has advanced by
+    // wait_need since wait_seen, then the last CTA to get through advances wait_seen.  All counters live in device
+    // memory, so a captured graph can be replayed.
+    int npeers;
+    long long peer_delta[PIPE_MAX_PEERS];
+    unsigned int *pub_flag[PIPE_MAX_PEERS];   // the peers' arrival counters (peer memory)
+    unsigned int *pub_arrived;                // local: CTAs of this launch that finished publishing
+    unsigned int *wait_flag;                  // local: bumped by the peers
+    unsigned int *wait_seen;                  // local: value of wait_flag consumed so far
+    unsigned int *wait_arrived;               // local: CTAs of this launch that got through the wait
+    unsigned int wait_need;                   // world - 1
 };
 
 // ---- PTX wrappers ---------------------------------------------------------
@@ -121,6 +145,28 @@ __device__ __forceinline__ uint64_t global_ns()
 __device__ __forceinline__ void stamp(unsigned long long *trace, int k)
 {
     if (trace) trace[(size_t)blockIdx.x * 8 + k] = global_ns();
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int *p)
+{
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void red_release_sys_add(unsigned int *p, unsigned int v)
+{
+    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Wait until *flag has advanced by `need` since `seen`, at most PIPE_WAIT_NS.  Returns false on expiry.
+__device__ __forceinline__ bool flag_wait_bounded(const unsigned int *flag, unsigned int seen, unsigned int need)
+{
+    if (ld_acquire_sys(flag) - seen >= need) return true;
+    const uint64_t t0 = global_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 32; ++i)
+            if (ld_acquire_sys(flag) - seen >= need) return true;
+        if (global_ns() - t0 > PIPE_WAIT_NS) return false;
+    }
 }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
@@ -200,6 +246,17 @@ struct XGroup {
     float scale;
 };
 
+template <int NP, int G>
+__device__ __forceinline__ XqView make_xq_view(const uint8_t *xq, uint32_t in_dim)
+{
+    XqView xv;
+    xv.planes = xq;
+    xv.scales = reinterpret_cast<const float *>(xq + (size_t)NP * in_dim);
+    xv.sums = xv.scales + in_dim / G;
+    xv.in_dim = in_dim;
+    return xv;
+}
+
 // N/4 words of every plane for N consecutive elements starting at element e0 (multiple of 16)
 template <int NP, int N>
 __device__ __forceinline__ void load_group(const XqView &xv, uint32_t e0, uint32_t scale_idx, XGroup<NP, N> &g)
@@ -245,29 +302,33 @@ __device__ __forceinline__ void dot_s(uint32_t q, const XGroup<NP, N> &g, int k,
 
 // Cooperative pass over x by `nthreads` consumer threads (whole warps): every lane owns 4
 // consecutive floats, a group of G elements is G/4 adjacent lanes.
+// `nvec` vectors of in_dim floats, x_stride floats apart, are quantized in one pass (all loads of a batch are in
+// flight together); vector v goes to xq + v * vec_bytes.  in_dim is a multiple of 32, so groups never straddle vectors.
 template <int NP, int G, bool SUMS>
-__device__ __forceinline__ void quantize_x_to_smem(const float *__restrict__ x, uint32_t in_dim, uint8_t *xq,
-                                                   uint32_t tid, uint32_t nthreads)
+__device__ __forceinline__ void quantize_x_to_smem(const float *__restrict__ x, uint32_t in_dim, uint32_t nvec, uint32_t x_stride,
+                                                   uint8_t *xq0, uint32_t vec_bytes, uint32_t tid, uint32_t nthreads)
 {
     constexpr float QMAX = NP == 3 ? 8388607.0f : 32767.0f;
     constexpr int BATCH = 8;
-    const uint32_t n4 = in_dim / 4, lane = tid & 31u;
-    uint32_t *planes = reinterpret_cast<uint32_t *>(xq);
-    float *scales = reinterpret_cast<float *>(xq + (size_t)NP * in_dim);
-    float *sums = scales + in_dim / G;
-    const float4 *x4 = reinterpret_cast<const float4 *>(x);
-    for (uint32_t base = tid - lane; base < n4; base += nthreads * BATCH) {
+    const uint32_t n4 = in_dim / 4, n4_all = n4 * nvec, lane = tid & 31u;
+    for (uint32_t base = tid - lane; base < n4_all; base += nthreads * BATCH) {
         float4 v[BATCH];
 #pragma unroll
         for (int b = 0; b < BATCH; ++b) {
-            const uint32_t f = base + b * nthreads + lane;
-            v[b] = f < n4 ? __ldg(x4 + f) : make_float4(0.f, 0.f, 0.f, 0.f);
+            const uint32_t fa = base + b * nthreads + lane;
+            const uint32_t vec = nvec == 1 ? 0u : fa / n4, fl = fa - vec * n4;      // no division on the single-vector path
+            v[b] = fa < n4_all ? __ldcg(reinterpret_cast<const float4 *>(x + (size_t)vec * x_stride) + fl) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
 #pragma unroll
         for (int b = 0; b < BATCH; ++b) {
             const uint32_t fb = base + b * nthreads;       // warp-uniform
-            if (fb >= n4) break;
-            const uint32_t f = fb + lane;
+            if (fb >= n4_all) break;
+            const uint32_t fa = fb + lane;
+            const uint32_t vec = nvec == 1 ? 0u : fa / n4, f = fa - vec * n4;
+            uint8_t *xq = xq0 + (size_t)vec * vec_bytes;
+            uint32_t *planes = reinterpret_cast<uint32_t *>(xq);
+            float *scales = reinterpret_cast<float *>(xq + (size_t)NP * in_dim);
+            float *sums = scales + in_dim / G;
             float amax = fmaxf(fmaxf(fabsf(v[b].x), fabsf(v[b].y)), fmaxf(fabsf(v[b].z), fabsf(v[b].w)));
 #pragma unroll
             for (int o = 1; o < G / 4; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
@@ -283,7 +344,7 @@ __device__ __forceinline__ void quantize_x_to_smem(const float *__restrict__ x, 
 #pragma unroll
                 for (int o = 1; o < 8; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
             }
-            if (f < n4) {
+            if (fa < n4_all) {
 #pragma unroll
                 for (int p = 0; p < NP; ++p) {
                     const uint32_t sel = (uint32_t)p | ((uint32_t)(4 + p) << 4);
@@ -512,29 +573,71 @@ struct Slot<FMT_Q6_K, NP> {
 
 // ---- tile walk -------------------------------------------------------------
 struct PipeTile { int seg; uint32_t row0, n; };
+struct PipeWalk { uint32_t cur, lo, hi; int seg; };
 
-__device__ __forceinline__ bool next_tile(const PipeArgs &a, uint32_t &cur, uint32_t vend, PipeTile &t)
+// Rows of this CTA.  Plain forms: a contiguous range of the concatenated (virtual) rows, walked once.
+// Combine form: the same range of segment-local rows, walked once per segment.
+template <bool COMBINE>
+__device__ __forceinline__ void walk_init(const PipeArgs &a, PipeWalk &w)
 {
-    if (cur >= vend) return false;
-    int s = 0;
-    while (s + 1 < a.nseg && cur >= a.seg[s + 1].vstart) ++s;
-    uint32_t seg_end = a.seg[s].vstart + a.seg[s].rows;
-    uint32_t lim = vend < seg_end ? vend : seg_end;
-    uint32_t n = lim - cur, cap = a.rows_par * a.iters;
-    if (n > cap) n = cap;
-    t.seg = s; t.row0 = cur - a.seg[s].vstart; t.n = n;
-    cur += n;
-    return true;
+    const uint32_t R = COMBINE ? a.seg[0].rows : a.total_rows;
+    w.lo = (uint32_t)((uint64_t)blockIdx.x * R / gridDim.x);
+    w.hi = (uint32_t)((uint64_t)(blockIdx.x + 1) * R / gridDim.x);
+    w.cur = w.lo;
+    w.seg = 0;
 }
 
-template <bool SWIGLU>
+template <bool COMBINE>
+__device__ __forceinline__ bool next_tile(const PipeArgs &a, PipeWalk &w, PipeTile &t)
+{
+    const uint32_t cap = a.rows_par * a.iters;
+    if constexpr (COMBINE) {
+        if (w.lo >= w.hi) return false;
+        if (w.cur >= w.hi) { ++w.seg; w.cur = w.lo; }
+        if (w.seg >= a.nseg) return false;
+        uint32_t n = w.hi - w.cur;
+        if (n > cap) n = cap;
+        t.seg = w.seg; t.row0 = w.cur; t.n = n;
+        w.cur += n;
+        return true;
+    } else {
+        if (w.cur >= w.hi) return false;
+        int s = w.seg;
+        while (s + 1 < a.nseg && w.cur >= a.seg[s + 1].vstart) ++s;
+        w.seg = s;
+        const uint32_t seg_end = a.seg[s].vstart + a.seg[s].rows;
+        const uint32_t lim = w.hi < seg_end ? w.hi : seg_end;
+        uint32_t n = lim - w.cur;
+        if (n > cap) n = cap;
+        t.seg = s; t.row0 = w.cur - a.seg[s].vstart; t.n = n;
+        w.cur += n;
+        return true;
+    }
+}
+
+template <bool EXT>
+__device__ __forceinline__ const uint8_t *seg_w(const PipeArgs &a, int s)
+{
+    const uint8_t *p = a.seg[s].w;
+    if constexpr (EXT) { if (a.seg_expert) p += (uint64_t)a.seg_expert[s] * a.w_stride; }
+    return p;
+}
+template <bool EXT>
+__device__ __forceinline__ const uint8_t *seg_w2(const PipeArgs &a, int s)
+{
+    const uint8_t *p = a.seg[s].w2;
+    if constexpr (EXT) { if (a.seg_expert) p += (uint64_t)a.seg_expert[s] * a.w2_stride; }
+    return p;
+}
+
+template <bool SWIGLU, bool EXT>
 __device__ __forceinline__ void issue_tile(const PipeArgs &a, const PipeTile &t, uint8_t *stage, uint32_t bar)
 {
     uint32_t tx = 0;
     uintptr_t a0[2], e1[2];
 #pragma unroll
     for (int h = 0; h < (SWIGLU ? 2 : 1); ++h) {
-        const uint8_t *base = h ? a.seg[t.seg].w2 : a.seg[t.seg].w;
+        const uint8_t *base = h ? seg_w2<EXT>(a, t.seg) : seg_w<EXT>(a, t.seg);
         uintptr_t src = reinterpret_cast<uintptr_t>(base) + (size_t)t.row0 * a.row_bytes;
         uintptr_t end = src + (size_t)t.n * a.row_bytes;
         a0[h] = src & ~(uintptr_t)15;
@@ -551,10 +654,14 @@ __device__ __forceinline__ void issue_tile(const PipeArgs &a, const PipeTile &t,
         bulk_g2s(smem_u32(stage + h * a.half_stride), reinterpret_cast<const void *>(a0[h]), (uint32_t)(e1[h] - a0[h]), bar);
 }
 
-template <int FMT, int NP, bool SWIGLU, int MINB>
+// MODE 0: y = W x.  MODE 1: fused gate/up, y = silu(Wg x) * (Wu x).  MODE 2: combine, y = sum_s weight_s * (W_s x_s).
+// EXT compiles in the expert indirection and the multi-GPU publish / wait paths; dense single-GPU launches use the
+// EXT = false instance, which carries none of that code.
+template <int FMT, int NP, int MODE, int MINB, bool EXT>
 __global__ void __launch_bounds__(MINB == 2 ? PIPE_THREADS_2CTA : PIPE_MAX_THREADS, MINB)
 gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
 {
+    constexpr bool SWIGLU = MODE == 1, COMBINE = MODE == 2;
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);
     uint64_t *empty = full + PIPE_MAX_STAGES;
@@ -569,8 +676,6 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
     const uint32_t U = a.units;
     const bool producer = tid >= C;
 
-    const uint32_t v0 = (uint32_t)((uint64_t)blockIdx.x * a.total_rows / gridDim.x);
-    const uint32_t v1 = (uint32_t)((uint64_t)(blockIdx.x + 1) * a.total_rows / gridDim.x);
 
     if (tid == 0) {
         s_abort = 0;
@@ -588,9 +693,12 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
     if (producer) {
         // The weight copies do not depend on the previous kernel: no griddepcontrol.wait on this path.
         if (lane == 0) {
-            uint32_t cur = v0, i = 0;
+            if constexpr (EXT) { if (a.seg_expert) pdl_wait(); }   // the expert indices are the previous kernel's output
+            PipeWalk w;
+            walk_init<COMBINE>(a, w);
+            uint32_t i = 0;
             PipeTile t;
-            while (next_tile(a, cur, v1, t)) {
+            while (next_tile<COMBINE>(a, w, t)) {
                 const uint32_t s = i % a.nstages, k = i / a.nstages;
                 if (k > 0) {
                     if (s_abort || !mbar_wait_bounded(smem_u32(empty + s), (k - 1) & 1u)) {
@@ -599,7 +707,7 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 }
-                issue_tile<SWIGLU>(a, t, stages + (size_t)s * a.stage_stride, smem_u32(full + s));
+                issue_tile<SWIGLU, EXT>(a, t, stages + (size_t)s * a.stage_stride, smem_u32(full + s));
                 ++i;
             }
             stamp(a.trace, 1);
@@ -630,20 +738,35 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
     const uint32_t unit = j % U;
 
     pdl_wait();   // x is the previous kernel's output
+    if (EXT && a.wait_flag) {
+        // x is completed by the peers' stores: wait for their arrival counts (one thread polls, the barrier and the
+        // acquire load order everybody's reads of x behind it)
+        if (tid == 0) {
+            const unsigned int seen = *reinterpret_cast<volatile unsigned int *>(a.wait_seen);
+            if (!flag_wait_bounded(a.wait_flag, seen, a.wait_need)) {
+                s_abort = 1;
+                atomicExch(a.status, 3);
+            }
+            __threadfence();
+            if (atomicAdd(a.wait_arrived, 1u) == gridDim.x - 1) {   // last CTA through: consume this round of arrivals
+                *reinterpret_cast<volatile unsigned int *>(a.wait_arrived) = 0;
+                *reinterpret_cast<volatile unsigned int *>(a.wait_seen) = seen + a.wait_need;
+                __threadfence();
+            }
+        }
+        named_bar_sync(PIPE_BAR_CONSUMERS, (int)C);
+    }
     if (tid == 0) stamp(a.trace, 2);
 
     SlotT slot;
     {
         uint8_t *xq = smem + a.xs_base;
-        quantize_x_to_smem<NP, SlotT::GROUP, SlotT::SUMS>(a.x, a.in_dim, xq, tid, C);
+        quantize_x_to_smem<NP, SlotT::GROUP, SlotT::SUMS>(a.x, a.in_dim, COMBINE ? (uint32_t)a.nseg : 1u, a.x_stride, xq, a.xq_vec_bytes, tid, C);
         named_bar_sync(PIPE_BAR_CONSUMERS, (int)C);
         if (tid == 0) stamp(a.trace, 3);
-        XqView xv;
-        xv.planes = xq;
-        xv.scales = reinterpret_cast<const float *>(xq + (size_t)NP * a.in_dim);
-        xv.sums = xv.scales + a.in_dim / SlotT::GROUP;
-        xv.in_dim = a.in_dim;
-        if (active) slot.load(xv, unit, part);
+        if constexpr (!COMBINE) {
+            if (active) slot.load(make_xq_view<NP, SlotT::GROUP>(xq, a.in_dim), unit, part);
+        }
         if (tid == 0) stamp(a.trace, 4);
     }
 
@@ -651,6 +774,12 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
     // batch of rows at a time, by all consumer threads: one consumer-wide barrier per batch, coalesced stores of y.
     // Two buffers alternate, so the barrier that opens a flush also protects the buffer written two flushes ago.
     const uint32_t CAP = a.red_rows, PLANE = CAP * GW;                 // floats per buffer (per tensor)
+    PipeWalk wk;
+    walk_init<COMBINE>(a, wk);
+    float *accbuf = reinterpret_cast<float *>(smem + a.acc_base);
+    if constexpr (COMBINE) {
+        for (uint32_t r = tid; r < wk.hi - wk.lo; r += C) accbuf[r] = 0.0f;   // ordered before its first use by the first flush's barrier
+    }
     float *pbuf = red;
     uint32_t which = 0, buf_n = 0, buf_row0 = 0;
     int buf_seg = 0;
@@ -664,7 +793,15 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
                 g += src[r * GW + w];
                 if constexpr (SWIGLU) u += src[PLANE + r * GW + w];
             }
-            y[r] = SWIGLU ? silu_mul(g, u) : g;
+            if constexpr (COMBINE) accbuf[buf_row0 - wk.lo + r] += a.seg_weight[buf_seg] * g;   // one owner per row and flush
+            else {
+                const float val = SWIGLU ? silu_mul(g, u) : g;
+                y[r] = val;
+                if constexpr (EXT) {
+                    for (int p = 0; p < a.npeers; ++p)
+                        *reinterpret_cast<float *>(reinterpret_cast<char *>(y + r) + a.peer_delta[p]) = val;
+                }
+            }
         }
         which ^= 1u;
         buf_n = 0;
@@ -672,23 +809,30 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
 
     const uint32_t stages_s = smem_u32(stages);
     const uint32_t unit_off = unit * SlotT::UNIT_BYTES;
-    uint32_t cur = v0, i = 0;
+    uint32_t i = 0;
+    int slot_seg = -1;
     PipeTile t;
-    while (next_tile(a, cur, v1, t)) {
+    while (next_tile<COMBINE>(a, wk, t)) {
         if (buf_n && (t.seg != buf_seg || buf_n + t.n > CAP)) flush();
         if (buf_n == 0) { buf_seg = t.seg; buf_row0 = t.row0; }
+        if constexpr (COMBINE) {
+            if (t.seg != slot_seg) {   // this segment's own input vector
+                slot_seg = t.seg;
+                if (active) slot.load(make_xq_view<NP, SlotT::GROUP>(smem + a.xs_base + (size_t)t.seg * a.xq_vec_bytes, a.in_dim), unit, part);
+            }
+        }
         const uint32_t s = i % a.nstages, parity = (i / a.nstages) & 1u;
         if (!s_abort && !mbar_wait_bounded(smem_u32(full + s), parity)) {
             s_abort = 1;
             atomicExch(a.status, 1);
         }
         if (i == 0 && tid == 0) stamp(a.trace, 5);
-        const uint32_t delta = (uint32_t)((reinterpret_cast<uintptr_t>(a.seg[t.seg].w) + (size_t)t.row0 * a.row_bytes) & 15u);
+        const uint32_t delta = (uint32_t)((reinterpret_cast<uintptr_t>(seg_w<EXT>(a, t.seg)) + (size_t)t.row0 * a.row_bytes) & 15u);
         const uint32_t base = stages_s + s * a.stage_stride + delta + unit_off;
         uint32_t base2 = 0;
         if constexpr (SWIGLU)
             base2 = stages_s + s * a.stage_stride + a.half_stride + unit_off +
-                    (uint32_t)((reinterpret_cast<uintptr_t>(a.seg[t.seg].w2) + (size_t)t.row0 * a.row_bytes) & 15u);
+                    (uint32_t)((reinterpret_cast<uintptr_t>(seg_w2<EXT>(a, t.seg)) + (size_t)t.row0 * a.row_bytes) & 15u);
         float *dst = pbuf + (size_t)which * PLANE * (SWIGLU ? 2 : 1) + (size_t)buf_n * GW + wig;
 #pragma unroll 1
         for (uint32_t r = group; r < t.n; r += a.rows_par) {
@@ -711,6 +855,29 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
     }
     if (tid == 0) stamp(a.trace, 6);
     if (buf_n) flush();
+    if constexpr (COMBINE) {
+        named_bar_sync(PIPE_BAR_CONSUMERS, (int)C);
+        for (uint32_t r = tid; r < wk.hi - wk.lo; r += C) {
+            float *dst = a.seg[0].y + wk.lo + r;
+            *dst = accbuf[r];
+            if constexpr (EXT) {
+                for (int p = 0; p < a.npeers; ++p) *reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + a.peer_delta[p]) = accbuf[r];
+            }
+        }
+    }
+    if (EXT && a.npeers > 0) {
+        // every consumer thread's peer stores are fenced, then one thread counts this CTA in; the last CTA of the
+        // grid tells every peer that this rank's slice has landed
+        __threadfence_system();
+        named_bar_sync(PIPE_BAR_CONSUMERS, (int)C);
+        if (tid == 0) {
+            if (atomicAdd(a.pub_arrived, 1u) == gridDim.x - 1) {
+                *reinterpret_cast<volatile unsigned int *>(a.pub_arrived) = 0;
+                __threadfence_system();
+                for (int p = 0; p < a.npeers; ++p) red_release_sys_add(a.pub_flag[p], 1u);
+            }
+        }
+    }
     if (tid == 0) stamp(a.trace, 7);
 }
 

@@ -16,6 +16,7 @@ route_topk_kernel(const float *__restrict__ logits, int ld_logits, uint32_t n_ex
     __shared__ uint32_t s_idx[8];
     __shared__ float f_val[8];
     __shared__ uint32_t f_idx[8];
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // the logits are the previous kernel's output
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const float *lg = logits + (size_t)blockIdx.x * ld_logits;
     float my = tid < n_experts ? lg[tid] : -INFINITY;

@@ -35,6 +35,12 @@ struct orome_cuda_ctx {
     int prefetch_mb = 24;    // at most this many MiB of the next tensor are pulled into L2 by the current launch
     const uint8_t *hint_ptr = nullptr;   // set by orome_cuda_hint_next, consumed by the next pipelined launch
     uint64_t hint_bytes = 0;
+    // multi-GPU gather state (orome_cuda_gather_setup)
+    int g_rank = 0, g_world = 1, g_nflags = 0;
+    uint8_t *g_arena[8] = {nullptr};          // every rank's arena as mapped in this process
+    size_t g_data_bytes = 0;
+    unsigned int *g_local = nullptr;          // [n_flags] seen + pub_arrived + wait_arrived (local device memory)
+    int g_wait = -1, g_publish = -1;          // request for the next pipelined launch
     unsigned long long *trace_dev = nullptr;   // diagnostics buffer [trace_cap][sm_count][8]
     int trace_cap = 0, trace_next = 0;
     // staging for the host-buffer entry point
@@ -101,6 +107,7 @@ extern "C" void orome_cuda_ctx_destroy(orome_cuda_ctx *c)
     cudaFree(c->logits_dev);
     cudaFree(c->gu_dev);
     cudaFree(c->trace_dev);
+    cudaFree(c->g_local);
     cudaFreeHost(c->stage_x_host);
     cudaFreeHost(c->stage_y_host);
     if (c->own_stream) cudaStreamDestroy(c->own_stream);
@@ -253,6 +260,43 @@ static int post_launch(orome_cuda_ctx *c, const char *what)
     return OROME_OK;
 }
 
+// Launch with programmatic stream serialization, so the kernel's launch overlaps the tail of its predecessor
+// (the kernel itself starts with griddepcontrol.wait).
+template <typename... KArgs, typename... Args>
+static int launch_pdl(orome_cuda_ctx *c, const char *what, void (*kern)(KArgs...), dim3 grid, dim3 block, cudaStream_t st, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = c->pdl ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+    if (e != cudaSuccess) return fail(OROME_ECUDA, "%s launch: %s", what, cudaGetErrorString(e));
+    ++c->launches;
+    return OROME_OK;
+}
+
+static int launch_generic(orome_cuda_ctx *c, int fmt, const uint8_t *data, uint32_t out_dim, uint32_t in_dim, int layout,
+                          const float *x, int batch, int ldx, float *y, int ldy, cudaStream_t st);
+
+static int launch_router(orome_cuda_ctx *c, const uint8_t *data, uint32_t ne, uint32_t in_dim, const float *x, int n_tokens, int ldx,
+                         float *logits, uint32_t K, uint32_t *idx, float *w, cudaStream_t st)
+{
+    int rc;
+    if (in_dim % 4 == 0 && !(reinterpret_cast<uintptr_t>(x) & 15) && (n_tokens == 1 || ldx % 4 == 0))
+        rc = launch_pdl(c, "gemv_f32", gemv_f32_kernel, dim3((ne + 3) / 4), dim3(128), st, reinterpret_cast<const float *>(data), ne, in_dim,
+                        x, n_tokens, ldx, logits, (int)ne);
+    else
+        rc = launch_generic(c, FMT_F32, data, ne, in_dim, 0, x, n_tokens, ldx, logits, (int)ne, st);
+    if (rc) return rc;
+    return launch_pdl(c, "route_topk", route_topk_kernel, dim3(n_tokens), dim3(256), st, (const float *)logits, (int)ne, ne, K, idx, w);
+}
+
 // ---------------------------------------------------------------------------
 // generic kernels
 // ---------------------------------------------------------------------------
@@ -309,15 +353,16 @@ static bool pipe_supported(int fmt, uint32_t in_dim)
 }
 
 // Fill everything of the plan except the segments' pointers.
-static int plan_pipe(orome_cuda_ctx *c, int fmt, uint32_t in_dim, uint32_t total_rows, bool swiglu, PipePlan &p)
+static int plan_pipe(orome_cuda_ctx *c, int fmt, uint32_t in_dim, uint32_t total_rows, int mode, PipePlan &p)
 {
+    const bool swiglu = mode == 1, combine = mode == 2;   // combine: total_rows = rows of one segment, args.nseg input vectors
     PipeArgs &a = p.args;
     a.in_dim = in_dim;
     a.row_bytes = (uint32_t)row_bytes_of(fmt, in_dim);
     a.units = fmt == FMT_Q8_0 ? in_dim / 64 : in_dim / 256;
     a.group_threads = pipe_group_threads(fmt, in_dim);
     a.total_rows = total_rows;
-    p.minb = c->ctas_per_sm >= 2 && a.group_threads <= PIPE_CONSUMERS_2CTA ? 2 : 1;
+    p.minb = c->ctas_per_sm >= 2 && a.group_threads <= PIPE_CONSUMERS_2CTA && !combine ? 2 : 1;
     if (fmt == FMT_Q6_K && c->x_bits == 24 && swiglu) p.minb = 1;   // needs more than the 96 registers of the two-CTA build
     const uint32_t max_consumers = p.minb == 2 ? PIPE_CONSUMERS_2CTA : PIPE_MAX_CONSUMERS;
     a.rows_par = std::max(1u, std::min((uint32_t)PIPE_MAX_ROWS_PAR, max_consumers / a.group_threads));
@@ -346,8 +391,11 @@ static int plan_pipe(orome_cuda_ctx *c, int fmt, uint32_t in_dim, uint32_t total
     a.xs_base = (uint32_t)((a.red_base + red_bytes + 127) / 128 * 128);
     // quantized x: one byte plane per 8 bits of x, a scale per group (16 for Q6_K, else 32), a sum per 32 elements
     const size_t np = c->x_bits == 24 ? 3 : 2;
-    const size_t xq_bytes = np * in_dim + (size_t)in_dim / (fmt == FMT_Q6_K ? 16 : 32) * 4 + (size_t)in_dim / 32 * 4;
-    a.stage_base = (uint32_t)((a.xs_base + xq_bytes + 127) / 128 * 128);
+    const size_t xq_vec = (np * in_dim + (size_t)in_dim / (fmt == FMT_Q6_K ? 16 : 32) * 4 + (size_t)in_dim / 32 * 4 + 15) / 16 * 16;
+    a.xq_vec_bytes = (uint32_t)xq_vec;
+    const size_t xq_bytes = xq_vec * (combine ? std::max(a.nseg, 1) : 1);
+    a.acc_base = (uint32_t)((a.xs_base + xq_bytes + 15) / 16 * 16);
+    a.stage_base = (uint32_t)((a.acc_base + (combine ? (size_t)(share + 1) * sizeof(float) : 0) + 127) / 128 * 128);
     for (;;) {
         a.half_stride = (a.rows_par * a.iters * a.row_bytes + 48 + 127) / 128 * 128;
         a.stage_stride = a.half_stride * (swiglu ? 2 : 1);
@@ -365,6 +413,29 @@ static int plan_pipe(orome_cuda_ctx *c, int fmt, uint32_t in_dim, uint32_t total
     a.status = c->status_dev;
     a.trace = nullptr;
     if (c->trace_dev && c->trace_next < c->trace_cap) a.trace = c->trace_dev + (size_t)(c->trace_next++) * c->sm_count * 8;
+    a.npeers = 0;
+    a.wait_flag = nullptr;
+    if (c->g_world > 1) {
+        constexpr size_t FLAG_STRIDE = 32;   // counters sit 128 bytes apart
+        if (c->g_publish >= 0) {
+            int n = 0;
+            for (int r = 0; r < c->g_world; ++r) {
+                if (r == c->g_rank) continue;
+                a.peer_delta[n] = (long long)(c->g_arena[r] - c->g_arena[c->g_rank]);
+                a.pub_flag[n] = reinterpret_cast<unsigned int *>(c->g_arena[r] + c->g_data_bytes) + (size_t)c->g_publish * FLAG_STRIDE;
+                ++n;
+            }
+            a.npeers = n;
+            a.pub_arrived = c->g_local + c->g_nflags;
+        }
+        if (c->g_wait >= 0) {
+            a.wait_flag = reinterpret_cast<unsigned int *>(c->g_arena[c->g_rank] + c->g_data_bytes) + (size_t)c->g_wait * FLAG_STRIDE;
+            a.wait_seen = c->g_local + c->g_wait;
+            a.wait_arrived = c->g_local + c->g_nflags + 1;
+            a.wait_need = (unsigned int)(c->g_world - 1);
+        }
+        c->g_wait = c->g_publish = -1;
+    }
     a.pf_ptr = c->hint_ptr;
     a.pf_bytes = c->hint_bytes;
     c->hint_ptr = nullptr;
@@ -372,10 +443,10 @@ static int plan_pipe(orome_cuda_ctx *c, int fmt, uint32_t in_dim, uint32_t total
     return OROME_OK;
 }
 
-template <int FMT, int NP, bool SW, int MINB>
-static int launch_pipe_inst(orome_cuda_ctx *c, const PipePlan &p, cudaStream_t st)
+template <int FMT, int NP, int MODE, int MINB, bool EXT>
+static int launch_pipe_ext(orome_cuda_ctx *c, const PipePlan &p, cudaStream_t st)
 {
-    auto kern = gemv_pipe_kernel<FMT, NP, SW, MINB>;
+    auto kern = gemv_pipe_kernel<FMT, NP, MODE, MINB, EXT>;
     static size_t configured[64] = {0};   // per device: dynamic shared memory opted in so far
     if (configured[c->device] < p.smem) {
         cudaFuncAttributes fa;
@@ -400,26 +471,35 @@ static int launch_pipe_inst(orome_cuda_ctx *c, const PipePlan &p, cudaStream_t s
     return OROME_OK;
 }
 
-template <int FMT, int NP>
-static int launch_pipe_np(orome_cuda_ctx *c, const PipePlan &p, bool swiglu, cudaStream_t st)
+template <int FMT, int NP, int MODE, int MINB>
+static int launch_pipe_inst(orome_cuda_ctx *c, const PipePlan &p, cudaStream_t st)
 {
-    if (p.minb == 2) return swiglu ? launch_pipe_inst<FMT, NP, true, 2>(c, p, st) : launch_pipe_inst<FMT, NP, false, 2>(c, p, st);
-    return swiglu ? launch_pipe_inst<FMT, NP, true, 1>(c, p, st) : launch_pipe_inst<FMT, NP, false, 1>(c, p, st);
+    const bool ext = p.args.seg_expert || p.args.npeers > 0 || p.args.wait_flag;
+    if constexpr (MODE == 2) return launch_pipe_ext<FMT, NP, MODE, MINB, true>(c, p, st);
+    else return ext ? launch_pipe_ext<FMT, NP, MODE, MINB, true>(c, p, st) : launch_pipe_ext<FMT, NP, MODE, MINB, false>(c, p, st);
+}
+
+template <int FMT, int NP>
+static int launch_pipe_np(orome_cuda_ctx *c, const PipePlan &p, int mode, cudaStream_t st)
+{
+    if (mode == 2) return launch_pipe_inst<FMT, NP, 2, 1>(c, p, st);
+    if (p.minb == 2) return mode == 1 ? launch_pipe_inst<FMT, NP, 1, 2>(c, p, st) : launch_pipe_inst<FMT, NP, 0, 2>(c, p, st);
+    return mode == 1 ? launch_pipe_inst<FMT, NP, 1, 1>(c, p, st) : launch_pipe_inst<FMT, NP, 0, 1>(c, p, st);
 }
 
 template <int FMT>
-static int launch_pipe_fmt(orome_cuda_ctx *c, const PipePlan &p, bool swiglu, cudaStream_t st)
+static int launch_pipe_fmt(orome_cuda_ctx *c, const PipePlan &p, int mode, cudaStream_t st)
 {
-    return c->x_bits == 24 ? launch_pipe_np<FMT, 3>(c, p, swiglu, st) : launch_pipe_np<FMT, 2>(c, p, swiglu, st);
+    return c->x_bits == 24 ? launch_pipe_np<FMT, 3>(c, p, mode, st) : launch_pipe_np<FMT, 2>(c, p, mode, st);
 }
 
-static int launch_pipe(orome_cuda_ctx *c, int fmt, const PipePlan &p, bool swiglu, cudaStream_t st)
+static int launch_pipe(orome_cuda_ctx *c, int fmt, const PipePlan &p, int mode, cudaStream_t st)
 {
     switch (fmt) {
-    case FMT_Q4_K: return launch_pipe_fmt<FMT_Q4_K>(c, p, swiglu, st);
-    case FMT_Q5_K: return launch_pipe_fmt<FMT_Q5_K>(c, p, swiglu, st);
-    case FMT_Q6_K: return launch_pipe_fmt<FMT_Q6_K>(c, p, swiglu, st);
-    case FMT_Q8_0: return launch_pipe_fmt<FMT_Q8_0>(c, p, swiglu, st);
+    case FMT_Q4_K: return launch_pipe_fmt<FMT_Q4_K>(c, p, mode, st);
+    case FMT_Q5_K: return launch_pipe_fmt<FMT_Q5_K>(c, p, mode, st);
+    case FMT_Q6_K: return launch_pipe_fmt<FMT_Q6_K>(c, p, mode, st);
+    case FMT_Q8_0: return launch_pipe_fmt<FMT_Q8_0>(c, p, mode, st);
     }
     return fail(OROME_ENOTSUP, "no pipelined kernel for format %d", fmt);
 }
@@ -439,6 +519,108 @@ extern "C" int orome_cuda_hint_next(orome_cuda_ctx *c, const OromeTensorRef *nex
     c->hint_ptr = p;
     c->hint_bytes = std::min<uint64_t>(total, (uint64_t)c->prefetch_mb << 20) & ~(uint64_t)15;
     return OROME_OK;
+}
+
+// ---------------------------------------------------------------------------
+// multi-GPU gather
+// ---------------------------------------------------------------------------
+static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the ABI passes IPC handles as 64 bytes");
+
+extern "C" size_t orome_cuda_gather_arena_bytes(size_t data_bytes, int n_flags)
+{
+    return (data_bytes + 255) / 256 * 256 + (size_t)std::max(n_flags, 0) * 128 + 256;
+}
+
+extern "C" int orome_cuda_peer_alloc(orome_cuda_ctx *c, size_t bytes, void **dev_ptr, unsigned char handle_out[64])
+{
+    if (!c || !dev_ptr || !handle_out || !bytes) return fail(OROME_EINVAL, "peer_alloc: bad argument");
+    CU(cudaSetDevice(c->device));
+    void *p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes);
+    if (e != cudaSuccess) return fail(OROME_ENOMEM, "peer_alloc: cudaMalloc(%zu): %s", bytes, cudaGetErrorString(e));
+    CU(cudaMemset(p, 0, bytes));
+    cudaIpcMemHandle_t h;
+    e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) { cudaFree(p); return fail(OROME_ECUDA, "peer_alloc: cudaIpcGetMemHandle: %s", cudaGetErrorString(e)); }
+    memcpy(handle_out, &h, 64);
+    CU(cudaDeviceSynchronize());
+    *dev_ptr = p;
+    return OROME_OK;
+}
+
+extern "C" int orome_cuda_peer_open(orome_cuda_ctx *c, const unsigned char handle[64], void **dev_ptr)
+{
+    if (!c || !handle || !dev_ptr) return fail(OROME_EINVAL, "peer_open: NULL argument");
+    CU(cudaSetDevice(c->device));
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, 64);
+    void *p = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return fail(OROME_ECUDA, "peer_open: cudaIpcOpenMemHandle: %s", cudaGetErrorString(e));
+    *dev_ptr = p;
+    return OROME_OK;
+}
+
+extern "C" int orome_cuda_peer_close(orome_cuda_ctx *c, void *dev_ptr)
+{
+    if (!c || !dev_ptr) return fail(OROME_EINVAL, "peer_close: NULL argument");
+    CU(cudaSetDevice(c->device));
+    CU(cudaIpcCloseMemHandle(dev_ptr));
+    return OROME_OK;
+}
+
+extern "C" int orome_cuda_gather_setup(orome_cuda_ctx *c, int rank, int world, void *const *arenas, size_t data_bytes, int n_flags)
+{
+    if (!c) return fail(OROME_EINVAL, "gather_setup: NULL ctx");
+    if (world == 1 || !arenas) {   // back to single-GPU behaviour
+        c->g_world = 1; c->g_rank = 0; c->g_wait = c->g_publish = -1;
+        return OROME_OK;
+    }
+    if (world < 2 || world > PIPE_MAX_PEERS + 1 || rank < 0 || rank >= world) return fail(OROME_EINVAL, "gather_setup: rank %d of %d (at most %d GPUs)", rank, world, PIPE_MAX_PEERS + 1);
+    if (n_flags < 1 || n_flags > 64) return fail(OROME_EINVAL, "gather_setup: n_flags %d (1..64)", n_flags);
+    if (data_bytes % 256) return fail(OROME_EINVAL, "gather_setup: data_bytes must be a multiple of 256");
+    for (int r = 0; r < world; ++r)
+        if (!arenas[r] || (reinterpret_cast<uintptr_t>(arenas[r]) & 255)) return fail(OROME_EINVAL, "gather_setup: arena %d is NULL or not 256-byte aligned", r);
+    CU(cudaSetDevice(c->device));
+    cudaFree(c->g_local);
+    c->g_local = nullptr;
+    CU(cudaMalloc(&c->g_local, (size_t)(n_flags + 2) * sizeof(unsigned int)));
+    CU(cudaMemset(c->g_local, 0, (size_t)(n_flags + 2) * sizeof(unsigned int)));
+    for (int r = 0; r < world; ++r) c->g_arena[r] = static_cast<uint8_t *>(arenas[r]);
+    c->g_rank = rank; c->g_world = world; c->g_nflags = n_flags; c->g_data_bytes = data_bytes;
+    c->g_wait = c->g_publish = -1;
+    return OROME_OK;
+}
+
+extern "C" int orome_cuda_gather_next(orome_cuda_ctx *c, int wait_flag, int publish_flag)
+{
+    if (!c) return fail(OROME_EINVAL, "gather_next: NULL ctx");
+    if (c->g_world < 2) { c->g_wait = c->g_publish = -1; return OROME_OK; }   // single GPU: nothing to wait for or publish
+    if (wait_flag >= c->g_nflags || publish_flag >= c->g_nflags) return fail(OROME_EINVAL, "gather_next: flag out of range (%d flags)", c->g_nflags);
+    c->g_wait = wait_flag < 0 ? -1 : wait_flag;
+    c->g_publish = publish_flag < 0 ? -1 : publish_flag;
+    return OROME_OK;
+}
+
+// One thread: wait (bounded) for one round of arrivals on `flag`, then consume it.
+__global__ void gather_wait_kernel(const unsigned int *flag, unsigned int *seen, unsigned int need, int *status)
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const unsigned int s = *reinterpret_cast<volatile unsigned int *>(seen);
+    if (!flag_wait_bounded(flag, s, need)) atomicExch(status, 3);
+    *reinterpret_cast<volatile unsigned int *>(seen) = s + need;
+    __threadfence();
+}
+
+extern "C" int orome_cuda_gather_wait(orome_cuda_ctx *c, int flag, void *stream)
+{
+    if (!c) return fail(OROME_EINVAL, "gather_wait: NULL ctx");
+    if (c->g_world < 2) return OROME_OK;
+    if (flag < 0 || flag >= c->g_nflags) return fail(OROME_EINVAL, "gather_wait: flag %d of %d", flag, c->g_nflags);
+    CU(cudaSetDevice(c->device));
+    const unsigned int *f = reinterpret_cast<unsigned int *>(c->g_arena[c->g_rank] + c->g_data_bytes) + (size_t)flag * 32;
+    return launch_pdl(c, "gather_wait", gather_wait_kernel, dim3(1), dim3(1), static_cast<cudaStream_t>(stream), f, c->g_local + flag,
+                      (unsigned int)(c->g_world - 1), c->status_dev);
 }
 
 // ---------------------------------------------------------------------------
@@ -462,7 +644,15 @@ extern "C" int orome_cuda_matvec_group(orome_cuda_ctx *c, const OromeTensorRef *
     }
     if (!x_dev || (reinterpret_cast<uintptr_t>(x_dev) & 15)) return fail(OROME_EINVAL, "matvec_group: x must be a 16-byte aligned device pointer");
     const int fmt = (int)refs[0].format, layout = (int)refs[0].variant;
+    if (c->g_world > 1 && c->g_publish >= 0) {
+        const uint8_t *lo = c->g_arena[c->g_rank], *hi = lo + c->g_data_bytes;
+        for (int i = 0; i < n_refs; ++i) {
+            const uint8_t *y0 = reinterpret_cast<const uint8_t *>(y_dev[i]);
+            if (y0 < lo || y0 + (size_t)refs[i].out_dim * 4 > hi) { c->g_wait = c->g_publish = -1; return fail(OROME_EINVAL, "matvec_group: a published y must lie inside the gather arena"); }
+        }
+    }
     if (c->force_generic || !pipe_supported(fmt, refs[0].in_dim)) {
+        if (c->g_world > 1 && (c->g_publish >= 0 || c->g_wait >= 0)) { c->g_wait = c->g_publish = -1; return fail(OROME_ENOTSUP, "matvec_group: this shape has no multi-GPU form"); }
         for (int i = 0; i < n_refs; ++i) {
             int rc = launch_generic(c, fmt, data[i], refs[i].out_dim, refs[i].in_dim, layout, x_dev, 1, 0, y_dev[i], 0, st);
             if (rc) return rc;
@@ -483,9 +673,9 @@ extern "C" int orome_cuda_matvec_group(orome_cuda_ctx *c, const OromeTensorRef *
     p.args.nseg = n_refs;
     p.args.x = x_dev;
     p.args.layout = layout;
-    int rc = plan_pipe(c, fmt, refs[0].in_dim, total, false, p);
+    int rc = plan_pipe(c, fmt, refs[0].in_dim, total, 0, p);
     if (rc) return rc;
-    return launch_pipe(c, fmt, p, false, st);
+    return launch_pipe(c, fmt, p, 0, st);
 }
 
 extern "C" int orome_cuda_matvec(orome_cuda_ctx *c, const OromeTensorRef *ref, const float *x_dev, float *y_dev, int batch,
@@ -549,6 +739,14 @@ extern "C" int orome_cuda_gate_up_swiglu(orome_cuda_ctx *c, const OromeTensorRef
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     CU(cudaSetDevice(c->device));
     const int fmt = (int)gate->format, layout = (int)gate->variant;
+    if (c->g_world > 1 && c->g_publish >= 0) {
+        const uint8_t *lo = c->g_arena[c->g_rank], *hi = lo + c->g_data_bytes, *y0 = reinterpret_cast<const uint8_t *>(out_dev);
+        if (y0 < lo || y0 + (size_t)gate->out_dim * 4 > hi) { c->g_wait = c->g_publish = -1; return fail(OROME_EINVAL, "gate_up_swiglu: a published output must lie inside the gather arena"); }
+    }
+    if (c->g_world > 1 && (c->g_publish >= 0 || c->g_wait >= 0) && !(batch == 1 && !c->force_generic && pipe_supported(fmt, gate->in_dim))) {
+        c->g_wait = c->g_publish = -1;
+        return fail(OROME_ENOTSUP, "gate_up_swiglu: this shape has no multi-GPU form");
+    }
     if (batch == 1 && !c->force_generic && pipe_supported(fmt, gate->in_dim)) {
         if (reinterpret_cast<uintptr_t>(x_dev) & 15) return fail(OROME_EINVAL, "gate_up_swiglu: x must be 16-byte aligned");
         PipePlan p;
@@ -557,9 +755,9 @@ extern "C" int orome_cuda_gate_up_swiglu(orome_cuda_ctx *c, const OromeTensorRef
         p.args.nseg = 1;
         p.args.x = x_dev;
         p.args.layout = layout;
-        rc = plan_pipe(c, fmt, gate->in_dim, gate->out_dim, true, p);
+        rc = plan_pipe(c, fmt, gate->in_dim, gate->out_dim, 1, p);
         if (rc) return rc;
-        return launch_pipe(c, fmt, p, true, st);
+        return launch_pipe(c, fmt, p, 1, st);
     }
     // two matvecs into context scratch, then the elementwise epilogue (the reference's unfused branch, engine.m:388-404)
     if (batch > 1 && (ldx < (int)gate->in_dim || ldo < (int)gate->out_dim))
@@ -632,10 +830,7 @@ extern "C" int orome_cuda_moe_route(orome_cuda_ctx *c, const OromeTensorRef *rou
         if (rc) return rc;
         logits_dev = c->logits_dev;
     }
-    rc = launch_generic(c, FMT_F32, data, ne, router->in_dim, 0, x_dev, n_tokens, ldx, logits_dev, (int)ne, st);
-    if (rc) return rc;
-    route_topk_kernel<<<n_tokens, 256, 0, st>>>(logits_dev, (int)ne, ne, K, idx_dev, w_dev);
-    return post_launch(c, "route_topk");
+    return launch_router(c, data, ne, router->in_dim, x_dev, n_tokens, ldx, logits_dev, K, idx_dev, w_dev, st);
 }
 
 // ---------------------------------------------------------------------------
@@ -674,10 +869,7 @@ extern "C" int orome_cuda_moe_route_static(orome_cuda_ctx *c, const OromeTensorR
     }
     float *logits = g_route_logits_addr[c->device];
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    rc = launch_generic(c, FMT_F32, data, ne, router->in_dim, 0, x_dev, n_tokens, ldx, logits, (int)ne, st);
-    if (rc) return rc;
-    route_topk_kernel<<<n_tokens, 256, 0, st>>>(logits, (int)ne, ne, K, idx_dev, w_dev);
-    return post_launch(c, "route_topk");
+    return launch_router(c, data, ne, router->in_dim, x_dev, n_tokens, ldx, logits, K, idx_dev, w_dev, st);
 }
 
 extern "C" int orome_cuda_moe_ffn(orome_cuda_ctx *c, const OromeExpertLayerRef *L, uint32_t variant, const float *x_dev,
@@ -701,6 +893,42 @@ extern "C" int orome_cuda_moe_ffn(orome_cuda_ctx *c, const OromeExpertLayerRef *
     CU(cudaSetDevice(c->device));
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const size_t grb = row_bytes_of(gfmt, hidden), drb = row_bytes_of(dfmt, inter);
+    if (!c->force_generic && pipe_supported(gfmt, hidden) && pipe_supported(dfmt, inter) && K <= (uint32_t)PIPE_MAX_SEG &&
+        !((reinterpret_cast<uintptr_t>(x_dev) | reinterpret_cast<uintptr_t>(act_dev)) & 15) && (ldx % 4 == 0 || n_tokens == 1) && inter % 4 == 0) {
+        // Per token: one fused gate/up launch over the K selected experts (device-side expert indices), then one
+        // down launch that gives every expert its own input vector and adds the K results with the routing weights.
+        for (int t = 0; t < n_tokens; ++t) {
+            PipePlan p;
+            memset(&p, 0, sizeof p);
+            for (uint32_t k = 0; k < K; ++k)
+                p.args.seg[k] = PipeSeg{gate, up, act_dev + ((size_t)t * K + k) * inter, inter, k * inter};
+            p.args.nseg = (int)K;
+            p.args.x = x_dev + (size_t)t * ldx;
+            p.args.layout = (int)variant;
+            int rc = plan_pipe(c, gfmt, hidden, K * inter, 1, p);
+            if (rc) return rc;
+            p.args.seg_expert = idx_dev + (size_t)t * 8;
+            p.args.w_stride = L->gate.expert_stride;
+            p.args.w2_stride = L->up.expert_stride;
+            rc = launch_pipe(c, gfmt, p, 1, st);
+            if (rc) return rc;
+
+            memset(&p, 0, sizeof p);
+            for (uint32_t k = 0; k < K; ++k) p.args.seg[k] = PipeSeg{down, nullptr, out_dev + (size_t)t * (n_tokens == 1 ? hidden : ldo), hidden, 0};
+            p.args.nseg = (int)K;
+            p.args.x = act_dev + (size_t)t * K * inter;
+            p.args.layout = (int)variant;
+            rc = plan_pipe(c, dfmt, inter, hidden, 2, p);
+            if (rc) return rc;
+            p.args.seg_expert = idx_dev + (size_t)t * 8;
+            p.args.w_stride = L->down.expert_stride;
+            p.args.x_stride = inter;
+            p.args.seg_weight = w_dev + (size_t)t * 8;
+            rc = launch_pipe(c, dfmt, p, 2, st);
+            if (rc) return rc;
+        }
+        return OROME_OK;
+    }
     dim3 g1((inter + 7) / 8, (unsigned)n_tokens * K), g2((hidden + 7) / 8, (unsigned)n_tokens);
 #define GU(F) moe_gate_up_kernel<F><<<g1, 256, 0, st>>>(gate, L->gate.expert_stride, up, L->up.expert_stride, grb, inter, hidden, (int)variant, x_dev, ldx, idx_dev, K, act_dev)
     switch (gfmt) {

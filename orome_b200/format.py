@@ -46,7 +46,8 @@ EXPORTS = [
     "orome_cuda_free", "orome_format_from_ggml_type", "orome_format_row_bytes", "orome_format_dispatch_matvec",
     "orome_cuda_matvec", "orome_cuda_matvec_group", "orome_cuda_gate_up_swiglu", "orome_cuda_dequant_rows",
     "orome_cuda_moe_route", "orome_cuda_moe_route_static", "orome_cuda_moe_ffn", "orome_cuda_matvec_host", "orome_cuda_set_option",
-    "orome_cuda_get_option", "orome_cuda_launch_count", "orome_cuda_hint_next", "orome_cuda_trace_begin", "orome_cuda_trace_read",
+    "orome_cuda_get_option", "orome_cuda_launch_count", "orome_cuda_hint_next", "orome_cuda_peer_alloc", "orome_cuda_peer_open", "orome_cuda_peer_close", "orome_cuda_gather_setup",
+    "orome_cuda_gather_arena_bytes", "orome_cuda_gather_next", "orome_cuda_gather_wait", "orome_cuda_trace_begin", "orome_cuda_trace_read",
 ]
 
 _lib = None
@@ -85,6 +86,14 @@ def lib():
     L.orome_cuda_set_option.argtypes = [vp, i32, i32]
     L.orome_cuda_get_option.argtypes = [vp, i32, C.POINTER(i32)]
     L.orome_cuda_hint_next.argtypes = [vp, TR]
+    L.orome_cuda_peer_alloc.argtypes = [vp, sz, C.POINTER(vp), C.c_char_p]
+    L.orome_cuda_peer_open.argtypes = [vp, C.c_char_p, C.POINTER(vp)]
+    L.orome_cuda_peer_close.argtypes = [vp, vp]
+    L.orome_cuda_gather_setup.argtypes = [vp, i32, i32, C.POINTER(vp), sz, i32]
+    L.orome_cuda_gather_arena_bytes.argtypes = [sz, i32]
+    L.orome_cuda_gather_arena_bytes.restype = sz
+    L.orome_cuda_gather_next.argtypes = [vp, i32, i32]
+    L.orome_cuda_gather_wait.argtypes = [vp, i32, vp]
     L.orome_cuda_trace_begin.argtypes = [vp, i32]
     L.orome_cuda_trace_read.argtypes = [vp, vp, sz]
     L.orome_cuda_launch_count.argtypes = [vp]
@@ -164,6 +173,32 @@ class Context:
         _chk(lib().orome_cuda_trace_read(self._h, out.ctypes.data_as(C.c_void_p), out.size))
         return out
 
+    # -- multi-GPU gather ----------------------------------------------------------
+    def peer_alloc(self, nbytes: int):
+        """(device address, 64-byte IPC handle) of a new zeroed allocation that other processes can map."""
+        out = C.c_void_p()
+        h = C.create_string_buffer(64)
+        _chk(lib().orome_cuda_peer_alloc(self._h, nbytes, C.byref(out), h))
+        return int(out.value), h.raw
+
+    def peer_open(self, handle: bytes) -> int:
+        out = C.c_void_p()
+        _chk(lib().orome_cuda_peer_open(self._h, handle, C.byref(out)))
+        return int(out.value)
+
+    def peer_close(self, ptr: int):
+        _chk(lib().orome_cuda_peer_close(self._h, C.c_void_p(ptr)))
+
+    def gather_setup(self, rank: int, world: int, arenas, data_bytes: int, n_flags: int):
+        arr = (C.c_void_p * world)(*arenas) if world > 1 else None
+        _chk(lib().orome_cuda_gather_setup(self._h, rank, world, arr, data_bytes, n_flags))
+
+    def gather_next(self, wait_flag: int = -1, publish_flag: int = -1):
+        _chk(lib().orome_cuda_gather_next(self._h, wait_flag, publish_flag))
+
+    def gather_wait(self, flag: int, stream: int = 0):
+        _chk(lib().orome_cuda_gather_wait(self._h, flag, stream))
+
     def hint_next(self, ref: TensorRef | None):
         _chk(lib().orome_cuda_hint_next(self._h, C.byref(ref) if ref is not None else None))
 
@@ -203,6 +238,10 @@ class Context:
         """x_host / y_host: contiguous float32 numpy arrays (host memory)."""
         _chk(lib().orome_cuda_matvec_host(self._h, C.byref(ref), x_host.ctypes.data_as(C.c_void_p),
                                           y_host.ctypes.data_as(C.c_void_p), batch))
+
+
+def gather_arena_bytes(data_bytes: int, n_flags: int) -> int:
+    return int(lib().orome_cuda_gather_arena_bytes(data_bytes, n_flags))
 
 
 def tensor_ref(buffer: int, offset: int, fmt: int, out_dim: int, in_dim: int, variant: int = VARIANT_DEFAULT) -> TensorRef:

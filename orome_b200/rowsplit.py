@@ -34,3 +34,43 @@ def all_gather_rows(dist, buf, n: int, rank: int, world: int, group=None) -> Non
         return
     per = rows_per_rank(n, world)
     dist.all_gather_into_tensor(buf, buf[rank * per:(rank + 1) * per], group=group)
+
+
+class _DeviceMemory:
+    """Raw device memory exposed through __cuda_array_interface__ so torch can view it."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3, "strides": None}
+
+
+class PeerArena:
+    """Gather arena of the fused all-gather: one allocation per rank that every other rank maps (CUDA IPC).
+
+    Buffers are carved out at equal offsets on every rank, so a kernel that produces rows [lo, hi) of a vector can
+    store them straight into the same place of every peer's arena.  `dist` (any backend, gloo is enough) is only used
+    to hand the 64-byte IPC handles around."""
+
+    def __init__(self, ctx, dist, rank: int, world: int, data_bytes: int, n_flags: int):
+        import torch
+        from . import format as F
+        self.ctx, self.rank, self.world = ctx, rank, world
+        self.data_bytes = (data_bytes + 255) // 256 * 256
+        self.total = F.gather_arena_bytes(self.data_bytes, n_flags)
+        self.ptr, handle = ctx.peer_alloc(self.total)
+        handles = [None] * world
+        dist.all_gather_object(handles, handle)
+        self.ptrs = [self.ptr if r == rank else ctx.peer_open(handles[r]) for r in range(world)]
+        dist.barrier()
+        ctx.gather_setup(rank, world, self.ptrs, self.data_bytes, n_flags)
+        self._mem = torch.as_tensor(_DeviceMemory(self.ptr, self.data_bytes), device=f"cuda:{ctx.device}")
+        self._off = 0
+
+    def floats(self, n: int):
+        """A zeroed fp32 buffer of n elements inside the arena (same offset on every rank)."""
+        import torch
+        nbytes = (n * 4 + 255) // 256 * 256
+        if self._off + nbytes > self.data_bytes:
+            raise MemoryError("gather arena exhausted")
+        t = self._mem[self._off:self._off + n * 4].view(torch.float32)
+        self._off += nbytes
+        return t

@@ -1,0 +1,85 @@
+"""Row-split products with the fused peer all-gather on two GPUs: two chained matvecs whose
+intermediate vector only exists once both ranks have stored their slices into each other's arena."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from orome_b200 import rowsplit, synth
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, fmt, n, q):
+    import torch.distributed as dist
+    import oracle
+    from orome_b200 import format as F
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    ok, err = False, ""
+    try:
+        ctx = F.Context(rank)
+        W1 = synth.host_tensor(fmt, n, n, seed=71)
+        W2 = synth.host_tensor(fmt, n, n, seed=72)
+        x = synth.host_x(n, seed=73)
+        rb = synth.row_bytes(fmt, n)
+        lo, hi = rowsplit.shard_rows(n, rank, world)
+        npad = rowsplit.padded_rows(n, world)
+        arena = rowsplit.PeerArena(ctx, dist, rank, world, 2 * (npad * 4 + 256), 2)
+        y1, y2 = arena.floats(npad), arena.floats(npad)
+        w1 = torch.from_numpy(W1[lo * rb:hi * rb].copy()).cuda()
+        w2 = torch.from_numpy(W2[lo * rb:hi * rb].copy()).cuda()
+        xt = torch.from_numpy(x).cuda()
+        st = torch.cuda.current_stream().cuda_stream
+        r1 = F.tensor_ref(w1.data_ptr(), 0, fmt, hi - lo, n)
+        r2 = F.tensor_ref(w2.data_ptr(), 0, fmt, hi - lo, n)
+        for rep in range(3):                                  # several rounds: the counters must keep pairing up
+            ctx.gather_next(-1, 0)
+            ctx.matvec(r1, xt.data_ptr(), y1[lo:hi].data_ptr(), 1, 0, 0, st)
+            ctx.gather_next(0, 1)
+            ctx.matvec(r2, y1.data_ptr(), y2[lo:hi].data_ptr(), 1, 0, 0, st)
+            ctx.gather_wait(1, st)
+            torch.cuda.synchronize()
+            dist.barrier()
+        want1 = oracle.matvec_f64(fmt, W1, n, n, x)
+        want2 = oracle.matvec_f64(fmt, W2, n, n, want1.astype(np.float32))
+        got1, got2 = y1[:n].cpu().numpy(), y2[:n].cpu().numpy()
+        e1 = np.linalg.norm(got1 - want1) / np.linalg.norm(want1)
+        e2 = np.linalg.norm(got2 - want2) / np.linalg.norm(want2)
+        ok = bool(e1 <= 1e-4 and e2 <= 1e-4 and ctx.status() == 0)
+        err = f"e1={e1:.2e} e2={e2:.2e}"
+    except Exception as ex:   # report instead of leaving the peer waiting on a barrier
+        err = repr(ex)
+    q.put((rank, ok, err))
+    try:
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("fmt", [synth.Q8_0, synth.Q4_K])
+def test_fused_gather_two_gpus(fmt):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world, n = 2, 1024
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, fmt, n, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=240) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+    assert all(ok for _, ok, _ in results), results
