@@ -109,6 +109,7 @@ def cpu_layer_sample(set_name: str, reps: int, budget_s: float = 0.0):
     import oracle
     from orome_b200 import decode_set, synth
 
+    oracle.use_all_cores()
     cfg = decode_set.SETS[set_name]
     H, A, KV = cfg["hidden"], cfg["ffn"], cfg["kv"]
     shapes = dict(q=(H, H), k=(KV, H), v=(KV, H), o=(H, H), gate=(A, H), up=(A, H), down=(H, A))

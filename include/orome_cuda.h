@@ -142,7 +142,11 @@ int  orome_format_dispatch_matvec(orome_cuda_ctx *ctx, const OromeTensorRef *ref
 /* Batched form of the same product: y[b][r] = sum_c W[r][c] x[b][c] for
  * b < batch, x row stride ldx, y row stride ldy (in floats).  batch == 1 is the
  * decode matvec; larger batches are the prefill form, which the reference runs
- * as one matvec per token (main.m:745-747). */
+ * as one matvec per token (main.m:745-747).  Batches of 9 and more on Q8_0 / Q4_K /
+ * Q5_K tensors whose in_dim is a multiple of 256 run on the tensor cores (tcgen05) with
+ * weights and x rounded to fp16 and fp32 accumulation: rel-L2 of a few 1e-4 against an
+ * exact evaluation, the class of rounding the reference's own kernels apply to x
+ * (shaders.metal:1470).  Smaller batches keep fp32 activations (rel-L2 <= 1e-4). */
 int  orome_cuda_matvec(orome_cuda_ctx *ctx, const OromeTensorRef *ref,
                        const float *x_dev, float *y_dev, int batch, int ldx, int ldy, void *stream);
 
@@ -275,6 +279,7 @@ int  orome_cuda_matvec_host(orome_cuda_ctx *ctx, const OromeTensorRef *ref,
 #define OROME_OPT_PDL            5
 #define OROME_OPT_GRID_PER_SM    6
 #define OROME_OPT_PREFETCH_MB     7   /* cap on the L2 prefetch of orome_cuda_hint_next, MiB (0 = off) */
+#define OROME_OPT_TC_MIN_BATCH    8   /* batches from this size on use the tensor-core kernel (default 9) */
 int  orome_cuda_set_option(orome_cuda_ctx *ctx, int key, int value);
 int  orome_cuda_get_option(orome_cuda_ctx *ctx, int key, int *value);
 

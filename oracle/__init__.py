@@ -191,5 +191,14 @@ def moe_ffn_f64(gate, up, down, fmts, strides, x, hidden, inter, idx, w, layout=
     return out
 
 
+def use_all_cores() -> int:
+    """Make the OpenMP loops of both checkers use every host core (torchrun sets OMP_NUM_THREADS=1)."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().oracle_set_threads(n)
+    if ref() is not None:
+        ref().ref_set_threads(n)
+    return n
+
+
 def num_threads() -> int:
     return int(lib().oracle_num_threads())

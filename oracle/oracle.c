@@ -363,3 +363,13 @@ int oracle_num_threads(void)
     return 1;
 #endif
 }
+
+/* Launchers such as torchrun export OMP_NUM_THREADS=1; the timed CPU baseline asks for its thread count explicitly. */
+void oracle_set_threads(int n)
+{
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}

@@ -1,0 +1,306 @@
+// gemm_tc.cuh -- the batched (prefill) form on the 5th-generation tensor cores.
+//
+//   Y[b][r] = sum_c W[r][c] * X[b][c],   b < batch (16..128 after padding), W block-quantized.
+//
+// With tens of input vectors the product is a real contraction (about 2*batch flop per weight
+// byte), so the weights are dequantized once into fp16 tiles and multiplied with tcgen05.mma:
+//
+//   producer warp   1-D bulk async copies: 128 packed rows x one 256-weight chunk per stage, and the
+//                   matching pre-packed fp16 tile of X
+//   8 dequant warps packed stage -> fp16 A slabs of 128 rows x 64 k in the K-major 128-byte-swizzle
+//                   layout the tensor core reads (row = 128 bytes, 16-byte pieces XORed with row % 8)
+//   MMA warp        one thread issues 4 x tcgen05.mma (M128 x N x K16) per slab, accumulator in TMEM;
+//                   tcgen05.commit hands slabs and X tiles back
+//   epilogue        warps 0-3 read the accumulator with tcgen05.ld (lane = row) and store Y (or a
+//                   split-K partial)
+//
+// Operand precision: weights and x are rounded to fp16 once (the accumulator is fp32), the same
+// class of rounding the reference's kernels apply to x (shaders.metal:1470); measured rel-L2 against
+// the fp64 oracle is a few 1e-4.  X is packed to fp16 tiles by pack_x_f16_kernel beforehand, so no
+// CTA converts it again.  Every barrier wait is bounded (status code 4 on expiry).
+#pragma once
+#include "decode.cuh"
+#include "gemv_pipe.cuh"
+
+namespace orome {
+
+constexpr int TC_M = 128;            // rows per CTA tile
+constexpr int TC_KC = 256;           // weights per packed chunk (8 Q8_0 blocks / one K-quant superblock)
+constexpr int TC_SLAB_K = 64;        // k per A slab = one 128-byte swizzle row of fp16
+constexpr int TC_SLABS = 4;          // A slab ring (= slabs per chunk)
+constexpr int TC_PK_STAGES = 2;      // packed-weight stages
+constexpr int TC_MAX_N = 64;         // input vectors per launch (padded to a multiple of 16)
+constexpr int TC_B_STAGES = 2;       // X tile stages (one chunk each)
+constexpr int TC_DEQ_WARPS = 8;
+constexpr int TC_THREADS = (TC_DEQ_WARPS + 2) * 32;
+
+struct TcArgs {
+    const uint8_t *w;          // tensor
+    const __half *xp;          // packed X: [k_slab][npad rows][64] fp16, swizzled (pack_x_f16_kernel)
+    float *y;                  // Y [batch][ldy] when split == 1, else partials [split][batch][rows]
+    uint32_t rows, in_dim, row_bytes, chunk_bytes;   // chunk_bytes = packed bytes of 256 weights of one row
+    uint32_t batch, npad, ldy;
+    uint32_t split, chunks_per_split;
+    int layout;
+    int *status;
+};
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// K-major, 128-byte swizzle: 8-row groups are 1024 bytes apart (SBO), version 1 (sm_100), layout type 2.
+__device__ __forceinline__ uint64_t tc_desc_sw128(uint32_t saddr)
+{
+    return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+           ((uint64_t)2 << 61);
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+
+// Byte offset of 16-byte piece `c` (0..7) of row `r` inside a K-major SW128 tile.
+__device__ __forceinline__ uint32_t sw128_off(uint32_t r, uint32_t c) { return (r >> 3) * 1024u + (r & 7u) * 128u + ((c ^ (r & 7u)) << 4); }
+
+// X fp32 [batch][ldx] -> fp16 tiles [k_slab][npad][64] in the same swizzled layout; rows >= batch are zero.
+__global__ void pack_x_f16_kernel(const float *__restrict__ x, int batch, int ldx, uint32_t in_dim, uint32_t npad, __half *__restrict__ xp)
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint32_t slabs = in_dim / TC_SLAB_K;
+    const size_t total = (size_t)slabs * npad * 8;   // one thread per 16-byte piece
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t c = (uint32_t)(i & 7), n = (uint32_t)((i >> 3) % npad), ks = (uint32_t)(i / ((size_t)npad * 8));
+        __half2 h[4];
+        if ((int)n < batch) {
+            const float4 *src = reinterpret_cast<const float4 *>(x + (size_t)n * ldx + (size_t)ks * TC_SLAB_K + c * 8);
+            const float4 a = src[0], b = src[1];
+            h[0] = __floats2half2_rn(a.x, a.y); h[1] = __floats2half2_rn(a.z, a.w);
+            h[2] = __floats2half2_rn(b.x, b.y); h[3] = __floats2half2_rn(b.z, b.w);
+        } else {
+            h[0] = h[1] = h[2] = h[3] = __floats2half2_rn(0.f, 0.f);
+        }
+        uint8_t *dst = reinterpret_cast<uint8_t *>(xp) + (size_t)ks * npad * 128 + sw128_off(n, c);
+        *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(h);
+    }
+}
+
+// 8 consecutive weights of one row as fp16 -> one 16-byte piece.
+__device__ __forceinline__ uint32_t h2_bits(__half2 v) { return *reinterpret_cast<uint32_t *>(&v); }
+
+// Two byte lanes of `w` (selected by `sel`) -> fp16 pair (byte - bias) * scale + addend.  0x6400 | byte is the
+// fp16 number 1024 + byte exactly, so the bias comes off exactly before the one rounded multiply-add.
+__device__ __forceinline__ __half2 two_weights(uint32_t w, uint32_t sel, __half2 bias, __half2 scale, __half2 addend)
+{
+    const uint32_t bits = __byte_perm(w, 0x64646464u, sel);
+    return __hfma2(__hsub2(*reinterpret_cast<const __half2 *>(&bits), bias), scale, addend);
+}
+
+template <int FMT>
+__device__ __forceinline__ void dequant_piece(const uint8_t *pk_row, uint32_t kpiece, int layout, uint32_t (&out)[4])
+{
+    // kpiece: index of the 8-weight piece inside the 256-weight chunk (0..31)
+    if constexpr (FMT == FMT_Q8_0) {
+        const uint32_t blk = kpiece >> 2, j = kpiece & 3u;                 // block of 32, 8 quants at 2 + 8j
+        const uint32_t a = smem_u32(pk_row) + blk * 34u;
+        const float d = __half2float(__ushort_as_half((unsigned short)lds16<0>(a)));
+        const uint32_t qa = a + 2u + 8u * j;                               // 2-byte aligned
+        const uint32_t base = qa & ~3u, sel = (qa & 2u) ? 0x5432u : 0x3210u;
+        const uint32_t v0 = lds32<0>(base), v1 = lds32<4>(base), v2 = lds32<8>(base);
+        const uint32_t w0 = __byte_perm(v0, v1, sel) ^ 0x80808080u, w1 = __byte_perm(v1, v2, sel) ^ 0x80808080u;   // q + 128
+        const __half2 s = __float2half2_rn(d), bias = __float2half2_rn(1152.0f), zero = __float2half2_rn(0.0f);   // 1024 + 128
+        out[0] = h2_bits(two_weights(w0, 0x5140u, bias, s, zero)); out[1] = h2_bits(two_weights(w0, 0x7362u, bias, s, zero));
+        out[2] = h2_bits(two_weights(w1, 0x5140u, bias, s, zero)); out[3] = h2_bits(two_weights(w1, 0x7362u, bias, s, zero));
+    } else {
+        // Q4_K / Q5_K: one superblock per chunk; sub-block sub = kpiece / 4 holds weights 32*sub + 8*(kpiece % 4) ..
+        constexpr int QOFF = FMT == FMT_Q4_K ? 16 : 48;
+        const uint32_t sub = kpiece >> 2, l0 = (kpiece & 3u) * 8u;
+        uint32_t sc, mn;
+        kq_scale_min(pk_row + 4, layout, (int)sub, sc, mn);
+        const float d = half_bits_to_float(ld16(pk_row)), dmin = half_bits_to_float(ld16(pk_row + 2));
+        const float a = d * (float)sc, m = dmin * (float)mn;
+        const uint32_t qa = smem_u32(pk_row) + QOFF + 32u * (sub >> 1) + l0;        // 8 bytes, 8-byte aligned
+        uint32_t w0 = lds32<0>(qa), w1 = lds32<4>(qa);
+        if (sub & 1u) { w0 >>= 4; w1 >>= 4; }
+        w0 &= 0x0F0F0F0Fu; w1 &= 0x0F0F0F0Fu;
+        if constexpr (FMT == FMT_Q5_K) {
+            const uint32_t ha = smem_u32(pk_row) + 16u + l0;
+            const uint32_t h0 = lds32<0>(ha) >> sub, h1 = lds32<4>(ha) >> sub;
+            w0 |= (h0 & 0x01010101u) << 4; w1 |= (h1 & 0x01010101u) << 4;
+        }
+        const __half2 s = __float2half2_rn(a), bias = __float2half2_rn(1024.0f), add = __float2half2_rn(-m);   // q * (d sc) - dmin mn
+        out[0] = h2_bits(two_weights(w0, 0x5140u, bias, s, add)); out[1] = h2_bits(two_weights(w0, 0x7362u, bias, s, add));
+        out[2] = h2_bits(two_weights(w1, 0x5140u, bias, s, add)); out[3] = h2_bits(two_weights(w1, 0x7362u, bias, s, add));
+    }
+}
+
+template <int FMT>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ TcArgs a)
+{
+    extern __shared__ uint8_t smem_raw[];
+    // swizzled tiles must start on 1024-byte boundaries: align the base by hand (the launch adds 1 KiB of slack)
+    uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    // layout: [A slabs 4 x 16 KiB][X tiles 2 x npad*512][packed stages 2 x 128*chunk_bytes][barriers]
+    uint8_t *a_slabs = smem;
+    const uint32_t b_tile_bytes = a.npad * 128u * TC_SLABS;
+    uint8_t *b_tiles = a_slabs + TC_SLABS * 16384;
+    const uint32_t pk_stage_bytes = (TC_M * a.chunk_bytes + 127u) & ~127u;
+    uint8_t *pk = b_tiles + TC_B_STAGES * b_tile_bytes;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(pk + TC_PK_STAGES * pk_stage_bytes);
+    uint64_t *pk_full = bars, *pk_empty = bars + TC_PK_STAGES, *b_full = pk_empty + TC_PK_STAGES, *b_empty = b_full + TC_B_STAGES;
+    uint64_t *a_full = b_empty + TC_B_STAGES, *a_empty = a_full + TC_SLABS, *acc_done = a_empty + TC_SLABS;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_done + 1);
+    __shared__ volatile int s_abort;
+
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    const uint32_t tile = blockIdx.x / a.split, sp = blockIdx.x % a.split;
+    const uint32_t row0 = tile * TC_M, nrows = min((uint32_t)TC_M, a.rows - row0);
+    const uint32_t chunk0 = sp * a.chunks_per_split, nchunks = a.chunks_per_split;
+    uint32_t ncols = 32;
+    while (ncols < a.npad) ncols <<= 1;
+
+    if (tid == 0) {
+        s_abort = 0;
+        for (int s = 0; s < TC_PK_STAGES; ++s) { mbar_init(smem_u32(pk_full + s), 1); mbar_init(smem_u32(pk_empty + s), TC_DEQ_WARPS); }
+        for (int s = 0; s < TC_B_STAGES; ++s) { mbar_init(smem_u32(b_full + s), 1); mbar_init(smem_u32(b_empty + s), 1); }
+        for (int s = 0; s < TC_SLABS; ++s) { mbar_init(smem_u32(a_full + s), TC_DEQ_WARPS); mbar_init(smem_u32(a_empty + s), 1); }
+        mbar_init(smem_u32(acc_done), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 0) {   // TMEM allocation: one warp, power-of-two columns
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(ncols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_acc = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
+    pdl_launch_dependents();
+
+    auto wait = [&](uint64_t *bar, uint32_t parity) {
+        if (!s_abort && !mbar_wait_bounded(smem_u32(bar), parity)) { s_abort = 1; atomicExch(a.status, 4); }
+    };
+
+    if (warp == TC_DEQ_WARPS) {
+        // ---- producer warp: packed weights (independent of the previous kernel) and X tiles (after it) ----
+        for (uint32_t c = 0; c < nchunks && !s_abort; ++c) {
+            const uint32_t s = c % TC_PK_STAGES, k = c / TC_PK_STAGES;
+            if (lane == 0) {
+                if (k > 0) { wait(pk_empty + s, (k - 1) & 1u); asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+                mbar_expect_tx(smem_u32(pk_full + s), nrows * a.chunk_bytes);
+            }
+            __syncwarp();
+            const uint8_t *src = a.w + (size_t)row0 * a.row_bytes + (size_t)(chunk0 + c) * a.chunk_bytes;
+            uint8_t *dst = pk + (size_t)s * pk_stage_bytes;
+            for (uint32_t r = lane; r < nrows; r += 32)      // one 1-D bulk copy per row, spread over the warp
+                bulk_g2s(smem_u32(dst + (size_t)r * a.chunk_bytes), src + (size_t)r * a.row_bytes, a.chunk_bytes, smem_u32(pk_full + s));
+            if (lane == 0) {
+                if (c == 0) pdl_wait();   // the packed X is the previous kernel's output
+                const uint32_t sb = c % TC_B_STAGES, kb = c / TC_B_STAGES;
+                if (kb > 0) { wait(b_empty + sb, (kb - 1) & 1u); asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+                mbar_expect_tx(smem_u32(b_full + sb), b_tile_bytes);
+                bulk_g2s(smem_u32(b_tiles + (size_t)sb * b_tile_bytes),
+                         reinterpret_cast<const uint8_t *>(a.xp) + (size_t)(chunk0 + c) * b_tile_bytes, b_tile_bytes, smem_u32(b_full + sb));
+            }
+            __syncwarp();
+        }
+    } else if (warp == TC_DEQ_WARPS + 1) {
+        // ---- MMA issue: one thread ----
+        if (lane == 0) {
+            const uint32_t idesc = (1u << 4) | ((a.npad >> 3) << 17) | ((uint32_t)(TC_M >> 4) << 24);   // fp32 accumulate, fp16 x fp16, K-major both
+            uint32_t slab_i = 0;
+            for (uint32_t c = 0; c < nchunks && !s_abort; ++c) {
+                const uint32_t sb = c % TC_B_STAGES;
+                wait(b_full + sb, (c / TC_B_STAGES) & 1u);
+                for (uint32_t j = 0; j < TC_SLABS; ++j, ++slab_i) {
+                    const uint32_t sa = slab_i % TC_SLABS;
+                    wait(a_full + sa, (slab_i / TC_SLABS) & 1u);
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(a_slabs + sa * 16384), b_addr = smem_u32(b_tiles + (size_t)sb * b_tile_bytes + (size_t)j * a.npad * 128);
+#pragma unroll
+                    for (uint32_t k16 = 0; k16 < 4; ++k16)
+                        tc_mma_f16(tmem_acc, tc_desc_sw128(a_addr + k16 * 32), tc_desc_sw128(b_addr + k16 * 32), idesc, (slab_i | k16) ? 1u : 0u);
+                    tc_commit(smem_u32(a_empty + sa));     // slab free once these MMAs have read it
+                }
+                tc_commit(smem_u32(b_empty + sb));
+            }
+            tc_commit(smem_u32(acc_done));
+        }
+    } else {
+        // ---- dequant warps: packed stage -> fp16 slabs ----
+        const uint32_t dt = tid;                           // 0..255
+        uint32_t slab_i = 0;
+        for (uint32_t c = 0; c < nchunks; ++c) {
+            const uint32_t s = c % TC_PK_STAGES;
+            wait(pk_full + s, (c / TC_PK_STAGES) & 1u);
+            const uint8_t *stage = pk + (size_t)s * pk_stage_bytes;
+            for (uint32_t j = 0; j < TC_SLABS; ++j, ++slab_i) {
+                const uint32_t sa = slab_i % TC_SLABS, ka = slab_i / TC_SLABS;
+                if (ka > 0) wait(a_empty + sa, (ka - 1) & 1u);
+                tc_fence_after();
+                uint8_t *slab = a_slabs + sa * 16384;
+                // 128 rows x 8 pieces = 1024 pieces, 4 per thread; a thread keeps one piece column, rows 32 apart
+#pragma unroll
+                for (uint32_t it = 0; it < 4; ++it) {
+                    const uint32_t r = (dt >> 3) + it * 32, cpiece = dt & 7u;
+                    uint32_t v[4] = {0u, 0u, 0u, 0u};
+                    if (r < nrows) dequant_piece<FMT>(stage + (size_t)r * a.chunk_bytes, j * 8 + cpiece, a.layout, v);
+                    *reinterpret_cast<uint4 *>(slab + sw128_off(r, cpiece)) = make_uint4(v[0], v[1], v[2], v[3]);
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> visible to the tensor core
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(a_full + sa));
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(pk_empty + s));
+        }
+        // ---- epilogue: warps 0-3, lane = row ----
+        if (warp < 4) {
+            wait(acc_done, 0);
+            tc_fence_after();
+            const uint32_t r = warp * 32 + lane;
+            float *ybase = a.split == 1 ? a.y : a.y + (size_t)sp * a.batch * a.rows;
+            const uint32_t ld = a.split == 1 ? a.ldy : a.rows;
+            for (uint32_t n0 = 0; n0 < a.npad; n0 += 16) {
+                uint32_t v[16];
+                asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                             : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+                               "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                             : "r"(tmem_acc + ((warp * 32u) << 16) + n0));
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (r < nrows && !s_abort) {
+#pragma unroll
+                    for (uint32_t i = 0; i < 16; ++i)
+                        if (n0 + i < a.batch) ybase[(size_t)(n0 + i) * ld + row0 + r] = __uint_as_float(v[i]);
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(ncols) : "memory");
+    }
+}
+
+// Y[b][r] = sum over splits of partial[s][b][r]
+__global__ void splitk_reduce_kernel(const float *__restrict__ part, uint32_t split, uint32_t batch, uint32_t rows, float *__restrict__ y, uint32_t ldy)
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const size_t n = (size_t)batch * rows;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float acc = 0.0f;
+        for (uint32_t s = 0; s < split; ++s) acc += part[(size_t)s * n + i];
+        y[(i / rows) * ldy + (i % rows)] = acc;
+    }
+}
+
+}  // namespace orome

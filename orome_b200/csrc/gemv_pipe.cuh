@@ -866,11 +866,12 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
         }
     }
     if (EXT && a.npeers > 0) {
-        // every consumer thread's peer stores are fenced, then one thread counts this CTA in; the last CTA of the
-        // grid tells every peer that this rank's slice has landed
-        __threadfence_system();
+        // the barrier orders every consumer thread's peer stores before thread 0, whose system-scope fence then
+        // covers them all (one fence per CTA, not one per thread); thread 0 counts this CTA in and the last CTA of
+        // the grid tells every peer that this rank's slice has landed
         named_bar_sync(PIPE_BAR_CONSUMERS, (int)C);
         if (tid == 0) {
+            __threadfence_system();
             if (atomicAdd(a.pub_arrived, 1u) == gridDim.x - 1) {
                 *reinterpret_cast<volatile unsigned int *>(a.pub_arrived) = 0;
                 __threadfence_system();

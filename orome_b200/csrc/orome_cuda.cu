@@ -16,6 +16,7 @@
 #include "gemv_generic.cuh"
 #include "gemv_pipe.cuh"
 #include "moe.cuh"
+#include "gemm_tc.cuh"
 
 using namespace orome;
 
@@ -53,6 +54,10 @@ struct orome_cuda_ctx {
     // scratch for the unfused gate/up fallback
     float *gu_dev = nullptr;
     size_t gu_cap = 0;
+    // scratch of the tensor-core batched form: packed fp16 X and split-K partial sums
+    float *tc_xp = nullptr, *tc_part = nullptr;
+    size_t tc_xp_cap = 0, tc_part_cap = 0;
+    int tc_min_batch = 9;    // batches from this size on use the tensor-core kernel
 };
 
 static thread_local std::string g_err;
@@ -106,6 +111,8 @@ extern "C" void orome_cuda_ctx_destroy(orome_cuda_ctx *c)
     cudaFree(c->stage_y_dev);
     cudaFree(c->logits_dev);
     cudaFree(c->gu_dev);
+    cudaFree(c->tc_xp);
+    cudaFree(c->tc_part);
     cudaFree(c->trace_dev);
     cudaFree(c->g_local);
     cudaFreeHost(c->stage_x_host);
@@ -185,6 +192,9 @@ extern "C" int orome_cuda_set_option(orome_cuda_ctx *c, int key, int value)
     case OROME_OPT_GRID_PER_SM:
         if (value < 1 || value > 2) return fail(OROME_EINVAL, "GRID_PER_SM must be 1 or 2");
         c->grid_per_sm = value; return OROME_OK;
+    case OROME_OPT_TC_MIN_BATCH:
+        if (value < 2) return fail(OROME_EINVAL, "TC_MIN_BATCH must be at least 2");
+        c->tc_min_batch = value; return OROME_OK;
     case OROME_OPT_PREFETCH_MB:
         if (value < 0 || value > 96) return fail(OROME_EINVAL, "PREFETCH_MB must be 0..96");
         c->prefetch_mb = value; return OROME_OK;
@@ -203,6 +213,7 @@ extern "C" int orome_cuda_get_option(orome_cuda_ctx *c, int key, int *value)
     case OROME_OPT_PDL: *value = c->pdl; return OROME_OK;
     case OROME_OPT_GRID_PER_SM: *value = c->grid_per_sm; return OROME_OK;
     case OROME_OPT_PREFETCH_MB: *value = c->prefetch_mb; return OROME_OK;
+    case OROME_OPT_TC_MIN_BATCH: *value = c->tc_min_batch; return OROME_OK;
     }
     return fail(OROME_EINVAL, "get_option: unknown key %d", key);
 }
@@ -263,12 +274,21 @@ static int post_launch(orome_cuda_ctx *c, const char *what)
 // Launch with programmatic stream serialization, so the kernel's launch overlaps the tail of its predecessor
 // (the kernel itself starts with griddepcontrol.wait).
 template <typename... KArgs, typename... Args>
+static int launch_pdl_smem(orome_cuda_ctx *c, const char *what, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args);
+
+template <typename... KArgs, typename... Args>
 static int launch_pdl(orome_cuda_ctx *c, const char *what, void (*kern)(KArgs...), dim3 grid, dim3 block, cudaStream_t st, Args... args)
+{
+    return launch_pdl_smem(c, what, kern, grid, block, 0, st, args...);
+}
+
+template <typename... KArgs, typename... Args>
+static int launch_pdl_smem(orome_cuda_ctx *c, const char *what, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args)
 {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
-    cfg.dynamicSmemBytes = 0;
+    cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -678,6 +698,78 @@ extern "C" int orome_cuda_matvec_group(orome_cuda_ctx *c, const OromeTensorRef *
     return launch_pipe(c, fmt, p, 0, st);
 }
 
+// ---------------------------------------------------------------------------
+// batched form on the tensor cores
+// ---------------------------------------------------------------------------
+static bool tc_supported(int fmt, uint32_t in_dim) { return (fmt == FMT_Q8_0 || fmt == FMT_Q4_K || fmt == FMT_Q5_K) && in_dim % TC_KC == 0; }
+
+template <int FMT>
+static int launch_tc_fmt(orome_cuda_ctx *c, const TcArgs &a, int grid, size_t smem, cudaStream_t st)
+{
+    auto kern = gemm_tc_kernel<FMT>;
+    static bool configured[64] = {false};
+    if (!configured[c->device]) {
+        cudaFuncAttributes fa;
+        CU(cudaFuncGetAttributes(&fa, kern));
+        CU(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, c->smem_optin - (int)fa.sharedSizeBytes));
+        configured[c->device] = true;
+    }
+    return launch_pdl_smem(c, "gemm_tc", kern, dim3(grid), dim3(TC_THREADS), smem, st, a);
+}
+
+static int ensure(float **p, size_t *cap, size_t floats);
+
+// Y[b][r] for b < batch (<= TC_MAX_N per launch; larger batches are cut into slices that each re-read the weights).
+static int launch_tc(orome_cuda_ctx *c, int fmt, const uint8_t *data, uint32_t out_dim, uint32_t in_dim, int layout, const float *x,
+                     int batch, int ldx, float *y, int ldy, cudaStream_t st)
+{
+    const uint32_t chunk_bytes = fmt == FMT_Q8_0 ? 272u : fmt == FMT_Q4_K ? 144u : 176u;
+    const uint32_t chunks = in_dim / TC_KC, tiles = (out_dim + TC_M - 1) / TC_M;
+    // split K so that the grid fills the SMs in whole waves as far as the chunk count allows
+    uint32_t split = 1;
+    double best = 0.0;
+    for (uint32_t s = 1; s <= 8 && s <= chunks; ++s) {
+        if (chunks % s) continue;
+        const uint32_t ctas = tiles * s, waves = (ctas + c->sm_count - 1) / c->sm_count;
+        const double eff = (double)ctas / ((double)waves * c->sm_count) - 0.02 * (s - 1);   // splitting costs a reduction pass
+        if (eff > best) { best = eff; split = s; }
+    }
+    for (int b0 = 0; b0 < batch; b0 += TC_MAX_N) {
+        const int nb = std::min(batch - b0, TC_MAX_N);
+        const uint32_t npad = (uint32_t)(nb + 15) / 16 * 16;
+        int rc = ensure(&c->tc_xp, &c->tc_xp_cap, (size_t)in_dim * npad / 2 + 64);
+        if (rc) return rc;
+        if (split > 1) { rc = ensure(&c->tc_part, &c->tc_part_cap, (size_t)split * nb * out_dim); if (rc) return rc; }
+        __half *xp = reinterpret_cast<__half *>(c->tc_xp);
+        const size_t pieces = (size_t)(in_dim / TC_SLAB_K) * npad * 8;
+        rc = launch_pdl(c, "pack_x_f16", pack_x_f16_kernel, dim3((unsigned)std::min<size_t>((pieces + 255) / 256, 1184)), dim3(256), st,
+                        x + (size_t)b0 * ldx, nb, ldx, in_dim, npad, xp);
+        if (rc) return rc;
+        TcArgs a;
+        memset(&a, 0, sizeof a);
+        a.w = data; a.xp = xp; a.y = split == 1 ? y + (size_t)b0 * ldy : c->tc_part;
+        a.rows = out_dim; a.in_dim = in_dim; a.row_bytes = (uint32_t)row_bytes_of(fmt, in_dim); a.chunk_bytes = chunk_bytes;
+        a.batch = (uint32_t)nb; a.npad = npad; a.ldy = (uint32_t)ldy; a.split = split; a.chunks_per_split = chunks / split;
+        a.layout = layout; a.status = c->status_dev;
+        const size_t smem = 1024 + (size_t)TC_SLABS * 16384 + (size_t)TC_B_STAGES * npad * 128 * TC_SLABS +
+                            (size_t)TC_PK_STAGES * ((TC_M * chunk_bytes + 127) & ~127u) + 512;
+        const int grid = (int)(tiles * split);
+        switch (fmt) {
+        case FMT_Q8_0: rc = launch_tc_fmt<FMT_Q8_0>(c, a, grid, smem, st); break;
+        case FMT_Q4_K: rc = launch_tc_fmt<FMT_Q4_K>(c, a, grid, smem, st); break;
+        default: rc = launch_tc_fmt<FMT_Q5_K>(c, a, grid, smem, st); break;
+        }
+        if (rc) return rc;
+        if (split > 1) {
+            const size_t n = (size_t)nb * out_dim;
+            rc = launch_pdl(c, "splitk_reduce", splitk_reduce_kernel, dim3((unsigned)std::min<size_t>((n + 255) / 256, 1184)), dim3(256), st,
+                            (const float *)c->tc_part, split, (uint32_t)nb, out_dim, y + (size_t)b0 * ldy, (uint32_t)ldy);
+            if (rc) return rc;
+        }
+    }
+    return OROME_OK;
+}
+
 extern "C" int orome_cuda_matvec(orome_cuda_ctx *c, const OromeTensorRef *ref, const float *x_dev, float *y_dev, int batch,
                                  int ldx, int ldy, void *stream)
 {
@@ -695,6 +787,10 @@ extern "C" int orome_cuda_matvec(orome_cuda_ctx *c, const OromeTensorRef *ref, c
     int rc = check_ref("matvec", ref, &data);
     if (rc) return rc;
     CU(cudaSetDevice(c->device));
+    if (batch >= c->tc_min_batch && !c->force_generic && tc_supported((int)ref->format, ref->in_dim) && ldx % 4 == 0 &&
+        !(reinterpret_cast<uintptr_t>(x_dev) & 15))
+        return launch_tc(c, (int)ref->format, data, ref->out_dim, ref->in_dim, (int)ref->variant, x_dev, batch, ldx, y_dev, ldy,
+                         static_cast<cudaStream_t>(stream));
     return launch_generic(c, (int)ref->format, data, ref->out_dim, ref->in_dim, (int)ref->variant, x_dev, batch, ldx, y_dev, ldy,
                           static_cast<cudaStream_t>(stream));
 }

@@ -12,6 +12,7 @@ from orome_b200 import synth
 pytestmark = pytest.mark.gpu
 
 REL_L2_TOL = 1e-4          # the tolerance the path states for fp32 accumulation
+TC_REL_L2_TOL = 1e-3       # tensor-core batched form: weights and x rounded to fp16 (the reference stages x as fp16 too)
 GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "decode_golden.npz"))
 FMTS = {"Q8_0": synth.Q8_0, "Q4_K": synth.Q4_K, "Q5_K": synth.Q5_K, "Q6_K": synth.Q6_K}
 QUANT = list(FMTS.values())
@@ -193,7 +194,35 @@ def test_batched_matvec(env, fmt, batch):
     x = synth.host_x(in_dim, batch, seed=3)
     y = gpu_matvec(env, fmt, data, out_dim, in_dim, x)
     want = oracle.matvec_f64(fmt, data, out_dim, in_dim, x)
-    assert y.shape == want.shape and rel_l2(y, want) <= REL_L2_TOL
+    on_tensor_cores = batch >= 9 and fmt in (synth.Q8_0, synth.Q4_K, synth.Q5_K)
+    assert y.shape == want.shape and rel_l2(y, want) <= (TC_REL_L2_TOL if on_tensor_cores else REL_L2_TOL)
+
+
+@pytest.mark.parametrize("fmt", [synth.Q8_0, synth.Q4_K, synth.Q5_K])
+@pytest.mark.parametrize("shape", [(300, 4096, 64), (128, 1024, 33), (1000, 2048, 16), (257, 12288, 48), (96, 512, 100)])
+def test_prefill_gemm_on_tensor_cores(env, fmt, shape):
+    """Ragged row tiles, split-K, padded and multi-slice batches; both scale layouts for the K-quants."""
+    torch, F, ctx = env
+    out_dim, in_dim, batch = shape
+    data = synth.host_tensor(fmt, out_dim, in_dim, seed=synth.seed_for("tc", fmt, *shape))
+    x = synth.host_x(in_dim, batch, seed=17)
+    for variant in ((0, 1) if fmt != synth.Q8_0 else (0,)):
+        before = ctx.launch_count
+        y = gpu_matvec(env, fmt, data, out_dim, in_dim, x, variant)
+        assert ctx.launch_count - before >= 2                       # pack + tensor-core kernel (+ split-K reduction)
+        want = oracle.matvec_f64(fmt, data, out_dim, in_dim, x, layout=variant)
+        err = rel_l2(y, want)
+        assert err <= TC_REL_L2_TOL, (fmt, shape, variant, err)
+        # every column individually, so that a misplaced batch column cannot hide in the norm
+        col = np.linalg.norm(y - want, axis=1) / np.linalg.norm(want, axis=1)
+        assert col.max() <= 3 * TC_REL_L2_TOL, (fmt, shape, variant, col.max())
+    # the fp32-activation kernel on the same inputs stays within the tight bound
+    ctx.set_option(F.OPT_TC_MIN_BATCH, 1 << 20)
+    try:
+        y32 = gpu_matvec(env, fmt, data, out_dim, in_dim, x[:4], 0)
+    finally:
+        ctx.set_option(F.OPT_TC_MIN_BATCH, 9)
+    assert rel_l2(y32, oracle.matvec_f64(fmt, data, out_dim, in_dim, x[:4])) <= REL_L2_TOL
 
 
 def test_format_dispatch_matvec_offsets_and_absent_tensor(env):
