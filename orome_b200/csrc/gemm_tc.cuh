@@ -5,9 +5,9 @@
 // With tens of input vectors the product is a real contraction (about 2*batch flop per weight
 // byte), so the weights are dequantized once into fp16 tiles and multiplied with tcgen05.mma:
 //
-//   producer warp   1-D bulk async copies: 128 packed rows x one 256-weight chunk per stage, and the
-//                   matching pre-packed fp16 tile of X
-//   8 dequant warps packed stage -> fp16 A slabs of 128 rows x 64 k in the K-major 128-byte-swizzle
+//   producer warp   one 2-D TMA tensor copy per stage (128 packed rows x one 256-weight chunk; rows past the
+//                   tensor are zero-filled) and one bulk copy of the matching pre-packed fp16 tile of X
+//   16 dequant warps packed stage -> fp16 A slabs (two groups of 8 warps take alternate slabs) of 128 rows x 64 k in the K-major 128-byte-swizzle
 //                   layout the tensor core reads (row = 128 bytes, 16-byte pieces XORed with row % 8)
 //   MMA warp        one thread issues 4 x tcgen05.mma (M128 x N x K16) per slab, accumulator in TMEM;
 //                   tcgen05.commit hands slabs and X tiles back
@@ -19,6 +19,8 @@
 // the fp64 oracle is a few 1e-4.  X is packed to fp16 tiles by pack_x_f16_kernel beforehand, so no
 // CTA converts it again.  Every barrier wait is bounded (status code 4 on expiry).
 #pragma once
+#include <cuda.h>
+
 #include "decode.cuh"
 #include "gemv_pipe.cuh"
 
@@ -31,10 +33,12 @@ constexpr int TC_SLABS = 4;          // A slab ring (= slabs per chunk)
 constexpr int TC_PK_STAGES = 2;      // packed-weight stages
 constexpr int TC_MAX_N = 64;         // input vectors per launch (padded to a multiple of 16)
 constexpr int TC_B_STAGES = 2;       // X tile stages (one chunk each)
-constexpr int TC_DEQ_WARPS = 8;
+constexpr int TC_DEQ_WARPS = 16;     // two groups of 8 warps take alternate slabs
+constexpr int TC_SLAB_WARPS = 8;     // warps that fill one slab
 constexpr int TC_THREADS = (TC_DEQ_WARPS + 2) * 32;
 
 struct TcArgs {
+    alignas(64) CUtensorMap wmap;   // the tensor as a 2-D array of 32-bit words [rows][row_bytes / 4], box = 128 rows x one chunk
     const uint8_t *w;          // tensor
     const __half *xp;          // packed X: [k_slab][npad rows][64] fp16, swizzled (pack_x_f16_kernel)
     float *y;                  // Y [batch][ldy] when split == 1, else partials [split][batch][rows]
@@ -101,41 +105,55 @@ __device__ __forceinline__ __half2 two_weights(uint32_t w, uint32_t sel, __half2
     return __hfma2(__hsub2(*reinterpret_cast<const __half2 *>(&bits), bias), scale, addend);
 }
 
+// 32 consecutive weights of one row (a Q8_0 block / a K-quant sub-block) -> four 16-byte fp16 pieces.
+// `g32` is the index of the 32-group inside the 256-weight chunk (0..7).
 template <int FMT>
-__device__ __forceinline__ void dequant_piece(const uint8_t *pk_row, uint32_t kpiece, int layout, uint32_t (&out)[4])
+__device__ __forceinline__ void dequant_group32(const uint8_t *pk_row, uint32_t g32, int layout, uint4 (&out)[4])
 {
-    // kpiece: index of the 8-weight piece inside the 256-weight chunk (0..31)
+    uint32_t w[8];          // the 32 quants as bytes, in element order
+    __half2 scale, bias, addend;
     if constexpr (FMT == FMT_Q8_0) {
-        const uint32_t blk = kpiece >> 2, j = kpiece & 3u;                 // block of 32, 8 quants at 2 + 8j
-        const uint32_t a = smem_u32(pk_row) + blk * 34u;
-        const float d = __half2float(__ushort_as_half((unsigned short)lds16<0>(a)));
-        const uint32_t qa = a + 2u + 8u * j;                               // 2-byte aligned
-        const uint32_t base = qa & ~3u, sel = (qa & 2u) ? 0x5432u : 0x3210u;
-        const uint32_t v0 = lds32<0>(base), v1 = lds32<4>(base), v2 = lds32<8>(base);
-        const uint32_t w0 = __byte_perm(v0, v1, sel) ^ 0x80808080u, w1 = __byte_perm(v1, v2, sel) ^ 0x80808080u;   // q + 128
-        const __half2 s = __float2half2_rn(d), bias = __float2half2_rn(1152.0f), zero = __float2half2_rn(0.0f);   // 1024 + 128
-        out[0] = h2_bits(two_weights(w0, 0x5140u, bias, s, zero)); out[1] = h2_bits(two_weights(w0, 0x7362u, bias, s, zero));
-        out[2] = h2_bits(two_weights(w1, 0x5140u, bias, s, zero)); out[3] = h2_bits(two_weights(w1, 0x7362u, bias, s, zero));
+        const uint32_t a = smem_u32(pk_row) + g32 * 34u;                   // 2-byte aligned block
+        const uint32_t base = a & ~3u;
+        uint32_t v[10];
+        v[0] = lds32<0>(base); v[1] = lds32<4>(base); v[2] = lds32<8>(base); v[3] = lds32<12>(base); v[4] = lds32<16>(base);
+        v[5] = lds32<20>(base); v[6] = lds32<24>(base); v[7] = lds32<28>(base); v[8] = lds32<32>(base); v[9] = lds32<36>(base);
+        const bool odd = (a & 2u) != 0;                                    // block starts in the upper half of v[0]
+        const uint32_t dbits = odd ? (v[0] >> 16) : (v[0] & 0xffffu);
+        const uint32_t sel = odd ? 0x3210u : 0x5432u;                      // quants start 2 bytes after the scale
+#pragma unroll
+        for (int i = 0; i < 8; ++i) w[i] = (odd ? __byte_perm(v[i + 1], v[i + 2], sel) : __byte_perm(v[i], v[i + 1], sel)) ^ 0x80808080u;
+        const float d = __half2float(__ushort_as_half((unsigned short)dbits));
+        scale = __float2half2_rn(d); bias = __float2half2_rn(1152.0f); addend = __float2half2_rn(0.0f);   // bytes are q + 128
     } else {
-        // Q4_K / Q5_K: one superblock per chunk; sub-block sub = kpiece / 4 holds weights 32*sub + 8*(kpiece % 4) ..
         constexpr int QOFF = FMT == FMT_Q4_K ? 16 : 48;
-        const uint32_t sub = kpiece >> 2, l0 = (kpiece & 3u) * 8u;
-        uint32_t sc, mn;
-        kq_scale_min(pk_row + 4, layout, (int)sub, sc, mn);
-        const float d = half_bits_to_float(ld16(pk_row)), dmin = half_bits_to_float(ld16(pk_row + 2));
-        const float a = d * (float)sc, m = dmin * (float)mn;
-        const uint32_t qa = smem_u32(pk_row) + QOFF + 32u * (sub >> 1) + l0;        // 8 bytes, 8-byte aligned
-        uint32_t w0 = lds32<0>(qa), w1 = lds32<4>(qa);
-        if (sub & 1u) { w0 >>= 4; w1 >>= 4; }
-        w0 &= 0x0F0F0F0Fu; w1 &= 0x0F0F0F0Fu;
+        const uint32_t sb = smem_u32(pk_row);
+        const uint4 h = lds128<0>(sb);
+        uint32_t scA, scB, mnA, mnB;
+        pair_scales(h.y, h.z, h.w, layout, (int)(g32 >> 1), scA, scB, mnA, mnB);
+        const uint32_t sc = (g32 & 1u) ? scB : scA, mn = (g32 & 1u) ? mnB : mnA;
+        const float d = __half2float(__ushort_as_half((unsigned short)(h.x & 0xffffu)));
+        const float dmin = __half2float(__ushort_as_half((unsigned short)(h.x >> 16)));
+        const uint32_t qa = sb + 32u * (g32 >> 1);
+        const uint4 q0 = lds128<QOFF>(qa), q1 = lds128<QOFF + 16>(qa);
+        w[0] = q0.x; w[1] = q0.y; w[2] = q0.z; w[3] = q0.w; w[4] = q1.x; w[5] = q1.y; w[6] = q1.z; w[7] = q1.w;
+        const uint32_t shift = (g32 & 1u) * 4u;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) w[i] = (w[i] >> shift) & 0x0F0F0F0Fu;
         if constexpr (FMT == FMT_Q5_K) {
-            const uint32_t ha = smem_u32(pk_row) + 16u + l0;
-            const uint32_t h0 = lds32<0>(ha) >> sub, h1 = lds32<4>(ha) >> sub;
-            w0 |= (h0 & 0x01010101u) << 4; w1 |= (h1 & 0x01010101u) << 4;
+            const uint4 h0 = lds128<16>(sb), h1 = lds128<32>(sb);
+            const uint32_t hb[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) w[i] |= ((hb[i] >> g32) & 0x01010101u) << 4;
         }
-        const __half2 s = __float2half2_rn(a), bias = __float2half2_rn(1024.0f), add = __float2half2_rn(-m);   // q * (d sc) - dmin mn
-        out[0] = h2_bits(two_weights(w0, 0x5140u, bias, s, add)); out[1] = h2_bits(two_weights(w0, 0x7362u, bias, s, add));
-        out[2] = h2_bits(two_weights(w1, 0x5140u, bias, s, add)); out[3] = h2_bits(two_weights(w1, 0x7362u, bias, s, add));
+        scale = __float2half2_rn(d * (float)sc); bias = __float2half2_rn(1024.0f); addend = __float2half2_rn(-(dmin * (float)mn));
+    }
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+        out[p].x = h2_bits(two_weights(w[2 * p], 0x5140u, bias, scale, addend));
+        out[p].y = h2_bits(two_weights(w[2 * p], 0x7362u, bias, scale, addend));
+        out[p].z = h2_bits(two_weights(w[2 * p + 1], 0x5140u, bias, scale, addend));
+        out[p].w = h2_bits(two_weights(w[2 * p + 1], 0x7362u, bias, scale, addend));
     }
 }
 
@@ -169,7 +187,7 @@ gemm_tc_kernel(const __grid_constant__ TcArgs a)
         s_abort = 0;
         for (int s = 0; s < TC_PK_STAGES; ++s) { mbar_init(smem_u32(pk_full + s), 1); mbar_init(smem_u32(pk_empty + s), TC_DEQ_WARPS); }
         for (int s = 0; s < TC_B_STAGES; ++s) { mbar_init(smem_u32(b_full + s), 1); mbar_init(smem_u32(b_empty + s), 1); }
-        for (int s = 0; s < TC_SLABS; ++s) { mbar_init(smem_u32(a_full + s), TC_DEQ_WARPS); mbar_init(smem_u32(a_empty + s), 1); }
+        for (int s = 0; s < TC_SLABS; ++s) { mbar_init(smem_u32(a_full + s), TC_SLAB_WARPS); mbar_init(smem_u32(a_empty + s), 1); }
         mbar_init(smem_u32(acc_done), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -189,19 +207,17 @@ gemm_tc_kernel(const __grid_constant__ TcArgs a)
     };
 
     if (warp == TC_DEQ_WARPS) {
-        // ---- producer warp: packed weights (independent of the previous kernel) and X tiles (after it) ----
-        for (uint32_t c = 0; c < nchunks && !s_abort; ++c) {
-            const uint32_t s = c % TC_PK_STAGES, k = c / TC_PK_STAGES;
-            if (lane == 0) {
+        // ---- producer: packed weights (independent of the previous kernel) and X tiles (after it) ----
+        if (lane == 0) {
+            const uint32_t words = a.chunk_bytes / 4;
+            for (uint32_t c = 0; c < nchunks && !s_abort; ++c) {
+                const uint32_t s = c % TC_PK_STAGES, k = c / TC_PK_STAGES;
                 if (k > 0) { wait(pk_empty + s, (k - 1) & 1u); asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-                mbar_expect_tx(smem_u32(pk_full + s), nrows * a.chunk_bytes);
-            }
-            __syncwarp();
-            const uint8_t *src = a.w + (size_t)row0 * a.row_bytes + (size_t)(chunk0 + c) * a.chunk_bytes;
-            uint8_t *dst = pk + (size_t)s * pk_stage_bytes;
-            for (uint32_t r = lane; r < nrows; r += 32)      // one 1-D bulk copy per row, spread over the warp
-                bulk_g2s(smem_u32(dst + (size_t)r * a.chunk_bytes), src + (size_t)r * a.row_bytes, a.chunk_bytes, smem_u32(pk_full + s));
-            if (lane == 0) {
+                mbar_expect_tx(smem_u32(pk_full + s), TC_M * a.chunk_bytes);   // the box is always full: out-of-range rows arrive as zeros
+                // x coordinate in 32-bit words: (chunk index) * chunk_bytes / 4, a multiple of 16 bytes for every format
+                asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                             ::"r"(smem_u32(pk + (size_t)s * pk_stage_bytes)), "l"(&a.wmap), "r"((chunk0 + c) * words), "r"(row0),
+                               "r"(smem_u32(pk_full + s)) : "memory");
                 if (c == 0) pdl_wait();   // the packed X is the previous kernel's output
                 const uint32_t sb = c % TC_B_STAGES, kb = c / TC_B_STAGES;
                 if (kb > 0) { wait(b_empty + sb, (kb - 1) & 1u); asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -209,7 +225,6 @@ gemm_tc_kernel(const __grid_constant__ TcArgs a)
                 bulk_g2s(smem_u32(b_tiles + (size_t)sb * b_tile_bytes),
                          reinterpret_cast<const uint8_t *>(a.xp) + (size_t)(chunk0 + c) * b_tile_bytes, b_tile_bytes, smem_u32(b_full + sb));
             }
-            __syncwarp();
         }
     } else if (warp == TC_DEQ_WARPS + 1) {
         // ---- MMA issue: one thread ----
@@ -235,24 +250,25 @@ gemm_tc_kernel(const __grid_constant__ TcArgs a)
         }
     } else {
         // ---- dequant warps: packed stage -> fp16 slabs ----
-        const uint32_t dt = tid;                           // 0..255
+        const uint32_t dt = tid & 255u, grp = warp / TC_SLAB_WARPS;   // group 0 fills even slabs, group 1 odd slabs
         uint32_t slab_i = 0;
         for (uint32_t c = 0; c < nchunks; ++c) {
             const uint32_t s = c % TC_PK_STAGES;
             wait(pk_full + s, (c / TC_PK_STAGES) & 1u);
             const uint8_t *stage = pk + (size_t)s * pk_stage_bytes;
             for (uint32_t j = 0; j < TC_SLABS; ++j, ++slab_i) {
+                if ((slab_i & 1u) != grp) continue;
                 const uint32_t sa = slab_i % TC_SLABS, ka = slab_i / TC_SLABS;
                 if (ka > 0) wait(a_empty + sa, (ka - 1) & 1u);
                 tc_fence_after();
                 uint8_t *slab = a_slabs + sa * 16384;
-                // 128 rows x 8 pieces = 1024 pieces, 4 per thread; a thread keeps one piece column, rows 32 apart
+                // a slab is 128 rows x two 32-weight groups: one (row, group) per thread, four 16-byte pieces each
+                {
+                    const uint32_t r = dt >> 1, half = dt & 1u;
+                    uint4 v[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+                    if (r < nrows) dequant_group32<FMT>(stage + (size_t)r * a.chunk_bytes, j * 2 + half, a.layout, v);
 #pragma unroll
-                for (uint32_t it = 0; it < 4; ++it) {
-                    const uint32_t r = (dt >> 3) + it * 32, cpiece = dt & 7u;
-                    uint32_t v[4] = {0u, 0u, 0u, 0u};
-                    if (r < nrows) dequant_piece<FMT>(stage + (size_t)r * a.chunk_bytes, j * 8 + cpiece, a.layout, v);
-                    *reinterpret_cast<uint4 *>(slab + sw128_off(r, cpiece)) = make_uint4(v[0], v[1], v[2], v[3]);
+                    for (uint32_t p = 0; p < 4; ++p) *reinterpret_cast<uint4 *>(slab + sw128_off(r, half * 4 + p)) = v[p];
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> visible to the tensor core
                 __syncwarp();

@@ -719,6 +719,22 @@ static int launch_tc_fmt(orome_cuda_ctx *c, const TcArgs &a, int grid, size_t sm
 
 static int ensure(float **p, size_t *cap, size_t floats);
 
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda)
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
 // Y[b][r] for b < batch (<= TC_MAX_N per launch; larger batches are cut into slices that each re-read the weights).
 static int launch_tc(orome_cuda_ctx *c, int fmt, const uint8_t *data, uint32_t out_dim, uint32_t in_dim, int layout, const float *x,
                      int batch, int ldx, float *y, int ldy, cudaStream_t st)
@@ -731,7 +747,7 @@ static int launch_tc(orome_cuda_ctx *c, int fmt, const uint8_t *data, uint32_t o
     for (uint32_t s = 1; s <= 8 && s <= chunks; ++s) {
         if (chunks % s) continue;
         const uint32_t ctas = tiles * s, waves = (ctas + c->sm_count - 1) / c->sm_count;
-        const double eff = (double)ctas / ((double)waves * c->sm_count) - 0.02 * (s - 1);   // splitting costs a reduction pass
+        const double eff = (double)ctas / ((double)waves * c->sm_count) - 0.02 * (s - 1) - 0.08 * (waves - 1);   // a split costs a reduction pass, a wave its prologue
         if (eff > best) { best = eff; split = s; }
     }
     for (int b0 = 0; b0 < batch; b0 += TC_MAX_N) {
@@ -747,6 +763,17 @@ static int launch_tc(orome_cuda_ctx *c, int fmt, const uint8_t *data, uint32_t o
         if (rc) return rc;
         TcArgs a;
         memset(&a, 0, sizeof a);
+        {
+            EncodeTiledFn enc = encode_tiled_fn();
+            if (!enc) return fail(OROME_ECUDA, "gemm_tc: cuTensorMapEncodeTiled is not available");
+            const cuuint64_t dims[2] = {(cuuint64_t)row_bytes_of(fmt, in_dim) / 4, out_dim};
+            const cuuint64_t strides[1] = {(cuuint64_t)row_bytes_of(fmt, in_dim)};
+            const cuuint32_t box[2] = {chunk_bytes / 4, (cuuint32_t)TC_M}, estr[2] = {1, 1};
+            CUresult r = enc(&a.wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint8_t *>(data), dims, strides, box, estr,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return fail(OROME_ECUDA, "gemm_tc: cuTensorMapEncodeTiled failed (%d)", (int)r);
+        }
         a.w = data; a.xp = xp; a.y = split == 1 ? y + (size_t)b0 * ldy : c->tc_part;
         a.rows = out_dim; a.in_dim = in_dim; a.row_bytes = (uint32_t)row_bytes_of(fmt, in_dim); a.chunk_bytes = chunk_bytes;
         a.batch = (uint32_t)nb; a.npad = npad; a.ldy = (uint32_t)ldy; a.split = split; a.chunks_per_split = chunks / split;
