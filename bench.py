@@ -281,6 +281,85 @@ class Stepper:
             self.issue(self.torch.cuda.current_stream().cuda_stream)
 
 
+def kernel_extras(torch, F, ctx, peak):
+    """Short per-kernel passes on the other benchmark configurations (rank 0, one GPU): absolute GB/s of the
+    algorithmic bytes and the fraction of the measured HBM peak, back-to-back launches over distinct weight copies."""
+    from orome_b200 import synth
+    dev = torch.device("cuda", ctx.device)
+    st = torch.cuda.current_stream().cuda_stream
+    out = {}
+
+    def timed(fn, n):
+        fn()
+        torch.cuda.synchronize()
+        best = float("inf")
+        for _ in range(3):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); fn(); e1.record(); torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1) / n)
+        return best * 1e-3
+
+    def gemv(name, fmt, od, idim, copies, batch=1, variant=0):
+        tb = (synth.tensor_bytes(fmt, od, idim) + 255) // 256 * 256
+        buf = torch.empty(tb * copies, dtype=torch.uint8, device=dev)
+        for i in range(copies):
+            synth.device_fill(buf[i * tb:(i + 1) * tb], fmt, od, idim, seed=synth.seed_for("extras", name, i))
+        x = torch.randn(batch, idim, device=dev)
+        y = torch.empty(batch, od, device=dev)
+        refs = [F.tensor_ref(buf.data_ptr(), i * tb, fmt, od, idim, variant) for i in range(copies)]
+
+        def go():
+            for i, r in enumerate(refs):
+                if batch == 1:
+                    ctx.hint_next(refs[(i + 1) % copies])
+                ctx.matvec(r, x.data_ptr(), y.data_ptr(), batch, idim, od, st)
+        t = timed(go, copies)
+        nbytes = synth.tensor_bytes(fmt, od, idim) + 4 * batch * (idim + od)
+        out[name] = {"us": round(t * 1e6, 2), "gbs": round(nbytes / t / 1e9, 1), "frac_of_measured_hbm": round(nbytes / t / 1e9 / peak, 3),
+                     "bytes": nbytes}
+        if batch > 1:
+            out[name]["tflops"] = round(2.0 * od * idim * batch / t / 1e12, 1)
+
+    gemv("q8_0_4096x4096_b1", synth.Q8_0, 4096, 4096, 24)
+    gemv("q4_k_12288x4096_b1", synth.Q4_K, 12288, 4096, 12)
+    gemv("q4_k_4096x12288_b1", synth.Q4_K, 4096, 12288, 12)
+    gemv("q4_k_12288x4096_b64_tcgen05", synth.Q4_K, 12288, 4096, 6, batch=64)
+    gemv("q4_k_4096x12288_b64_tcgen05", synth.Q4_K, 4096, 12288, 6, batch=64)
+    gemv("q5_k_12288x4096_b1", synth.Q5_K, 12288, 4096, 10)
+    gemv("q6_k_5120x17408_b1", synth.Q6_K, 5120, 17408, 6)
+    gemv("q6_k_lm_head_151936x5120_b1", synth.Q6_K, 151936, 5120, 2)
+    gemv("q8_0_lm_head_151936x4096_b1", synth.Q8_0, 151936, 4096, 2)
+
+    # MoE layer, one token: fp32 router 128 x 2048, top-8, gate/up Q4_K 768 x 2048, down Q5_K 2048 x 768 (6 distinct layers)
+    H, M, E, K, NL = 2048, 768, 128, 8, 6
+    sg, sd = synth.tensor_bytes(synth.Q4_K, M, H), synth.tensor_bytes(synth.Q5_K, H, M)
+    layers = []
+    for l in range(NL):
+        buf = torch.empty(E * (2 * sg + sd), dtype=torch.uint8, device=dev)
+        synth.device_fill(buf[:E * sg], synth.Q4_K, E * M, H, seed=3 * l)
+        synth.device_fill(buf[E * sg:2 * E * sg], synth.Q4_K, E * M, H, seed=3 * l + 1)
+        synth.device_fill(buf[2 * E * sg:], synth.Q5_K, E * H, M, seed=3 * l + 2)
+        rw = (torch.randn(E, H, device=dev) / (H ** 0.5)).contiguous()
+        layers.append((buf, rw, F.ExpertLayerRef(buf.data_ptr(), F.ExpertProjRef(0, sg, synth.Q4_K), F.ExpertProjRef(E * sg, sg, synth.Q4_K),
+                                                 F.ExpertProjRef(2 * E * sg, sd, synth.Q5_K)), F.tensor_ref(rw.data_ptr(), 0, synth.F32, E, H)))
+    x = torch.randn(1, H, device=dev)
+    idx = torch.zeros(1, 8, dtype=torch.int32, device=dev)
+    w = torch.zeros(1, 8, device=dev)
+    act = torch.empty(K, M, device=dev)
+    o = torch.empty(H, device=dev)
+    lg = torch.empty(E, device=dev)
+
+    def moe():
+        for buf, rw, layer, rref in layers:
+            ctx.moe_route(rref, x.data_ptr(), 1, H, K, idx.data_ptr(), w.data_ptr(), lg.data_ptr(), st)
+            ctx.moe_ffn(layer, 0, x.data_ptr(), 1, H, idx.data_ptr(), w.data_ptr(), K, H, M, act.data_ptr(), o.data_ptr(), H, st)
+    t = timed(moe, NL)
+    nbytes = K * (2 * sg + sd) + E * H * 4
+    out["moe_layer_top8_of_128_t1"] = {"us": round(t * 1e6, 2), "gbs": round(nbytes / t / 1e9, 1),
+                                       "frac_of_measured_hbm": round(nbytes / t / 1e9 / peak, 3), "bytes": nbytes, "launches": 4}
+    return out
+
+
 def run_ours(args):
     import numpy as np
     import torch
@@ -436,6 +515,10 @@ def run_ours(args):
     }
     if cpu is not None:
         line["cpu_baseline"] = cpu
+    if world == 1 and args.extras:
+        del st, ds
+        torch.cuda.empty_cache()
+        line["kernels"] = kernel_extras(torch, F, ctx, peak)
     print(json.dumps(line), flush=True)
     leave()
 
@@ -452,6 +535,7 @@ def main():
     ap.add_argument("--graph", dest="graph", action="store_true", default=True)
     ap.add_argument("--no-graph", dest="graph", action="store_false")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--extras", action="store_true", help="also time the other benchmark configurations kernel by kernel (adds ~20 s)")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="N > 1: complete y by peer stores from the kernel epilogue (fused) or by an NCCL all-gather per product")
     ap.add_argument("--prefetch-mb", type=int, default=-1, help="cap of the next-tensor L2 prefetch in MiB (0 = off, -1 = library default)")

@@ -602,6 +602,13 @@ __device__ __forceinline__ bool next_tile(const PipeArgs &a, PipeWalk &w, PipeTi
         return true;
     } else {
         if (w.cur >= w.hi) return false;
+        if (a.nseg == 1) {   // one tensor: no segment search, no segment clipping
+            uint32_t n = w.hi - w.cur;
+            if (n > cap) n = cap;
+            t.seg = 0; t.row0 = w.cur; t.n = n;
+            w.cur += n;
+            return true;
+        }
         int s = w.seg;
         while (s + 1 < a.nseg && w.cur >= a.seg[s + 1].vstart) ++s;
         w.seg = s;
@@ -696,10 +703,9 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
             if constexpr (EXT) { if (a.seg_expert) pdl_wait(); }   // the expert indices are the previous kernel's output
             PipeWalk w;
             walk_init<COMBINE>(a, w);
-            uint32_t i = 0;
+            uint32_t i = 0, s = 0, k = 0;       // tile index, its stage and how many times the ring has wrapped
             PipeTile t;
             while (next_tile<COMBINE>(a, w, t)) {
-                const uint32_t s = i % a.nstages, k = i / a.nstages;
                 if (k > 0) {
                     if (s_abort || !mbar_wait_bounded(smem_u32(empty + s), (k - 1) & 1u)) {
                         if (!s_abort) { s_abort = 1; atomicExch(a.status, 2); }
@@ -709,6 +715,7 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
                 }
                 issue_tile<SWIGLU, EXT>(a, t, stages + (size_t)s * a.stage_stride, smem_u32(full + s));
                 ++i;
+                if (++s == a.nstages) { s = 0; ++k; }
             }
             stamp(a.trace, 1);
             // All of this CTA's rows are requested.  Pull the head of the next launch's weights into L2 so that HBM
@@ -809,8 +816,10 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
 
     const uint32_t stages_s = smem_u32(stages);
     const uint32_t unit_off = unit * SlotT::UNIT_BYTES;
-    uint32_t i = 0;
-    int slot_seg = -1;
+    uint32_t i = 0, s = 0, parity = 0;
+    int slot_seg = -1, delta_seg = -1;
+    uint32_t delta = 0, delta2 = 0;
+    const bool rows16 = (a.row_bytes & 15u) == 0;     // then every row starts at the same offset inside its 16-byte piece
     PipeTile t;
     while (next_tile<COMBINE>(a, wk, t)) {
         if (buf_n && (t.seg != buf_seg || buf_n + t.n > CAP)) flush();
@@ -821,18 +830,19 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
                 if (active) slot.load(make_xq_view<NP, SlotT::GROUP>(smem + a.xs_base + (size_t)t.seg * a.xq_vec_bytes, a.in_dim), unit, part);
             }
         }
-        const uint32_t s = i % a.nstages, parity = (i / a.nstages) & 1u;
         if (!s_abort && !mbar_wait_bounded(smem_u32(full + s), parity)) {
             s_abort = 1;
             atomicExch(a.status, 1);
         }
         if (i == 0 && tid == 0) stamp(a.trace, 5);
-        const uint32_t delta = (uint32_t)((reinterpret_cast<uintptr_t>(seg_w<EXT>(a, t.seg)) + (size_t)t.row0 * a.row_bytes) & 15u);
+        if (!rows16 || t.seg != delta_seg) {   // offset of the tile's first byte inside its 16-byte piece
+            delta_seg = t.seg;
+            delta = ((uint32_t)reinterpret_cast<uintptr_t>(seg_w<EXT>(a, t.seg)) + t.row0 * a.row_bytes) & 15u;
+            if constexpr (SWIGLU) delta2 = ((uint32_t)reinterpret_cast<uintptr_t>(seg_w2<EXT>(a, t.seg)) + t.row0 * a.row_bytes) & 15u;
+        }
         const uint32_t base = stages_s + s * a.stage_stride + delta + unit_off;
         uint32_t base2 = 0;
-        if constexpr (SWIGLU)
-            base2 = stages_s + s * a.stage_stride + a.half_stride + unit_off +
-                    (uint32_t)((reinterpret_cast<uintptr_t>(seg_w2<EXT>(a, t.seg)) + (size_t)t.row0 * a.row_bytes) & 15u);
+        if constexpr (SWIGLU) base2 = stages_s + s * a.stage_stride + a.half_stride + unit_off + delta2;
         float *dst = pbuf + (size_t)which * PLANE * (SWIGLU ? 2 : 1) + (size_t)buf_n * GW + wig;
 #pragma unroll 1
         for (uint32_t r = group; r < t.n; r += a.rows_par) {
@@ -852,6 +862,7 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
         if (lane == 0) mbar_arrive(smem_u32(empty + s));   // this warp is done reading the stage
         buf_n += t.n;
         ++i;
+        if (++s == a.nstages) { s = 0; parity ^= 1u; }
     }
     if (tid == 0) stamp(a.trace, 6);
     if (buf_n) flush();
