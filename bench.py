@@ -281,9 +281,10 @@ class Stepper:
             self.issue(self.torch.cuda.current_stream().cuda_stream)
 
 
-def kernel_extras(torch, F, ctx, peak):
+def kernel_extras(torch, F, ctx, peak, only=None, reps=3):
     """Short per-kernel passes on the other benchmark configurations (rank 0, one GPU): absolute GB/s of the
-    algorithmic bytes and the fraction of the measured HBM peak, back-to-back launches over distinct weight copies."""
+    algorithmic bytes and the fraction of the measured HBM peak, back-to-back launches over distinct weight copies.
+    `only` restricts the run to the named cases (a small, short process for a profiler capture)."""
     from orome_b200 import synth
     dev = torch.device("cuda", ctx.device)
     st = torch.cuda.current_stream().cuda_stream
@@ -293,13 +294,15 @@ def kernel_extras(torch, F, ctx, peak):
         fn()
         torch.cuda.synchronize()
         best = float("inf")
-        for _ in range(3):
+        for _ in range(reps):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record(); fn(); e1.record(); torch.cuda.synchronize()
             best = min(best, e0.elapsed_time(e1) / n)
         return best * 1e-3
 
     def gemv(name, fmt, od, idim, copies, batch=1, variant=0):
+        if only and name not in only:
+            return
         tb = (synth.tensor_bytes(fmt, od, idim) + 255) // 256 * 256
         buf = torch.empty(tb * copies, dtype=torch.uint8, device=dev)
         for i in range(copies):
@@ -330,6 +333,8 @@ def kernel_extras(torch, F, ctx, peak):
     gemv("q6_k_lm_head_151936x5120_b1", synth.Q6_K, 151936, 5120, 2)
     gemv("q8_0_lm_head_151936x4096_b1", synth.Q8_0, 151936, 4096, 2)
 
+    if only and "moe_layer_top8_of_128_t1" not in only:
+        return out
     # MoE layer, one token: fp32 router 128 x 2048, top-8, gate/up Q4_K 768 x 2048, down Q5_K 2048 x 768 (6 distinct layers)
     H, M, E, K, NL = 2048, 768, 128, 8, 6
     sg, sd = synth.tensor_bytes(synth.Q4_K, M, H), synth.tensor_bytes(synth.Q5_K, H, M)
@@ -385,6 +390,12 @@ def run_ours(args):
     if args.prefetch_mb >= 0:
         ctx.set_option(F.OPT_PREFETCH_MB, args.prefetch_mb)
 
+    if args.kernel:
+        # one configuration alone, few launches: the process a profiler capture is taken from
+        peak, kind = measured_peak()
+        print(json.dumps({"kernels": kernel_extras(torch, F, ctx, peak, only=set(args.kernel.split(",")), reps=max(1, args.steps)),
+                          "peak_gbs": peak, "peak_kind": kind}), flush=True)
+        return
     ds = decode_set.DecodeSet(args.workload, dev, rank=rank, world=world, layers=args.layers)
     st = Stepper(torch, F, ctx, ds, dist, fused=args.gather == "fused")
     use_graph = args.graph
@@ -536,6 +547,7 @@ def main():
     ap.add_argument("--no-graph", dest="graph", action="store_false")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--extras", action="store_true", help="also time the other benchmark configurations kernel by kernel (adds ~20 s)")
+    ap.add_argument("--kernel", default="", help="run only the named --extras case(s), comma separated, --steps timing repeats, and exit")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="N > 1: complete y by peer stores from the kernel epilogue (fused) or by an NCCL all-gather per product")
     ap.add_argument("--prefetch-mb", type=int, default=-1, help="cap of the next-tensor L2 prefetch in MiB (0 = off, -1 = library default)")
