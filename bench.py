@@ -332,6 +332,8 @@ def kernel_extras(torch, F, ctx, peak, only=None, reps=3):
     gemv("q6_k_5120x17408_b1", synth.Q6_K, 5120, 17408, 6)
     gemv("q6_k_lm_head_151936x5120_b1", synth.Q6_K, 151936, 5120, 2)
     gemv("q8_0_lm_head_151936x4096_b1", synth.Q8_0, 151936, 4096, 2)
+    gemv("q4_k_lm_head_151936x4096_b1", synth.Q4_K, 151936, 4096, 2)
+    gemv("q5_k_lm_head_151936x4096_b1", synth.Q5_K, 151936, 4096, 2)
 
     if only and "moe_layer_top8_of_128_t1" not in only:
         return out

@@ -43,7 +43,7 @@ constexpr int PIPE_THREADS_2CTA = PIPE_CONSUMERS_2CTA + 32;
 constexpr int PIPE_MAX_ITERS = 8;               // rows a group handles per tile
 constexpr int PIPE_MAX_ROWS_PAR = 8;            // named barriers 1..8 belong to the row groups
 constexpr int PIPE_BAR_CONSUMERS = 9;           // named barrier over all consumer threads
-constexpr uint32_t PIPE_WAIT_NS = 1000000000u;  // 1 s per wait
+constexpr long long PIPE_WAIT_CYCLES = 2000000000ll;   // per wait: about one second of SM clock
 
 struct PipeSeg {
     const uint8_t *w;     // tensor (gate tensor in the fused form)
@@ -156,31 +156,32 @@ __device__ __forceinline__ void red_release_sys_add(unsigned int *p, unsigned in
 {
     asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-// Wait until *flag has advanced by `need` since `seen`, at most PIPE_WAIT_NS.  Returns false on expiry.
+// Wait until *flag has advanced by `need` since `seen`, at most PIPE_WAIT_CYCLES.  Returns false on expiry.
+// The bound is kept on the SM's own cycle counter: reading the global nanosecond timer costs far more than a poll.
 __device__ __forceinline__ bool flag_wait_bounded(const unsigned int *flag, unsigned int seen, unsigned int need)
 {
     if (ld_acquire_sys(flag) - seen >= need) return true;
-    const uint64_t t0 = global_ns();
+    const long long t0 = clock64();
     for (;;) {
 #pragma unroll 1
         for (int i = 0; i < 32; ++i)
             if (ld_acquire_sys(flag) - seen >= need) return true;
-        if (global_ns() - t0 > PIPE_WAIT_NS) return false;
+        if (clock64() - t0 > PIPE_WAIT_CYCLES) return false;
     }
 }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-// Wait for a phase of a copy barrier, at most PIPE_WAIT_NS.  Returns false on expiry.
+// Wait for a phase of a copy barrier, at most PIPE_WAIT_CYCLES.  Returns false on expiry.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
 {
     if (mbar_try_wait(bar, parity)) return true;
-    uint64_t t0 = global_ns();
+    const long long t0 = clock64();
     for (;;) {
 #pragma unroll 1
         for (int i = 0; i < 64; ++i)
             if (mbar_try_wait(bar, parity)) return true;
-        if (global_ns() - t0 > PIPE_WAIT_NS) return false;
+        if (clock64() - t0 > PIPE_WAIT_CYCLES) return false;
     }
 }
 

@@ -10,17 +10,27 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <map>
 #include <string>
+#include <tuple>
 
 #include "decode.cuh"
 #include "gemv_generic.cuh"
 #include "gemv_pipe.cuh"
+#include "gemv_mma.cuh"
 #include "moe.cuh"
 #include "gemm_tc.cuh"
 
 using namespace orome;
 
+struct MapKey {
+    const uint8_t *w;
+    uint32_t unit, units, rows, kb;
+    bool operator<(const MapKey &o) const { return std::tie(w, unit, units, rows, kb) < std::tie(o.w, o.unit, o.units, o.rows, o.kb); }
+};
+
 struct orome_cuda_ctx {
+    std::map<MapKey, CUtensorMap> maps;   // tensor maps of the mma kernel's tensors
     int device = 0;
     int sm_count = 0;
     int smem_optin = 0;
@@ -58,6 +68,7 @@ struct orome_cuda_ctx {
     float *tc_xp = nullptr, *tc_part = nullptr;
     size_t tc_xp_cap = 0, tc_part_cap = 0;
     int tc_min_batch = 9;    // batches from this size on use the tensor-core kernel
+    int kquant_mma = 1;      // Q4_K / Q5_K batch-1 products on the mma.sync kernel (0: dp4a kernel)
 };
 
 static thread_local std::string g_err;
@@ -192,6 +203,7 @@ extern "C" int orome_cuda_set_option(orome_cuda_ctx *c, int key, int value)
     case OROME_OPT_GRID_PER_SM:
         if (value < 1 || value > 2) return fail(OROME_EINVAL, "GRID_PER_SM must be 1 or 2");
         c->grid_per_sm = value; return OROME_OK;
+    case OROME_OPT_KQUANT_MMA: c->kquant_mma = value != 0; return OROME_OK;
     case OROME_OPT_TC_MIN_BATCH:
         if (value < 2) return fail(OROME_EINVAL, "TC_MIN_BATCH must be at least 2");
         c->tc_min_batch = value; return OROME_OK;
@@ -214,6 +226,7 @@ extern "C" int orome_cuda_get_option(orome_cuda_ctx *c, int key, int *value)
     case OROME_OPT_GRID_PER_SM: *value = c->grid_per_sm; return OROME_OK;
     case OROME_OPT_PREFETCH_MB: *value = c->prefetch_mb; return OROME_OK;
     case OROME_OPT_TC_MIN_BATCH: *value = c->tc_min_batch; return OROME_OK;
+    case OROME_OPT_KQUANT_MMA: *value = c->kquant_mma; return OROME_OK;
     }
     return fail(OROME_EINVAL, "get_option: unknown key %d", key);
 }
@@ -524,6 +537,150 @@ static int launch_pipe(orome_cuda_ctx *c, int fmt, const PipePlan &p, int mode, 
     return fail(OROME_ENOTSUP, "no pipelined kernel for format %d", fmt);
 }
 
+// ---------------------------------------------------------------------------
+// Q4_K / Q5_K batch-1 kernel on mma.sync: planning and launch
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled_fn();
+
+struct MmaPlan {
+    MmaArgs args;
+    int threads, grid;
+    size_t smem;
+};
+
+// Dense single-GPU launches only: every tensor 16-byte aligned (rows are then 16-byte aligned too, as the row length
+// is a multiple of 16 bytes), no expert indirection, no peers.
+static bool mma_supported(const orome_cuda_ctx *c, int fmt, uint32_t in_dim)
+{
+    return c->kquant_mma && !c->force_generic && c->g_world == 1 && (fmt == FMT_Q4_K || fmt == FMT_Q5_K) && in_dim % 256 == 0 && in_dim >= 256;
+}
+
+static int plan_mma(orome_cuda_ctx *c, int fmt, uint32_t in_dim, uint32_t total_rows, bool swiglu, MmaPlan &p)
+{
+    MmaArgs &a = p.args;
+    const uint32_t unit = fmt == FMT_Q4_K ? 144u : 176u;
+    a.in_dim = in_dim;
+    a.units = in_dim / 256;
+    a.row_bytes = a.units * unit;
+    a.total_rows = total_rows;
+    // a stage of about stage_kb (default 40) KiB: 16 rows (x2 in the fused form) of kc superblocks
+    const uint32_t want = (c->stage_kb ? (uint32_t)c->stage_kb : 40u) * 1024u;
+    const uint32_t kc_max = std::max(1u, std::min(a.units, want / (MMA_TILE_ROWS * unit * (swiglu ? 2u : 1u))));
+    a.nchunks = (a.units + kc_max - 1) / kc_max;
+    a.kc = (a.units + a.nchunks - 1) / a.nchunks;
+    const uint32_t rounds = (a.kc + MMA_MAX_WARPS - 1) / MMA_MAX_WARPS;
+    a.nwarps = (a.kc + rounds - 1) / rounds;
+    p.grid = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)c->sm_count, (total_rows + MMA_TILE_ROWS - 1) / MMA_TILE_ROWS));
+    const uint32_t share = (total_rows + p.grid - 1) / p.grid;
+    a.ngroups = share > MMA_TILE_ROWS ? MMA_MAX_GROUPS : 1;
+    p.threads = (int)(a.nwarps * a.ngroups + 1) * 32;
+    // box width in superblocks: the smallest kb >= kc with kb = 2 (mod 4), which makes the row pitch 32 or 96 (mod 128)
+    const uint32_t kb = a.kc + ((6 - a.kc % 4) % 4);
+    a.pitch = kb * unit;
+    a.box_bytes = MMA_TILE_ROWS * a.pitch;
+    a.half_stride = MMA_TILE_ROWS * a.pitch;
+    a.stage_stride = a.half_stride * (swiglu ? 2 : 1);
+    a.red_base = 2 * 8 * PIPE_MAX_STAGES;
+    a.red_rows = std::max<uint32_t>(MMA_TILE_ROWS, std::min<uint32_t>((share + MMA_TILE_ROWS - 1) / MMA_TILE_ROWS * MMA_TILE_ROWS, 128u));
+    const size_t red_bytes = (size_t)2 * a.red_rows * a.nwarps * (swiglu ? 2 : 1) * sizeof(float);
+    a.xs_base = (uint32_t)((a.red_base + red_bytes + 127) / 128 * 128);
+    const size_t xq_bytes = (size_t)a.units * MMA_XQ_SB + (size_t)a.units * 8;
+    a.stage_base = (uint32_t)((a.xs_base + xq_bytes + 127) / 128 * 128);
+    const size_t budget = std::min<size_t>(228 * 1024 - 1024 - 256, (size_t)c->smem_optin - 256);
+    if (budget < a.stage_base + a.stage_stride) return fail(OROME_ENOTSUP, "mma plan: in_dim %u does not fit shared memory", in_dim);
+    const uint32_t tiles = ((share + MMA_TILE_ROWS - 1) / MMA_TILE_ROWS + 1) * a.nchunks;
+    a.nstages = (uint32_t)std::min<size_t>(std::min<size_t>(PIPE_MAX_STAGES, tiles), (budget - a.stage_base) / a.stage_stride);
+    p.smem = a.stage_base + (size_t)a.stage_stride * a.nstages;
+    a.status = c->status_dev;
+    a.trace = nullptr;
+    if (c->trace_dev && c->trace_next < c->trace_cap) a.trace = c->trace_dev + (size_t)(c->trace_next++) * c->sm_count * 8;
+    a.pf_ptr = c->hint_ptr;
+    a.pf_bytes = c->hint_bytes;
+    c->hint_ptr = nullptr;
+    c->hint_bytes = 0;
+    return OROME_OK;
+}
+
+// Tensor map of one K-quant tensor for the boxes above: {words of a superblock, superblocks of a row, rows}.
+// Encoding costs the host about a microsecond, so maps are kept per (address, shape, box).
+static int mma_tensor_map(orome_cuda_ctx *c, const uint8_t *w, uint32_t unit, uint32_t units, uint32_t rows, uint32_t kb, CUtensorMap *out)
+{
+    const MapKey key{w, unit, units, rows, kb};
+    auto it = c->maps.find(key);
+    if (it == c->maps.end()) {
+        EncodeTiledFn enc = encode_tiled_fn();
+        if (!enc) return fail(OROME_ECUDA, "mma plan: cuTensorMapEncodeTiled is not available");
+        CUtensorMap m;
+        const cuuint64_t dims[3] = {unit / 4, units, rows};
+        const cuuint64_t strides[2] = {unit, (cuuint64_t)unit * units};
+        const cuuint32_t box[3] = {unit / 4, kb, (cuuint32_t)MMA_TILE_ROWS}, estr[3] = {1, 1, 1};
+        CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<uint8_t *>(w), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(OROME_ECUDA, "mma plan: cuTensorMapEncodeTiled failed (%d)", (int)r);
+        if (c->maps.size() >= 4096) c->maps.clear();
+        it = c->maps.emplace(key, m).first;
+    }
+    *out = it->second;
+    return OROME_OK;
+}
+
+static int mma_encode_maps(orome_cuda_ctx *c, int fmt, MmaPlan &p, bool swiglu)
+{
+    MmaArgs &a = p.args;
+    const uint32_t unit = fmt == FMT_Q4_K ? 144u : 176u, kb = a.pitch / unit;
+    for (int i = 0; i < a.nseg; ++i) {
+        int rc = mma_tensor_map(c, a.seg[i].w, unit, a.units, a.seg[i].rows, kb, &a.map[i][0]);
+        if (rc) return rc;
+        if (swiglu) { rc = mma_tensor_map(c, a.seg[i].w2, unit, a.units, a.seg[i].rows, kb, &a.map[i][1]); if (rc) return rc; }
+    }
+    return OROME_OK;
+}
+
+template <int FMT, int NP, bool SWIGLU>
+static int launch_mma_inst(orome_cuda_ctx *c, const MmaPlan &p, cudaStream_t st)
+{
+    auto kern = gemv_mma_kernel<FMT, NP, SWIGLU>;
+    static size_t configured[64] = {0};   // per device: dynamic shared memory opted in so far
+    if (configured[c->device] < p.smem) {
+        cudaFuncAttributes fa;
+        CU(cudaFuncGetAttributes(&fa, kern));
+        const int max_dyn = c->smem_optin - (int)fa.sharedSizeBytes;
+        if ((size_t)max_dyn < p.smem) return fail(OROME_ENOTSUP, "mma launch: %zu bytes of shared memory exceed the limit %d", p.smem, max_dyn);
+        CU(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, max_dyn));
+        configured[c->device] = (size_t)max_dyn;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.grid);
+    cfg.blockDim = dim3(p.threads);
+    cfg.dynamicSmemBytes = p.smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = c->pdl ? 1 : 0;
+    CU(cudaLaunchKernelEx(&cfg, kern, p.args));
+    ++c->launches;
+    return OROME_OK;
+}
+
+static int launch_mma(orome_cuda_ctx *c, int fmt, MmaPlan &p, bool swiglu, cudaStream_t st)
+{
+    int rc = mma_encode_maps(c, fmt, p, swiglu);
+    if (rc) return rc;
+    const bool b24 = c->x_bits == 24;
+    if (fmt == FMT_Q4_K) {
+        if (swiglu) return b24 ? launch_mma_inst<FMT_Q4_K, 3, true>(c, p, st) : launch_mma_inst<FMT_Q4_K, 2, true>(c, p, st);
+        return b24 ? launch_mma_inst<FMT_Q4_K, 3, false>(c, p, st) : launch_mma_inst<FMT_Q4_K, 2, false>(c, p, st);
+    }
+    if (swiglu) return b24 ? launch_mma_inst<FMT_Q5_K, 3, true>(c, p, st) : launch_mma_inst<FMT_Q5_K, 2, true>(c, p, st);
+    return b24 ? launch_mma_inst<FMT_Q5_K, 3, false>(c, p, st) : launch_mma_inst<FMT_Q5_K, 2, false>(c, p, st);
+}
+
 extern "C" int orome_cuda_hint_next(orome_cuda_ctx *c, const OromeTensorRef *next)
 {
     if (!c) return fail(OROME_EINVAL, "hint_next: NULL ctx");
@@ -679,6 +836,23 @@ extern "C" int orome_cuda_matvec_group(orome_cuda_ctx *c, const OromeTensorRef *
         }
         return OROME_OK;
     }
+    bool aligned16 = true;
+    for (int i = 0; i < n_refs; ++i) aligned16 = aligned16 && !(reinterpret_cast<uintptr_t>(data[i]) & 15);
+    if (aligned16 && mma_supported(c, fmt, refs[0].in_dim)) {
+        MmaPlan m;
+        memset(&m, 0, sizeof m);
+        uint32_t rows = 0;
+        for (int i = 0; i < n_refs; ++i) {
+            m.args.seg[i] = PipeSeg{data[i], nullptr, y_dev[i], refs[i].out_dim, rows};
+            rows += refs[i].out_dim;
+        }
+        m.args.nseg = n_refs;
+        m.args.x = x_dev;
+        m.args.layout = layout;
+        int rc = plan_mma(c, fmt, refs[0].in_dim, rows, false, m);
+        if (rc == OROME_OK) return launch_mma(c, fmt, m, false, st);
+        if (rc != OROME_ENOTSUP) return rc;      // too wide for this kernel's shared memory: the dp4a kernel takes it
+    }
     PipePlan p;
     memset(&p, 0, sizeof p);
     uint32_t total = 0;
@@ -720,9 +894,6 @@ static int launch_tc_fmt(orome_cuda_ctx *c, const TcArgs &a, int grid, size_t sm
 static int ensure(float **p, size_t *cap, size_t floats);
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda)
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 static EncodeTiledFn encode_tiled_fn()
 {
     static EncodeTiledFn fn = nullptr;
@@ -872,6 +1043,17 @@ extern "C" int orome_cuda_gate_up_swiglu(orome_cuda_ctx *c, const OromeTensorRef
     }
     if (batch == 1 && !c->force_generic && pipe_supported(fmt, gate->in_dim)) {
         if (reinterpret_cast<uintptr_t>(x_dev) & 15) return fail(OROME_EINVAL, "gate_up_swiglu: x must be 16-byte aligned");
+        if (!((reinterpret_cast<uintptr_t>(gd) | reinterpret_cast<uintptr_t>(ud)) & 15) && mma_supported(c, fmt, gate->in_dim)) {
+            MmaPlan m;
+            memset(&m, 0, sizeof m);
+            m.args.seg[0] = PipeSeg{gd, ud, out_dev, gate->out_dim, 0};
+            m.args.nseg = 1;
+            m.args.x = x_dev;
+            m.args.layout = layout;
+            rc = plan_mma(c, fmt, gate->in_dim, gate->out_dim, true, m);
+            if (rc == OROME_OK) return launch_mma(c, fmt, m, true, st);
+            if (rc != OROME_ENOTSUP) return rc;
+        }
         PipePlan p;
         memset(&p, 0, sizeof p);
         p.args.seg[0] = PipeSeg{gd, ud, out_dev, gate->out_dim, 0};
