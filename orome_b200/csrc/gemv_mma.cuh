@@ -44,6 +44,7 @@ struct MmaArgs {
     uint32_t ngroups;          // groups; row tile i belongs to group i % ngroups
     uint32_t kc;               // superblocks per stage
     uint32_t nchunks;          // stages per row tile = ceil(units / kc)
+    uint32_t dbg_tile;         // diagnostics build: first row tile whose per-warp timeline is recorded
     uint32_t pitch;            // bytes between rows inside a stage = box width in superblocks * superblock bytes
     uint32_t box_bytes;        // bytes one tensor copy delivers (16 rows * pitch)
     uint32_t nstages, stage_stride, half_stride, stage_base;
@@ -101,7 +102,7 @@ __device__ __forceinline__ void unpack_scales4(uint32_t w0, uint32_t w1, uint32_
 template <int K>
 __device__ __forceinline__ int byte_of(uint32_t lo, uint32_t hi)   // byte K (0..7) of the pair as an int
 {
-    return (int)(((K < 4 ? lo : hi) >> (8 * (K & 3))) & 0xFFu);
+    return (int)__byte_perm(K < 4 ? lo : hi, 0u, 0x4440u + (K & 3));
 }
 
 // One superblock of rows g and g+8 against the superblock's x: y0 += (W x)[row g], y1 += (W x)[row g + 8],
@@ -174,19 +175,13 @@ __device__ __forceinline__ void mma_superblock(uint32_t h0, uint32_t h1, uint32_
     y1 = fmaf(-n1, fmaf(cw1, (float)m[3], cw0 * (float)m[2]), y1);
 }
 
-// Balanced base-256 digits of a clamped integer: v = d0 + 256 d1 + 65536 d2, every digit in [-128, 127].
-template <int NP>
-__device__ __forceinline__ void balanced_digits(int v, int (&d)[3])
+// Balanced base-256 digits, all elements at once: for |v| <= 0x7F7F7F (0x7F7F) the bytes of v + 0x808080 (0x8080) are
+// the digits plus 128, so a plane word is three byte permutes and one xor with 0x80808080.
+template <int NP> __device__ __forceinline__ uint32_t digit_bias() { return NP == 3 ? 0x00808080u : 0x00008080u; }
+__device__ __forceinline__ uint32_t plane_word(uint32_t u0, uint32_t u1, uint32_t u2, uint32_t u3, int p)
 {
-    d[0] = (int)(signed char)(v & 0xFF);
-    v = (v - d[0]) >> 8;
-    if constexpr (NP == 3) {
-        d[1] = (int)(signed char)(v & 0xFF);
-        d[2] = (v - d[1]) >> 8;
-    } else {
-        d[1] = v;
-        d[2] = 0;
-    }
+    const uint32_t sel = (uint32_t)p | ((uint32_t)(4 + p) << 4);
+    return __byte_perm(__byte_perm(u0, u1, sel), __byte_perm(u2, u3, sel), 0x5410) ^ 0x80808080u;
 }
 
 // x -> shared memory, one warp per superblock: lane l owns elements 8l..8l+7 (sub-block l / 4, bytes 8 (l % 4)..).
@@ -241,22 +236,18 @@ __device__ __forceinline__ void quantize_x_mma(const float *__restrict__ x, uint
             if (u >= units) break;
             const float inv = amax[b] > 0.0f ? QMAX / amax[b] : 0.0f, sinv = smax[b] > 0.0f ? QMAX / smax[b] : 0.0f;
             const float v[8] = {v0[b].x, v0[b].y, v0[b].z, v0[b].w, v1[b].x, v1[b].y, v1[b].z, v1[b].w};
-            int dg[8][3];
+            uint32_t uq[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) balanced_digits<NP>(max(-QMAXI, min(QMAXI, __float2int_rn(v[i] * inv))), dg[i]);
+            for (int i = 0; i < 8; ++i) uq[i] = (uint32_t)max(-QMAXI, min(QMAXI, __float2int_rn(v[i] * inv))) + digit_bias<NP>();
             uint8_t *sb = xq + (size_t)u * MMA_XQ_SB;
 #pragma unroll
-            for (int p = 0; p < NP; ++p) {
-                uint2 w;
-                w.x = (uint32_t)(dg[0][p] & 255) | ((uint32_t)(dg[1][p] & 255) << 8) | ((uint32_t)(dg[2][p] & 255) << 16) | ((uint32_t)dg[3][p] << 24);
-                w.y = (uint32_t)(dg[4][p] & 255) | ((uint32_t)(dg[5][p] & 255) << 8) | ((uint32_t)(dg[6][p] & 255) << 16) | ((uint32_t)dg[7][p] << 24);
-                *reinterpret_cast<uint2 *>(sb + (lane >> 2) * 96 + p * 32 + (lane & 3u) * 8) = w;
-            }
-            int sd[3];
-            balanced_digits<NP>(max(-QMAXI, min(QMAXI, __float2int_rn(sum[b] * sinv))), sd);
+            for (int p = 0; p < NP; ++p)
+                *reinterpret_cast<uint2 *>(sb + (lane >> 2) * 96 + p * 32 + (lane & 3u) * 8) =
+                    make_uint2(plane_word(uq[0], uq[1], uq[2], uq[3], p), plane_word(uq[4], uq[5], uq[6], uq[7], p));
+            const uint32_t us = (uint32_t)max(-QMAXI, min(QMAXI, __float2int_rn(sum[b] * sinv))) + digit_bias<NP>();
             if ((lane & 3u) == 0) {
 #pragma unroll
-                for (int p = 0; p < NP; ++p) sb[768 + p * 8 + (lane >> 2)] = (uint8_t)(sd[p] & 255);
+                for (int p = 0; p < NP; ++p) sb[768 + p * 8 + (lane >> 2)] = (uint8_t)(((us >> (8 * p)) & 255u) ^ 0x80u);
             }
             if (lane == 0) { xs[u] = amax[b] / QMAX; sxs[u] = smax[b] / QMAX; }
         }
@@ -271,6 +262,18 @@ __device__ __forceinline__ void tma_box(uint32_t dst, const CUtensorMap *map, ui
 }
 
 struct MmaTile { int seg; uint32_t row0, n; };
+
+// Diagnostics build only (-DOROME_MMA_TILE_TRACE): CTA 0 records, for eight row tiles from OROME_DBG_TILE on, when each
+// consumer warp starts waiting for the tile, gets it and is done with it, into the trace area of ten launches later.
+#ifdef OROME_MMA_TILE_TRACE
+#define MMA_TILE_STAMP(a, tile, warp, k)                                                                                      \
+    do {                                                                                                                      \
+        if ((a).trace && blockIdx.x == 0 && (threadIdx.x & 31u) == 0 && (tile) >= (a).dbg_tile && (tile) < (a).dbg_tile + 8)    \
+            (a).trace[(size_t)gridDim.x * 80 + 3 * (((tile) - (a).dbg_tile) * 16 + (warp)) + (k)] = global_ns();             \
+    } while (0)
+#else
+#define MMA_TILE_STAMP(a, tile, warp, k) do { } while (0)
+#endif
 
 // Tiles of at most 16 rows over this CTA's range of the concatenated rows; a tile never crosses a segment.
 __device__ __forceinline__ bool mma_next_tile(const MmaArgs &a, uint32_t &cur, uint32_t hi, int &seg, MmaTile &t)
@@ -300,7 +303,9 @@ gemv_mma_kernel(const __grid_constant__ MmaArgs a)
     uint8_t *stages = smem + a.stage_base;
     __shared__ volatile int s_abort;
 
-    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    // the warp index goes through a shuffle so that the compiler treats it (and every loop bound and address derived
+    // from it) as warp-uniform: no convergence barriers around the mma instructions, uniform-datapath address math
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
     const uint32_t NW = a.nwarps, NG = a.ngroups, CW = NW * NG, C = CW * 32, U = a.units;
     const bool producer = warp >= CW;
 
@@ -376,7 +381,7 @@ gemv_mma_kernel(const __grid_constant__ MmaArgs a)
     quantize_x_mma<NP>(a.x, U, xq, warp, lane, CW);
     named_bar_sync(PIPE_BAR_CONSUMERS, (int)C);
     if (tid == 0) stamp(a.trace, 3);
-    const float *xs = reinterpret_cast<const float *>(xq + (size_t)U * MMA_XQ_SB), *sxs = xs + U;
+    const uint32_t xs_s = smem_u32(xq) + U * MMA_XQ_SB;                // xs[U], then sxs[U]
     const uint32_t plane = g < (uint32_t)NP ? g : 0u;                  // columns past the planes repeat plane 0 and are weighted 0
     const uint32_t xq_s = smem_u32(xq) + plane * 32u + t4 * 8u;       // this thread's x bytes of sub-block 0, superblock 0
     const uint32_t sx_s = smem_u32(xq) + 768u + plane * 8u + (t4 & 1u) * 4u;
@@ -404,10 +409,10 @@ gemv_mma_kernel(const __grid_constant__ MmaArgs a)
 
     const uint32_t stages_s = smem_u32(stages);
     const uint32_t group = warp / NW, wig = warp - group * NW;
-    uint32_t cur = lo, s = 0, parity = 0, i = 0, turn = 0;
+    uint32_t cur = lo, s = 0, parity = 0, i = 0, turn = 0, tile_no = 0;
     int seg = 0;
     MmaTile t;
-    while (mma_next_tile(a, cur, hi, seg, t)) {
+    for (; mma_next_tile(a, cur, hi, seg, t); ++tile_no) {
         if (buf_n && (t.seg != buf_seg || buf_n + t.n > CAP)) flush();
         if (buf_n == 0) { buf_seg = t.seg; buf_row0 = t.row0; }
         if (turn != group) {     // another group's tile: step over its stages
@@ -420,10 +425,12 @@ gemv_mma_kernel(const __grid_constant__ MmaArgs a)
         if (++turn == NG) turn = 0;
         float yg0 = 0.0f, yg1 = 0.0f, yu0 = 0.0f, yu1 = 0.0f;
         for (uint32_t c = 0; c < a.nchunks; ++c) {
+            if (c == 0) MMA_TILE_STAMP(a, tile_no, warp, 0);
             if (!s_abort && !mbar_wait_bounded(smem_u32(full + s), parity)) {
                 s_abort = 1;
                 atomicExch(a.status, 1);
             }
+            if (c == 0) MMA_TILE_STAMP(a, tile_no, warp, 1);
             if (i == 0 && tid == 0) stamp(a.trace, 5);
             const uint32_t u0 = c * a.kc, kn = U - u0 < a.kc ? U - u0 : a.kc;
             const uint32_t row_s = stages_s + s * a.stage_stride + g * a.pitch;
@@ -433,7 +440,7 @@ gemv_mma_kernel(const __grid_constant__ MmaArgs a)
                 const uint32_t xa = xq_s + ug * MMA_XQ_SB;
                 B[0] = lds64<0>(xa);   B[1] = lds64<96>(xa);  B[2] = lds64<192>(xa); B[3] = lds64<288>(xa);
                 B[4] = lds64<384>(xa); B[5] = lds64<480>(xa); B[6] = lds64<576>(xa); B[7] = lds64<672>(xa);
-                const float xsu = xs[ug], sxsu = sxs[ug];
+                const float xsu = __uint_as_float(lds32<0>(xs_s + 4u * ug)), sxsu = __uint_as_float(lds32<0>(xs_s + 4u * (U + ug)));
                 const uint32_t h0 = row_s + u * UNIT, h1 = h0 + 8u * a.pitch;
                 mma_superblock<FMT>(h0, h1, t4, B, sx_s + ug * MMA_XQ_SB, xsu, sxsu, cw0, cw1, a.layout, yg0, yg1);
                 if constexpr (SWIGLU)
@@ -457,6 +464,7 @@ gemv_mma_kernel(const __grid_constant__ MmaArgs a)
             if (g + 8 < t.n) { dst[(g + 8) * NW] = yg1; if constexpr (SWIGLU) dst[PLANE + (g + 8) * NW] = yu1; }
         }
         buf_n += t.n;
+        MMA_TILE_STAMP(a, tile_no, warp, 2);
     }
     if (tid == 0) stamp(a.trace, 6);
     if (buf_n) flush();

@@ -594,6 +594,9 @@ static int plan_mma(orome_cuda_ctx *c, int fmt, uint32_t in_dim, uint32_t total_
     const uint32_t tiles = ((share + MMA_TILE_ROWS - 1) / MMA_TILE_ROWS + 1) * a.nchunks;
     a.nstages = (uint32_t)std::min<size_t>(std::min<size_t>(PIPE_MAX_STAGES, tiles), (budget - a.stage_base) / a.stage_stride);
     p.smem = a.stage_base + (size_t)a.stage_stride * a.nstages;
+#ifdef OROME_MMA_TILE_TRACE
+    a.dbg_tile = getenv("OROME_DBG_TILE") ? (uint32_t)atoi(getenv("OROME_DBG_TILE")) : 0u;
+#endif
     a.status = c->status_dev;
     a.trace = nullptr;
     if (c->trace_dev && c->trace_next < c->trace_cap) a.trace = c->trace_dev + (size_t)(c->trace_next++) * c->sm_count * 8;
