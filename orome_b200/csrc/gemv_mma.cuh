@@ -29,9 +29,11 @@ namespace orome {
 
 constexpr int MMA_TILE_ROWS = 16;
 constexpr int MMA_MAX_WARPS = 8;                  // consumer warps of a group
-constexpr int MMA_MAX_GROUPS = 2;
-constexpr int MMA_MAX_THREADS = (MMA_MAX_WARPS * MMA_MAX_GROUPS + 1) * 32;   // one more warp produces
-constexpr uint32_t MMA_XQ_SB = 800;               // quantized x per superblock: 8 sub-blocks x 3 planes x 32 B, 3 x 8 sum bytes, pad
+constexpr int MMA_MAX_GROUPS = 3;
+constexpr int MMA_MAX_CONSUMER_WARPS = 16;        // groups * warps per group
+constexpr int MMA_MAX_PRODUCERS = 2;              // producer warps (two where every row is its own copy)
+constexpr int MMA_MAX_THREADS = (MMA_MAX_CONSUMER_WARPS + MMA_MAX_PRODUCERS) * 32;
+constexpr uint32_t MMA_XQ_SB = 864;               // quantized x per superblock: 8 groups x 3 planes x 32 B, then the sums (<= 96 B)
 
 struct MmaArgs {
     alignas(64) CUtensorMap map[PIPE_MAX_SEG][2];   // per segment: its tensor (and the up tensor in the fused form)
@@ -41,7 +43,7 @@ struct MmaArgs {
     uint32_t in_dim, row_bytes;
     uint32_t units;            // superblocks per row
     uint32_t nwarps;           // consumer warps of one group: a group covers the kc superblocks of a stage
-    uint32_t ngroups;          // groups; row tile i belongs to group i % ngroups
+    uint32_t ngroups;          // groups; stage i (counted over row tiles and their chunks) belongs to group i % ngroups
     uint32_t kc;               // superblocks per stage
     uint32_t nchunks;          // stages per row tile = ceil(units / kc)
     uint32_t dbg_tile;         // diagnostics build: first row tile whose per-warp timeline is recorded
@@ -175,6 +177,136 @@ __device__ __forceinline__ void mma_superblock(uint32_t h0, uint32_t h1, uint32_
     y1 = fmaf(-n1, fmaf(cw1, (float)m[3], cw0 * (float)m[2]), y1);
 }
 
+
+// ---- Q6_K -----------------------------------------------------------------
+// Superblock = 210 bytes, only 2-byte aligned: ql[128] low nibbles, qh[64] two high bits, 16 int8 scales (one per 16
+// weights), fp16 d.  Group (h, j) = weights 128h + 32j .. +31, with scales 8h + 2j (first 16) and 8h + 2j + 1.
+// One m16n8k32 per group: the B columns are the x planes of the group's first 16 elements (columns 0..2, zero in the
+// other 16 k-slots) and of its second 16 (columns 3..5), so the two scale groups come out in separate columns.
+// The quants stay unsigned (0..63); their -32 offset is one more small mma per superblock: the row's 16 scales
+// against the 16 per-group sums of the x digits.
+
+// prmt in its generic form: a selector nibble with bit 3 set yields the sign of the chosen byte in all eight bits
+// (the __byte_perm intrinsic documents only the three index bits)
+__device__ __forceinline__ int prmt_sext(uint32_t x, uint32_t sel)
+{
+    int r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(x), "r"(0u), "r"(sel));
+    return r;
+}
+// D = A(16x16, s8) * B(16x8, s8)
+__device__ __forceinline__ void mma_s8s8_k16(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0)
+{
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+                 : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                 : "r"(a0), "r"(a1), "r"(b0), "r"(0));
+}
+
+// Per-thread constants of the Q6_K step.  Thread t of a quad holds product columns 2t, 2t+1:
+// t = 0: (first 16, plane 0), (first 16, plane 1); t = 1: (first 16, plane 2), (second 16, plane 0);
+// t = 2: (second 16, plane 1), (second 16, plane 2); t = 3: unused columns.
+struct Q6Lane {
+    uint32_t sel[2][2];   // [scale byte pair 0/1 or 2/3 of a word][column c0 / c1]: permute selector, sign-extending
+    float cw0, cw1, cwm;  // weights of the two columns' planes, and of the offset term's plane
+};
+template <int NP>
+__device__ __forceinline__ Q6Lane q6_lane(uint32_t t)
+{
+    auto sext = [](uint32_t b) { return b | ((8u | b) << 4) | ((8u | b) << 8) | ((8u | b) << 12); };
+    Q6Lane L;
+    const uint32_t s0 = t <= 1 ? 0u : 1u, s1 = t == 0 ? 0u : 1u;   // which of the group's two scales column c0 / c1 takes
+    L.sel[0][0] = sext(s0);     L.sel[0][1] = sext(s1);
+    L.sel[1][0] = sext(2 + s0); L.sel[1][1] = sext(2 + s1);
+    constexpr float W0 = 1.0f, W1 = 256.0f, W2 = NP == 3 ? 65536.0f : 0.0f;
+    L.cw0 = t == 0 ? W0 : t == 1 ? W2 : t == 2 ? W1 : 0.0f;
+    L.cw1 = t == 0 ? W1 : t == 1 ? W0 : t == 2 ? W2 : 0.0f;
+    L.cwm = t == 0 ? W0 : t == 1 ? W1 : t == 2 ? W2 : 0.0f;
+    return L;
+}
+
+// Four bytes from a shared address: aligned form, or two aligned words realigned by a byte permute when the address
+// is only 2-byte aligned (sel = 0x5432 for addresses 2 mod 4, 0x3210 else).
+template <bool ALIGNED>
+__device__ __forceinline__ uint32_t q6_word(uint32_t a, uint32_t sel)
+{
+    if constexpr (ALIGNED) return lds32<0>(a);
+    else {
+        const uint32_t q = a & ~3u;
+        return __byte_perm(lds32<0>(q), lds32<4>(q), sel);
+    }
+}
+
+// Group (H, J) of rows g, g+8.  ql*/qh*: this thread's words of the half's ql (J even: bytes 0..31, J odd: 32..63) and
+// qh, index 0 = elements 4t..4t+3, 1 = elements 16+4t..16+4t+3; suffix 0 / 1 = row g / g+8.
+template <int H, int J>
+__device__ __forceinline__ void q6_group(const uint32_t (&ql0)[2], const uint32_t (&ql1)[2], const uint32_t (&qh0)[2], const uint32_t (&qh1)[2],
+                                         uint32_t b0, uint32_t b1, const uint32_t (&sc0)[4], const uint32_t (&sc1)[4], const Q6Lane &L, int (&acc)[4])
+{
+    auto unpack = [](uint32_t ql, uint32_t qh) {
+        const uint32_t lo = J < 2 ? (ql & 0x0F0F0F0Fu) : ((ql >> 4) & 0x0F0F0F0Fu);
+        const uint32_t hi = J == 0 ? (qh << 4) : J == 1 ? (qh << 2) : J == 2 ? qh : (qh >> 2);
+        return lo | (hi & 0x30303030u);
+    };
+    const uint32_t av[4] = {unpack(ql0[0], qh0[0]), unpack(ql1[0], qh1[0]), unpack(ql0[1], qh0[1]), unpack(ql1[1], qh1[1])};
+    int c[4];
+    mma_u8s8_k32(c, av, b0, b1);
+    constexpr int W = 2 * H + J / 2, P = J & 1;      // scale word and byte pair of this group
+    acc[0] += prmt_sext(sc0[W], L.sel[P][0]) * c[0];
+    acc[1] += prmt_sext(sc0[W], L.sel[P][1]) * c[1];
+    acc[2] += prmt_sext(sc1[W], L.sel[P][0]) * c[2];
+    acc[3] += prmt_sext(sc1[W], L.sel[P][1]) * c[3];
+}
+
+// One Q6_K superblock of rows g and g+8.  s0, s1: shared addresses of the rows' superblocks (2-byte aligned);
+// bx: this thread's x word of group 0 (plane of its column; first or second 16 elements); first: the column covers
+// the first 16 elements of a group (the word is operand b0 and b1 is zero) or the second 16 (b0 zero);
+// bsx: the digit sums of its column.  Thread t owns elements 4t..4t+3 and 16+4t..16+4t+3 of every group, so the
+// quad reads four consecutive words per row and the eight rows of a load fall into different banks.
+template <bool ALIGNED>
+__device__ __forceinline__ void mma_superblock_q6(uint32_t s0, uint32_t s1, uint32_t t, uint32_t bx, bool first, uint32_t bsx, float xs,
+                                                  const Q6Lane &L, float &y0, float &y1)
+{
+    const uint32_t o = 4u * t;
+    const uint32_t sel0 = (s0 & 2u) ? 0x5432u : 0x3210u, sel1 = (s1 & 2u) ? 0x5432u : 0x3210u;
+    uint32_t xb[8];
+    xb[0] = lds32<0>(bx);   xb[1] = lds32<96>(bx);  xb[2] = lds32<192>(bx); xb[3] = lds32<288>(bx);
+    xb[4] = lds32<384>(bx); xb[5] = lds32<480>(bx); xb[6] = lds32<576>(bx); xb[7] = lds32<672>(bx);
+    const uint32_t bs = lds32<0>(bsx);
+    uint32_t sc0[4], sc1[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { sc0[k] = q6_word<ALIGNED>(s0 + 192 + 4 * k, sel0); sc1[k] = q6_word<ALIGNED>(s1 + 192 + 4 * k, sel1); }
+    const uint32_t d0h = lds16<208>(s0), d1h = lds16<208>(s1);
+    int acc[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        uint32_t qa0[2], qa1[2], qb0[2], qb1[2], h0[2], h1[2];
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            qa0[k] = q6_word<ALIGNED>(s0 + 64 * h + 16 * k + o, sel0);       qa1[k] = q6_word<ALIGNED>(s1 + 64 * h + 16 * k + o, sel1);
+            qb0[k] = q6_word<ALIGNED>(s0 + 64 * h + 32 + 16 * k + o, sel0);  qb1[k] = q6_word<ALIGNED>(s1 + 64 * h + 32 + 16 * k + o, sel1);
+            h0[k] = q6_word<ALIGNED>(s0 + 128 + 32 * h + 16 * k + o, sel0);  h1[k] = q6_word<ALIGNED>(s1 + 128 + 32 * h + 16 * k + o, sel1);
+        }
+        if (h == 0) {
+            q6_group<0, 0>(qa0, qa1, h0, h1, first ? xb[0] : 0u, first ? 0u : xb[0], sc0, sc1, L, acc);
+            q6_group<0, 1>(qb0, qb1, h0, h1, first ? xb[1] : 0u, first ? 0u : xb[1], sc0, sc1, L, acc);
+            q6_group<0, 2>(qa0, qa1, h0, h1, first ? xb[2] : 0u, first ? 0u : xb[2], sc0, sc1, L, acc);
+            q6_group<0, 3>(qb0, qb1, h0, h1, first ? xb[3] : 0u, first ? 0u : xb[3], sc0, sc1, L, acc);
+        } else {
+            q6_group<1, 0>(qa0, qa1, h0, h1, first ? xb[4] : 0u, first ? 0u : xb[4], sc0, sc1, L, acc);
+            q6_group<1, 1>(qb0, qb1, h0, h1, first ? xb[5] : 0u, first ? 0u : xb[5], sc0, sc1, L, acc);
+            q6_group<1, 2>(qa0, qa1, h0, h1, first ? xb[6] : 0u, first ? 0u : xb[6], sc0, sc1, L, acc);
+            q6_group<1, 3>(qb0, qb1, h0, h1, first ? xb[7] : 0u, first ? 0u : xb[7], sc0, sc1, L, acc);
+        }
+    }
+    // offset: sum over the 16 groups of scale * (sum of the x digits), columns (plane, low / high byte of the sum)
+    int m[4];
+    mma_s8s8_k16(m, t == 0 ? sc0[0] : t == 1 ? sc0[1] : t == 2 ? sc0[2] : sc0[3], t == 0 ? sc1[0] : t == 1 ? sc1[1] : t == 2 ? sc1[2] : sc1[3], bs);
+    const float d0 = __half2float(__ushort_as_half((unsigned short)d0h)) * xs, d1 = __half2float(__ushort_as_half((unsigned short)d1h)) * xs;
+    const float off0 = fmaf((float)m[1], 256.0f, (float)m[0]) * (32.0f * L.cwm), off1 = fmaf((float)m[3], 256.0f, (float)m[2]) * (32.0f * L.cwm);
+    y0 = fmaf(d0, fmaf(L.cw1, (float)acc[1], fmaf(L.cw0, (float)acc[0], -off0)), y0);
+    y1 = fmaf(d1, fmaf(L.cw1, (float)acc[3], fmaf(L.cw0, (float)acc[2], -off1)), y1);
+}
+
 // Balanced base-256 digits, all elements at once: for |v| <= 0x7F7F7F (0x7F7F) the bytes of v + 0x808080 (0x8080) are
 // the digits plus 128, so a plane word is three byte permutes and one xor with 0x80808080.
 template <int NP> __device__ __forceinline__ uint32_t digit_bias() { return NP == 3 ? 0x00808080u : 0x00008080u; }
@@ -188,7 +320,9 @@ __device__ __forceinline__ uint32_t plane_word(uint32_t u0, uint32_t u1, uint32_
 // Layout per superblock u at xq + u * MMA_XQ_SB: [sub-block j][plane p][32 bytes], then at +768 [plane p][8 sum bytes];
 // xs[u], sxs[u] after all superblocks.  A warp takes up to four superblocks at a time: their loads are issued together
 // and their shuffle reductions interleave.
-template <int NP>
+// Q6 form: instead of the float sums, the sums of the signed digits over every 16 elements, as two balanced bytes:
+// at +768 [plane p][low / high byte][16 groups].
+template <int NP, bool Q6>
 __device__ __forceinline__ void quantize_x_mma(const float *__restrict__ x, uint32_t units, uint8_t *xq, uint32_t warp, uint32_t lane,
                                                uint32_t nwarps)
 {
@@ -241,13 +375,25 @@ __device__ __forceinline__ void quantize_x_mma(const float *__restrict__ x, uint
             for (int i = 0; i < 8; ++i) uq[i] = (uint32_t)max(-QMAXI, min(QMAXI, __float2int_rn(v[i] * inv))) + digit_bias<NP>();
             uint8_t *sb = xq + (size_t)u * MMA_XQ_SB;
 #pragma unroll
-            for (int p = 0; p < NP; ++p)
-                *reinterpret_cast<uint2 *>(sb + (lane >> 2) * 96 + p * 32 + (lane & 3u) * 8) =
-                    make_uint2(plane_word(uq[0], uq[1], uq[2], uq[3], p), plane_word(uq[4], uq[5], uq[6], uq[7], p));
-            const uint32_t us = (uint32_t)max(-QMAXI, min(QMAXI, __float2int_rn(sum[b] * sinv))) + digit_bias<NP>();
-            if ((lane & 3u) == 0) {
+            for (int p = 0; p < NP; ++p) {
+                const uint2 pw = make_uint2(plane_word(uq[0], uq[1], uq[2], uq[3], p), plane_word(uq[4], uq[5], uq[6], uq[7], p));
+                *reinterpret_cast<uint2 *>(sb + (lane >> 2) * 96 + p * 32 + (lane & 3u) * 8) = pw;
+                if constexpr (Q6) {
+                    int sd = __dp4a((int)pw.x, 0x01010101, __dp4a((int)pw.y, 0x01010101, 0));
+                    sd += __shfl_xor_sync(0xffffffffu, sd, 1);                    // 16 elements = two lanes
+                    const int lo8 = (int)(signed char)(sd & 0xFF);
+                    if ((lane & 1u) == 0) {
+                        sb[768 + (2 * p) * 16 + (lane >> 1)] = (uint8_t)(lo8 & 255);
+                        sb[768 + (2 * p + 1) * 16 + (lane >> 1)] = (uint8_t)(((sd - lo8) >> 8) & 255);
+                    }
+                }
+            }
+            if constexpr (!Q6) {
+                const uint32_t us = (uint32_t)max(-QMAXI, min(QMAXI, __float2int_rn(sum[b] * sinv))) + digit_bias<NP>();
+                if ((lane & 3u) == 0) {
 #pragma unroll
-                for (int p = 0; p < NP; ++p) sb[768 + p * 8 + (lane >> 2)] = (uint8_t)(((us >> (8 * p)) & 255u) ^ 0x80u);
+                    for (int p = 0; p < NP; ++p) sb[768 + p * 8 + (lane >> 2)] = (uint8_t)(((us >> (8 * p)) & 255u) ^ 0x80u);
+                }
             }
             if (lane == 0) { xs[u] = amax[b] / QMAX; sxs[u] = smax[b] / QMAX; }
         }
@@ -295,7 +441,9 @@ template <int FMT, int NP, bool SWIGLU>
 __global__ void __launch_bounds__(MMA_MAX_THREADS, 1)
 gemv_mma_kernel(const __grid_constant__ MmaArgs a)
 {
-    constexpr uint32_t UNIT = FMT == FMT_Q4_K ? 144 : 176;
+    constexpr uint32_t UNIT = FMT == FMT_Q4_K ? 144 : FMT == FMT_Q5_K ? 176 : 210;
+    constexpr bool Q6 = FMT == FMT_Q6_K;
+    static_assert(!(Q6 && SWIGLU), "the fused gate/up form is built for Q4_K and Q5_K only");
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);
     uint64_t *empty = full + PIPE_MAX_STAGES;
@@ -306,6 +454,7 @@ gemv_mma_kernel(const __grid_constant__ MmaArgs a)
     // the warp index goes through a shuffle so that the compiler treats it (and every loop bound and address derived
     // from it) as warp-uniform: no convergence barriers around the mma instructions, uniform-datapath address math
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
+    constexpr uint32_t NPROD = Q6 ? 2u : 1u;
     const uint32_t NW = a.nwarps, NG = a.ngroups, CW = NW * NG, C = CW * 32, U = a.units;
     const bool producer = warp >= CW;
 
@@ -327,36 +476,67 @@ gemv_mma_kernel(const __grid_constant__ MmaArgs a)
 
     if (producer) {
         // The weight copies do not depend on the previous kernel: no griddepcontrol.wait on this path.
-        uint32_t cur = lo, s = 0, k = 0, issued = 0;
+        // With two producer warps, warp p issues the stages i with i % 2 == p.
+        const uint32_t pw = warp - CW;
+        uint32_t cur = lo, s = 0, k = 0, issued = 0, used_mask = 0, par_mask = 0;
         int seg = 0;
         bool ok = true;
         MmaTile t;
         while (ok && mma_next_tile(a, cur, hi, seg, t)) {
-            for (uint32_t c = 0; c < a.nchunks && ok; ++c) {
-                if (k > 0) {
+            for (uint32_t c = 0; c < a.nchunks && ok; ++c, ++issued) {
+                const uint32_t sc = s, kc_ = k;
+                if (++s == a.nstages) { s = 0; ++k; }
+                if (NPROD > 1 && issued % NPROD != pw) continue;
+                if (kc_ > 0) {
                     int good = 1;
                     if (lane == 0) {
-                        good = !s_abort && mbar_wait_bounded(smem_u32(empty + s), (k - 1) & 1u);
+                        good = !s_abort && mbar_wait_bounded(smem_u32(empty + sc), (kc_ - 1) & 1u);
                         if (!good && !s_abort) { s_abort = 1; atomicExch(a.status, 2); }
                     }
                     good = __shfl_sync(0xffffffffu, good, 0);
                     if (!good) { ok = false; break; }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 }
-                const uint32_t bar = smem_u32(full + s);
-                if (lane == 0) {
-                    const uint32_t dst = smem_u32(stages + (size_t)s * a.stage_stride);
+                used_mask |= 1u << sc;
+                par_mask = (par_mask & ~(1u << sc)) | ((kc_ & 1u) << sc);
+                const uint32_t bar = smem_u32(full + sc);
+                if constexpr (Q6) {
+                    // 210-byte superblocks rule out a tensor map (strides must be multiples of 16 bytes): one bulk copy per
+                    // row, each widened to 16-byte boundaries; the consumers add the row's offset inside its first piece
+                    const uint32_t u0 = c * a.kc, kn = U - u0 < a.kc ? U - u0 : a.kc;
+                    uint32_t bytes = 0, dst = 0;
+                    uintptr_t a0 = 0;
+                    if (lane < t.n) {
+                        const uintptr_t base = reinterpret_cast<uintptr_t>(a.seg[t.seg].w);
+                        const uintptr_t src = base + (size_t)(t.row0 + lane) * a.row_bytes + (size_t)u0 * UNIT, end = src + (size_t)kn * UNIT;
+                        const uintptr_t lim = base + (size_t)a.seg[t.seg].rows * a.row_bytes;
+                        uint8_t *drow = stages + (size_t)sc * a.stage_stride + (size_t)lane * a.pitch;
+                        a0 = src & ~(uintptr_t)15;
+                        uintptr_t e1 = (end + 15) & ~(uintptr_t)15;
+                        if (e1 > lim) {   // the tensor's last bytes: the copy stops at the last boundary, plain loads fetch the rest
+                            e1 = end & ~(uintptr_t)15;
+                            for (uintptr_t q = e1; q < end; q += 2)
+                                *reinterpret_cast<uint16_t *>(drow + (q - a0)) = *reinterpret_cast<const uint16_t *>(q);
+                        }
+                        bytes = (uint32_t)(e1 - a0);
+                        dst = smem_u32(drow);
+                    }
+                    const uint32_t total = __reduce_add_sync(0xffffffffu, bytes);
+                    __syncwarp();
+                    if (lane == 0) mbar_expect_tx(bar, total);
+                    __syncwarp();
+                    if (bytes) bulk_g2s(dst, reinterpret_cast<const void *>(a0), bytes, bar);
+                } else if (lane == 0) {
+                    const uint32_t dst = smem_u32(stages + (size_t)sc * a.stage_stride);
                     mbar_expect_tx(bar, a.box_bytes * (SWIGLU ? 2u : 1u));   // a box is always whole: what lies outside the tensor arrives as zeros
                     tma_box(dst, &a.map[t.seg][0], c * a.kc, t.row0, bar);
                     if constexpr (SWIGLU) tma_box(dst + a.half_stride, &a.map[t.seg][1], c * a.kc, t.row0, bar);
                 }
-                ++issued;
-                if (++s == a.nstages) { s = 0; ++k; }
             }
         }
-        if (lane == 0) stamp(a.trace, 1);
+        if (lane == 0 && pw == 0) stamp(a.trace, 1);
         // All of this CTA's rows are requested: pull the head of the next launch's weights into L2.
-        if (a.pf_ptr && ok) {
+        if (a.pf_ptr && ok && pw == 0) {
             const uint64_t per = (a.pf_bytes / gridDim.x) & ~(uint64_t)15;
             const uint8_t *p = a.pf_ptr + (uint64_t)blockIdx.x * per;
             for (uint64_t off = (uint64_t)lane * 32768; off < per; off += 32 * 32768) {
@@ -364,11 +544,9 @@ gemv_mma_kernel(const __grid_constant__ MmaArgs a)
                 bulk_prefetch_l2(p + off, (uint32_t)n);
             }
         }
-        if (!ok && lane == 0) {   // give copies still in flight a bounded time to land before this warp leaves
-            for (uint32_t q = 0; q < a.nstages && q < issued; ++q) {
-                const uint32_t last = ((issued - 1 - q) / a.nstages) * a.nstages + q;   // newest copy set issued into stage q
-                mbar_wait_bounded(smem_u32(full + q), (last / a.nstages) & 1u);
-            }
+        if (!ok && lane == 0) {   // give this warp's copies still in flight a bounded time to land before it leaves
+            for (uint32_t q = 0; q < a.nstages; ++q)
+                if (used_mask >> q & 1u) mbar_wait_bounded(smem_u32(full + q), par_mask >> q & 1u);
         }
         return;
     }
@@ -378,7 +556,10 @@ gemv_mma_kernel(const __grid_constant__ MmaArgs a)
     pdl_wait();   // x is the previous kernel's output
     if (tid == 0) stamp(a.trace, 2);
     uint8_t *xq = smem + a.xs_base;
-    quantize_x_mma<NP>(a.x, U, xq, warp, lane, CW);
+    quantize_x_mma<NP, Q6>(a.x, U, xq, warp, lane, CW);
+    if constexpr (Q6) {   // a block of zeros for lanes whose product column is empty
+        for (uint32_t z = tid; z < 768 / 4; z += C) reinterpret_cast<uint32_t *>(xq + (size_t)U * MMA_XQ_SB + 8 * U)[z] = 0u;
+    }
     named_bar_sync(PIPE_BAR_CONSUMERS, (int)C);
     if (tid == 0) stamp(a.trace, 3);
     const uint32_t xs_s = smem_u32(xq) + U * MMA_XQ_SB;                // xs[U], then sxs[U]
@@ -388,7 +569,15 @@ gemv_mma_kernel(const __grid_constant__ MmaArgs a)
     // columns 2t, 2t+1 of the products are byte planes 2t, 2t+1
     const float cw0 = t4 == 0 ? 1.0f : (t4 == 1 && NP == 3 ? 65536.0f : 0.0f), cw1 = t4 == 0 ? 256.0f : 0.0f;
 
-    const uint32_t CAP = a.red_rows, PLANE = CAP * NW;
+    // Q6_K: column g = (first / second 16 elements of a group, plane g % 3); lanes of unused columns read a block of zeros
+    const uint32_t q6_plane = g % 3u;
+    const bool q6_col = Q6 && g < 6u && q6_plane < (uint32_t)NP;
+    const uint32_t q6_bx = q6_col ? smem_u32(xq) + q6_plane * 32u + (g < 3u ? 0u : 16u) + t4 * 4u : xs_s + 8u * U;
+    const uint32_t q6_bstride = q6_col ? MMA_XQ_SB : 0u;
+    const uint32_t q6_sx = smem_u32(xq) + 768u + (g < 6u ? g : 0u) * 16u + t4 * 4u;
+    const Q6Lane q6l = q6_lane<NP>(t4);
+
+    const uint32_t CAP = a.red_rows, SLOTS = NW * NG, PLANE = CAP * SLOTS;   // every warp of every group leaves one partial sum per row
     uint32_t which = 0, buf_n = 0, buf_row0 = 0;
     int buf_seg = 0;
     auto flush = [&]() {
@@ -397,9 +586,9 @@ gemv_mma_kernel(const __grid_constant__ MmaArgs a)
         float *y = a.seg[buf_seg].y + buf_row0;
         for (uint32_t r = tid; r < buf_n; r += C) {
             float gsum = 0.0f, usum = 0.0f;
-            for (uint32_t w = 0; w < NW; ++w) {
-                gsum += src[r * NW + w];
-                if constexpr (SWIGLU) usum += src[PLANE + r * NW + w];
+            for (uint32_t w = 0; w < SLOTS; ++w) {
+                gsum += src[r * SLOTS + w];
+                if constexpr (SWIGLU) usum += src[PLANE + r * SLOTS + w];
             }
             y[r] = SWIGLU ? silu_mul(gsum, usum) : gsum;
         }
@@ -415,16 +604,14 @@ gemv_mma_kernel(const __grid_constant__ MmaArgs a)
     for (; mma_next_tile(a, cur, hi, seg, t); ++tile_no) {
         if (buf_n && (t.seg != buf_seg || buf_n + t.n > CAP)) flush();
         if (buf_n == 0) { buf_seg = t.seg; buf_row0 = t.row0; }
-        if (turn != group) {     // another group's tile: step over its stages
-            if (++turn == NG) turn = 0;
-            s += a.nchunks;
-            while (s >= a.nstages) { s -= a.nstages; parity ^= 1u; }
-            buf_n += t.n;
-            continue;
-        }
-        if (++turn == NG) turn = 0;
         float yg0 = 0.0f, yg1 = 0.0f, yu0 = 0.0f, yu1 = 0.0f;
         for (uint32_t c = 0; c < a.nchunks; ++c) {
+            const bool mine = turn == group;        // stages go round the groups
+            if (++turn == NG) turn = 0;
+            if (!mine) {
+                if (++s == a.nstages) { s = 0; parity ^= 1u; }
+                continue;
+            }
             if (c == 0) MMA_TILE_STAMP(a, tile_no, warp, 0);
             if (!s_abort && !mbar_wait_bounded(smem_u32(full + s), parity)) {
                 s_abort = 1;
@@ -434,17 +621,33 @@ gemv_mma_kernel(const __grid_constant__ MmaArgs a)
             if (i == 0 && tid == 0) stamp(a.trace, 5);
             const uint32_t u0 = c * a.kc, kn = U - u0 < a.kc ? U - u0 : a.kc;
             const uint32_t row_s = stages_s + s * a.stage_stride + g * a.pitch;
-            for (uint32_t u = wig; u < kn; u += NW) {
-                const uint32_t ug = u0 + u;
-                uint2 B[8];
-                const uint32_t xa = xq_s + ug * MMA_XQ_SB;
-                B[0] = lds64<0>(xa);   B[1] = lds64<96>(xa);  B[2] = lds64<192>(xa); B[3] = lds64<288>(xa);
-                B[4] = lds64<384>(xa); B[5] = lds64<480>(xa); B[6] = lds64<576>(xa); B[7] = lds64<672>(xa);
-                const float xsu = __uint_as_float(lds32<0>(xs_s + 4u * ug)), sxsu = __uint_as_float(lds32<0>(xs_s + 4u * (U + ug)));
-                const uint32_t h0 = row_s + u * UNIT, h1 = h0 + 8u * a.pitch;
-                mma_superblock<FMT>(h0, h1, t4, B, sx_s + ug * MMA_XQ_SB, xsu, sxsu, cw0, cw1, a.layout, yg0, yg1);
-                if constexpr (SWIGLU)
-                    mma_superblock<FMT>(h0 + a.half_stride, h1 + a.half_stride, t4, B, sx_s + ug * MMA_XQ_SB, xsu, sxsu, cw0, cw1, a.layout, yu0, yu1);
+            if constexpr (Q6) {
+                // where the two rows start inside their first 16-byte piece (the copies were widened to 16-byte boundaries)
+                const uint32_t wlo = (uint32_t)reinterpret_cast<uintptr_t>(a.seg[t.seg].w) + u0 * UNIT;
+                const uint32_t r0 = row_s + ((wlo + (t.row0 + g) * a.row_bytes) & 15u);
+                const uint32_t r1 = row_s + 8u * a.pitch + ((wlo + (t.row0 + g + 8u) * a.row_bytes) & 15u);
+                for (uint32_t u = wig; u < kn; u += NW) {
+                    const uint32_t ug = u0 + u;
+                    const float xsu = __uint_as_float(lds32<0>(xs_s + 4u * ug));
+                    const uint32_t sa = r0 + u * UNIT, sb = r1 + u * UNIT;
+                    if (__all_sync(0xffffffffu, ((sa | sb) & 2u) == 0u))
+                        mma_superblock_q6<true>(sa, sb, t4, q6_bx + ug * q6_bstride, g < 3u, q6_sx + ug * MMA_XQ_SB, xsu, q6l, yg0, yg1);
+                    else
+                        mma_superblock_q6<false>(sa, sb, t4, q6_bx + ug * q6_bstride, g < 3u, q6_sx + ug * MMA_XQ_SB, xsu, q6l, yg0, yg1);
+                }
+            } else {
+                for (uint32_t u = wig; u < kn; u += NW) {
+                    const uint32_t ug = u0 + u;
+                    uint2 B[8];
+                    const uint32_t xa = xq_s + ug * MMA_XQ_SB;
+                    B[0] = lds64<0>(xa);   B[1] = lds64<96>(xa);  B[2] = lds64<192>(xa); B[3] = lds64<288>(xa);
+                    B[4] = lds64<384>(xa); B[5] = lds64<480>(xa); B[6] = lds64<576>(xa); B[7] = lds64<672>(xa);
+                    const float xsu = __uint_as_float(lds32<0>(xs_s + 4u * ug)), sxsu = __uint_as_float(lds32<0>(xs_s + 4u * (U + ug)));
+                    const uint32_t h0 = row_s + u * UNIT, h1 = h0 + 8u * a.pitch;
+                    mma_superblock<FMT>(h0, h1, t4, B, sx_s + ug * MMA_XQ_SB, xsu, sxsu, cw0, cw1, a.layout, yg0, yg1);
+                    if constexpr (SWIGLU)
+                        mma_superblock<FMT>(h0 + a.half_stride, h1 + a.half_stride, t4, B, sx_s + ug * MMA_XQ_SB, xsu, sxsu, cw0, cw1, a.layout, yu0, yu1);
+                }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(empty + s));   // this warp is done reading the stage
@@ -459,9 +662,9 @@ gemv_mma_kernel(const __grid_constant__ MmaArgs a)
             yu0 += __shfl_xor_sync(0xffffffffu, yu0, 2); yu1 += __shfl_xor_sync(0xffffffffu, yu1, 2);
         }
         if (t4 == 0) {
-            float *dst = red + (size_t)which * PLANE * (SWIGLU ? 2 : 1) + (size_t)buf_n * NW + wig;
-            if (g < t.n) { dst[g * NW] = yg0; if constexpr (SWIGLU) dst[PLANE + g * NW] = yu0; }
-            if (g + 8 < t.n) { dst[(g + 8) * NW] = yg1; if constexpr (SWIGLU) dst[PLANE + (g + 8) * NW] = yu1; }
+            float *dst = red + (size_t)which * PLANE * (SWIGLU ? 2 : 1) + (size_t)buf_n * SLOTS + warp;
+            if (g < t.n) { dst[g * SLOTS] = yg0; if constexpr (SWIGLU) dst[PLANE + g * SLOTS] = yu0; }
+            if (g + 8 < t.n) { dst[(g + 8) * SLOTS] = yg1; if constexpr (SWIGLU) dst[PLANE + (g + 8) * SLOTS] = yu1; }
         }
         buf_n += t.n;
         MMA_TILE_STAMP(a, tile_no, warp, 2);

@@ -553,15 +553,16 @@ struct MmaPlan {
 
 // Dense single-GPU launches only: every tensor 16-byte aligned (rows are then 16-byte aligned too, as the row length
 // is a multiple of 16 bytes), no expert indirection, no peers.
-static bool mma_supported(const orome_cuda_ctx *c, int fmt, uint32_t in_dim)
+static bool mma_supported(const orome_cuda_ctx *c, int fmt, uint32_t in_dim, bool swiglu)
 {
-    return c->kquant_mma && !c->force_generic && c->g_world == 1 && (fmt == FMT_Q4_K || fmt == FMT_Q5_K) && in_dim % 256 == 0 && in_dim >= 256;
+    const bool fmt_ok = fmt == FMT_Q4_K || fmt == FMT_Q5_K || (fmt == FMT_Q6_K && !swiglu);
+    return c->kquant_mma && !c->force_generic && c->g_world == 1 && fmt_ok && in_dim % 256 == 0 && in_dim >= 256;
 }
 
 static int plan_mma(orome_cuda_ctx *c, int fmt, uint32_t in_dim, uint32_t total_rows, bool swiglu, MmaPlan &p)
 {
     MmaArgs &a = p.args;
-    const uint32_t unit = fmt == FMT_Q4_K ? 144u : 176u;
+    const uint32_t unit = fmt == FMT_Q4_K ? 144u : fmt == FMT_Q5_K ? 176u : 210u;
     a.in_dim = in_dim;
     a.units = in_dim / 256;
     a.row_bytes = a.units * unit;
@@ -575,19 +576,26 @@ static int plan_mma(orome_cuda_ctx *c, int fmt, uint32_t in_dim, uint32_t total_
     a.nwarps = (a.kc + rounds - 1) / rounds;
     p.grid = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)c->sm_count, (total_rows + MMA_TILE_ROWS - 1) / MMA_TILE_ROWS));
     const uint32_t share = (total_rows + p.grid - 1) / p.grid;
-    a.ngroups = share > MMA_TILE_ROWS ? MMA_MAX_GROUPS : 1;
-    p.threads = (int)(a.nwarps * a.ngroups + 1) * 32;
+    // stages (row tiles x chunks) go round the groups: as many groups as the warp budget and the CTA's stage count allow
+    const uint32_t cta_stages = (share + MMA_TILE_ROWS - 1) / MMA_TILE_ROWS * a.nchunks;
+    a.ngroups = std::max(1u, std::min(std::min<uint32_t>(MMA_MAX_GROUPS, MMA_MAX_CONSUMER_WARPS / a.nwarps), cta_stages));
+    p.threads = (int)(a.nwarps * a.ngroups + (fmt == FMT_Q6_K ? 2 : 1)) * 32;
     // box width in superblocks: the smallest kb >= kc with kb = 2 (mod 4), which makes the row pitch 32 or 96 (mod 128)
     const uint32_t kb = a.kc + ((6 - a.kc % 4) % 4);
     a.pitch = kb * unit;
+    if (fmt == FMT_Q6_K) {
+        // rows arrive by their own copies, widened to 16-byte boundaries (up to 15 bytes before and after the chunk)
+        a.pitch = (a.kc * unit + 30 + 15) / 16 * 16;
+        while (a.pitch % 128 != 16) a.pitch += 16;      // the quads of the eight rows of a load then read eight different four-bank groups
+    }
     a.box_bytes = MMA_TILE_ROWS * a.pitch;
     a.half_stride = MMA_TILE_ROWS * a.pitch;
     a.stage_stride = a.half_stride * (swiglu ? 2 : 1);
     a.red_base = 2 * 8 * PIPE_MAX_STAGES;
     a.red_rows = std::max<uint32_t>(MMA_TILE_ROWS, std::min<uint32_t>((share + MMA_TILE_ROWS - 1) / MMA_TILE_ROWS * MMA_TILE_ROWS, 128u));
-    const size_t red_bytes = (size_t)2 * a.red_rows * a.nwarps * (swiglu ? 2 : 1) * sizeof(float);
+    const size_t red_bytes = (size_t)2 * a.red_rows * a.nwarps * a.ngroups * (swiglu ? 2 : 1) * sizeof(float);
     a.xs_base = (uint32_t)((a.red_base + red_bytes + 127) / 128 * 128);
-    const size_t xq_bytes = (size_t)a.units * MMA_XQ_SB + (size_t)a.units * 8;
+    const size_t xq_bytes = (size_t)a.units * MMA_XQ_SB + (size_t)a.units * 8 + 768;   // planes and sums, two scales per superblock, a block of zeros
     a.stage_base = (uint32_t)((a.xs_base + xq_bytes + 127) / 128 * 128);
     const size_t budget = std::min<size_t>(228 * 1024 - 1024 - 256, (size_t)c->smem_optin - 256);
     if (budget < a.stage_base + a.stage_stride) return fail(OROME_ENOTSUP, "mma plan: in_dim %u does not fit shared memory", in_dim);
@@ -634,6 +642,7 @@ static int mma_tensor_map(orome_cuda_ctx *c, const uint8_t *w, uint32_t unit, ui
 static int mma_encode_maps(orome_cuda_ctx *c, int fmt, MmaPlan &p, bool swiglu)
 {
     MmaArgs &a = p.args;
+    if (fmt == FMT_Q6_K) return OROME_OK;        // no tensor map: 210-byte superblocks move by plain bulk copies
     const uint32_t unit = fmt == FMT_Q4_K ? 144u : 176u, kb = a.pitch / unit;
     for (int i = 0; i < a.nseg; ++i) {
         int rc = mma_tensor_map(c, a.seg[i].w, unit, a.units, a.seg[i].rows, kb, &a.map[i][0]);
@@ -680,6 +689,7 @@ static int launch_mma(orome_cuda_ctx *c, int fmt, MmaPlan &p, bool swiglu, cudaS
         if (swiglu) return b24 ? launch_mma_inst<FMT_Q4_K, 3, true>(c, p, st) : launch_mma_inst<FMT_Q4_K, 2, true>(c, p, st);
         return b24 ? launch_mma_inst<FMT_Q4_K, 3, false>(c, p, st) : launch_mma_inst<FMT_Q4_K, 2, false>(c, p, st);
     }
+    if (fmt == FMT_Q6_K) return b24 ? launch_mma_inst<FMT_Q6_K, 3, false>(c, p, st) : launch_mma_inst<FMT_Q6_K, 2, false>(c, p, st);
     if (swiglu) return b24 ? launch_mma_inst<FMT_Q5_K, 3, true>(c, p, st) : launch_mma_inst<FMT_Q5_K, 2, true>(c, p, st);
     return b24 ? launch_mma_inst<FMT_Q5_K, 3, false>(c, p, st) : launch_mma_inst<FMT_Q5_K, 2, false>(c, p, st);
 }
@@ -841,7 +851,7 @@ extern "C" int orome_cuda_matvec_group(orome_cuda_ctx *c, const OromeTensorRef *
     }
     bool aligned16 = true;
     for (int i = 0; i < n_refs; ++i) aligned16 = aligned16 && !(reinterpret_cast<uintptr_t>(data[i]) & 15);
-    if (aligned16 && mma_supported(c, fmt, refs[0].in_dim)) {
+    if ((aligned16 || fmt == FMT_Q6_K) && mma_supported(c, fmt, refs[0].in_dim, false)) {
         MmaPlan m;
         memset(&m, 0, sizeof m);
         uint32_t rows = 0;
@@ -1046,7 +1056,7 @@ extern "C" int orome_cuda_gate_up_swiglu(orome_cuda_ctx *c, const OromeTensorRef
     }
     if (batch == 1 && !c->force_generic && pipe_supported(fmt, gate->in_dim)) {
         if (reinterpret_cast<uintptr_t>(x_dev) & 15) return fail(OROME_EINVAL, "gate_up_swiglu: x must be 16-byte aligned");
-        if (!((reinterpret_cast<uintptr_t>(gd) | reinterpret_cast<uintptr_t>(ud)) & 15) && mma_supported(c, fmt, gate->in_dim)) {
+        if (!((reinterpret_cast<uintptr_t>(gd) | reinterpret_cast<uintptr_t>(ud)) & 15) && mma_supported(c, fmt, gate->in_dim, true)) {
             MmaPlan m;
             memset(&m, 0, sizeof m);
             m.args.seg[0] = PipeSeg{gd, ud, out_dev, gate->out_dim, 0};
