@@ -220,6 +220,11 @@ class Stepper:
         ctx, ds = self.ctx, self.ds
         H, A, KV, V = ds.hidden, ds.ffn, ds.kv, ds.vocab
         xh, xa = self.x_h.data_ptr(), self.x_a.data_ptr()
+        # fused gather: a product reads the gathered output of the one before it (that read IS the wait)
+        fz = self.fused
+        x_o = self.q.data_ptr() if fz else xh
+        x_gu = self.o.data_ptr() if fz else xh
+        x_dn = self.act.data_ptr() if fz else xa
         c0 = ctx.launch_count
         hint = ctx.hint_next if self.hints else (lambda r: None)
         gn = ctx.gather_next if self.fused else (lambda w, p: None)     # (counter to wait on, counter to publish)
@@ -230,7 +235,7 @@ class Stepper:
             hint(ro if ro.out_dim else None)
             if rq.out_dim and rk.out_dim and rv.out_dim:
                 gn(self.FLAG_DN if li else -1, self.FLAG_QKV)
-                ctx.matvec_group([rq, rk, rv], xh, [self._slice(self.q, H).data_ptr(), self._slice(self.k, KV).data_ptr(),
+                ctx.matvec_group([rq, rk, rv], self.dn.data_ptr() if fz and li else xh, [self._slice(self.q, H).data_ptr(), self._slice(self.k, KV).data_ptr(),
                                                     self._slice(self.v, KV).data_ptr()], stream)
             else:   # some rank holds no rows of a small tensor
                 for r, buf, n in ((rq, self.q, H), (rk, self.k, KV), (rv, self.v, KV)):
@@ -240,25 +245,25 @@ class Stepper:
             if ro.out_dim:
                 hint(rg)
                 gn(self.FLAG_QKV, self.FLAG_O)
-                ctx.matvec(ro, xh, self._slice(self.o, H).data_ptr(), 1, 0, 0, stream)
+                ctx.matvec(ro, x_o, self._slice(self.o, H).data_ptr(), 1, 0, 0, stream)
             self._gather(self.o, H)
             if rg.out_dim:
                 hint(rd)
                 gn(self.FLAG_O, self.FLAG_ACT)
-                ctx.gate_up_swiglu(rg, ru, xh, self._slice(self.act, A).data_ptr(), 1, 0, 0, stream)
+                ctx.gate_up_swiglu(rg, ru, x_gu, self._slice(self.act, A).data_ptr(), 1, 0, 0, stream)
             self._gather(self.act, A)
             if rd.out_dim:
                 hint(nxt_q if nxt_q.out_dim else None)
                 gn(self.FLAG_ACT, self.FLAG_DN)
-                ctx.matvec(rd, xa, self._slice(self.dn, H).data_ptr(), 1, 0, 0, stream)
+                ctx.matvec(rd, x_dn, self._slice(self.dn, H).data_ptr(), 1, 0, 0, stream)
             self._gather(self.dn, H)
         if self.lm_ref.out_dim:
             hint(self.refs[0][0] if nl and self.refs[0][0].out_dim else None)   # the next token starts at layer 0 again
             gn(self.FLAG_DN if nl else -1, self.FLAG_LOGITS)
-            ctx.matvec(self.lm_ref, xh, self._slice(self.logits, V).data_ptr(), 1, 0, 0, stream)
+            ctx.matvec(self.lm_ref, self.dn.data_ptr() if fz and nl else xh, self._slice(self.logits, V).data_ptr(), 1, 0, 0, stream)
         self._gather(self.logits, V)
         if self.fused:
-            ctx.gather_wait(self.FLAG_LOGITS, stream)     # the logits are complete on this rank from here on
+            ctx.gather_wait(self.FLAG_LOGITS, self.logits.data_ptr(), V, stream)     # the logits are complete on this rank from here on
         self.launches_per_step = ctx.launch_count - c0
 
     def capture(self):
@@ -517,7 +522,7 @@ def run_ours(args):
         "config": {"workload": args.workload, "batch": 1, "layers": ds.layers, "weight_bytes": w_bytes,
                    "l2": "inputs larger than L2: every layer has its own weights", "cuda_graph": bool(use_graph),
                    "parallelism": "single GPU" if world == 1 else
-                   (f"row-split x{world}, y completed by peer stores from the kernel epilogue (NVLink) + arrival counters" if st.fused
+                   (f"row-split x{world}, y completed by tagged peer stores from the kernel epilogue (NVLink), consumers poll the data" if st.fused
                     else f"row-split x{world} + all-gather (NCCL)")},
         "roofline": roofline,
         "e2e": {"value": e2e_tok_s, "unit": "tok/s", "h2d_bytes_per_step": ds.hidden * 4, "d2h_bytes_per_step": ds.vocab * 4,

@@ -234,20 +234,28 @@ int  orome_cuda_hint_next(orome_cuda_ctx *ctx, const OromeTensorRef *next);
  * No counterpart in the reference (single GPU, unified memory).  Output rows of a matvec are
  * independent, so rank r of `world` GPUs in one box keeps a slice of the rows of every tensor
  * and the full y must reach every GPU before the next product.  Instead of a collective after
- * the kernel, the kernel that produces a slice also stores every value into the same offset of
- * each peer's "gather arena" over NVLink (plain peer stores), and when its grid is done bumps
- * an arrival counter on each peer; the launch that consumes the vector waits on its own
- * counter (bounded: after 1 s it records status 3, see orome_cuda_status, and carries on).
+ * the kernel, the kernel that produces a slice stores every value, together with a generation
+ * tag in the same 8-byte store, into the same slot of its own and of each peer's "gather
+ * arena" over NVLink (plain peer stores).  The launch that consumes the vector reads x from
+ * those slots and polls each element until it carries the generation expected (bounded: after
+ * about a second it records status 3, see orome_cuda_status, and carries on).  No fence, no
+ * separate flag, no collective call.
  *
- * Set-up: every process allocates an arena with orome_cuda_peer_alloc, exchanges the 64-byte
- * handles by any host channel, opens the others with orome_cuda_peer_open and passes all
- * `world` pointers (its own included, at index rank) to orome_cuda_gather_setup.  The arena
- * holds data_bytes of buffers followed by n_flags counters.  Then, before a matvec / group /
- * gate-up launch, orome_cuda_gather_next(ctx, wait_flag, publish_flag) says which counter the
- * launch waits on before reading x (-1: none) and which one it bumps on the peers after
- * mirroring its y rows (-1: y stays local); it applies to the next launch only.  A published
- * launch must write y inside the local arena.  Each published round of a counter must be
- * consumed by exactly one later launch (or orome_cuda_gather_wait) on every rank. */
+ * Set-up: every process allocates an arena of orome_cuda_gather_arena_bytes(data_bytes, n_flags)
+ * bytes with orome_cuda_peer_alloc, exchanges the 64-byte handles by any host channel, opens the
+ * others with orome_cuda_peer_open and passes all `world` pointers (its own included, at index
+ * rank) to orome_cuda_gather_setup.  The first data_bytes of the arena hold the gathered vectors
+ * as plain floats (the caller places them), the rest their slots.  n_flags (<= 64) is the number
+ * of vectors in flight the caller tells apart ("flags"; each has a generation counter).
+ * Before a matvec / group / gate-up launch, orome_cuda_gather_next(ctx, wait_flag, publish_flag)
+ * says that the launch's x is the gathered vector published under wait_flag (-1: x is a plain
+ * vector) and that its y rows are to be published under publish_flag (-1: y stays local); it
+ * applies to the next launch only.  A waiting launch must take x from the local arena, a
+ * publishing launch must write y into it.  Every rank must run the same sequence of publishing
+ * launches per flag, and a flag may be published again only after every rank has consumed its
+ * previous generation.  orome_cuda_gather_wait(ctx, flag, vec, n, stream) completes the plain
+ * copy of a gathered vector (n floats at vec, inside the arena) for readers other than this
+ * library's kernels. */
 int  orome_cuda_peer_alloc(orome_cuda_ctx *ctx, size_t bytes, void **dev_ptr, unsigned char handle_out[64]);
 int  orome_cuda_peer_open(orome_cuda_ctx *ctx, const unsigned char handle[64], void **dev_ptr);
 int  orome_cuda_peer_close(orome_cuda_ctx *ctx, void *dev_ptr);
@@ -256,7 +264,7 @@ size_t orome_cuda_gather_arena_bytes(size_t data_bytes, int n_flags);
 int  orome_cuda_gather_next(orome_cuda_ctx *ctx, int wait_flag, int publish_flag);
 /* Enqueue a wait for one round of `flag` with nothing else attached (e.g. before copying the
  * gathered logits to the host). */
-int  orome_cuda_gather_wait(orome_cuda_ctx *ctx, int flag, void *stream);
+int  orome_cuda_gather_wait(orome_cuda_ctx *ctx, int flag, float *vec_dev, uint32_t n, void *stream);
 
 /* ---- host-buffer convenience (end-to-end form) --------------------------- */
 

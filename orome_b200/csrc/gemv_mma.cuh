@@ -57,6 +57,14 @@ struct MmaArgs {
     const uint8_t *pf_ptr;
     uint64_t pf_bytes;
     unsigned long long *trace;
+    // multi-GPU forms, as in PipeArgs: tagged {value, tag} slots in the gather arenas
+    int npeers;
+    long long peer_delta[PIPE_MAX_PEERS];
+    const uint8_t *arena_base;
+    uint8_t *ll_origin;
+    unsigned int *pub_gen, *pub_arrived;
+    const uint2 *x_ll;
+    const unsigned int *wait_gen;
 };
 
 template <int OFF>
@@ -322,10 +330,12 @@ __device__ __forceinline__ uint32_t plane_word(uint32_t u0, uint32_t u1, uint32_
 // and their shuffle reductions interleave.
 // Q6 form: instead of the float sums, the sums of the signed digits over every 16 elements, as two balanced bytes:
 // at +768 [plane p][low / high byte][16 groups].
+// With `slots` set x is a gathered vector read from its {value, tag} slots (polled for `tag`); false = a poll expired.
 template <int NP, bool Q6>
-__device__ __forceinline__ void quantize_x_mma(const float *__restrict__ x, uint32_t units, uint8_t *xq, uint32_t warp, uint32_t lane,
-                                               uint32_t nwarps)
+__device__ __forceinline__ bool quantize_x_mma(const float *__restrict__ x, uint32_t units, uint8_t *xq, uint32_t warp, uint32_t lane,
+                                               uint32_t nwarps, const uint2 *slots = nullptr, unsigned int tag = 0)
 {
+    bool ok = true;
     constexpr int QMAXI = NP == 3 ? 127 * 65536 + 127 * 256 + 127 : 127 * 256 + 127;
     constexpr float QMAX = (float)QMAXI;
     constexpr int XB = 4;
@@ -336,8 +346,14 @@ __device__ __forceinline__ void quantize_x_mma(const float *__restrict__ x, uint
         for (int b = 0; b < XB; ++b) {
             const uint32_t u = ub + b * nwarps;
             const float4 *src = reinterpret_cast<const float4 *>(x + (size_t)u * 256) + 2 * lane;
-            v0[b] = u < units ? __ldcg(src) : make_float4(0.f, 0.f, 0.f, 0.f);
-            v1[b] = u < units ? __ldcg(src + 1) : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (slots) {
+                const uint2 *sl = slots + (size_t)u * 256 + 8 * lane;
+                v0[b] = u < units ? ld_gathered4(sl, tag, &ok) : make_float4(0.f, 0.f, 0.f, 0.f);
+                v1[b] = u < units ? ld_gathered4(sl + 4, tag, &ok) : make_float4(0.f, 0.f, 0.f, 0.f);
+            } else {
+                v0[b] = u < units ? __ldcg(src) : make_float4(0.f, 0.f, 0.f, 0.f);
+                v1[b] = u < units ? __ldcg(src + 1) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
         }
         float amax[XB], sum[XB], smax[XB];
 #pragma unroll
@@ -398,6 +414,7 @@ __device__ __forceinline__ void quantize_x_mma(const float *__restrict__ x, uint
             if (lane == 0) { xs[u] = amax[b] / QMAX; sxs[u] = smax[b] / QMAX; }
         }
     }
+    return ok;
 }
 
 // One box: words 0.. of superblocks sb0.. of rows row0..row0+15 (coordinates in elements of the tensor map).
@@ -437,7 +454,7 @@ __device__ __forceinline__ bool mma_next_tile(const MmaArgs &a, uint32_t &cur, u
     return true;
 }
 
-template <int FMT, int NP, bool SWIGLU>
+template <int FMT, int NP, bool SWIGLU, bool EXT>
 __global__ void __launch_bounds__(MMA_MAX_THREADS, 1)
 gemv_mma_kernel(const __grid_constant__ MmaArgs a)
 {
@@ -556,7 +573,15 @@ gemv_mma_kernel(const __grid_constant__ MmaArgs a)
     pdl_wait();   // x is the previous kernel's output
     if (tid == 0) stamp(a.trace, 2);
     uint8_t *xq = smem + a.xs_base;
-    quantize_x_mma<NP, Q6>(a.x, U, xq, warp, lane, CW);
+    {
+        const uint2 *slots = EXT ? a.x_ll : nullptr;
+        const unsigned int want = EXT && a.x_ll ? *reinterpret_cast<const volatile unsigned int *>(a.wait_gen) : 0u;
+        if (!quantize_x_mma<NP, Q6>(a.x, U, xq, warp, lane, CW, slots, want)) {
+            s_abort = 1;
+            atomicExch(a.status, 3);
+        }
+    }
+    const unsigned int pub_tag = EXT && a.npeers > 0 ? *reinterpret_cast<const volatile unsigned int *>(a.pub_gen) + 1u : 0u;
     if constexpr (Q6) {   // a block of zeros for lanes whose product column is empty
         for (uint32_t z = tid; z < 768 / 4; z += C) reinterpret_cast<uint32_t *>(xq + (size_t)U * MMA_XQ_SB + 8 * U)[z] = 0u;
     }
@@ -590,7 +615,15 @@ gemv_mma_kernel(const __grid_constant__ MmaArgs a)
                 gsum += src[r * SLOTS + w];
                 if constexpr (SWIGLU) usum += src[PLANE + r * SLOTS + w];
             }
-            y[r] = SWIGLU ? silu_mul(gsum, usum) : gsum;
+            const float val = SWIGLU ? silu_mul(gsum, usum) : gsum;
+            y[r] = val;
+            if constexpr (EXT) {
+                if (a.npeers > 0) {
+                    uint8_t *slot = a.ll_origin + 2 * (reinterpret_cast<const uint8_t *>(y + r) - a.arena_base);
+                    st_slot(reinterpret_cast<uint2 *>(slot), val, pub_tag);
+                    for (int p = 0; p < a.npeers; ++p) st_slot(reinterpret_cast<uint2 *>(slot + a.peer_delta[p]), val, pub_tag);
+                }
+            }
         }
         which ^= 1u;
         buf_n = 0;
@@ -671,6 +704,12 @@ gemv_mma_kernel(const __grid_constant__ MmaArgs a)
     }
     if (tid == 0) stamp(a.trace, 6);
     if (buf_n) flush();
+    if (EXT && a.npeers > 0) {
+        if (tid == 0 && atomicAdd(a.pub_arrived, 1u) == gridDim.x - 1) {   // last CTA: the new generation becomes current
+            *reinterpret_cast<volatile unsigned int *>(a.pub_arrived) = 0;
+            *reinterpret_cast<volatile unsigned int *>(a.pub_gen) = pub_tag;
+        }
+    }
     if (tid == 0) stamp(a.trace, 7);
 }
 

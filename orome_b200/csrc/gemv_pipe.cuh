@@ -85,19 +85,22 @@ struct PipeArgs {
     const float *seg_weight;   // [nseg]
     uint32_t acc_base;         // offset of the fp32 accumulators of the CTA's rows
     uint32_t xq_vec_bytes;     // bytes of one quantized input vector in shared memory
-    // Multi-GPU (row-split) forms.  Publishing: every y value is also stored at the same offset of each peer's
-    // gather arena (peer address = local address + peer_delta[p]); when the whole grid is done, the last CTA adds 1
-    // to pub_flag[p] on every peer.  Waiting: before x is read, the launch waits until wait_flag has advanced by
-    // wait_need since wait_seen, then the last CTA to get through advances wait_seen.  All counters live in device
+    // Multi-GPU (row-split) forms.  A gathered vector lives in every rank's gather arena as 8-byte slots
+    // {value, tag}: slot of the float at arena address A = ll_origin + 2 * (A - arena_base).  Publishing: every y
+    // value goes, with tag = *pub_gen + 1, into the local slot and into the same slot of each peer (peer address =
+    // local address + peer_delta[p]); the last CTA of the grid then stores the tag to *pub_gen.  Value and tag
+    // travel in one 8-byte store, so no fence and no separate flag are needed.  Waiting: x is read from its slots
+    // (x_ll) and every element is polled until its tag equals *wait_gen -- this rank published its own slice of
+    // that vector with the same tag in an earlier launch of the stream.  The generation words live in device
     // memory, so a captured graph can be replayed.
     int npeers;
     long long peer_delta[PIPE_MAX_PEERS];
-    unsigned int *pub_flag[PIPE_MAX_PEERS];   // the peers' arrival counters (peer memory)
-    unsigned int *pub_arrived;                // local: CTAs of this launch that finished publishing
-    unsigned int *wait_flag;                  // local: bumped by the peers
-    unsigned int *wait_seen;                  // local: value of wait_flag consumed so far
-    unsigned int *wait_arrived;               // local: CTAs of this launch that got through the wait
-    unsigned int wait_need;                   // world - 1
+    const uint8_t *arena_base;                // this rank's arena
+    uint8_t *ll_origin;                       // its slot region
+    unsigned int *pub_gen;                    // generation of the vector being published
+    unsigned int *pub_arrived;                // CTAs of this launch that finished publishing
+    const uint2 *x_ll;                        // slots of x, or NULL when x is a plain vector
+    const unsigned int *wait_gen;             // generation x must carry
 };
 
 // ---- PTX wrappers ---------------------------------------------------------
@@ -146,28 +149,31 @@ __device__ __forceinline__ void stamp(unsigned long long *trace, int k)
 {
     if (trace) trace[(size_t)blockIdx.x * 8 + k] = global_ns();
 }
-__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int *p)
+// Two {value, tag} slots in one 16-byte load that is not served from L1 (the peers write these slots).
+__device__ __forceinline__ uint4 ld_slots2(const uint2 *p)
 {
-    unsigned int v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
     return v;
 }
-__device__ __forceinline__ void red_release_sys_add(unsigned int *p, unsigned int v)
+__device__ __forceinline__ void st_slot(uint2 *p, float v, unsigned int tag)
 {
-    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+    asm volatile("st.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(tag) : "memory");
 }
-// Wait until *flag has advanced by `need` since `seen`, at most PIPE_WAIT_CYCLES.  Returns false on expiry.
-// The bound is kept on the SM's own cycle counter: reading the global nanosecond timer costs far more than a poll.
-__device__ __forceinline__ bool flag_wait_bounded(const unsigned int *flag, unsigned int seen, unsigned int need)
+// Four consecutive floats of a gathered vector from their slots, polled until all four carry `tag`
+// (at most PIPE_WAIT_CYCLES; *ok is cleared on expiry and whatever is there is returned).
+__device__ __forceinline__ float4 ld_gathered4(const uint2 *slots, unsigned int tag, bool *ok)
 {
-    if (ld_acquire_sys(flag) - seen >= need) return true;
-    const long long t0 = clock64();
-    for (;;) {
-#pragma unroll 1
-        for (int i = 0; i < 32; ++i)
-            if (ld_acquire_sys(flag) - seen >= need) return true;
-        if (clock64() - t0 > PIPE_WAIT_CYCLES) return false;
+    uint4 a = ld_slots2(slots), b = ld_slots2(slots + 2);
+    if (a.y != tag || a.w != tag || b.y != tag || b.w != tag) {
+        const long long t0 = clock64();
+        for (;;) {
+            a = ld_slots2(slots); b = ld_slots2(slots + 2);
+            if (a.y == tag && a.w == tag && b.y == tag && b.w == tag) break;
+            if (clock64() - t0 > PIPE_WAIT_CYCLES) { *ok = false; break; }
+        }
     }
+    return make_float4(__uint_as_float(a.x), __uint_as_float(a.z), __uint_as_float(b.x), __uint_as_float(b.z));
 }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
@@ -305,10 +311,14 @@ __device__ __forceinline__ void dot_s(uint32_t q, const XGroup<NP, N> &g, int k,
 // consecutive floats, a group of G elements is G/4 adjacent lanes.
 // `nvec` vectors of in_dim floats, x_stride floats apart, are quantized in one pass (all loads of a batch are in
 // flight together); vector v goes to xq + v * vec_bytes.  in_dim is a multiple of 32, so groups never straddle vectors.
+// With `slots` set, x is a gathered vector: its elements come from {value, tag} slots and are polled for `tag`;
+// the return value is false when a poll expired.
 template <int NP, int G, bool SUMS>
-__device__ __forceinline__ void quantize_x_to_smem(const float *__restrict__ x, uint32_t in_dim, uint32_t nvec, uint32_t x_stride,
-                                                   uint8_t *xq0, uint32_t vec_bytes, uint32_t tid, uint32_t nthreads)
+__device__ __forceinline__ bool quantize_x_to_smem(const float *__restrict__ x, uint32_t in_dim, uint32_t nvec, uint32_t x_stride,
+                                                   uint8_t *xq0, uint32_t vec_bytes, uint32_t tid, uint32_t nthreads,
+                                                   const uint2 *slots = nullptr, unsigned int tag = 0)
 {
+    bool ok = true;
     constexpr float QMAX = NP == 3 ? 8388607.0f : 32767.0f;
     constexpr int BATCH = 8;
     const uint32_t n4 = in_dim / 4, n4_all = n4 * nvec, lane = tid & 31u;
@@ -318,7 +328,8 @@ __device__ __forceinline__ void quantize_x_to_smem(const float *__restrict__ x, 
         for (int b = 0; b < BATCH; ++b) {
             const uint32_t fa = base + b * nthreads + lane;
             const uint32_t vec = nvec == 1 ? 0u : fa / n4, fl = fa - vec * n4;      // no division on the single-vector path
-            v[b] = fa < n4_all ? __ldcg(reinterpret_cast<const float4 *>(x + (size_t)vec * x_stride) + fl) : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (slots) v[b] = fa < n4_all ? ld_gathered4(slots + 4 * (size_t)fl, tag, &ok) : make_float4(0.f, 0.f, 0.f, 0.f);
+            else v[b] = fa < n4_all ? __ldcg(reinterpret_cast<const float4 *>(x + (size_t)vec * x_stride) + fl) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
 #pragma unroll
         for (int b = 0; b < BATCH; ++b) {
@@ -359,6 +370,7 @@ __device__ __forceinline__ void quantize_x_to_smem(const float *__restrict__ x, 
             }
         }
     }
+    return ok;
 }
 
 // 16 (8) bytes from a shared address that is only 2-byte aligned: aligned words around it, fixed up with prmt.
@@ -746,30 +758,19 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
     const uint32_t unit = j % U;
 
     pdl_wait();   // x is the previous kernel's output
-    if (EXT && a.wait_flag) {
-        // x is completed by the peers' stores: wait for their arrival counts (one thread polls, the barrier and the
-        // acquire load order everybody's reads of x behind it)
-        if (tid == 0) {
-            const unsigned int seen = *reinterpret_cast<volatile unsigned int *>(a.wait_seen);
-            if (!flag_wait_bounded(a.wait_flag, seen, a.wait_need)) {
-                s_abort = 1;
-                atomicExch(a.status, 3);
-            }
-            __threadfence();
-            if (atomicAdd(a.wait_arrived, 1u) == gridDim.x - 1) {   // last CTA through: consume this round of arrivals
-                *reinterpret_cast<volatile unsigned int *>(a.wait_arrived) = 0;
-                *reinterpret_cast<volatile unsigned int *>(a.wait_seen) = seen + a.wait_need;
-                __threadfence();
-            }
-        }
-        named_bar_sync(PIPE_BAR_CONSUMERS, (int)C);
-    }
     if (tid == 0) stamp(a.trace, 2);
 
     SlotT slot;
     {
         uint8_t *xq = smem + a.xs_base;
-        quantize_x_to_smem<NP, SlotT::GROUP, SlotT::SUMS>(a.x, a.in_dim, COMBINE ? (uint32_t)a.nseg : 1u, a.x_stride, xq, a.xq_vec_bytes, tid, C);
+        // a gathered x: every element is polled for the generation this rank gave its own slice (visible after the wait above)
+        const uint2 *slots = EXT ? a.x_ll : nullptr;
+        const unsigned int want = EXT && a.x_ll ? *reinterpret_cast<const volatile unsigned int *>(a.wait_gen) : 0u;
+        if (!quantize_x_to_smem<NP, SlotT::GROUP, SlotT::SUMS>(a.x, a.in_dim, COMBINE ? (uint32_t)a.nseg : 1u, a.x_stride, xq, a.xq_vec_bytes, tid, C,
+                                                               slots, want)) {
+            s_abort = 1;
+            atomicExch(a.status, 3);
+        }
         named_bar_sync(PIPE_BAR_CONSUMERS, (int)C);
         if (tid == 0) stamp(a.trace, 3);
         if constexpr (!COMBINE) {
@@ -781,6 +782,7 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
     // Per-row partial sums (one per warp of the row's group) collect in shared memory and are added up, a whole
     // batch of rows at a time, by all consumer threads: one consumer-wide barrier per batch, coalesced stores of y.
     // Two buffers alternate, so the barrier that opens a flush also protects the buffer written two flushes ago.
+    const unsigned int pub_tag = EXT && a.npeers > 0 ? *reinterpret_cast<const volatile unsigned int *>(a.pub_gen) + 1u : 0u;
     const uint32_t CAP = a.red_rows, PLANE = CAP * GW;                 // floats per buffer (per tensor)
     PipeWalk wk;
     walk_init<COMBINE>(a, wk);
@@ -806,8 +808,11 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
                 const float val = SWIGLU ? silu_mul(g, u) : g;
                 y[r] = val;
                 if constexpr (EXT) {
-                    for (int p = 0; p < a.npeers; ++p)
-                        *reinterpret_cast<float *>(reinterpret_cast<char *>(y + r) + a.peer_delta[p]) = val;
+                    if (a.npeers > 0) {
+                        uint8_t *slot = a.ll_origin + 2 * (reinterpret_cast<const uint8_t *>(y + r) - a.arena_base);
+                        st_slot(reinterpret_cast<uint2 *>(slot), val, pub_tag);
+                        for (int p = 0; p < a.npeers; ++p) st_slot(reinterpret_cast<uint2 *>(slot + a.peer_delta[p]), val, pub_tag);
+                    }
                 }
             }
         }
@@ -873,22 +878,20 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
             float *dst = a.seg[0].y + wk.lo + r;
             *dst = accbuf[r];
             if constexpr (EXT) {
-                for (int p = 0; p < a.npeers; ++p) *reinterpret_cast<float *>(reinterpret_cast<char *>(dst) + a.peer_delta[p]) = accbuf[r];
+                if (a.npeers > 0) {
+                    uint8_t *slot = a.ll_origin + 2 * (reinterpret_cast<const uint8_t *>(dst) - a.arena_base);
+                    st_slot(reinterpret_cast<uint2 *>(slot), accbuf[r], pub_tag);
+                    for (int p = 0; p < a.npeers; ++p) st_slot(reinterpret_cast<uint2 *>(slot + a.peer_delta[p]), accbuf[r], pub_tag);
+                }
             }
         }
     }
     if (EXT && a.npeers > 0) {
-        // the barrier orders every consumer thread's peer stores before thread 0, whose system-scope fence then
-        // covers them all (one fence per CTA, not one per thread); thread 0 counts this CTA in and the last CTA of
-        // the grid tells every peer that this rank's slice has landed
-        named_bar_sync(PIPE_BAR_CONSUMERS, (int)C);
-        if (tid == 0) {
-            __threadfence_system();
-            if (atomicAdd(a.pub_arrived, 1u) == gridDim.x - 1) {
-                *reinterpret_cast<volatile unsigned int *>(a.pub_arrived) = 0;
-                __threadfence_system();
-                for (int p = 0; p < a.npeers; ++p) red_release_sys_add(a.pub_flag[p], 1u);
-            }
+        // the last CTA to get here makes the new generation this rank's current one; a launch that consumes the
+        // vector reads it after its griddepcontrol.wait, i.e. after this grid has completed
+        if (tid == 0 && atomicAdd(a.pub_arrived, 1u) == gridDim.x - 1) {
+            *reinterpret_cast<volatile unsigned int *>(a.pub_arrived) = 0;
+            *reinterpret_cast<volatile unsigned int *>(a.pub_gen) = pub_tag;
         }
     }
     if (tid == 0) stamp(a.trace, 7);

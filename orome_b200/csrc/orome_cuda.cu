@@ -50,7 +50,7 @@ struct orome_cuda_ctx {
     int g_rank = 0, g_world = 1, g_nflags = 0;
     uint8_t *g_arena[8] = {nullptr};          // every rank's arena as mapped in this process
     size_t g_data_bytes = 0;
-    unsigned int *g_local = nullptr;          // [n_flags] seen + pub_arrived + wait_arrived (local device memory)
+    unsigned int *g_local = nullptr;          // [n_flags] generation of each gathered vector, then the publish arrival counter
     int g_wait = -1, g_publish = -1;          // request for the next pipelined launch
     unsigned long long *trace_dev = nullptr;   // diagnostics buffer [trace_cap][sm_count][8]
     int trace_cap = 0, trace_next = 0;
@@ -385,6 +385,40 @@ static bool pipe_supported(int fmt, uint32_t in_dim)
     return false;
 }
 
+// Multi-GPU: turn the request left by orome_cuda_gather_next into the launch's publish / wait fields.
+template <typename Args>
+static int arm_gather(orome_cuda_ctx *c, Args &a, uint32_t in_dim)
+{
+    a.npeers = 0;
+    a.x_ll = nullptr;
+    if (c->g_world > 1) {
+        uint8_t *mine = c->g_arena[c->g_rank];
+        a.arena_base = mine;
+        a.ll_origin = mine + c->g_data_bytes;
+        if (c->g_publish >= 0) {
+            int n = 0;
+            for (int r = 0; r < c->g_world; ++r) {
+                if (r == c->g_rank) continue;
+                a.peer_delta[n++] = (long long)(c->g_arena[r] - mine);
+            }
+            a.npeers = n;
+            a.pub_gen = c->g_local + c->g_publish;
+            a.pub_arrived = c->g_local + c->g_nflags;
+        }
+        if (c->g_wait >= 0) {
+            const uint8_t *xb = reinterpret_cast<const uint8_t *>(a.x);
+            if (xb < mine || xb + (size_t)in_dim * 4 > mine + c->g_data_bytes || ((xb - mine) & 15)) {
+                c->g_wait = c->g_publish = -1;
+                return fail(OROME_EINVAL, "a launch that waits for a gathered vector must read x from the gather arena (16-byte aligned)");
+            }
+            a.x_ll = reinterpret_cast<const uint2 *>(a.ll_origin + 2 * (size_t)(xb - mine));
+            a.wait_gen = c->g_local + c->g_wait;
+        }
+        c->g_wait = c->g_publish = -1;
+    }
+    return OROME_OK;
+}
+
 // Fill everything of the plan except the segments' pointers.
 static int plan_pipe(orome_cuda_ctx *c, int fmt, uint32_t in_dim, uint32_t total_rows, int mode, PipePlan &p)
 {
@@ -446,28 +480,9 @@ static int plan_pipe(orome_cuda_ctx *c, int fmt, uint32_t in_dim, uint32_t total
     a.status = c->status_dev;
     a.trace = nullptr;
     if (c->trace_dev && c->trace_next < c->trace_cap) a.trace = c->trace_dev + (size_t)(c->trace_next++) * c->sm_count * 8;
-    a.npeers = 0;
-    a.wait_flag = nullptr;
-    if (c->g_world > 1) {
-        constexpr size_t FLAG_STRIDE = 32;   // counters sit 128 bytes apart
-        if (c->g_publish >= 0) {
-            int n = 0;
-            for (int r = 0; r < c->g_world; ++r) {
-                if (r == c->g_rank) continue;
-                a.peer_delta[n] = (long long)(c->g_arena[r] - c->g_arena[c->g_rank]);
-                a.pub_flag[n] = reinterpret_cast<unsigned int *>(c->g_arena[r] + c->g_data_bytes) + (size_t)c->g_publish * FLAG_STRIDE;
-                ++n;
-            }
-            a.npeers = n;
-            a.pub_arrived = c->g_local + c->g_nflags;
-        }
-        if (c->g_wait >= 0) {
-            a.wait_flag = reinterpret_cast<unsigned int *>(c->g_arena[c->g_rank] + c->g_data_bytes) + (size_t)c->g_wait * FLAG_STRIDE;
-            a.wait_seen = c->g_local + c->g_wait;
-            a.wait_arrived = c->g_local + c->g_nflags + 1;
-            a.wait_need = (unsigned int)(c->g_world - 1);
-        }
-        c->g_wait = c->g_publish = -1;
+    {
+        int rc = arm_gather(c, a, in_dim);
+        if (rc) return rc;
     }
     a.pf_ptr = c->hint_ptr;
     a.pf_bytes = c->hint_bytes;
@@ -507,7 +522,7 @@ static int launch_pipe_ext(orome_cuda_ctx *c, const PipePlan &p, cudaStream_t st
 template <int FMT, int NP, int MODE, int MINB>
 static int launch_pipe_inst(orome_cuda_ctx *c, const PipePlan &p, cudaStream_t st)
 {
-    const bool ext = p.args.seg_expert || p.args.npeers > 0 || p.args.wait_flag;
+    const bool ext = p.args.seg_expert || p.args.npeers > 0 || p.args.x_ll;
     if constexpr (MODE == 2) return launch_pipe_ext<FMT, NP, MODE, MINB, true>(c, p, st);
     else return ext ? launch_pipe_ext<FMT, NP, MODE, MINB, true>(c, p, st) : launch_pipe_ext<FMT, NP, MODE, MINB, false>(c, p, st);
 }
@@ -556,7 +571,7 @@ struct MmaPlan {
 static bool mma_supported(const orome_cuda_ctx *c, int fmt, uint32_t in_dim, bool swiglu)
 {
     const bool fmt_ok = fmt == FMT_Q4_K || fmt == FMT_Q5_K || (fmt == FMT_Q6_K && !swiglu);
-    return c->kquant_mma && !c->force_generic && c->g_world == 1 && fmt_ok && in_dim % 256 == 0 && in_dim >= 256;
+    return c->kquant_mma && !c->force_generic && fmt_ok && in_dim % 256 == 0 && in_dim >= 256;
 }
 
 static int plan_mma(orome_cuda_ctx *c, int fmt, uint32_t in_dim, uint32_t total_rows, bool swiglu, MmaPlan &p)
@@ -612,7 +627,7 @@ static int plan_mma(orome_cuda_ctx *c, int fmt, uint32_t in_dim, uint32_t total_
     a.pf_bytes = c->hint_bytes;
     c->hint_ptr = nullptr;
     c->hint_bytes = 0;
-    return OROME_OK;
+    return arm_gather(c, a, in_dim);
 }
 
 // Tensor map of one K-quant tensor for the boxes above: {words of a superblock, superblocks of a row, rows}.
@@ -652,10 +667,10 @@ static int mma_encode_maps(orome_cuda_ctx *c, int fmt, MmaPlan &p, bool swiglu)
     return OROME_OK;
 }
 
-template <int FMT, int NP, bool SWIGLU>
-static int launch_mma_inst(orome_cuda_ctx *c, const MmaPlan &p, cudaStream_t st)
+template <int FMT, int NP, bool SWIGLU, bool EXT>
+static int launch_mma_ext(orome_cuda_ctx *c, const MmaPlan &p, cudaStream_t st)
 {
-    auto kern = gemv_mma_kernel<FMT, NP, SWIGLU>;
+    auto kern = gemv_mma_kernel<FMT, NP, SWIGLU, EXT>;
     static size_t configured[64] = {0};   // per device: dynamic shared memory opted in so far
     if (configured[c->device] < p.smem) {
         cudaFuncAttributes fa;
@@ -678,6 +693,12 @@ static int launch_mma_inst(orome_cuda_ctx *c, const MmaPlan &p, cudaStream_t st)
     CU(cudaLaunchKernelEx(&cfg, kern, p.args));
     ++c->launches;
     return OROME_OK;
+}
+
+template <int FMT, int NP, bool SWIGLU>
+static int launch_mma_inst(orome_cuda_ctx *c, const MmaPlan &p, cudaStream_t st)
+{
+    return p.args.npeers > 0 || p.args.x_ll ? launch_mma_ext<FMT, NP, SWIGLU, true>(c, p, st) : launch_mma_ext<FMT, NP, SWIGLU, false>(c, p, st);
 }
 
 static int launch_mma(orome_cuda_ctx *c, int fmt, MmaPlan &p, bool swiglu, cudaStream_t st)
@@ -718,7 +739,8 @@ static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the ABI passes IPC handles as 6
 
 extern "C" size_t orome_cuda_gather_arena_bytes(size_t data_bytes, int n_flags)
 {
-    return (data_bytes + 255) / 256 * 256 + (size_t)std::max(n_flags, 0) * 128 + 256;
+    (void)n_flags;     // the generations live in local device memory, not in the arena
+    return 3 * ((data_bytes + 255) / 256 * 256) + 256;   // the vectors as plain floats, then their {value, tag} slots
 }
 
 extern "C" int orome_cuda_peer_alloc(orome_cuda_ctx *c, size_t bytes, void **dev_ptr, unsigned char handle_out[64])
@@ -792,25 +814,31 @@ extern "C" int orome_cuda_gather_next(orome_cuda_ctx *c, int wait_flag, int publ
     return OROME_OK;
 }
 
-// One thread: wait (bounded) for one round of arrivals on `flag`, then consume it.
-__global__ void gather_wait_kernel(const unsigned int *flag, unsigned int *seen, unsigned int need, int *status)
+// Copies a gathered vector from its {value, tag} slots to its plain place in the arena, polling every element
+// (bounded) for the generation this rank published last under the flag.
+__global__ void __launch_bounds__(256) gather_unpack_kernel(const uint2 *slots, float *dst, uint32_t n4, const unsigned int *gen, int *status)
 {
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const unsigned int s = *reinterpret_cast<volatile unsigned int *>(seen);
-    if (!flag_wait_bounded(flag, s, need)) atomicExch(status, 3);
-    *reinterpret_cast<volatile unsigned int *>(seen) = s + need;
-    __threadfence();
+    const unsigned int tag = *reinterpret_cast<const volatile unsigned int *>(gen);
+    bool ok = true;
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += gridDim.x * blockDim.x)
+        reinterpret_cast<float4 *>(dst)[i] = ld_gathered4(slots + 4 * (size_t)i, tag, &ok);
+    if (!ok) atomicExch(status, 3);
 }
 
-extern "C" int orome_cuda_gather_wait(orome_cuda_ctx *c, int flag, void *stream)
+extern "C" int orome_cuda_gather_wait(orome_cuda_ctx *c, int flag, float *vec_dev, uint32_t n, void *stream)
 {
     if (!c) return fail(OROME_EINVAL, "gather_wait: NULL ctx");
     if (c->g_world < 2) return OROME_OK;
     if (flag < 0 || flag >= c->g_nflags) return fail(OROME_EINVAL, "gather_wait: flag %d of %d", flag, c->g_nflags);
+    uint8_t *mine = c->g_arena[c->g_rank], *v = reinterpret_cast<uint8_t *>(vec_dev);
+    if (!vec_dev || n % 4 || v < mine || v + (size_t)n * 4 > mine + c->g_data_bytes || ((v - mine) & 15))
+        return fail(OROME_EINVAL, "gather_wait: the vector must lie in the gather arena, 16-byte aligned, a multiple of 4 long");
     CU(cudaSetDevice(c->device));
-    const unsigned int *f = reinterpret_cast<unsigned int *>(c->g_arena[c->g_rank] + c->g_data_bytes) + (size_t)flag * 32;
-    return launch_pdl(c, "gather_wait", gather_wait_kernel, dim3(1), dim3(1), static_cast<cudaStream_t>(stream), f, c->g_local + flag,
-                      (unsigned int)(c->g_world - 1), c->status_dev);
+    const uint2 *slots = reinterpret_cast<const uint2 *>(mine + c->g_data_bytes + 2 * (size_t)(v - mine));
+    const unsigned blocks = std::max(1u, std::min((n / 4 + 255) / 256, (unsigned)c->sm_count));
+    return launch_pdl(c, "gather_unpack", gather_unpack_kernel, dim3(blocks), dim3(256), static_cast<cudaStream_t>(stream), slots, vec_dev,
+                      n / 4, (const unsigned int *)(c->g_local + flag), c->status_dev);
 }
 
 // ---------------------------------------------------------------------------

@@ -93,7 +93,7 @@ def lib():
     L.orome_cuda_gather_arena_bytes.argtypes = [sz, i32]
     L.orome_cuda_gather_arena_bytes.restype = sz
     L.orome_cuda_gather_next.argtypes = [vp, i32, i32]
-    L.orome_cuda_gather_wait.argtypes = [vp, i32, vp]
+    L.orome_cuda_gather_wait.argtypes = [vp, i32, vp, u32, vp]
     L.orome_cuda_trace_begin.argtypes = [vp, i32]
     L.orome_cuda_trace_read.argtypes = [vp, vp, sz]
     L.orome_cuda_launch_count.argtypes = [vp]
@@ -196,8 +196,9 @@ class Context:
     def gather_next(self, wait_flag: int = -1, publish_flag: int = -1):
         _chk(lib().orome_cuda_gather_next(self._h, wait_flag, publish_flag))
 
-    def gather_wait(self, flag: int, stream: int = 0):
-        _chk(lib().orome_cuda_gather_wait(self._h, flag, stream))
+    def gather_wait(self, flag: int, vec_ptr: int, n: int, stream: int = 0):
+        """Complete the plain copy of the gathered vector of `n` floats at `vec_ptr` (inside the arena)."""
+        _chk(lib().orome_cuda_gather_wait(self._h, flag, vec_ptr, n, stream))
 
     def hint_next(self, ref: TensorRef | None):
         _chk(lib().orome_cuda_hint_next(self._h, C.byref(ref) if ref is not None else None))

@@ -44,12 +44,13 @@ def _worker(rank, world, port, fmt, n, q):
         st = torch.cuda.current_stream().cuda_stream
         r1 = F.tensor_ref(w1.data_ptr(), 0, fmt, hi - lo, n)
         r2 = F.tensor_ref(w2.data_ptr(), 0, fmt, hi - lo, n)
-        for rep in range(3):                                  # several rounds: the counters must keep pairing up
+        for rep in range(3):                                  # several rounds: the generations must keep pairing up
             ctx.gather_next(-1, 0)
             ctx.matvec(r1, xt.data_ptr(), y1[lo:hi].data_ptr(), 1, 0, 0, st)
             ctx.gather_next(0, 1)
             ctx.matvec(r2, y1.data_ptr(), y2[lo:hi].data_ptr(), 1, 0, 0, st)
-            ctx.gather_wait(1, st)
+            ctx.gather_wait(0, y1.data_ptr(), n, st)      # plain copies for the host-side check below
+            ctx.gather_wait(1, y2.data_ptr(), n, st)
             torch.cuda.synchronize()
             dist.barrier()
         want1 = oracle.matvec_f64(fmt, W1, n, n, x)
