@@ -221,6 +221,18 @@ int  orome_cuda_moe_ffn(orome_cuda_ctx *ctx, const OromeExpertLayerRef *layer, u
                         uint32_t hidden, uint32_t inter, float *act_dev, float *out_dev, int ldo,
                         void *stream);
 
+/* Expert-parallel share of the same operation -- no counterpart in the reference (one GPU).  This GPU holds the
+ * experts [first_expert, first_expert + n_local) of the layer, packed from index 0 in layer_local; the call adds
+ * up only those of each token's K selected experts that live here (out = 0 where none does), so the layer's
+ * output is the SUM of the ranks' outputs (one all-reduce of n_tokens x hidden floats, done by the caller).
+ * The activations x and the routing result are replicated on every rank, as they are after a row-split product,
+ * so no token dispatch is needed.  idx_local_dev: scratch of n_tokens * 8 indices.  A selected expert that lives
+ * elsewhere costs this GPU no weight traffic. */
+int  orome_cuda_moe_ffn_shard(orome_cuda_ctx *ctx, const OromeExpertLayerRef *layer_local, uint32_t variant,
+                              const float *x_dev, int n_tokens, int ldx, const uint32_t *idx_dev, const float *w_dev,
+                              uint32_t K, uint32_t hidden, uint32_t inter, uint32_t first_expert, uint32_t n_local,
+                              uint32_t *idx_local_dev, float *act_dev, float *out_dev, int ldo, void *stream);
+
 /* Optional hint: the tensor the NEXT matvec / group / gate-up call on this context will read.
  * The launch issued in between pulls the first bytes of that tensor into L2 once its own rows
  * are requested, so HBM keeps streaming across the launch boundary (a decode step is a fixed

@@ -600,13 +600,24 @@ __device__ __forceinline__ void walk_init(const PipeArgs &a, PipeWalk &w)
     w.seg = 0;
 }
 
-template <bool COMBINE>
+// Expert-parallel MoE: a segment whose device-side expert index is PIPE_NO_EXPERT belongs to another GPU and is
+// stepped over by producer and consumers alike (no copy, no arithmetic, its rows are left unwritten).
+constexpr uint32_t PIPE_NO_EXPERT = 0xFFFFFFFFu;
+template <bool EXT>
+__device__ __forceinline__ bool seg_skipped(const PipeArgs &a, int s)
+{
+    if constexpr (EXT) return a.seg_expert && a.seg_expert[s] == PIPE_NO_EXPERT;
+    else return false;
+}
+
+template <bool COMBINE, bool EXT = false>
 __device__ __forceinline__ bool next_tile(const PipeArgs &a, PipeWalk &w, PipeTile &t)
 {
     const uint32_t cap = a.rows_par * a.iters;
     if constexpr (COMBINE) {
         if (w.lo >= w.hi) return false;
         if (w.cur >= w.hi) { ++w.seg; w.cur = w.lo; }
+        while (w.seg < a.nseg && seg_skipped<EXT>(a, w.seg)) ++w.seg;
         if (w.seg >= a.nseg) return false;
         uint32_t n = w.hi - w.cur;
         if (n > cap) n = cap;
@@ -614,24 +625,28 @@ __device__ __forceinline__ bool next_tile(const PipeArgs &a, PipeWalk &w, PipeTi
         w.cur += n;
         return true;
     } else {
-        if (w.cur >= w.hi) return false;
         if (a.nseg == 1) {   // one tensor: no segment search, no segment clipping
+            if (w.cur >= w.hi) return false;
             uint32_t n = w.hi - w.cur;
             if (n > cap) n = cap;
             t.seg = 0; t.row0 = w.cur; t.n = n;
             w.cur += n;
             return true;
         }
-        int s = w.seg;
-        while (s + 1 < a.nseg && w.cur >= a.seg[s + 1].vstart) ++s;
-        w.seg = s;
-        const uint32_t seg_end = a.seg[s].vstart + a.seg[s].rows;
-        const uint32_t lim = w.hi < seg_end ? w.hi : seg_end;
-        uint32_t n = lim - w.cur;
-        if (n > cap) n = cap;
-        t.seg = s; t.row0 = w.cur - a.seg[s].vstart; t.n = n;
-        w.cur += n;
-        return true;
+        for (;;) {
+            if (w.cur >= w.hi) return false;
+            int s = w.seg;
+            while (s + 1 < a.nseg && w.cur >= a.seg[s + 1].vstart) ++s;
+            w.seg = s;
+            const uint32_t seg_end = a.seg[s].vstart + a.seg[s].rows;
+            const uint32_t lim = w.hi < seg_end ? w.hi : seg_end;
+            if (seg_skipped<EXT>(a, s)) { w.cur = lim; continue; }
+            uint32_t n = lim - w.cur;
+            if (n > cap) n = cap;
+            t.seg = s; t.row0 = w.cur - a.seg[s].vstart; t.n = n;
+            w.cur += n;
+            return true;
+        }
     }
 }
 
@@ -718,7 +733,7 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
             walk_init<COMBINE>(a, w);
             uint32_t i = 0, s = 0, k = 0;       // tile index, its stage and how many times the ring has wrapped
             PipeTile t;
-            while (next_tile<COMBINE>(a, w, t)) {
+            while (next_tile<COMBINE, EXT>(a, w, t)) {
                 if (k > 0) {
                     if (s_abort || !mbar_wait_bounded(smem_u32(empty + s), (k - 1) & 1u)) {
                         if (!s_abort) { s_abort = 1; atomicExch(a.status, 2); }
@@ -827,7 +842,7 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
     uint32_t delta = 0, delta2 = 0;
     const bool rows16 = (a.row_bytes & 15u) == 0;     // then every row starts at the same offset inside its 16-byte piece
     PipeTile t;
-    while (next_tile<COMBINE>(a, wk, t)) {
+    while (next_tile<COMBINE, EXT>(a, wk, t)) {
         if (buf_n && (t.seg != buf_seg || buf_n + t.n > CAP)) flush();
         if (buf_n == 0) { buf_seg = t.seg; buf_row0 = t.row0; }
         if constexpr (COMBINE) {

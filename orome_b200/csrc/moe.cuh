@@ -59,6 +59,18 @@ route_topk_kernel(const float *__restrict__ logits, int ld_logits, uint32_t n_ex
     }
 }
 
+// Expert-parallel form: indices of the experts [first, first + count) become local (0..count-1), all others the
+// "not here" mark that the expert kernels step over.
+__global__ void moe_localize_kernel(const uint32_t *__restrict__ idx, uint32_t n, uint32_t first, uint32_t count, uint32_t *__restrict__ out)
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // the indices are the routing kernel's output
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) {
+        const uint32_t e = idx[i] - first;
+        out[i] = e < count ? e : 0xFFFFFFFFu;
+    }
+}
+
 // act[t][k][m] = silu(Wg[e] x_t)[m] * (Wu[e] x_t)[m], e = idx[t][k]; one warp per (t, k, m).
 template <int FMT>
 __global__ void __launch_bounds__(256)
@@ -70,6 +82,7 @@ moe_gate_up_kernel(const uint8_t *__restrict__ gate, size_t gate_stride, const u
     const uint32_t m = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31u;
     if (m >= inter) return;
     const size_t e = idx[(size_t)t * 8 + k];
+    if (e == 0xFFFFFFFFu) return;                 // expert of another GPU (expert-parallel form)
     const uint8_t *gr = gate + e * gate_stride + (size_t)m * row_bytes;
     const uint8_t *ur = up + e * up_stride + (size_t)m * row_bytes;
     const float *xt = x + (size_t)t * ldx;
@@ -102,6 +115,7 @@ moe_down_kernel(const uint8_t *__restrict__ down, size_t down_stride, size_t row
     float total = 0.0f;
     for (uint32_t k = 0; k < K; ++k) {
         const size_t e = idx[(size_t)t * 8 + k];
+        if (e == 0xFFFFFFFFu) continue;           // expert of another GPU
         const uint8_t *row = down + e * down_stride + (size_t)h * row_bytes;
         const float *a = act + ((size_t)t * K + k) * inter;
         float acc = 0.0f;

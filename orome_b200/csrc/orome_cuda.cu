@@ -1297,6 +1297,27 @@ extern "C" int orome_cuda_moe_ffn(orome_cuda_ctx *c, const OromeExpertLayerRef *
     return post_launch(c, "moe_down");
 }
 
+extern "C" int orome_cuda_moe_ffn_shard(orome_cuda_ctx *c, const OromeExpertLayerRef *L_local, uint32_t variant, const float *x_dev,
+                                        int n_tokens, int ldx, const uint32_t *idx_dev, const float *w_dev, uint32_t K, uint32_t hidden,
+                                        uint32_t inter, uint32_t first_expert, uint32_t n_local, uint32_t *idx_local_dev, float *act_dev,
+                                        float *out_dev, int ldo, void *stream)
+{
+    if (!c || !idx_dev || !idx_local_dev) return fail(OROME_EINVAL, "moe_ffn_shard: NULL argument");
+    if (n_tokens < 1) return fail(OROME_EINVAL, "moe_ffn_shard: n_tokens %d", n_tokens);
+    if (L_local && !L_local->buffer) {      // this GPU holds no expert of the layer: its share of the sum is zero
+        CU(cudaSetDevice(c->device));
+        for (int t = 0; t < n_tokens; ++t)
+            CU(cudaMemsetAsync(out_dev + (size_t)t * (n_tokens == 1 ? hidden : ldo), 0, (size_t)hidden * 4, static_cast<cudaStream_t>(stream)));
+        return OROME_OK;
+    }
+    CU(cudaSetDevice(c->device));
+    const uint32_t n = (uint32_t)n_tokens * 8;
+    int rc = launch_pdl(c, "moe_localize", moe_localize_kernel, dim3((n + 127) / 128), dim3(128), static_cast<cudaStream_t>(stream), idx_dev, n,
+                        first_expert, n_local, idx_local_dev);
+    if (rc) return rc;
+    return orome_cuda_moe_ffn(c, L_local, variant, x_dev, n_tokens, ldx, idx_local_dev, w_dev, K, hidden, inter, act_dev, out_dev, ldo, stream);
+}
+
 // ---------------------------------------------------------------------------
 // host-buffer form
 // ---------------------------------------------------------------------------

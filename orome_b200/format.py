@@ -45,7 +45,7 @@ EXPORTS = [
     "orome_cuda_ctx_create", "orome_cuda_ctx_destroy", "orome_cuda_last_error", "orome_cuda_status", "orome_cuda_upload",
     "orome_cuda_free", "orome_format_from_ggml_type", "orome_format_row_bytes", "orome_format_dispatch_matvec",
     "orome_cuda_matvec", "orome_cuda_matvec_group", "orome_cuda_gate_up_swiglu", "orome_cuda_dequant_rows",
-    "orome_cuda_moe_route", "orome_cuda_moe_route_static", "orome_cuda_moe_ffn", "orome_cuda_matvec_host", "orome_cuda_set_option",
+    "orome_cuda_moe_route", "orome_cuda_moe_route_static", "orome_cuda_moe_ffn", "orome_cuda_moe_ffn_shard", "orome_cuda_matvec_host", "orome_cuda_set_option",
     "orome_cuda_get_option", "orome_cuda_launch_count", "orome_cuda_hint_next", "orome_cuda_peer_alloc", "orome_cuda_peer_open", "orome_cuda_peer_close", "orome_cuda_gather_setup",
     "orome_cuda_gather_arena_bytes", "orome_cuda_gather_next", "orome_cuda_gather_wait", "orome_cuda_trace_begin", "orome_cuda_trace_read",
 ]
@@ -82,6 +82,7 @@ def lib():
     L.orome_cuda_moe_route.argtypes = [vp, TR, vp, i32, i32, u32, vp, vp, vp, vp]
     L.orome_cuda_moe_route_static.argtypes = [vp, TR, vp, i32, i32, u32, vp, vp, vp]
     L.orome_cuda_moe_ffn.argtypes = [vp, EL, u32, vp, i32, i32, vp, vp, u32, u32, u32, vp, vp, i32, vp]
+    L.orome_cuda_moe_ffn_shard.argtypes = [vp, EL, u32, vp, i32, i32, vp, vp, u32, u32, u32, u32, u32, vp, vp, vp, i32, vp]
     L.orome_cuda_matvec_host.argtypes = [vp, TR, vp, vp, i32]
     L.orome_cuda_set_option.argtypes = [vp, i32, i32]
     L.orome_cuda_get_option.argtypes = [vp, i32, C.POINTER(i32)]
@@ -234,6 +235,13 @@ class Context:
                 hidden: int, inter: int, act: int, out: int, ldo: int, stream: int = 0):
         _chk(lib().orome_cuda_moe_ffn(self._h, C.byref(layer), variant, x, n_tokens, ldx, idx, w, K, hidden, inter, act, out,
                                       ldo, stream))
+
+    def moe_ffn_shard(self, layer_local: ExpertLayerRef, variant: int, x: int, n_tokens: int, ldx: int, idx: int, w: int, K: int,
+                      hidden: int, inter: int, first_expert: int, n_local: int, idx_local: int, act: int, out: int, ldo: int,
+                      stream: int = 0):
+        """This GPU's share of the expert FFN: only the selected experts in [first_expert, first_expert + n_local)."""
+        _chk(lib().orome_cuda_moe_ffn_shard(self._h, C.byref(layer_local), variant, x, n_tokens, ldx, idx, w, K, hidden, inter,
+                                            first_expert, n_local, idx_local, act, out, ldo, stream))
 
     def matvec_host(self, ref: TensorRef, x_host, y_host, batch: int = 1):
         """x_host / y_host: contiguous float32 numpy arrays (host memory)."""

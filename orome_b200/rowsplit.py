@@ -36,6 +36,24 @@ def all_gather_rows(dist, buf, n: int, rank: int, world: int, group=None) -> Non
     dist.all_gather_into_tensor(buf, buf[rank * per:(rank + 1) * per], group=group)
 
 
+def shard_experts(n_experts: int, rank: int, world: int) -> tuple[int, int]:
+    """[first, last) experts of this rank for expert-parallel MoE: contiguous blocks, expert e lives on rank
+    e // ceil(n_experts / world) (16 per GPU for 128 experts on 8 GPUs)."""
+    per = -(-n_experts // world)
+    first = min(rank * per, n_experts)
+    return first, min(first + per, n_experts)
+
+
+def expert_owner(e: int, n_experts: int, world: int) -> int:
+    return e // (-(-n_experts // world))
+
+
+def all_reduce_sum(dist, buf, group=None) -> None:
+    """Combine step of the expert-parallel FFN: every rank holds the sum over ITS experts, the layer output is the
+    sum over ranks (activations and routing are replicated, so there is no dispatch step)."""
+    dist.all_reduce(buf, group=group)
+
+
 class _DeviceMemory:
     """Raw device memory exposed through __cuda_array_interface__ so torch can view it."""
 

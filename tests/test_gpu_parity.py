@@ -171,6 +171,36 @@ def test_generic_and_pipelined_kernels_agree(env, fmt):
     assert rel_l2(y_gen, want) <= 2e-6 and rel_l2(y_pipe, want) <= 2e-6
 
 
+@pytest.mark.parametrize("fmt", QUANT)
+@pytest.mark.parametrize("shape", [(47360, 256), (6000, 1024), (2500, 5120)])
+def test_matvec_many_rows_per_cta(env, fmt, shape):
+    """Shapes that give every CTA several row tiles: stage ring wrap-around, the rotation of stages over the
+    consumer groups, more than one flush of the partial sums."""
+    out_dim, in_dim = shape
+    data = synth.host_tensor(fmt, out_dim, in_dim, seed=synth.seed_for("rows", fmt, out_dim))
+    x = synth.host_x(in_dim, seed=5)
+    y = gpu_matvec(env, fmt, data, out_dim, in_dim, x)
+    assert rel_l2(y, oracle.matvec_f64(fmt, data, out_dim, in_dim, x)) <= 2e-6
+
+
+@pytest.mark.parametrize("fmt", [synth.Q4_K, synth.Q5_K, synth.Q6_K])
+def test_kquant_mma_and_dp4a_kernels_agree(env, fmt):
+    torch, F, ctx = env
+    out_dim, in_dim = 3000, 2048
+    data = synth.host_tensor(fmt, out_dim, in_dim, seed=91)
+    x = synth.host_x(in_dim, seed=92)
+    want = oracle.matvec_f64(fmt, data, out_dim, in_dim, x)
+    c0 = ctx.launch_count
+    y_mma = gpu_matvec(env, fmt, data, out_dim, in_dim, x)
+    ctx.set_option(F.OPT_KQUANT_MMA, 0)
+    try:
+        y_dp4a = gpu_matvec(env, fmt, data, out_dim, in_dim, x)
+    finally:
+        ctx.set_option(F.OPT_KQUANT_MMA, 1)
+    assert ctx.launch_count == c0 + 2
+    assert rel_l2(y_mma, want) <= 2e-6 and rel_l2(y_dp4a, want) <= 2e-6
+
+
 def test_matvec_x_edge_cases(env):
     """Zero vector, one huge element among tiny ones, denormal-sized inputs."""
     fmt, out_dim, in_dim = synth.Q8_0, 64, 1024
@@ -280,6 +310,31 @@ def test_matvec_group_shares_x(env):
         assert rel_l2(y.cpu().numpy(), oracle.matvec_f64(fmt, data, d, in_dim, x)) <= 2e-6
 
 
+@pytest.mark.parametrize("fmt", [synth.Q4_K, synth.Q5_K])
+def test_matvec_group_and_fused_gate_up_many_rows(env, fmt):
+    """Grouped tensors whose boundaries fall inside CTAs, and the fused gate/up form with several row tiles per CTA."""
+    torch, F, ctx = env
+    in_dim, dims = 1024, [4000, 1000, 1000]
+    datas = [synth.host_tensor(fmt, d, in_dim, seed=40 + i) for i, d in enumerate(dims)]
+    wts = [dev_bytes(torch, d) for d in datas]
+    x = synth.host_x(in_dim, seed=6)
+    xt = dev_bytes(torch, x)
+    ys = [torch.full((d,), float("nan"), device="cuda") for d in dims]
+    ctx.matvec_group([make_ref(F, w, fmt, d, in_dim) for w, d in zip(wts, dims)], xt.data_ptr(), [y.data_ptr() for y in ys])
+    torch.cuda.synchronize()
+    for d, data, y in zip(dims, datas, ys):
+        assert rel_l2(y.cpu().numpy(), oracle.matvec_f64(fmt, data, d, in_dim, x)) <= 2e-6
+    out_dim = 5000
+    gd, ud = synth.host_tensor(fmt, out_dim, in_dim, seed=51), synth.host_tensor(fmt, out_dim, in_dim, seed=52)
+    xs = x * np.float32(8.0)
+    gt, ut, xt = dev_bytes(torch, gd), dev_bytes(torch, ud), dev_bytes(torch, xs)
+    out = torch.full((out_dim,), float("nan"), device="cuda")
+    ctx.gate_up_swiglu(make_ref(F, gt, fmt, out_dim, in_dim), make_ref(F, ut, fmt, out_dim, in_dim), xt.data_ptr(), out.data_ptr(), 1, 0, 0)
+    torch.cuda.synchronize()
+    want = oracle.swiglu_f64(oracle.matvec_f64(fmt, gd, out_dim, in_dim, xs), oracle.matvec_f64(fmt, ud, out_dim, in_dim, xs))
+    assert rel_l2(out.cpu().numpy(), want) <= REL_L2_TOL
+
+
 @pytest.mark.parametrize("fmt", [synth.Q8_0, synth.Q4_K, synth.Q6_K])
 @pytest.mark.parametrize("batch", [1, 3])
 def test_gate_up_swiglu(env, fmt, batch):
@@ -387,3 +442,44 @@ def test_moe_ffn_matches_oracle(env, T, down_fmt):
     for t in range(T):
         want = oracle.moe_ffn_f64(gate, up, down, (synth.Q4_K, synth.Q4_K, down_fmt), (sg, sg, sd), xm[t], H, M, idx[t], w[t])
         assert rel_l2(got[t], want) <= REL_L2_TOL
+
+
+@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("T", [1, 3])
+def test_moe_ffn_expert_parallel_shares_add_up(env, world, T):
+    """Expert-parallel form on one GPU: every rank's share (its own experts only, packed from index 0) computed in turn;
+    the shares must add up to the whole layer (the all-reduce of the multi-GPU run is this sum)."""
+    from orome_b200 import rowsplit
+    torch, F, ctx = env
+    H, M, E, K, dfmt = 512, 256, 16, 8, synth.Q5_K
+    gate = synth.host_tensor(synth.Q4_K, E * M, H, seed=61)
+    up = synth.host_tensor(synth.Q4_K, E * M, H, seed=62)
+    down = synth.host_tensor(dfmt, E * H, M, seed=63)
+    sg, sd = synth.tensor_bytes(synth.Q4_K, M, H), synth.tensor_bytes(dfmt, H, M)
+    xm = np.atleast_2d(synth.host_x(H, T, seed=64))
+    rng = np.random.default_rng(65)
+    idx = np.stack([rng.permutation(E)[:8] for _ in range(T)]).astype(np.uint32)
+    idx[0, :] = np.arange(8)                      # token 0 selects nothing from the upper half: some rank gets no work for it
+    w = rng.random((T, 8)).astype(np.float32)
+    w /= w.sum(1, keepdims=True)
+    xt, it, wtt = dev_bytes(torch, xm), dev_bytes(torch, idx.view(np.int32)), dev_bytes(torch, w)
+    total = np.zeros((T, H), np.float64)
+    for rank in range(world):
+        e0, e1 = rowsplit.shard_experts(E, rank, world)
+        blob = np.concatenate([gate[e0 * sg:e1 * sg], up[e0 * sg:e1 * sg], down[e0 * sd:e1 * sd]])
+        wt = dev_bytes(torch, blob)
+        n = e1 - e0
+        layer = F.ExpertLayerRef(wt.data_ptr(), F.ExpertProjRef(0, sg, synth.Q4_K), F.ExpertProjRef(n * sg, sg, synth.Q4_K),
+                                 F.ExpertProjRef(2 * n * sg, sd, dfmt))
+        act = torch.full((T, K, M), float("nan"), device="cuda")
+        out = torch.full((T, H), float("nan"), device="cuda")
+        loc = torch.zeros((T, 8), dtype=torch.int32, device="cuda")
+        ctx.moe_ffn_shard(layer, 0, xt.data_ptr(), T, H, it.data_ptr(), wtt.data_ptr(), K, H, M, e0, n, loc.data_ptr(),
+                          act.data_ptr(), out.data_ptr(), H)
+        torch.cuda.synchronize()
+        share = out.cpu().numpy().astype(np.float64)
+        assert np.all(np.isfinite(share))
+        total += share
+    for t in range(T):
+        want = oracle.moe_ffn_f64(gate, up, down, (synth.Q4_K, synth.Q4_K, dfmt), (sg, sg, sd), xm[t], H, M, idx[t], w[t])
+        assert rel_l2(total[t], want) <= REL_L2_TOL

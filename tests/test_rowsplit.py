@@ -67,3 +67,16 @@ def test_two_gloo_ranks_reassemble_the_product(fmt, out_dim, in_dim, world):
         assert p.exitcode == 0
     results = dict(q.get(timeout=10) for _ in range(world))
     assert results == {r: True for r in range(world)}
+
+
+def test_shard_experts_covers_every_expert_once():
+    from orome_b200 import rowsplit
+    for n, world in ((128, 8), (128, 3), (16, 4), (5, 8), (256, 2)):
+        seen = []
+        for r in range(world):
+            lo, hi = rowsplit.shard_experts(n, r, world)
+            assert 0 <= lo <= hi <= n
+            seen += list(range(lo, hi))
+            assert all(rowsplit.expert_owner(e, n, world) == r for e in range(lo, hi))
+        assert seen == list(range(n))
+    assert rowsplit.shard_experts(128, 0, 8) == (0, 16) and rowsplit.shard_experts(128, 7, 8) == (112, 128)
