@@ -30,7 +30,7 @@ constexpr int TC_M = 128;            // rows per CTA tile
 constexpr int TC_KC = 256;           // weights per packed chunk (8 Q8_0 blocks / one K-quant superblock)
 constexpr int TC_SLAB_K = 64;        // k per A slab = one 128-byte swizzle row of fp16
 constexpr int TC_SLABS = 4;          // A slab ring (= slabs per chunk)
-constexpr int TC_PK_STAGES = 2;      // packed-weight stages
+constexpr int TC_PK_MAX_STAGES = 6;  // packed-weight stages: as many as fit shared memory (TcArgs::pk_stages), at least 2
 constexpr int TC_MAX_N = 64;         // input vectors per launch (padded to a multiple of 16)
 constexpr int TC_B_STAGES = 2;       // X tile stages (one chunk each)
 constexpr int TC_DEQ_WARPS = 16;     // two groups of 8 warps take alternate slabs
@@ -44,7 +44,8 @@ struct TcArgs {
     float *y;                  // Y [batch][ldy] when split == 1, else partials [split][batch][rows]
     uint32_t rows, in_dim, row_bytes, chunk_bytes;   // chunk_bytes = packed bytes of 256 weights of one row
     uint32_t batch, npad, ldy;
-    uint32_t split, chunks_per_split;
+    uint32_t pk_stages;           // packed-weight stages in flight (2..TC_PK_MAX_STAGES)
+    uint32_t split, chunks;       // split-K parts and 256-weight chunks per row: part p takes chunks [p*chunks/split, (p+1)*chunks/split)
     int layout;
     int *status;
 };
@@ -170,8 +171,9 @@ gemm_tc_kernel(const __grid_constant__ TcArgs a)
     uint8_t *b_tiles = a_slabs + TC_SLABS * 16384;
     const uint32_t pk_stage_bytes = (TC_M * a.chunk_bytes + 127u) & ~127u;
     uint8_t *pk = b_tiles + TC_B_STAGES * b_tile_bytes;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(pk + TC_PK_STAGES * pk_stage_bytes);
-    uint64_t *pk_full = bars, *pk_empty = bars + TC_PK_STAGES, *b_full = pk_empty + TC_PK_STAGES, *b_empty = b_full + TC_B_STAGES;
+    const uint32_t PKS = a.pk_stages;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(pk + PKS * pk_stage_bytes);
+    uint64_t *pk_full = bars, *pk_empty = bars + TC_PK_MAX_STAGES, *b_full = pk_empty + TC_PK_MAX_STAGES, *b_empty = b_full + TC_B_STAGES;
     uint64_t *a_full = b_empty + TC_B_STAGES, *a_empty = a_full + TC_SLABS, *acc_done = a_empty + TC_SLABS;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_done + 1);
     __shared__ volatile int s_abort;
@@ -179,13 +181,13 @@ gemm_tc_kernel(const __grid_constant__ TcArgs a)
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t tile = blockIdx.x / a.split, sp = blockIdx.x % a.split;
     const uint32_t row0 = tile * TC_M, nrows = min((uint32_t)TC_M, a.rows - row0);
-    const uint32_t chunk0 = sp * a.chunks_per_split, nchunks = a.chunks_per_split;
+    const uint32_t chunk0 = sp * a.chunks / a.split, nchunks = (sp + 1) * a.chunks / a.split - chunk0;
     uint32_t ncols = 32;
     while (ncols < a.npad) ncols <<= 1;
 
     if (tid == 0) {
         s_abort = 0;
-        for (int s = 0; s < TC_PK_STAGES; ++s) { mbar_init(smem_u32(pk_full + s), 1); mbar_init(smem_u32(pk_empty + s), TC_DEQ_WARPS); }
+        for (uint32_t s = 0; s < PKS; ++s) { mbar_init(smem_u32(pk_full + s), 1); mbar_init(smem_u32(pk_empty + s), TC_DEQ_WARPS); }
         for (int s = 0; s < TC_B_STAGES; ++s) { mbar_init(smem_u32(b_full + s), 1); mbar_init(smem_u32(b_empty + s), 1); }
         for (int s = 0; s < TC_SLABS; ++s) { mbar_init(smem_u32(a_full + s), TC_SLAB_WARPS); mbar_init(smem_u32(a_empty + s), 1); }
         mbar_init(smem_u32(acc_done), 1);
@@ -211,7 +213,7 @@ gemm_tc_kernel(const __grid_constant__ TcArgs a)
         if (lane == 0) {
             const uint32_t words = a.chunk_bytes / 4;
             for (uint32_t c = 0; c < nchunks && !s_abort; ++c) {
-                const uint32_t s = c % TC_PK_STAGES, k = c / TC_PK_STAGES;
+                const uint32_t s = c % PKS, k = c / PKS;
                 if (k > 0) { wait(pk_empty + s, (k - 1) & 1u); asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
                 mbar_expect_tx(smem_u32(pk_full + s), TC_M * a.chunk_bytes);   // the box is always full: out-of-range rows arrive as zeros
                 // x coordinate in 32-bit words: (chunk index) * chunk_bytes / 4, a multiple of 16 bytes for every format
@@ -253,8 +255,8 @@ gemm_tc_kernel(const __grid_constant__ TcArgs a)
         const uint32_t dt = tid & 255u, grp = warp / TC_SLAB_WARPS;   // group 0 fills even slabs, group 1 odd slabs
         uint32_t slab_i = 0;
         for (uint32_t c = 0; c < nchunks; ++c) {
-            const uint32_t s = c % TC_PK_STAGES;
-            wait(pk_full + s, (c / TC_PK_STAGES) & 1u);
+            const uint32_t s = c % PKS;
+            wait(pk_full + s, (c / PKS) & 1u);
             const uint8_t *stage = pk + (size_t)s * pk_stage_bytes;
             for (uint32_t j = 0; j < TC_SLABS; ++j, ++slab_i) {
                 if ((slab_i & 1u) != grp) continue;

@@ -953,14 +953,15 @@ static int launch_tc(orome_cuda_ctx *c, int fmt, const uint8_t *data, uint32_t o
 {
     const uint32_t chunk_bytes = fmt == FMT_Q8_0 ? 272u : fmt == FMT_Q4_K ? 144u : 176u;
     const uint32_t chunks = in_dim / TC_KC, tiles = (out_dim + TC_M - 1) / TC_M;
-    // split K so that the grid fills the SMs in whole waves as far as the chunk count allows
+    // Split K so that the SMs stay busy: a CTA costs about one time unit per chunk plus about five to set up (TMEM,
+    // barriers, pipeline fill -- measured: three parts in two waves were slower than one part on 96 of 148 SMs), the
+    // grid runs in waves of sm_count CTAs, a split adds a reduction pass.  Parts may be uneven.
     uint32_t split = 1;
-    double best = 0.0;
-    for (uint32_t s = 1; s <= 8 && s <= chunks; ++s) {
-        if (chunks % s) continue;
+    double best = 1e30;
+    for (uint32_t s = 1; s <= 12 && s <= chunks; ++s) {
         const uint32_t ctas = tiles * s, waves = (ctas + c->sm_count - 1) / c->sm_count;
-        const double eff = (double)ctas / ((double)waves * c->sm_count) - 0.02 * (s - 1) - 0.08 * (waves - 1);   // a split costs a reduction pass, a wave its prologue
-        if (eff > best) { best = eff; split = s; }
+        const double cost = (double)waves * ((double)((chunks + s - 1) / s) + 5.0) + (s > 1 ? 1.0 + 0.25 * s : 0.0);
+        if (cost < best) { best = cost; split = s; }
     }
     for (int b0 = 0; b0 < batch; b0 += TC_MAX_N) {
         const int nb = std::min(batch - b0, TC_MAX_N);
@@ -988,10 +989,14 @@ static int launch_tc(orome_cuda_ctx *c, int fmt, const uint8_t *data, uint32_t o
         }
         a.w = data; a.xp = xp; a.y = split == 1 ? y + (size_t)b0 * ldy : c->tc_part;
         a.rows = out_dim; a.in_dim = in_dim; a.row_bytes = (uint32_t)row_bytes_of(fmt, in_dim); a.chunk_bytes = chunk_bytes;
-        a.batch = (uint32_t)nb; a.npad = npad; a.ldy = (uint32_t)ldy; a.split = split; a.chunks_per_split = chunks / split;
+        a.batch = (uint32_t)nb; a.npad = npad; a.ldy = (uint32_t)ldy; a.split = split; a.chunks = chunks;
         a.layout = layout; a.status = c->status_dev;
-        const size_t smem = 1024 + (size_t)TC_SLABS * 16384 + (size_t)TC_B_STAGES * npad * 128 * TC_SLABS +
-                            (size_t)TC_PK_STAGES * ((TC_M * chunk_bytes + 127) & ~127u) + 512;
+        // packed-weight stages: what is left of shared memory after the fp16 slabs and the X tiles (more bytes in flight per SM)
+        const size_t fixed = 1024 + (size_t)TC_SLABS * 16384 + (size_t)TC_B_STAGES * npad * 128 * TC_SLABS + 512;
+        const size_t pk_stage = (TC_M * chunk_bytes + 127) & ~127u;
+        const size_t room = (size_t)c->smem_optin > fixed + 1024 ? (size_t)c->smem_optin - fixed - 1024 : 0;
+        a.pk_stages = (uint32_t)std::max<size_t>(2, std::min<size_t>(TC_PK_MAX_STAGES, room / pk_stage));
+        const size_t smem = fixed + a.pk_stages * pk_stage;
         const int grid = (int)(tiles * split);
         switch (fmt) {
         case FMT_Q8_0: rc = launch_tc_fmt<FMT_Q8_0>(c, a, grid, smem, st); break;
