@@ -310,7 +310,7 @@ def test_matvec_group_shares_x(env):
         assert rel_l2(y.cpu().numpy(), oracle.matvec_f64(fmt, data, d, in_dim, x)) <= 2e-6
 
 
-@pytest.mark.parametrize("fmt", [synth.Q4_K, synth.Q5_K])
+@pytest.mark.parametrize("fmt", [synth.Q4_K, synth.Q5_K, synth.Q6_K])
 def test_matvec_group_and_fused_gate_up_many_rows(env, fmt):
     """Grouped tensors whose boundaries fall inside CTAs, and the fused gate/up form with several row tiles per CTA."""
     torch, F, ctx = env
