@@ -30,13 +30,14 @@ constexpr int TC_M = 128;            // rows per CTA tile
 constexpr int TC_KC = 256;           // weights per packed chunk (8 Q8_0 blocks / one K-quant superblock)
 constexpr int TC_SLAB_K = 64;        // k per A slab = one 128-byte swizzle row of fp16
 constexpr int TC_SLABS = 4;          // fp16 slabs per 256-weight chunk
-constexpr int TC_MAX_RING = 8;       // slab buffers: TcArgs::ring, 4..8 as shared memory allows (more than one chunk's worth lets the
-                                     // dequantizing warps run ahead of the tensor core instead of waiting for its commits)
-constexpr int TC_PK_MAX_STAGES = 6;  // packed-weight stages: as many as fit shared memory (TcArgs::pk_stages), at least 2
+constexpr int TC_MAX_RING = TC_SLABS; // slab buffers = one chunk's worth (six made no difference and do not fit next to Q8_0 stages)
+constexpr int TC_PK_STAGES = 2;      // packed-weight stages
+constexpr int TC_PK_MAX_STAGES = TC_PK_STAGES;
 constexpr int TC_MAX_N = 64;         // input vectors per launch (padded to a multiple of 16)
-constexpr int TC_B_MAX_STAGES = 3;   // X tile stages (one chunk each): TcArgs::b_stages, 2 or 3 as shared memory allows
+constexpr int TC_B_STAGES = 2;       // X tile stages (one chunk each)
+constexpr int TC_B_MAX_STAGES = TC_B_STAGES;
 constexpr int TC_DEQ_WARPS = 16;     // two groups of 8 warps take alternate slabs
-constexpr int TC_SLAB_WARPS = 4;     // warps that fill one slab
+constexpr int TC_SLAB_WARPS = 8;     // warps that fill one slab
 constexpr int TC_THREADS = (TC_DEQ_WARPS + 2) * 32;
 
 struct TcArgs {
@@ -46,9 +47,6 @@ struct TcArgs {
     float *y;                  // Y [batch][ldy] when split == 1, else partials [split][batch][rows]
     uint32_t rows, in_dim, row_bytes, chunk_bytes;   // chunk_bytes = packed bytes of 256 weights of one row
     uint32_t batch, npad, ldy;
-    uint32_t pk_stages;           // packed-weight stages in flight (2..TC_PK_MAX_STAGES)
-    uint32_t b_stages;            // X tile stages in flight (2..TC_B_MAX_STAGES)
-    uint32_t ring;                // slab buffers (TC_SLABS..TC_MAX_RING)
     uint32_t split, chunks;       // split-K parts and 256-weight chunks per row: part p takes chunks [p*chunks/split, (p+1)*chunks/split)
     int layout;
     int *status;
@@ -162,55 +160,6 @@ __device__ __forceinline__ void dequant_group32(const uint8_t *pk_row, uint32_t 
     }
 }
 
-// 64 consecutive weights of one row = one fp16 slab row (a sub-block pair of a K-quant superblock, or two Q8_0
-// blocks) -> eight 16-byte pieces.  For the K-quants the pair shares its 32 quant bytes (low / high nibbles), the
-// superblock header and the scale unpacking, so one thread does the pair.
-template <int FMT>
-__device__ __forceinline__ void dequant_pair64(const uint8_t *pk_row, uint32_t pair, int layout, uint4 (&out)[8])
-{
-    if constexpr (FMT == FMT_Q8_0) {
-        uint4 lo[4], hi[4];
-        dequant_group32<FMT>(pk_row, 2 * pair, layout, lo);
-        dequant_group32<FMT>(pk_row, 2 * pair + 1, layout, hi);
-#pragma unroll
-        for (int p = 0; p < 4; ++p) { out[p] = lo[p]; out[4 + p] = hi[p]; }
-    } else {
-        constexpr int QOFF = FMT == FMT_Q4_K ? 16 : 48;
-        const uint32_t sb = smem_u32(pk_row);
-        const uint4 h = lds128<0>(sb);
-        uint32_t scA, scB, mnA, mnB;
-        pair_scales(h.y, h.z, h.w, layout, (int)pair, scA, scB, mnA, mnB);
-        const float d = __half2float(__ushort_as_half((unsigned short)(h.x & 0xffffu)));
-        const float dmin = __half2float(__ushort_as_half((unsigned short)(h.x >> 16)));
-        const uint32_t qa = sb + 32u * pair;
-        const uint4 q0 = lds128<QOFF>(qa), q1 = lds128<QOFF + 16>(qa);
-        const uint32_t q[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-        uint32_t hb[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
-        if constexpr (FMT == FMT_Q5_K) {
-            const uint4 h0 = lds128<16>(sb), h1 = lds128<32>(sb);
-            hb[0] = h0.x; hb[1] = h0.y; hb[2] = h0.z; hb[3] = h0.w; hb[4] = h1.x; hb[5] = h1.y; hb[6] = h1.z; hb[7] = h1.w;
-        }
-        const __half2 bias = __float2half2_rn(1024.0f);
-        const __half2 scaleA = __float2half2_rn(d * (float)scA), addA = __float2half2_rn(-(dmin * (float)mnA));
-        const __half2 scaleB = __float2half2_rn(d * (float)scB), addB = __float2half2_rn(-(dmin * (float)mnB));
-        uint32_t o[32];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            uint32_t wl = q[i] & 0x0F0F0F0Fu, wh = (q[i] >> 4) & 0x0F0F0F0Fu;
-            if constexpr (FMT == FMT_Q5_K) {
-                wl |= ((hb[i] >> (2 * pair)) & 0x01010101u) << 4;
-                wh |= ((hb[i] >> (2 * pair + 1)) & 0x01010101u) << 4;
-            }
-            o[2 * i] = h2_bits(two_weights(wl, 0x5140u, bias, scaleA, addA));
-            o[2 * i + 1] = h2_bits(two_weights(wl, 0x7362u, bias, scaleA, addA));
-            o[16 + 2 * i] = h2_bits(two_weights(wh, 0x5140u, bias, scaleB, addB));
-            o[16 + 2 * i + 1] = h2_bits(two_weights(wh, 0x7362u, bias, scaleB, addB));
-        }
-#pragma unroll
-        for (int p = 0; p < 8; ++p) out[p] = make_uint4(o[4 * p], o[4 * p + 1], o[4 * p + 2], o[4 * p + 3]);
-    }
-}
-
 template <int FMT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ TcArgs a)
@@ -221,12 +170,12 @@ gemm_tc_kernel(const __grid_constant__ TcArgs a)
     // layout: [A slabs 4 x 16 KiB][X tiles 2 x npad*512][packed stages 2 x 128*chunk_bytes][barriers]
     uint8_t *a_slabs = smem;
     const uint32_t b_tile_bytes = a.npad * 128u * TC_SLABS;
-    const uint32_t RING = a.ring;
+    constexpr uint32_t RING = TC_MAX_RING;   // compile-time ring sizes: the divisions below sit on the hand-off path of every slab
     uint8_t *b_tiles = a_slabs + RING * 16384;
     const uint32_t pk_stage_bytes = (TC_M * a.chunk_bytes + 127u) & ~127u;
-    const uint32_t BS = a.b_stages;
+    constexpr uint32_t BS = TC_B_STAGES;
     uint8_t *pk = b_tiles + BS * b_tile_bytes;
-    const uint32_t PKS = a.pk_stages;
+    constexpr uint32_t PKS = TC_PK_STAGES;
     uint64_t *bars = reinterpret_cast<uint64_t *>(pk + PKS * pk_stage_bytes);
     uint64_t *pk_full = bars, *pk_empty = bars + TC_PK_MAX_STAGES, *b_full = pk_empty + TC_PK_MAX_STAGES, *b_empty = b_full + TC_B_MAX_STAGES;
     uint64_t *a_full = b_empty + TC_B_MAX_STAGES, *a_empty = a_full + TC_MAX_RING, *acc_done = a_empty + TC_MAX_RING;
@@ -307,27 +256,27 @@ gemm_tc_kernel(const __grid_constant__ TcArgs a)
         }
     } else {
         // ---- dequant warps: packed stage -> fp16 slabs ----
-        const uint32_t dt = tid & 127u, grp = warp / TC_SLAB_WARPS;   // group g fills the slabs i with i % 4 == g, one row per thread
+        // Two groups of eight warps fill alternate slabs, one (row, 32-weight group) per thread.  (One thread per row and
+        // sub-block pair, which shares the header and scale unpacking, measured 10 % slower: the slab's latency counts.)
+        const uint32_t dt = tid & 255u, grp = warp / TC_SLAB_WARPS;
         uint32_t slab_i = 0;
         for (uint32_t c = 0; c < nchunks; ++c) {
             const uint32_t s = c % PKS;
             wait(pk_full + s, (c / PKS) & 1u);
             const uint8_t *stage = pk + (size_t)s * pk_stage_bytes;
             for (uint32_t j = 0; j < TC_SLABS; ++j, ++slab_i) {
-                if ((slab_i & 3u) != grp) continue;
+                if ((slab_i & 1u) != grp) continue;
                 const uint32_t sa = slab_i % RING, ka = slab_i / RING;
                 if (ka > 0) wait(a_empty + sa, (ka - 1) & 1u);
                 tc_fence_after();
                 uint8_t *slab = a_slabs + sa * 16384;
-                // a slab is 128 rows x 64 weights (one sub-block pair): one row per thread, eight 16-byte pieces
+                // a slab is 128 rows x two 32-weight groups: one (row, group) per thread, four 16-byte pieces each
                 {
-                    const uint32_t r = dt;
-                    uint4 v[8];
+                    const uint32_t r = dt >> 1, half = dt & 1u;
+                    uint4 v[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+                    if (r < nrows) dequant_group32<FMT>(stage + (size_t)r * a.chunk_bytes, j * 2 + half, a.layout, v);
 #pragma unroll
-                    for (int p = 0; p < 8; ++p) v[p] = make_uint4(0, 0, 0, 0);
-                    if (r < nrows) dequant_pair64<FMT>(stage + (size_t)r * a.chunk_bytes, j, a.layout, v);
-#pragma unroll
-                    for (uint32_t p = 0; p < 8; ++p) *reinterpret_cast<uint4 *>(slab + sw128_off(r, p)) = v[p];
+                    for (uint32_t p = 0; p < 4; ++p) *reinterpret_cast<uint4 *>(slab + sw128_off(r, half * 4 + p)) = v[p];
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> visible to the tensor core
                 __syncwarp();

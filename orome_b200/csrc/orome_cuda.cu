@@ -991,18 +991,14 @@ static int launch_tc(orome_cuda_ctx *c, int fmt, const uint8_t *data, uint32_t o
         a.rows = out_dim; a.in_dim = in_dim; a.row_bytes = (uint32_t)row_bytes_of(fmt, in_dim); a.chunk_bytes = chunk_bytes;
         a.batch = (uint32_t)nb; a.npad = npad; a.ldy = (uint32_t)ldy; a.split = split; a.chunks = chunks;
         a.layout = layout; a.status = c->status_dev;
-        // Shared memory: one chunk's worth of fp16 slab buffers, two X tile stages, then packed-weight stages with what
-        // is left.  Measured on Q4_K 12288x4096, batch 64: seven slab buffers (dequantizing warps running ahead) or a
-        // third X stage did not shorten the launch (35-40 us against 34-36 us), and neither does removing the dequant
-        // arithmetic altogether (31 us), so the depth of these rings is not what bounds it.
+        // Shared memory: one chunk's worth of fp16 slab buffers, two X tile stages, two packed-weight stages (169 KB for
+        // Q4_K at batch 64).  Measured on Q4_K 12288x4096, batch 64: deeper rings (seven slab buffers, a third X stage, up
+        // to six packed-weight stages, sized at run time) made the launch slower (35-41 us against 34 us), and removing
+        // the dequant arithmetic altogether only brings it to 31 us: ring depth is not what bounds this kernel, and
+        // run-time ring sizes put integer divisions on the hand-off path of every slab.
         const size_t pk_stage = (TC_M * chunk_bytes + 127) & ~127u, b_tile = (size_t)npad * 128 * TC_SLABS;
-        const size_t avail = (size_t)c->smem_optin - 1024;
-        a.b_stages = 2;
-        a.ring = TC_SLABS;
-        const size_t fixed = 1024 + (size_t)a.ring * 16384 + a.b_stages * b_tile + 512;
-        if (fixed + 2 * pk_stage > avail) return fail(OROME_ENOTSUP, "gemm_tc: batch %d does not fit shared memory", nb);
-        a.pk_stages = (uint32_t)std::max<size_t>(2, std::min<size_t>(TC_PK_MAX_STAGES, (avail - fixed) / pk_stage));
-        const size_t smem = fixed + a.pk_stages * pk_stage;
+        const size_t smem = 1024 + (size_t)TC_MAX_RING * 16384 + (size_t)TC_B_STAGES * b_tile + 512 + (size_t)TC_PK_STAGES * pk_stage;
+        if (smem > (size_t)c->smem_optin - 1024) return fail(OROME_ENOTSUP, "gemm_tc: batch %d does not fit shared memory", nb);
         const int grid = (int)(tiles * split);
         switch (fmt) {
         case FMT_Q8_0: rc = launch_tc_fmt<FMT_Q8_0>(c, a, grid, smem, st); break;
