@@ -67,7 +67,7 @@ struct orome_cuda_ctx {
     // scratch of the tensor-core batched form: packed fp16 X and split-K partial sums
     float *tc_xp = nullptr, *tc_part = nullptr;
     size_t tc_xp_cap = 0, tc_part_cap = 0;
-    int tc_min_batch = 9;    // batches from this size on use the tensor-core kernel
+    int tc_min_batch = 4;    // batches from this size on use the tensor-core kernel (smaller ones: one decode launch per vector)
     int kquant_mma = 1;      // Q4_K / Q5_K batch-1 products on the mma.sync kernel (0: dp4a kernel)
 };
 
@@ -1033,10 +1033,22 @@ extern "C" int orome_cuda_matvec(orome_cuda_ctx *c, const OromeTensorRef *ref, c
     int rc = check_ref("matvec", ref, &data);
     if (rc) return rc;
     CU(cudaSetDevice(c->device));
-    if (batch >= c->tc_min_batch && !c->force_generic && tc_supported((int)ref->format, ref->in_dim) && ldx % 4 == 0 &&
-        !(reinterpret_cast<uintptr_t>(x_dev) & 15))
+    const bool x_ok = ldx % 4 == 0 && !(reinterpret_cast<uintptr_t>(x_dev) & 15);
+    if (batch >= c->tc_min_batch && !c->force_generic && tc_supported((int)ref->format, ref->in_dim) && x_ok)
         return launch_tc(c, (int)ref->format, data, ref->out_dim, ref->in_dim, (int)ref->variant, x_dev, batch, ldx, y_dev, ldy,
                          static_cast<cudaStream_t>(stream));
+    // Small batches, and formats the tensor-core form does not take (Q6_K): one batch-1 launch per input vector.  The
+    // weights are read once per vector, but the decode kernels run near the memory rate while the shape-agnostic
+    // kernel below needs ~190 us per vector for a 12288 x 4096 tensor (measured: batch 8 in 1.5 ms).
+    if (!c->force_generic && x_ok && (int)ref->format <= FMT_Q8_0 && c->g_world == 1 &&
+        (pipe_supported((int)ref->format, ref->in_dim) || mma_supported(c, (int)ref->format, ref->in_dim, false))) {
+        for (int b = 0; b < batch; ++b) {
+            float *ys[1] = {y_dev + (size_t)b * ldy};
+            rc = orome_cuda_matvec_group(c, ref, 1, x_dev + (size_t)b * ldx, ys, stream);
+            if (rc) return rc;
+        }
+        return OROME_OK;
+    }
     return launch_generic(c, (int)ref->format, data, ref->out_dim, ref->in_dim, (int)ref->variant, x_dev, batch, ldx, y_dev, ldy,
                           static_cast<cudaStream_t>(stream));
 }

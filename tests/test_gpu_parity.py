@@ -224,7 +224,7 @@ def test_batched_matvec(env, fmt, batch):
     x = synth.host_x(in_dim, batch, seed=3)
     y = gpu_matvec(env, fmt, data, out_dim, in_dim, x)
     want = oracle.matvec_f64(fmt, data, out_dim, in_dim, x)
-    on_tensor_cores = batch >= 9 and fmt in (synth.Q8_0, synth.Q4_K, synth.Q5_K)
+    on_tensor_cores = batch >= 4 and fmt in (synth.Q8_0, synth.Q4_K, synth.Q5_K)
     assert y.shape == want.shape and rel_l2(y, want) <= (TC_REL_L2_TOL if on_tensor_cores else REL_L2_TOL)
 
 
@@ -251,7 +251,7 @@ def test_prefill_gemm_on_tensor_cores(env, fmt, shape):
     try:
         y32 = gpu_matvec(env, fmt, data, out_dim, in_dim, x[:4], 0)
     finally:
-        ctx.set_option(F.OPT_TC_MIN_BATCH, 9)
+        ctx.set_option(F.OPT_TC_MIN_BATCH, 4)
     assert rel_l2(y32, oracle.matvec_f64(fmt, data, out_dim, in_dim, x[:4])) <= REL_L2_TOL
 
 
