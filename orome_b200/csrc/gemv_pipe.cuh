@@ -41,7 +41,7 @@ constexpr int PIPE_MAX_THREADS = PIPE_MAX_CONSUMERS + 32;
 constexpr int PIPE_CONSUMERS_2CTA = 288;           // consumer threads of a CTA meant to share an SM with another
 constexpr int PIPE_THREADS_2CTA = PIPE_CONSUMERS_2CTA + 32;
 constexpr int PIPE_MAX_ITERS = 8;               // rows a group handles per tile
-constexpr int PIPE_MAX_ROWS_PAR = 8;            // named barriers 1..8 belong to the row groups
+constexpr int PIPE_MAX_ROWS_PAR = 15;           // row groups side by side (one warp each for the narrowest rows)
 constexpr int PIPE_BAR_CONSUMERS = 9;           // named barrier over all consumer threads
 constexpr long long PIPE_WAIT_CYCLES = 2000000000ll;   // per wait: about one second of SM clock
 
@@ -806,6 +806,17 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
         for (uint32_t r = tid; r < wk.hi - wk.lo; r += C) accbuf[r] = 0.0f;   // ordered before its first use by the first flush's barrier
     }
     float *pbuf = red;
+    // Combine form with the CTA's rows fitting one buffer: every segment adds weight * partial sum into the same
+    // slots (a slot always belongs to the same lane), so there is one flush at the end instead of one barrier and
+    // flush per segment.
+    // and the row groups split the SEGMENTS among them (group g takes segments g, g + rows_par, ...; all rows of a
+    // segment's tile), each with its own slots: the eight experts of a token advance side by side.
+    const uint32_t SL = COMBINE ? GW * a.rows_par : GW;                 // partial sums per row
+    const bool comb_acc = COMBINE && (wk.hi - wk.lo) * SL <= 2 * PLANE;
+    if (comb_acc) {
+        for (uint32_t r = tid; r < (wk.hi - wk.lo) * SL; r += C) pbuf[r] = 0.0f;
+        named_bar_sync(PIPE_BAR_CONSUMERS, (int)C);
+    }
     uint32_t which = 0, buf_n = 0, buf_row0 = 0;
     int buf_seg = 0;
     auto flush = [&]() {
@@ -814,11 +825,12 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
         float *y = a.seg[buf_seg].y + buf_row0;
         for (uint32_t r = tid; r < buf_n; r += C) {
             float g = 0.0f, u = 0.0f;
-            for (uint32_t w = 0; w < GW; ++w) {
-                g += src[r * GW + w];
+            const uint32_t nsl = comb_acc ? SL : GW;
+            for (uint32_t w = 0; w < nsl; ++w) {
+                g += src[r * nsl + w];
                 if constexpr (SWIGLU) u += src[PLANE + r * GW + w];
             }
-            if constexpr (COMBINE) accbuf[buf_row0 - wk.lo + r] += a.seg_weight[buf_seg] * g;   // one owner per row and flush
+            if constexpr (COMBINE) accbuf[buf_row0 - wk.lo + r] += (comb_acc ? 1.0f : a.seg_weight[buf_seg]) * g;   // one owner per row and flush
             else {
                 const float val = SWIGLU ? silu_mul(g, u) : g;
                 y[r] = val;
@@ -843,12 +855,26 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
     const bool rows16 = (a.row_bytes & 15u) == 0;     // then every row starts at the same offset inside its 16-byte piece
     PipeTile t;
     while (next_tile<COMBINE, EXT>(a, wk, t)) {
-        if (buf_n && (t.seg != buf_seg || buf_n + t.n > CAP)) flush();
-        if (buf_n == 0) { buf_seg = t.seg; buf_row0 = t.row0; }
+        if (!comb_acc && buf_n && (t.seg != buf_seg || buf_n + t.n > CAP)) flush();
+        if (!comb_acc && buf_n == 0) { buf_seg = t.seg; buf_row0 = t.row0; }
+        const bool mine = !comb_acc || (uint32_t)t.seg % a.rows_par == group;    // segment-parallel combine: one group per segment
         if constexpr (COMBINE) {
-            if (t.seg != slot_seg) {   // this segment's own input vector
+            if (mine && t.seg != slot_seg) {   // this segment's own input vector
                 slot_seg = t.seg;
                 if (active) slot.load(make_xq_view<NP, SlotT::GROUP>(smem + a.xs_base + (size_t)t.seg * a.xq_vec_bytes, a.in_dim), unit, part);
+            }
+            if (!mine) {                       // another group's segment: hand the stage on untouched (after its data
+                                               // has landed, so that no warp gets a whole ring ahead of the barriers' phases)
+                if (!s_abort && !mbar_wait_bounded(smem_u32(full + s), parity)) {
+                    s_abort = 1;
+                    atomicExch(a.status, 1);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(empty + s));
+                buf_n = wk.hi - wk.lo; buf_seg = 0; buf_row0 = wk.lo;
+                ++i;
+                if (++s == a.nstages) { s = 0; parity ^= 1u; }
+                continue;
             }
         }
         if (!s_abort && !mbar_wait_bounded(smem_u32(full + s), parity)) {
@@ -864,9 +890,12 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
         const uint32_t base = stages_s + s * a.stage_stride + delta + unit_off;
         uint32_t base2 = 0;
         if constexpr (SWIGLU) base2 = stages_s + s * a.stage_stride + a.half_stride + unit_off + delta2;
-        float *dst = pbuf + (size_t)which * PLANE * (SWIGLU ? 2 : 1) + (size_t)buf_n * GW + wig;
+        float *dst = comb_acc ? pbuf + (size_t)(t.row0 - wk.lo) * SL + group * GW + wig
+                              : pbuf + (size_t)which * PLANE * (SWIGLU ? 2 : 1) + (size_t)buf_n * GW + wig;
+        const float segw = comb_acc ? a.seg_weight[t.seg] : 0.0f;
+        const uint32_t rstride = comb_acc ? SL : GW;
 #pragma unroll 1
-        for (uint32_t r = group; r < t.n; r += a.rows_par) {
+        for (uint32_t r = comb_acc ? 0u : group; r < t.n; r += comb_acc ? 1u : a.rows_par) {
             float v = 0.0f, v2 = 0.0f;
             if (active) {
                 v = slot.dot(base + r * a.row_bytes, part, a.layout);
@@ -875,13 +904,15 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
             v = warp_sum(v);
             if constexpr (SWIGLU) v2 = warp_sum(v2);
             if (lane == 0) {
-                dst[r * GW] = v;
+                if (comb_acc) dst[r * rstride] = fmaf(segw, v, dst[r * rstride]);
+                else dst[r * GW] = v;
                 if constexpr (SWIGLU) dst[PLANE + r * GW] = v2;
             }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(empty + s));   // this warp is done reading the stage
-        buf_n += t.n;
+        if (comb_acc) { buf_n = wk.hi - wk.lo; buf_seg = 0; buf_row0 = wk.lo; }
+        else buf_n += t.n;
         ++i;
         if (++s == a.nstages) { s = 0; parity ^= 1u; }
     }

@@ -454,6 +454,7 @@ static int plan_pipe(orome_cuda_ctx *c, int fmt, uint32_t in_dim, uint32_t total
     // partial-sum buffers: a whole CTA share when it is small, else batches of 256 rows (at most 16 KiB per buffer)
     a.red_rows = std::min<uint32_t>(std::max<uint32_t>(share, a.rows_par * PIPE_MAX_ITERS), 256u);
     a.red_rows = std::max<uint32_t>(std::min<uint32_t>(a.red_rows, 4096u / gw), a.rows_par * PIPE_MAX_ITERS);
+    if (combine) a.red_rows = std::max<uint32_t>(a.red_rows, (share * a.rows_par + 1) / 2);   // one slot per row, group and warp fits the two buffers
     const size_t red_bytes = (size_t)2 * a.red_rows * gw * (swiglu ? 2 : 1) * sizeof(float);
     a.xs_base = (uint32_t)((a.red_base + red_bytes + 127) / 128 * 128);
     // quantized x: one byte plane per 8 bits of x, a scale per group (16 for Q6_K, else 32), a sum per 32 elements
@@ -470,7 +471,8 @@ static int plan_pipe(orome_cuda_ctx *c, int fmt, uint32_t in_dim, uint32_t total
         uint32_t ns = (uint32_t)std::min<size_t>(PIPE_MAX_STAGES, room / a.stage_stride);
         if (ns >= 3 || a.iters == 1) {
             if (ns < 1) return fail(OROME_ENOTSUP, "pipe plan: a stage of %u bytes does not fit shared memory", a.stage_stride);
-            const uint32_t tiles = (share + a.rows_par * a.iters - 1) / (a.rows_par * a.iters) + 1;
+            // the combine form walks the CTA's row range once per segment
+            const uint32_t tiles = ((share + a.rows_par * a.iters - 1) / (a.rows_par * a.iters)) * (combine ? (uint32_t)std::max(a.nseg, 1) : 1u) + 1;
             a.nstages = std::min(ns, tiles);
             break;
         }
