@@ -36,6 +36,11 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 FALLBACK_HBM_GBS = 6650.0      # used only when MEASURED_PEAKS.json is absent
+# DRAM bytes (read + write) per algorithmic byte, from the ncu capture of a 2-layer cut of the 9B set
+# (profiles/gemv_pipe_q8_0_decode_set.md: 272.7 MB read + 4.1 MB written for 205.3 MB of algorithmic bytes over the four
+# launch shapes).  ncu flushes the caches between launches, so the next tensor's L2 prefetch (up to 24 MiB per launch)
+# is counted in the launch that issues it AND in the launch that would otherwise have found it in L2.
+NCU_DRAM_PER_ALGORITHMIC = {"9b_q8_0": (272.7 + 4.1) / 205.3}
 NOMINAL_HBM_GBS = 8000.0
 
 
@@ -498,9 +503,13 @@ def run_ours(args):
     alg_bytes = w_bytes + ds.io_bytes()
     achieved = alg_bytes / (total / args.steps) / 1e9
     launches_per_step = st.launches_per_step
+    alg_per_launch = alg_bytes / max(1, launches_per_step)
     roofline = {
         "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
-        "frac_of_8tbs_nominal": achieved / NOMINAL_HBM_GBS, "traffic": None,
+        "frac_of_8tbs_nominal": achieved / NOMINAL_HBM_GBS,
+        "traffic": (alg_per_launch * NCU_DRAM_PER_ALGORITHMIC[args.workload]
+                    if world == 1 and args.workload in NCU_DRAM_PER_ALGORITHMIC and ctx.get_option(F.OPT_PREFETCH_MB) == 24 else None),
+        "traffic_note": "ncu capture of a 2-layer cut scaled by algorithmic bytes; counts the next tensor's L2 prefetch twice (caches flushed between launches under ncu)",
         "kernel": "gemv_pipe_kernel", "algorithmic_bytes_per_step": alg_bytes, "launches_per_step": launches_per_step,
         "avg_launch_us": ms_per_step * 1e3 / max(1, launches_per_step),
         "algorithmic_bytes_per_launch": alg_bytes / max(1, launches_per_step),
