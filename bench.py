@@ -5,19 +5,24 @@
 
 One "step" is one decode-token pass over a Qwen3.5-shape matvec set: per layer the
 grouped q/k/v projections, the o projection, the fused gate/up + SwiGLU and the down
-projection, then the lm_head (129 launches per step for the 9B Q8_0 set).  Every layer
-has its own weights (7.2 GB for the 9B set), far above the 126 MB L2, so no weight byte
-is served from cache between or within steps.
+projection, then the lm_head and the arg-max of the logits (129 products per step for
+the 9B Q8_0 set).  Every product reads the output of the one before it, as in the
+engine.  Every layer has its own weights (7.2 GB for the 9B set), far above the 126 MB
+L2, so no weight byte is served from cache between or within steps.
+
+Default form (`--mode chain`): the step is recorded once through the C ABI and runs as ONE
+resident kernel per step.  `--mode launches` issues one kernel per product (CUDA graph).
 
 Prints ONE JSON line: metric decode_matvec_tok_s (tokens per second of the whole job),
 `roofline` (algorithmic HBM bytes per step / device time against the measured copy
 bandwidth), `e2e` (same steps with the input vector copied from pinned host memory and
-the logits read back every step), `cpu_baseline` (the reference's CPU decode + dot on
-the host cores, on a bounded sample) and the clocks seen during the timed region.
+the token read back every step), `cpu_baseline` (the reference's CPU decode + dot on
+the host cores, on a bounded sample), `parity_check` (products of the timed kernel against
+the CPU oracle on sampled rows) and the clocks seen during the timed region.
 
 With N > 1 (launched by torch.distributed.run) every tensor is row-split over the
-ranks and each product is followed by an all-gather of the output vector over NCCL,
-so the scaling is "strong" (the same token step on more GPUs).
+ranks and every output vector is completed on all GPUs by peer stores from the
+producing kernel, so the scaling is "strong" (the same token step on more GPUs).
 
 `--impl reference` times the reference's own CPU implementation of the path (its
 format.m decode compiled into oracle/_ref, else the C restatement) on the host cores.
@@ -36,12 +41,17 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 FALLBACK_HBM_GBS = 6650.0      # used only when MEASURED_PEAKS.json is absent
-# DRAM bytes (read + write) per algorithmic byte, from the ncu capture of a 2-layer cut of the 9B set
-# (profiles/gemv_pipe_q8_0_decode_set.md: 272.7 MB read + 4.1 MB written for 205.3 MB of algorithmic bytes over the four
-# launch shapes).  ncu flushes the caches between launches, so the next tensor's L2 prefetch (up to 24 MiB per launch)
-# is counted in the launch that issues it AND in the launch that would otherwise have found it in L2.
-NCU_DRAM_PER_ALGORITHMIC = {"9b_q8_0": (272.7 + 4.1) / 205.3}
 NOMINAL_HBM_GBS = 8000.0
+
+
+def dram_per_algorithmic(workload: str, mode: str):
+    """DRAM bytes (read + write) per algorithmic byte of the dominant kernel, from the committed summary of an ncu
+    capture of a small cut of the same workload (traffic grows in proportion to the rows), or None."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "dram_traffic.json")) as f:
+            return float(json.load(f)[f"{workload}/{mode}"]["dram_bytes_per_algorithmic_byte"])
+    except Exception:
+        return None
 
 
 def measured_peak():
@@ -108,38 +118,55 @@ class ClockSampler(threading.Thread):
 # ----------------------------------------------------------------------------------------------
 # CPU arm: the reference's CPU decode + dot on the host cores
 # ----------------------------------------------------------------------------------------------
-def cpu_layer_sample(set_name: str, reps: int, budget_s: float = 0.0):
-    """Time one layer's matvecs (q,k,v,o,gate,up,down) on the host; returns (seconds per layer, meta)."""
-    import numpy as np
-    import oracle
-    from orome_b200 import decode_set, synth
+class CpuSteps:
+    """Whole token steps on the host: the reference's CPU decode (oracle/_ref when it was compiled, else the C
+    restatement) followed by an fp32 dot, OpenMP over rows on every host core.  One layer's tensors stand for all
+    layers (each layer is decoded again every time: nothing is cached between products), plus the lm_head once per
+    step.  Inputs are fixed vectors: on a CPU a chain of shrinking activations would end in denormal arithmetic."""
 
-    oracle.use_all_cores()
-    cfg = decode_set.SETS[set_name]
-    H, A, KV = cfg["hidden"], cfg["ffn"], cfg["kv"]
-    shapes = dict(q=(H, H), k=(KV, H), v=(KV, H), o=(H, H), gate=(A, H), up=(A, H), down=(H, A))
-    use_ref = oracle.ref() is not None and cfg["variant"] == 0     # the reference's CPU decode knows only its default scale layout
-    rng = np.random.default_rng(0)
-    xh, xa = rng.standard_normal(H, dtype=np.float32), rng.standard_normal(A, dtype=np.float32)
-    tensors = {k: synth.host_tensor(cfg["fmt"][k], *shapes[k], seed=synth.seed_for(set_name, "cpu", k)) for k in shapes}
-    layer_bytes = sum(t.size for t in tensors.values())
+    def __init__(self, set_name: str):
+        import numpy as np
+        import oracle
+        from orome_b200 import decode_set, synth
+        self.oracle = oracle
+        self.threads_requested = oracle.use_all_cores()
+        cfg = decode_set.SETS[set_name]
+        self.cfg, self.name = cfg, set_name
+        H, A, KV, V = cfg["hidden"], cfg["ffn"], cfg["kv"], cfg["vocab"]
+        self.shapes = dict(q=(H, H), k=(KV, H), v=(KV, H), o=(H, H), gate=(A, H), up=(A, H), down=(H, A))
+        # the reference's CPU decode knows only its default scale layout
+        self.use_ref = oracle.ref() is not None and cfg["variant"] == 0
+        rng = np.random.default_rng(0)
+        self.xh, self.xa = rng.standard_normal(H, dtype=np.float32), rng.standard_normal(A, dtype=np.float32)
+        self.tensors = {k: synth.host_tensor(cfg["fmt"][k], *self.shapes[k], seed=synth.seed_for(set_name, "cpu", k)) for k in self.shapes}
+        self.lm = synth.host_tensor(cfg["fmt"]["lm_head"], V, H, seed=synth.seed_for(set_name, "cpu", "lm_head"))
+        self.layer_bytes = sum(t.size for t in self.tensors.values())
+        self.step_bytes = self.layer_bytes * cfg["layers"] + self.lm.size
+        self.kind = "reference" if self.use_ref else "port"
+        self.cores = int(oracle.ref().ref_num_threads() if self.use_ref else oracle.num_threads())
 
-    def one_layer():
-        for k, (od, idim) in shapes.items():
-            oracle.matvec_f32(cfg["fmt"][k], tensors[k], od, idim, xa if k == "down" else xh, layout=cfg["variant"],
-                              use_ref=use_ref)
+    def step(self):
+        cfg, mv = self.cfg, self.oracle.matvec_f32
+        for _ in range(cfg["layers"]):
+            for k, (od, idim) in self.shapes.items():
+                mv(cfg["fmt"][k], self.tensors[k], od, idim, self.xa if k == "down" else self.xh, layout=cfg["variant"], use_ref=self.use_ref)
+        mv(cfg["fmt"]["lm_head"], self.lm, cfg["vocab"], cfg["hidden"], self.xh, layout=cfg["variant"], use_ref=self.use_ref)
 
-    one_layer()
-    times = []
-    t_all = time.perf_counter()
-    for _ in range(reps):
-        t0 = time.perf_counter()
-        one_layer()
-        times.append(time.perf_counter() - t0)
-        if budget_s and time.perf_counter() - t_all > budget_s:
-            break
-    threads = (oracle.ref().ref_num_threads() if use_ref else oracle.num_threads())
-    return times, dict(kind="reference" if use_ref else "port", cores=int(threads), layer_bytes=int(layer_bytes))
+    def timed(self, steps: int, warmup: int, budget_s: float = 0.0):
+        for _ in range(warmup):
+            self.step()
+        times, t_all = [], time.perf_counter()
+        for _ in range(steps):
+            t0 = time.perf_counter()
+            self.step()
+            times.append(time.perf_counter() - t0)
+            if budget_s and time.perf_counter() - t_all > budget_s:
+                break
+        return times
+
+    def sample_text(self, n: int) -> str:
+        return (f"{n} whole token steps of {self.name}: {self.cfg['layers']} x one layer's tensors ({self.layer_bytes} B, decoded again "
+                f"for every layer) + lm_head, {self.step_bytes} weight bytes per step, fixed input vectors")
 
 
 def run_reference_arm(args):
@@ -147,28 +174,18 @@ def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    from orome_b200 import decode_set, synth
     name = args.workload
-    cfg = decode_set.SETS[name]
-    H, A, KV = cfg["hidden"], cfg["ffn"], cfg["kv"]
-    shapes = dict(q=(H, H), k=(KV, H), v=(KV, H), o=(H, H), gate=(A, H), up=(A, H), down=(H, A))
-    total_bytes = sum(synth.tensor_bytes(cfg["fmt"][k], *shapes[k]) for k in shapes) * cfg["layers"] + \
-        synth.tensor_bytes(cfg["fmt"]["lm_head"], cfg["vocab"], H)
-    for _ in range(max(0, args.warmup - 1)):
-        pass
-    times, meta = cpu_layer_sample(name, max(1, args.steps))
-    per_layer = statistics.median(times)
-    # a step is sampled by one layer; the whole token step scales by the byte ratio
-    step_s = per_layer * total_bytes / meta["layer_bytes"]
+    cpu = CpuSteps(name)
+    times = cpu.timed(max(1, args.steps), max(1, args.warmup))
+    step_s = sum(times) / len(times)
     tok_s = 1.0 / step_s
-    sample = f"one layer of {name} ({meta['layer_bytes']} weight bytes) per step, scaled to the full set by bytes ({total_bytes})"
     line = {
         "impl": "reference", "metric": "decode_matvec_tok_s", "value": tok_s, "unit": "tok/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True,
+        "steps": len(times), "warmup": max(1, args.warmup), "ms_per_step": step_s * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": name, "batch": 1, "inputs": "seeded synthetic GGUF blocks"},
-        "cpu_baseline": {"value": tok_s, "unit": "tok/s", "cores": meta["cores"], "kind": meta["kind"], "sample": sample,
-                         "cpu_gbs": meta["layer_bytes"] / per_layer / 1e9},
+        "cpu_baseline": {"value": tok_s, "unit": "tok/s", "cores": cpu.cores, "kind": cpu.kind, "sample": cpu.sample_text(len(times)),
+                         "cpu_gbs": cpu.step_bytes / step_s / 1e9},
         "e2e": {"value": tok_s, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -178,23 +195,24 @@ def run_reference_arm(args):
 # GPU arm
 # ----------------------------------------------------------------------------------------------
 class Stepper:
-    """Issues one token step of a DecodeSet through the C ABI (optionally replayed from a CUDA graph)."""
+    """One token step of a DecodeSet through the C ABI.  mode "chain": recorded once, one launch per step;
+    mode "launches": one launch per product, replayed from a CUDA graph."""
 
-    # arrival counters of the fused all-gather, one per gathered vector
+    # flags of the gathered vectors (armed single launches on several GPUs)
     FLAG_QKV, FLAG_O, FLAG_ACT, FLAG_DN, FLAG_LOGITS = range(5)
 
-    def __init__(self, torch, F, ctx, ds, dist=None, fused=False):
+    def __init__(self, torch, F, ctx, ds, dist=None, fused=True, mode="chain"):
         self.torch, self.F, self.ctx, self.ds, self.dist = torch, F, ctx, ds, dist
+        self.mode = mode
         self.fused = fused and ds.world > 1
         dev = ds.arena.device
         H, A, KV, V = ds.hidden, ds.ffn, ds.kv, ds.vocab
         g = torch.Generator(device=dev)
         g.manual_seed(1234)
-        self.x_h = torch.randn(H, device=dev, generator=g)           # input of every hidden-sized product
-        self.x_a = torch.randn(A, device=dev, generator=g)           # input of the down projection
+        self.x_h = torch.randn(H, device=dev, generator=g)           # the step's input vector
         from orome_b200.rowsplit import padded_rows
         w = ds.world
-        # gather buffers (padded to equal slices per rank when sharded); local slices are written in place
+        # output vectors (padded to equal slices per rank when sharded); local slices are written in place
         sizes = [padded_rows(n, w) for n in (H, KV, KV, H, A, H, V)]
         if self.fused:
             from orome_b200.rowsplit import PeerArena
@@ -203,11 +221,12 @@ class Stepper:
         else:
             bufs = [torch.zeros(n, device=dev) for n in sizes]
         self.q, self.k, self.v, self.o, self.act, self.dn, self.logits = bufs
+        self.token = torch.full((1,), -1, device=dev, dtype=torch.int32)
         self.refs = [[ds.ref(t) for t in lt] for lt in ds.tensors]
         self.lm_ref = ds.ref(ds.lm_head)
-        self.graph = None
+        self.graph = self.chain = None
         self.launches_per_step = 0
-        self.hints = True
+        self.products_per_step = 0
 
     def _slice(self, full, full_out):
         from orome_b200.rowsplit import shard_rows
@@ -215,80 +234,168 @@ class Stepper:
         return full[lo:hi]
 
     def _gather(self, full, full_out):
-        """All-gather of the output vector when the rows are split over ranks."""
-        if self.fused:
-            return      # the producing kernel already stored this rank's rows into every peer's arena
+        """All-gather of the output vector when the rows are split over ranks and the kernels do not do it themselves."""
+        if self.fused or self.ds.world == 1:
+            return
         from orome_b200.rowsplit import all_gather_rows
         all_gather_rows(self.dist, full, full_out, self.ds.rank, self.ds.world)
 
-    def issue(self, stream):
+    def issue(self, stream, layers=None, recording=False):
+        """The products of one step, each reading its predecessor's output (engine.m:481-1046)."""
         ctx, ds = self.ctx, self.ds
         H, A, KV, V = ds.hidden, ds.ffn, ds.kv, ds.vocab
-        xh, xa = self.x_h.data_ptr(), self.x_a.data_ptr()
-        # fused gather: a product reads the gathered output of the one before it (that read IS the wait)
-        fz = self.fused
-        x_o = self.q.data_ptr() if fz else xh
-        x_gu = self.o.data_ptr() if fz else xh
-        x_dn = self.act.data_ptr() if fz else xa
         c0 = ctx.launch_count
-        hint = ctx.hint_next if self.hints else (lambda r: None)
-        gn = ctx.gather_next if self.fused else (lambda w, p: None)     # (counter to wait on, counter to publish)
-        nl = len(self.refs)
-        for li, refs in enumerate(self.refs):
-            rq, rk, rv, ro, rg, ru, rd = refs
-            nxt_q = self.refs[li + 1][0] if li + 1 < nl else self.lm_ref      # first tensor the step reads after this layer
-            hint(ro if ro.out_dim else None)
-            if rq.out_dim and rk.out_dim and rv.out_dim:
-                gn(self.FLAG_DN if li else -1, self.FLAG_QKV)
-                ctx.matvec_group([rq, rk, rv], self.dn.data_ptr() if fz and li else xh, [self._slice(self.q, H).data_ptr(), self._slice(self.k, KV).data_ptr(),
-                                                    self._slice(self.v, KV).data_ptr()], stream)
-            else:   # some rank holds no rows of a small tensor
-                for r, buf, n in ((rq, self.q, H), (rk, self.k, KV), (rv, self.v, KV)):
-                    if r.out_dim:
-                        ctx.matvec(r, xh, self._slice(buf, n).data_ptr(), 1, 0, 0, stream)
+        armed = self.fused and not recording                               # armed single launches say what to wait for / publish
+        hint = (lambda r: None) if recording else ctx.hint_next
+        gn = ctx.gather_next if armed else (lambda w, p: None)
+        layer_ids = list(range(len(self.refs))) if layers is None else list(layers)
+        x_in, first, nprod = self.x_h, True, 0
+        for n, li in enumerate(layer_ids):
+            rq, rk, rv, ro, rg, ru, rd = self.refs[li]
+            nxt_q = self.refs[layer_ids[n + 1]][0] if n + 1 < len(layer_ids) else self.lm_ref
+            if not (rq.out_dim and rk.out_dim and rv.out_dim and ro.out_dim and rg.out_dim and rd.out_dim):
+                raise SystemExit("bench.py: a rank holds no row of some tensor; use fewer GPUs for this workload")
+            hint(ro)
+            gn(-1 if first else self.FLAG_DN, self.FLAG_QKV)
+            ctx.matvec_group([rq, rk, rv], x_in.data_ptr(), [self._slice(self.q, H).data_ptr(), self._slice(self.k, KV).data_ptr(),
+                                                            self._slice(self.v, KV).data_ptr()], stream)
             self._gather(self.q, H); self._gather(self.k, KV); self._gather(self.v, KV)
-            if ro.out_dim:
-                hint(rg)
-                gn(self.FLAG_QKV, self.FLAG_O)
-                ctx.matvec(ro, x_o, self._slice(self.o, H).data_ptr(), 1, 0, 0, stream)
+            hint(rg)
+            gn(self.FLAG_QKV, self.FLAG_O)
+            ctx.matvec(ro, self.q.data_ptr(), self._slice(self.o, H).data_ptr(), 1, 0, 0, stream)
             self._gather(self.o, H)
-            if rg.out_dim:
-                hint(rd)
-                gn(self.FLAG_O, self.FLAG_ACT)
-                ctx.gate_up_swiglu(rg, ru, x_gu, self._slice(self.act, A).data_ptr(), 1, 0, 0, stream)
+            hint(rd)
+            gn(self.FLAG_O, self.FLAG_ACT)
+            ctx.gate_up_swiglu(rg, ru, self.o.data_ptr(), self._slice(self.act, A).data_ptr(), 1, 0, 0, stream)
             self._gather(self.act, A)
-            if rd.out_dim:
-                hint(nxt_q if nxt_q.out_dim else None)
-                gn(self.FLAG_ACT, self.FLAG_DN)
-                ctx.matvec(rd, x_dn, self._slice(self.dn, H).data_ptr(), 1, 0, 0, stream)
+            hint(nxt_q)
+            gn(self.FLAG_ACT, self.FLAG_DN)
+            ctx.matvec(rd, self.act.data_ptr(), self._slice(self.dn, H).data_ptr(), 1, 0, 0, stream)
             self._gather(self.dn, H)
-        if self.lm_ref.out_dim:
-            hint(self.refs[0][0] if nl and self.refs[0][0].out_dim else None)   # the next token starts at layer 0 again
-            gn(self.FLAG_DN if nl else -1, self.FLAG_LOGITS)
-            ctx.matvec(self.lm_ref, self.dn.data_ptr() if fz and nl else xh, self._slice(self.logits, V).data_ptr(), 1, 0, 0, stream)
+            x_in, first, nprod = self.dn, False, nprod + 4
+        hint(self.refs[layer_ids[0]][0] if layer_ids else None)            # the next token starts at the first layer again
+        gn(-1 if first else self.FLAG_DN, self.FLAG_LOGITS)
+        ctx.matvec(self.lm_ref, x_in.data_ptr(), self._slice(self.logits, V).data_ptr(), 1, 0, 0, stream)
         self._gather(self.logits, V)
+        nprod += 1
         if self.fused:
             ctx.gather_wait(self.FLAG_LOGITS, self.logits.data_ptr(), V, stream)     # the logits are complete on this rank from here on
-        self.launches_per_step = ctx.launch_count - c0
+        if ds.world == 1 or not recording:
+            ctx.argmax(self.logits.data_ptr(), V, self.token.data_ptr(), stream)     # engine.m:1036-1046
+        if not recording:
+            self.launches_per_step = ctx.launch_count - c0
+        if layers is None:
+            self.products_per_step = nprod
 
-    def capture(self):
+    def record(self, layers=None):
+        """A chain over the given layers (default: all) and the lm_head."""
+        self.ctx.chain_begin()
+        try:
+            self.issue(0, layers=layers, recording=True)
+        except BaseException:
+            try:
+                self.ctx.chain_end().close()
+            except Exception:
+                pass
+            raise
+        return self.ctx.chain_end()
+
+    def build(self):
         torch = self.torch
+        if self.mode == "chain":
+            self.chain = self.record()
+            self.launches_per_step = 1 if self.ds.world == 1 else 2         # several GPUs: the arg-max of the gathered logits is its own launch
+            return
         s = torch.cuda.Stream()
         s.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(s):
             self.issue(s.cuda_stream)           # warm every kernel variant before capturing
         torch.cuda.current_stream().wait_stream(s)
         torch.cuda.synchronize()
+        if self.ds.world > 1 and not self.fused:
+            return                              # NCCL all-gathers between the launches: issued eagerly
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g, stream=s):
             self.issue(torch.cuda.current_stream().cuda_stream)
         self.graph = g
 
     def step(self):
-        if self.graph is not None:
+        st = self.torch.cuda.current_stream().cuda_stream
+        if self.chain is not None:
+            self.chain.launch(st)
+            if self.ds.world > 1:
+                self.ctx.argmax(self.logits.data_ptr(), self.ds.vocab, self.token.data_ptr(), st)
+        elif self.graph is not None:
             self.graph.replay()
         else:
-            self.issue(self.torch.cuda.current_stream().cuda_stream)
+            self.issue(st)
+
+    # ---- correctness of what was timed -------------------------------------------------------------------------
+    def parity_check(self, rows_per_product=48):
+        """Run the first layer and the lm_head through the timed form once more (fresh, healthy values: after a few
+        layers the synthetic activations of the full step underflow) and compare sampled rows of every product with
+        the CPU oracle fed the SAME input vector the GPU product read.  Returns (worst rel-L2, rows checked)."""
+        import numpy as np
+        import oracle
+        from orome_b200 import synth
+        from orome_b200.rowsplit import shard_rows
+        torch, ds = self.torch, self.ds
+        st = torch.cuda.current_stream().cuda_stream
+        if self.mode == "chain":
+            chain = self.record(layers=[0])
+            chain.launch(st)
+            if ds.world > 1:
+                self.ctx.argmax(self.logits.data_ptr(), ds.vocab, self.token.data_ptr(), st)
+        else:
+            keep = self.launches_per_step
+            self.issue(st, layers=[0])
+            self.launches_per_step = keep
+        torch.cuda.synchronize()
+        if self.dist is not None:
+            self.dist.barrier()
+        H, A, KV, V = ds.hidden, ds.ffn, ds.kv, ds.vocab
+        host = lambda t, n: t[:n].detach().cpu().numpy().astype(np.float32)
+        xh, q, k, v, o, act, dn, logits = (host(self.x_h, H), host(self.q, H), host(self.k, KV), host(self.v, KV), host(self.o, H),
+                                           host(self.act, A), host(self.dn, H), host(self.logits, V))
+        tq, tk, tv, to, tg, tu, td = ds.tensors[0]
+        rng = np.random.default_rng(99 + ds.rank)
+        worst, nrows = 0.0, 0
+
+        def rows_of(t, sel):
+            rb = synth.row_bytes(t.fmt, t.in_dim)
+            idx = torch.as_tensor(sel, device=ds.arena.device, dtype=torch.int64)
+            view = ds.arena[t.offset:t.offset + t.nbytes].view(t.out_dim, rb)
+            return view.index_select(0, idx).cpu().numpy().reshape(-1)
+
+        def check(t, x, got_full, t2=None):
+            nonlocal worst, nrows
+            lo, hi = shard_rows(t.full_out, ds.rank, ds.world)
+            if hi <= lo:
+                return
+            sel = np.sort(rng.choice(hi - lo, size=min(rows_per_product, hi - lo), replace=False))
+            want = oracle.matvec_f64(t.fmt, rows_of(t, sel), len(sel), t.in_dim, x, layout=ds.variant)
+            if t2 is not None:
+                want = oracle.swiglu_f64(want, oracle.matvec_f64(t2.fmt, rows_of(t2, sel), len(sel), t2.in_dim, x, layout=ds.variant))
+            got = got_full[lo + sel]
+            err = float(np.linalg.norm(got - want) / max(np.linalg.norm(want), 1e-300))
+            worst, nrows = max(worst, err), nrows + len(sel)
+
+        check(tq, xh, q); check(tk, xh, k); check(tv, xh, v)
+        check(to, q, o)
+        check(tg, o, act, t2=tu)
+        check(td, act, dn)
+        check(ds.lm_head, dn, logits)
+        token_ok = int(self.token.item()) == oracle.argmax(logits)
+        if self.dist is not None:
+            t = torch.tensor([worst, float(nrows), 0.0 if token_ok else 1.0], device=ds.arena.device, dtype=torch.float64)
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+            w2 = torch.tensor([float(nrows)], device=ds.arena.device, dtype=torch.float64)
+            self.dist.all_reduce(w2, op=self.dist.ReduceOp.SUM)
+            worst, nrows, token_ok = float(t[0].item()), int(w2.item()), t[2].item() == 0.0
+        finite = bool(np.isfinite(logits).all())
+        return {"rel_l2": worst, "rows": nrows, "token_matches_reference_argmax": bool(token_ok), "finite": finite,
+                "what": "first layer + lm_head through the timed form, sampled rows of every product against the fp64 CPU oracle fed the "
+                        "GPU product's own input vector; every rank checks its own rows"}
 
 
 def kernel_extras(torch, F, ctx, peak, only=None, reps=3):
@@ -411,18 +518,9 @@ def run_ours(args):
                           "peak_gbs": peak, "peak_kind": kind}), flush=True)
         return
     ds = decode_set.DecodeSet(args.workload, dev, rank=rank, world=world, layers=args.layers)
-    st = Stepper(torch, F, ctx, ds, dist, fused=args.gather == "fused")
-    use_graph = args.graph
-    if use_graph:
-        try:
-            st.capture()
-        except Exception as ex:     # report and run eagerly rather than hide the failure
-            if rank == 0:
-                print(f"bench.py: graph capture failed ({ex}); running without a graph", file=sys.stderr)
-            st.graph = None
-            use_graph = False
-    else:
-        st.issue(torch.cuda.current_stream().cuda_stream)
+    mode = args.mode if (world == 1 or args.gather == "fused") else "launches"      # an NCCL all-gather per product cannot be chained
+    st = Stepper(torch, F, ctx, ds, dist, fused=args.gather == "fused", mode=mode)
+    st.build()
     torch.cuda.synchronize()
 
     def barrier():
@@ -449,27 +547,28 @@ def run_ours(args):
         return total, per
 
     # ---- device-resident timing ---------------------------------------------------------
-    for _ in range(max(3, args.warmup)):
+    warmup = max(3, args.warmup)
+    for _ in range(warmup):
         st.step()
     torch.cuda.synchronize()
     sampler = ClockSampler(local)
     sampler.start()
-    c0 = ctx.launch_count
     total, per = timed(st.step, args.steps)
-    launches = (ctx.launch_count - c0) if not use_graph else st.launches_per_step * args.steps
+    launches = st.launches_per_step * args.steps
     clocks = sampler.finish()
     ms_per_step = total / args.steps * 1e3
     tok_s = args.steps / total
 
-    # ---- end to end: x from pinned host memory, logits back to the host every step ---------
+    # ---- end to end: x from pinned host memory, the token back to the host every step ---------
+    # (the reference reads its 4-byte arg-max result after every token, engine.m:1057)
     x_pin = torch.randn(ds.hidden).pin_memory()
-    logits_pin = torch.empty(ds.vocab).pin_memory()
+    tok_pin = torch.empty(1, dtype=torch.int32).pin_memory()
 
     def e2e_step():
         st.x_h.copy_(x_pin, non_blocking=True)
         st.step()
-        logits_pin.copy_(st.logits[:ds.vocab], non_blocking=True)
-        torch.cuda.current_stream().synchronize()      # the host needs the logits before the next token
+        tok_pin.copy_(st.token, non_blocking=True)
+        torch.cuda.current_stream().synchronize()      # the host needs the token before the next one starts
 
     for _ in range(3):
         e2e_step()
@@ -481,6 +580,14 @@ def run_ours(args):
 
     if ctx.status() != 0:
         raise SystemExit("bench.py: a kernel reported an expired wait; the numbers are void")
+
+    parity = st.parity_check()
+    if ctx.status() != 0:
+        raise SystemExit("bench.py: a kernel reported an expired wait during the parity check")
+    if not (parity["rel_l2"] <= 1e-4 and parity["token_matches_reference_argmax"] and parity["finite"]):
+        if rank == 0:
+            print(json.dumps({"error": "parity check failed; the timing is void", "parity_check": parity}), flush=True)
+        raise SystemExit(2)
 
     def leave():
         """Multi-rank exit: agree that every rank is done, then leave without tearing NCCL down
@@ -502,42 +609,48 @@ def run_ours(args):
     w_bytes = ds.full_weight_bytes()
     alg_bytes = w_bytes + ds.io_bytes()
     achieved = alg_bytes / (total / args.steps) / 1e9
-    launches_per_step = st.launches_per_step
-    alg_per_launch = alg_bytes / max(1, launches_per_step)
+    # the dominant kernel: the resident chain kernel (one launch = one step) or the per-product GEMV launches
+    dom_launches = 1 if mode == "chain" else st.products_per_step
+    alg_per_launch = alg_bytes / dom_launches / world                       # bytes ONE GPU's launch moves
+    ratio = dram_per_algorithmic(args.workload, mode) if world == 1 else None
     roofline = {
-        "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
-        "frac_of_8tbs_nominal": achieved / NOMINAL_HBM_GBS,
-        "traffic": (alg_per_launch * NCU_DRAM_PER_ALGORITHMIC[args.workload]
-                    if world == 1 and args.workload in NCU_DRAM_PER_ALGORITHMIC and ctx.get_option(F.OPT_PREFETCH_MB) == 24 else None),
-        "traffic_note": "ncu capture of a 2-layer cut scaled by algorithmic bytes; counts the next tensor's L2 prefetch twice (caches flushed between launches under ncu)",
-        "kernel": "gemv_pipe_kernel", "algorithmic_bytes_per_step": alg_bytes, "launches_per_step": launches_per_step,
-        "avg_launch_us": ms_per_step * 1e3 / max(1, launches_per_step),
-        "algorithmic_bytes_per_launch": alg_bytes / max(1, launches_per_step),
+        "bound": "hbm", "achieved": achieved / world, "peak": peak, "unit": "GB/s", "frac": achieved / world / peak, "peak_kind": peak_kind,
+        "per": "GPU: algorithmic bytes one GPU's launches move per second against one GPU's peak",
+        "aggregate_gbs": achieved, "frac_of_8tbs_nominal": achieved / world / NOMINAL_HBM_GBS,
+        "traffic": alg_per_launch * ratio if ratio else None,
+        "traffic_note": "DRAM read + write bytes per algorithmic byte from the committed ncu capture of a short cut of this workload "
+                        "(profiles/dram_traffic.json), times the algorithmic bytes of one launch",
+        "kernel": "gemv_chain_kernel" if mode == "chain" else "gemv_pipe_kernel / gemv_mma_kernel",
+        "algorithmic_bytes_per_step": alg_bytes, "launches_per_step": st.launches_per_step, "products_per_step": st.products_per_step,
+        "avg_launch_us": ms_per_step * 1e3 / dom_launches,
+        "algorithmic_bytes_per_launch": alg_per_launch,
     }
 
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
-        times, meta = cpu_layer_sample(args.workload, 400, budget_s=12.0)    # about 12 s of CPU work
-        per_layer = statistics.median(times)
-        step_s = per_layer * w_bytes / meta["layer_bytes"]
-        cpu = {"value": 1.0 / step_s, "unit": "tok/s", "cores": meta["cores"], "kind": meta["kind"],
-               "sample": f"one layer ({meta['layer_bytes']} weight bytes) x{len(times)}, median, scaled to the full set by bytes",
-               "cpu_gbs": meta["layer_bytes"] / per_layer / 1e9}
+        cs = CpuSteps(args.workload)
+        times = cs.timed(64, 1, budget_s=12.0)                                # about 12 s of CPU work
+        step_s = sum(times) / len(times)
+        cpu = {"value": 1.0 / step_s, "unit": "tok/s", "cores": cs.cores, "kind": cs.kind, "sample": cs.sample_text(len(times)),
+               "cpu_gbs": cs.step_bytes / step_s / 1e9}
 
     line = {
         "metric": "decode_matvec_tok_s", "value": tok_s, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
-        "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+        "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "int8 dot products on 24-bit fixed-point x, fp32 accumulate" if ctx.get_option(F.OPT_X_BITS) == 24
         else "int8 dot products on 16-bit fixed-point x, fp32 accumulate",
         "data": "synthetic",
         "config": {"workload": args.workload, "batch": 1, "layers": ds.layers, "weight_bytes": w_bytes,
-                   "l2": "inputs larger than L2: every layer has its own weights", "cuda_graph": bool(use_graph),
+                   "l2": "inputs larger than L2: every layer has its own weights",
+                   "form": ("one resident kernel per token step (recorded chain), every product reads its predecessor's output" if mode == "chain"
+                            else "one launch per product" + (", CUDA graph" if st.graph is not None else "")),
                    "parallelism": "single GPU" if world == 1 else
                    (f"row-split x{world}, y completed by tagged peer stores from the kernel epilogue (NVLink), consumers poll the data" if st.fused
                     else f"row-split x{world} + all-gather (NCCL)")},
         "roofline": roofline,
-        "e2e": {"value": e2e_tok_s, "unit": "tok/s", "h2d_bytes_per_step": ds.hidden * 4, "d2h_bytes_per_step": ds.vocab * 4,
+        "e2e": {"value": e2e_tok_s, "unit": "tok/s", "h2d_bytes_per_step": ds.hidden * 4, "d2h_bytes_per_step": 4,
                 "wall_tok_s": args.steps / wall},
+        "parity_check": parity,
         "gpu_launches": int(launches),
         "clocks": clocks,
         "step_ms_min_med_max": [min(per) * 1e3, statistics.median(per) * 1e3, max(per) * 1e3],
@@ -561,8 +674,8 @@ def main():
     ap.add_argument("--workload", default="9b_q8_0", choices=["9b_q8_0", "27b_q4_k_m"])
     ap.add_argument("--layers", type=int, default=None, help="override the number of layers (smaller captures for profiling)")
     ap.add_argument("--x-bits", type=int, default=0, choices=[0, 16, 24])
-    ap.add_argument("--graph", dest="graph", action="store_true", default=True)
-    ap.add_argument("--no-graph", dest="graph", action="store_false")
+    ap.add_argument("--mode", default="chain", choices=["chain", "launches"],
+                    help="chain: the step is recorded once and runs as one resident kernel; launches: one kernel per product (CUDA graph)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--extras", action="store_true", help="also time the other benchmark configurations kernel by kernel (adds ~20 s)")
     ap.add_argument("--kernel", default="", help="run only the named --extras case(s), comma separated, --steps timing repeats, and exit")

@@ -107,8 +107,12 @@ void orome_cuda_ctx_destroy(orome_cuda_ctx *ctx);
 /* Message of the last failed call on this thread ("" if none). */
 const char *orome_cuda_last_error(void);
 
-/* Device-side status word: 0, or the code left by a kernel whose bounded wait
- * on its own copy pipeline ran out.  Synchronises the context's device. */
+/* Device-side status word: 0, or the code left by a kernel whose bounded wait ran out
+ * (1, 2: a stage of its own copy pipeline; 3: an input element that a peer GPU or an
+ * earlier product of a chain should have written; 4: the tensor-core form's pipeline).
+ * Synchronises the context's device, returns OROME_ETIMEOUT when the word is set and then
+ * clears it, so the condition is reported once.  While the word is set, chain launches and
+ * gather waits do not wait at all (their results are void until the word is cleared). */
 int  orome_cuda_status(orome_cuda_ctx *ctx, int *status_out);
 
 /* Replaces format_provider_open_gguf (format.m:343-363).  The reference wraps
@@ -142,11 +146,14 @@ int  orome_format_dispatch_matvec(orome_cuda_ctx *ctx, const OromeTensorRef *ref
 /* Batched form of the same product: y[b][r] = sum_c W[r][c] x[b][c] for
  * b < batch, x row stride ldx, y row stride ldy (in floats).  batch == 1 is the
  * decode matvec; larger batches are the prefill form, which the reference runs
- * as one matvec per token (main.m:745-747).  Batches of 9 and more on Q8_0 / Q4_K /
- * Q5_K tensors whose in_dim is a multiple of 256 run on the tensor cores (tcgen05) with
- * weights and x rounded to fp16 and fp32 accumulation: rel-L2 of a few 1e-4 against an
- * exact evaluation, the class of rounding the reference's own kernels apply to x
- * (shaders.metal:1470).  Smaller batches keep fp32 activations (rel-L2 <= 1e-4). */
+ * as one matvec per token (main.m:745-747).  Batches of OROME_OPT_TC_MIN_BATCH (default 4)
+ * and more on Q8_0 / Q4_K / Q5_K tensors whose in_dim is a multiple of 256 run on the tensor
+ * cores (tcgen05) with weights and x rounded to fp16 and fp32 accumulation: rel-L2 <= 5e-4
+ * against an exact evaluation, the class of rounding the reference's own kernels apply to x
+ * (shaders.metal:1470).  The first such call allocates scratch inside the context: make it
+ * before any stream capture.  Smaller batches keep fp32 activations (rel-L2 <= 1e-4).
+ * With a multi-GPU gather request armed (orome_cuda_gather_next), only the batch-1 quantized
+ * form is available: other calls drop the request and return OROME_ENOTSUP. */
 int  orome_cuda_matvec(orome_cuda_ctx *ctx, const OromeTensorRef *ref,
                        const float *x_dev, float *y_dev, int batch, int ldx, int ldy, void *stream);
 
@@ -169,6 +176,16 @@ int  orome_cuda_gate_up_swiglu(orome_cuda_ctx *ctx, const OromeTensorRef *gate, 
  * the reference's CPU decode (also the embedding lookup of engine.m:122-141). */
 int  orome_cuda_dequant_rows(orome_cuda_ctx *ctx, const OromeTensorRef *ref,
                              uint32_t row0, uint32_t nrows, float *out_dev, void *stream);
+
+/* argmax_kernel (shaders.metal:1249-1305) as dispatched after the lm_head (engine.m:1036-1046):
+ * *result_dev = index of the largest of `count` floats, so that a token costs the host a 4-byte
+ * read (engine.m:1057) instead of the logits.  Equal values resolve exactly as the reference's kernel resolves them
+ * (its 1024 threads stride over the vector, then two shuffle-down trees pick among threads; the
+ * smallest index wins only among elements of the same thread); NaN and -inf never win; no
+ * candidate gives index 0.
+ * While a chain is being recorded, the call must name the whole output of the product
+ * recorded last: the reduction then runs inside that product's epilogue (single GPU). */
+int  orome_cuda_argmax(orome_cuda_ctx *ctx, const float *data_dev, uint32_t count, uint32_t *result_dev, void *stream);
 
 /* MoE routing: logits = Wr x per token (matvec_f32 / matvec_f32_pair,
  * shaders.metal:1342-1392, engine.m:656-684) followed by softmax_topk_route
@@ -241,6 +258,47 @@ int  orome_cuda_moe_ffn_shard(orome_cuda_ctx *ctx, const OromeExpertLayerRef *la
  * performance hint: results do not depend on it. */
 int  orome_cuda_hint_next(orome_cuda_ctx *ctx, const OromeTensorRef *next);
 
+/* ---- one token step as ONE launch ---------------------------------------------------------
+ *
+ * The reference encodes every product of a token into one command buffer and commits it once
+ * (engine.m:453-454 open the buffer and its encoder, format_dispatch_matvec and the fused
+ * gate/up dispatch only encode, engine.m:1048-1050 commit and wait).  The same shape here:
+ * between orome_cuda_chain_begin and orome_cuda_chain_end, orome_format_dispatch_matvec,
+ * orome_cuda_matvec (batch 1), orome_cuda_matvec_group, orome_cuda_gate_up_swiglu,
+ * orome_cuda_argmax and orome_cuda_gather_wait RECORD their operation instead of launching it;
+ * orome_cuda_chain_launch then runs the recorded sequence as a single resident kernel (one CTA
+ * per SM) in which the weights of the next product stream into shared memory while the current
+ * one is still being consumed.  A chain is reusable: pointers and shapes are fixed at record
+ * time, the vectors' contents are read at launch time.
+ *
+ * Ordering.  A product whose input vector is (inside) the output of an earlier recorded product
+ * waits for it element by element; inputs that no recorded product writes are read as they are
+ * at launch.  A product may overwrite a vector an earlier product reads or writes only if a
+ * chain of such data dependencies orders the two (true for a decode step, where each product
+ * consumes its predecessor's output); otherwise chain_end returns OROME_ENOTSUP.  Outputs are
+ * complete for other readers when the launch has completed in stream order.
+ *
+ * Quantized tensors only (Q8_0 with in_dim a multiple of 64; Q4_K / Q5_K / Q6_K with in_dim a
+ * multiple of 256), batch 1, at most 4 tensors per grouped product.  chain_end allocates (device
+ * table, {value, tag} slots of every output); chain_launch allocates nothing.  All CTAs of the
+ * launch must be resident at once, so it is issued as a cooperative launch: it fails with
+ * OROME_ECUDA rather than hang when the device cannot hold one CTA per SM.
+ *
+ * Several GPUs (after orome_cuda_gather_setup): products whose outputs lie in the gather arena
+ * publish them to every peer from their epilogue, exactly like an armed single launch; a
+ * product that reads such a vector polls the peers' elements too.  Every rank records the same
+ * sequence and launches it the same number of times; gather_next is not needed inside a
+ * recording.  orome_cuda_gather_wait inside a recording copies a gathered vector to its plain
+ * place as part of the chain.  The chains of one context share a tag counter: launch them one at a
+ * time (stream order on one stream is enough). */
+typedef struct orome_cuda_chain orome_cuda_chain;
+int  orome_cuda_chain_begin(orome_cuda_ctx *ctx);
+int  orome_cuda_chain_end(orome_cuda_ctx *ctx, orome_cuda_chain **out);     /* always closes the recording */
+int  orome_cuda_chain_launch(orome_cuda_ctx *ctx, orome_cuda_chain *chain, void *stream);
+void orome_cuda_chain_destroy(orome_cuda_ctx *ctx, orome_cuda_chain *chain);
+/* What was recorded: products, packed weight bytes they read, ring stages and bytes per stage. */
+int  orome_cuda_chain_info(orome_cuda_chain *chain, int *n_products, uint64_t *weight_bytes, int *stages, int *stage_bytes);
+
 /* ---- multi-GPU: row-split products, output vector completed on every GPU ---------------
  *
  * No counterpart in the reference (single GPU, unified memory).  Output rows of a matvec are
@@ -264,8 +322,8 @@ int  orome_cuda_hint_next(orome_cuda_ctx *ctx, const OromeTensorRef *next);
  * vector) and that its y rows are to be published under publish_flag (-1: y stays local); it
  * applies to the next launch only.  A waiting launch must take x from the local arena, a
  * publishing launch must write y into it.  Every rank must run the same sequence of publishing
- * launches per flag, and a flag may be published again only after every rank has consumed its
- * previous generation.  orome_cuda_gather_wait(ctx, flag, vec, n, stream) completes the plain
+ * launches per flag (so every rank must hold at least one row of every published tensor), and a
+ * flag may be published again only after every rank has consumed its previous generation.  orome_cuda_gather_wait(ctx, flag, vec, n, stream) completes the plain
  * copy of a gathered vector (n floats at vec, inside the arena) for readers other than this
  * library's kernels. */
 int  orome_cuda_peer_alloc(orome_cuda_ctx *ctx, size_t bytes, void **dev_ptr, unsigned char handle_out[64]);
@@ -301,15 +359,10 @@ int  orome_cuda_matvec_host(orome_cuda_ctx *ctx, const OromeTensorRef *ref,
 #define OROME_OPT_PREFETCH_MB     7   /* cap on the L2 prefetch of orome_cuda_hint_next, MiB (0 = off) */
 #define OROME_OPT_TC_MIN_BATCH    8   /* batches from this size on use the tensor-core kernel (default 4); smaller ones run one decode launch per vector */
 #define OROME_OPT_KQUANT_MMA      9   /* 1 (default): Q4_K / Q5_K batch-1 products run on the mma.sync kernel; 0: on the dp4a kernel */
+#define OROME_OPT_CHAIN_INFLIGHT 11   /* stages a chain's weight stream keeps outstanding at most (0, default: the whole ring); read at chain_end */
+#define OROME_OPT_WAIT_US        10   /* bound of one device-side wait (peer data, chain inputs, chain stages) in microseconds; 0 (default): about a second */
 int  orome_cuda_set_option(orome_cuda_ctx *ctx, int key, int value);
 int  orome_cuda_get_option(orome_cuda_ctx *ctx, int key, int *value);
-
-/* Diagnostics.  orome_cuda_trace_begin makes the next `launches` pipelined launches record eight
- * %globaltimer stamps per CTA (entry, copies issued, dependency wait over, x quantized, x slice
- * loaded, first tile landed, last tile done, exit); orome_cuda_trace_read synchronises and copies
- * launches * 148 * 8 values out.  Tracing allocates; it is off unless begun. */
-int  orome_cuda_trace_begin(orome_cuda_ctx *ctx, int launches);
-int  orome_cuda_trace_read(orome_cuda_ctx *ctx, unsigned long long *out, size_t n_values);
 
 /* Number of kernel launches issued through this context since creation. */
 uint64_t orome_cuda_launch_count(orome_cuda_ctx *ctx);

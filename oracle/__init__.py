@@ -48,6 +48,8 @@ def lib():
         L.oracle_route.argtypes = [_f32p, C.c_uint32, C.c_uint32, _u32p, _f32p]
         L.oracle_moe_ffn_f64.argtypes = [_u8p, C.c_size_t, C.c_int, _u8p, C.c_size_t, C.c_int, _u8p, C.c_size_t, C.c_int,
                                          C.c_int, _f32p, C.c_uint32, C.c_uint32, _u32p, _f32p, C.c_uint32, _f64p]
+        L.oracle_argmax.restype = C.c_uint32
+        L.oracle_argmax.argtypes = [_f32p, C.c_uint32]
         L.oracle_num_threads.restype = C.c_int
         _lib = L
     return _lib
@@ -189,6 +191,12 @@ def moe_ffn_f64(gate, up, down, fmts, strides, x, hidden, inter, idx, w, layout=
     if rc:
         raise ValueError("moe ffn failed")
     return out
+
+
+def argmax(data) -> int:
+    """Index the reference's argmax_kernel returns for this vector (ties resolved as its 1024 threads do)."""
+    d = np.ascontiguousarray(data, np.float32).reshape(-1)
+    return int(lib().oracle_argmax(_p(d, _f32p), d.size))
 
 
 def use_all_cores() -> int:

@@ -20,7 +20,8 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF_ROOT = os.environ.get("OROME_REFERENCE_ROOT", "/root/reference")
+# the reference tree: named by the environment, else a directory "reference" beside the repository
+REF_ROOT = os.environ.get("OROME_REFERENCE_ROOT") or os.path.join(os.path.dirname(HERE), os.pardir, "reference")
 REF_FORMAT = os.path.join(REF_ROOT, "inference", "src", "format.m")
 REF_LINES = (17, 174)   # format_fp16_to_f32 .. end of format_decode_q6_k_row
 

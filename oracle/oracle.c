@@ -355,6 +355,45 @@ int oracle_moe_ffn_f64(const uint8_t *gate, size_t gate_stride, int gate_fmt,
     return rc ? -1 : 0;
 }
 
+/* argmax_kernel, shaders.metal:1249-1305, as a simulation of its 1024 threads: each thread scans
+ * i = lid, lid + 1024, ... keeping its first maximum (strict >, start at -inf / index 0: 1260-1268);
+ * a shuffle-down tree inside every 32-lane simdgroup takes the other lane's pair only when its
+ * value is strictly greater (1271-1278; lanes whose partner lies beyond the simdgroup keep their
+ * own pair); lane 0 of every simdgroup stores its pair, and simdgroup 0 reduces the 32 pairs the
+ * same way (1281-1304).  NaN never satisfies `>`, so it never wins. */
+uint32_t oracle_argmax(const float *data, uint32_t count)
+{
+    enum { T = 1024 };
+    float val[T]; uint32_t idx[T];
+    for (uint32_t lid = 0; lid < T; ++lid) {
+        float m = -INFINITY; uint32_t mi = 0;
+        for (uint32_t i = lid; i < count; i += T) if (data[i] > m) { m = data[i]; mi = i; }
+        val[lid] = m; idx[lid] = mi;
+    }
+    float tv[32]; uint32_t ti[32];
+    for (uint32_t g = 0; g < T / 32; ++g) {
+        float *v = val + 32 * g; uint32_t *ix = idx + 32 * g;
+        for (uint32_t off = 16; off > 0; off >>= 1) {
+            float nv[32]; uint32_t ni[32];
+            for (uint32_t l = 0; l < 32; ++l) {
+                nv[l] = v[l]; ni[l] = ix[l];
+                if (l + off < 32 && v[l + off] > v[l]) { nv[l] = v[l + off]; ni[l] = ix[l + off]; }
+            }
+            memcpy(v, nv, sizeof nv); memcpy(ix, ni, sizeof ni);
+        }
+        tv[g] = v[0]; ti[g] = ix[0];
+    }
+    for (uint32_t off = 16; off > 0; off >>= 1) {
+        float nv[32]; uint32_t ni[32];
+        for (uint32_t l = 0; l < 32; ++l) {
+            nv[l] = tv[l]; ni[l] = ti[l];
+            if (l + off < 32 && tv[l + off] > tv[l]) { nv[l] = tv[l + off]; ni[l] = ti[l + off]; }
+        }
+        memcpy(tv, nv, sizeof nv); memcpy(ti, ni, sizeof ni);
+    }
+    return ti[0];
+}
+
 int oracle_num_threads(void)
 {
 #ifdef _OPENMP

@@ -2,7 +2,8 @@
 
     python -m orome_b200.build [--force] [--verbose]
 
-Produces orome_b200/liborome_cuda.so with nvcc (cross-compiles without a GPU).
+Produces orome_b200/liborome_cuda.so with nvcc (cross-compiles without a GPU): every
+csrc/*.cu becomes an object file (compiled side by side), then one link step.
 """
 from __future__ import annotations
 
@@ -11,15 +12,17 @@ import os
 import shutil
 import subprocess
 import sys
+from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
+OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "liborome_cuda.so")
 
 NVCC_FLAGS = [
     "-std=c++17", "-O3", "-lineinfo",
     "-gencode", "arch=compute_100a,code=sm_100a",
-    "-Xcompiler", "-fPIC", "-shared",
+    "-Xcompiler", "-fPIC",
     "--expt-relaxed-constexpr",
 ]
 
@@ -35,21 +38,37 @@ def sources() -> list[str]:
     return sorted(glob.glob(os.path.join(CSRC, "*.cu")))
 
 
+def _deps() -> list[str]:
+    return glob.glob(os.path.join(CSRC, "*")) + [os.path.join(HERE, "..", "include", "orome_cuda.h")]
+
+
 def stale() -> bool:
     if not os.path.exists(LIB):
         return True
     t = os.path.getmtime(LIB)
-    deps = glob.glob(os.path.join(CSRC, "*")) + [os.path.join(HERE, "..", "include", "orome_cuda.h")]
-    return any(os.path.getmtime(d) > t for d in deps if os.path.exists(d))
+    return any(os.path.getmtime(d) > t for d in _deps() if os.path.exists(d))
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False, defines: tuple[str, ...] = ()) -> str:
     if not force and not stale():
         return LIB
-    cmd = [nvcc(), *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), "-o", LIB, *sources()]
-    subprocess.check_call(cmd)
+    os.makedirs(OBJ, exist_ok=True)
+    # every translation unit includes the shared headers, so a change to any of them recompiles all
+    newest_header = max(os.path.getmtime(d) for d in _deps() if not d.endswith(".cu") and os.path.exists(d))
+    extra = [f"-D{d}" for d in defines] + (["-Xptxas", "-v"] if verbose else [])
+
+    def compile_one(src: str) -> str:
+        obj = os.path.join(OBJ, os.path.basename(src)[:-3] + ".o")
+        if force or not os.path.exists(obj) or os.path.getmtime(obj) < max(os.path.getmtime(src), newest_header):
+            subprocess.check_call([nvcc(), *NVCC_FLAGS, *extra, "-c", "-o", obj, src])
+        return obj
+
+    with ThreadPoolExecutor(max_workers=max(1, min(len(sources()), os.cpu_count() or 1))) as pool:
+        objs = list(pool.map(compile_one, sources()))
+    subprocess.check_call([nvcc(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB, *objs])
     return LIB
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv,
+                defines=tuple(a[2:] for a in sys.argv[1:] if a.startswith("-D"))))

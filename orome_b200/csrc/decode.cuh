@@ -122,4 +122,23 @@ __device__ __forceinline__ float warp_sum(float v)
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
 
+// Order-preserving key of a float (larger float, larger key), so that {key, ~index} packed in 64 bits orders
+// candidates by value first and by LOWER index second.
+__device__ __forceinline__ uint32_t float_key(float v)
+{
+    const uint32_t b = __float_as_uint(v + 0.0f);      // -0 and +0 compare equal, so they share a key
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+// Tie order of the reference's argmax_kernel (shaders.metal:1249-1305).  Its 1024 threads stride over the vector and
+// each keeps its FIRST maximum; a shuffle-down tree (offsets 16, 8, 4, 2, 1; the lower lane keeps its pair unless the
+// other value is strictly greater) reduces the 32 lanes of a simdgroup, and the same tree reduces the 32 simdgroups.
+// In such a tree lane 0 ends up preferring, among equal values, the lane whose 5-bit number read backwards is
+// smallest (the last step decides between even and odd lanes, the one before between lanes = 0 and 2 mod 4, ...).
+// So among equal values the winner has the smallest bit-reversed simdgroup, then the smallest bit-reversed lane,
+// then the smallest index: argmax_rank() packs exactly that order.
+__device__ __host__ __forceinline__ uint32_t brev5(uint32_t v) { return ((v & 1u) << 4) | ((v & 2u) << 2) | (v & 4u) | ((v & 8u) >> 2) | ((v & 16u) >> 4); }
+__device__ __host__ __forceinline__ uint32_t argmax_rank(uint32_t i) { return (brev5((i >> 5) & 31u) << 27) | (brev5(i & 31u) << 22) | (i >> 10); }
+__device__ __host__ __forceinline__ uint32_t argmax_unrank(uint32_t r) { return ((r & 0x3FFFFFu) << 10) | (brev5(r >> 27) << 5) | brev5((r >> 22) & 31u); }
+
 }  // namespace orome

@@ -120,4 +120,44 @@ __global__ void swiglu_kernel(const float *__restrict__ gate, const float *__res
     out[(size_t)b * ldo + c] = silu_mul(gate[(size_t)b * ldg + c], up[(size_t)b * ldg + c]);
 }
 
+// Index of the largest element: argmax_kernel (shaders.metal:1249-1305), dispatched after the lm_head at
+// engine.m:1036-1046 so that a token costs the host a 4-byte read.  The reference runs one threadgroup of 1024
+// threads; one CTA reading 600 KB takes tens of microseconds here, so the vector is cut over up to 148 CTAs.
+// Candidates are compared as {value key, ~tie rank} (argmax_rank), a total order in which equal values resolve
+// exactly as the reference's strided scan and shuffle-down trees do, so the cut changes nothing; NaN and -inf never
+// win, an input without candidates gives index 0.  state[0]: running best (atomicMax), state[1]: CTAs done; the last
+// CTA writes the result and clears both for the next call.
+__global__ void __launch_bounds__(256)
+argmax_kernel(const float *__restrict__ data, uint32_t count, uint32_t *__restrict__ result, unsigned long long *__restrict__ state)
+{
+    __shared__ unsigned long long s_best[8];
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    unsigned long long best = 0ull;
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < count; i += gridDim.x * blockDim.x) {
+        const float v = __ldcg(data + i);
+        if (v > -INFINITY) {
+            const unsigned long long cand = ((unsigned long long)float_key(v) << 32) | (uint32_t)~argmax_rank(i);
+            if (cand > best) best = cand;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+        if (other > best) best = other;
+    }
+    if ((threadIdx.x & 31u) == 0) s_best[threadIdx.x >> 5] = best;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w) if (s_best[w] > best) best = s_best[w];
+        if (best) atomicMax(state, best);
+        __threadfence();
+        if (atomicAdd(state + 1, 1ull) == gridDim.x - 1) {
+            __threadfence();
+            const unsigned long long m = atomicExch(state, 0ull);
+            *result = m ? argmax_unrank(~(uint32_t)m) : 0u;
+            atomicExch(state + 1, 0ull);
+        }
+    }
+}
+
 }  // namespace orome

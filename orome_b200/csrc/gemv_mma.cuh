@@ -426,7 +426,7 @@ __device__ __forceinline__ void tma_box(uint32_t dst, const CUtensorMap *map, ui
 
 struct MmaTile { int seg; uint32_t row0, n; };
 
-// Diagnostics build only (-DOROME_MMA_TILE_TRACE): CTA 0 records, for eight row tiles from OROME_DBG_TILE on, when each
+// Diagnostics build only (-DOROME_MMA_TILE_TRACE): CTA 0 records, for eight row tiles from tile number OROME_MMA_TILE_TRACE on, when each
 // consumer warp starts waiting for the tile, gets it and is done with it, into the trace area of ten launches later.
 #ifdef OROME_MMA_TILE_TRACE
 #define MMA_TILE_STAMP(a, tile, warp, k)                                                                                      \

@@ -101,6 +101,7 @@ struct PipeArgs {
     unsigned int *pub_arrived;                // CTAs of this launch that finished publishing
     const uint2 *x_ll;                        // slots of x, or NULL when x is a plain vector
     const unsigned int *wait_gen;             // generation x must carry
+    long long wait_cycles;                    // bound of the polls of a gathered x
 };
 
 // ---- PTX wrappers ---------------------------------------------------------
@@ -135,6 +136,19 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
+// The same copy with an L2 eviction policy.  Weights are read exactly once per step: marked evict-first they do not
+// push the small vectors that the products hand to one another out of L2.
+__device__ __forceinline__ uint64_t l2_policy_evict_first()
+{
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void bulk_g2s_hint(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar, uint64_t policy)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(policy) : "memory");
+}
 __device__ __forceinline__ void bulk_prefetch_l2(const void *src, uint32_t bytes)
 {
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
@@ -153,7 +167,13 @@ __device__ __forceinline__ void stamp(unsigned long long *trace, int k)
 __device__ __forceinline__ uint4 ld_slots2(const uint2 *p)
 {
     uint4 v;
+#if OROME_SLOT_LD == 1
+    asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+#elif OROME_SLOT_LD == 2
+    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+#else
     asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+#endif
     return v;
 }
 __device__ __forceinline__ void st_slot(uint2 *p, float v, unsigned int tag)
@@ -162,15 +182,19 @@ __device__ __forceinline__ void st_slot(uint2 *p, float v, unsigned int tag)
 }
 // Four consecutive floats of a gathered vector from their slots, polled until all four carry `tag`
 // (at most PIPE_WAIT_CYCLES; *ok is cleared on expiry and whatever is there is returned).
-__device__ __forceinline__ float4 ld_gathered4(const uint2 *slots, unsigned int tag, bool *ok)
+// Expiry is sticky: once *ok is false this thread polls no more, and every so often the poll looks at the
+// context's status word, so one lost peer costs a launch one wait, not one wait per element.
+__device__ __forceinline__ float4 ld_gathered4(const uint2 *slots, unsigned int tag, bool *ok, long long limit = PIPE_WAIT_CYCLES,
+                                               const int *status = nullptr)
 {
     uint4 a = ld_slots2(slots), b = ld_slots2(slots + 2);
-    if (a.y != tag || a.w != tag || b.y != tag || b.w != tag) {
+    if ((a.y != tag || a.w != tag || b.y != tag || b.w != tag) && *ok) {
         const long long t0 = clock64();
-        for (;;) {
+        for (uint32_t it = 0;; ++it) {
             a = ld_slots2(slots); b = ld_slots2(slots + 2);
             if (a.y == tag && a.w == tag && b.y == tag && b.w == tag) break;
-            if (clock64() - t0 > PIPE_WAIT_CYCLES) { *ok = false; break; }
+            if (clock64() - t0 > limit) { *ok = false; break; }
+            if (status && (it & 255u) == 255u && *reinterpret_cast<const volatile int *>(status) != 0) { *ok = false; break; }
         }
     }
     return make_float4(__uint_as_float(a.x), __uint_as_float(a.z), __uint_as_float(b.x), __uint_as_float(b.z));
@@ -179,7 +203,7 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // Wait for a phase of a copy barrier, at most PIPE_WAIT_CYCLES.  Returns false on expiry.
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, long long limit = PIPE_WAIT_CYCLES)
 {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
@@ -187,7 +211,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
 #pragma unroll 1
         for (int i = 0; i < 64; ++i)
             if (mbar_try_wait(bar, parity)) return true;
-        if (clock64() - t0 > PIPE_WAIT_CYCLES) return false;
+        if (clock64() - t0 > limit) return false;
     }
 }
 
@@ -313,13 +337,55 @@ __device__ __forceinline__ void dot_s(uint32_t q, const XGroup<NP, N> &g, int k,
 // flight together); vector v goes to xq + v * vec_bytes.  in_dim is a multiple of 32, so groups never straddle vectors.
 // With `slots` set, x is a gathered vector: its elements come from {value, tag} slots and are polled for `tag`;
 // the return value is false when a poll expired.
+// One four-float piece (piece number f of its vector) into the quantized copy at xq: the lanes of a group agree on the
+// group's scale by shuffles, so whole warps must call this together (`valid` false for lanes past the end).
+template <int NP, int G, bool SUMS>
+__device__ __forceinline__ void quantize_piece(const float4 v, uint32_t f, bool valid, uint32_t lane, uint8_t *xq, uint32_t in_dim)
+{
+    constexpr float QMAX = NP == 3 ? 8388607.0f : 32767.0f;
+    const uint32_t n4 = in_dim / 4;
+    uint32_t *planes = reinterpret_cast<uint32_t *>(xq);
+    float *scales = reinterpret_cast<float *>(xq + (size_t)NP * in_dim);
+    float *sums = scales + in_dim / G;
+    float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+#pragma unroll
+    for (int o = 1; o < G / 4; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float inv = amax > 0.0f ? QMAX / amax : 0.0f;
+    int X[4];
+    X[0] = __float2int_rn(v.x * inv); X[1] = __float2int_rn(v.y * inv);
+    X[2] = __float2int_rn(v.z * inv); X[3] = __float2int_rn(v.w * inv);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) X[j] = max(-(int)QMAX, min((int)QMAX, X[j]));
+    float sum = 0.0f;
+    if constexpr (SUMS) {
+        sum = (v.x + v.y) + (v.z + v.w);
+#pragma unroll
+        for (int o = 1; o < 8; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    }
+    if (valid) {
+#pragma unroll
+        for (int p = 0; p < NP; ++p) {
+            const uint32_t sel = (uint32_t)p | ((uint32_t)(4 + p) << 4);
+            const uint32_t lo = __byte_perm((uint32_t)X[0], (uint32_t)X[1], sel);
+            const uint32_t hi = __byte_perm((uint32_t)X[2], (uint32_t)X[3], sel);
+            planes[(size_t)p * n4 + 4 * plane_swz(f >> 2) + (f & 3u)] = __byte_perm(lo, hi, 0x5410);
+        }
+        if ((lane & (G / 4 - 1)) == 0) scales[f / (G / 4)] = amax / QMAX;
+        if constexpr (SUMS)
+            if ((lane & 7u) == 0) sums[f / 8] = sum;
+    }
+}
+
 template <int NP, int G, bool SUMS>
 __device__ __forceinline__ bool quantize_x_to_smem(const float *__restrict__ x, uint32_t in_dim, uint32_t nvec, uint32_t x_stride,
                                                    uint8_t *xq0, uint32_t vec_bytes, uint32_t tid, uint32_t nthreads,
-                                                   const uint2 *slots = nullptr, unsigned int tag = 0)
+                                                   const uint2 *slots = nullptr, unsigned int tag = 0,
+                                                   long long limit = PIPE_WAIT_CYCLES, const int *status = nullptr, uint32_t rot = 0)
 {
+    // rot (single vector only; a multiple of 32 four-float pieces): this CTA walks the vector starting rot pieces in and
+    // wraps around.  When every CTA of a grid reads the same vector at the same moment, different rot values keep them
+    // on different cache lines (L2 slices) at any one time instead of all queueing on the same line.
     bool ok = true;
-    constexpr float QMAX = NP == 3 ? 8388607.0f : 32767.0f;
     constexpr int BATCH = 8;
     const uint32_t n4 = in_dim / 4, n4_all = n4 * nvec, lane = tid & 31u;
     for (uint32_t base = tid - lane; base < n4_all; base += nthreads * BATCH) {
@@ -327,8 +393,10 @@ __device__ __forceinline__ bool quantize_x_to_smem(const float *__restrict__ x, 
 #pragma unroll
         for (int b = 0; b < BATCH; ++b) {
             const uint32_t fa = base + b * nthreads + lane;
-            const uint32_t vec = nvec == 1 ? 0u : fa / n4, fl = fa - vec * n4;      // no division on the single-vector path
-            if (slots) v[b] = fa < n4_all ? ld_gathered4(slots + 4 * (size_t)fl, tag, &ok) : make_float4(0.f, 0.f, 0.f, 0.f);
+            const uint32_t vec = nvec == 1 ? 0u : fa / n4;      // no division on the single-vector path
+            uint32_t fl = fa - vec * n4;
+            if (nvec == 1) { fl += rot; if (fl >= n4) fl -= n4; }
+            if (slots) v[b] = fa < n4_all ? ld_gathered4(slots + 4 * (size_t)fl, tag, &ok, limit, status) : make_float4(0.f, 0.f, 0.f, 0.f);
             else v[b] = fa < n4_all ? __ldcg(reinterpret_cast<const float4 *>(x + (size_t)vec * x_stride) + fl) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
 #pragma unroll
@@ -336,38 +404,48 @@ __device__ __forceinline__ bool quantize_x_to_smem(const float *__restrict__ x, 
             const uint32_t fb = base + b * nthreads;       // warp-uniform
             if (fb >= n4_all) break;
             const uint32_t fa = fb + lane;
-            const uint32_t vec = nvec == 1 ? 0u : fa / n4, f = fa - vec * n4;
-            uint8_t *xq = xq0 + (size_t)vec * vec_bytes;
-            uint32_t *planes = reinterpret_cast<uint32_t *>(xq);
-            float *scales = reinterpret_cast<float *>(xq + (size_t)NP * in_dim);
-            float *sums = scales + in_dim / G;
-            float amax = fmaxf(fmaxf(fabsf(v[b].x), fabsf(v[b].y)), fmaxf(fabsf(v[b].z), fabsf(v[b].w)));
+            const uint32_t vec = nvec == 1 ? 0u : fa / n4;
+            uint32_t f = fa - vec * n4;
+            if (nvec == 1) { f += rot; if (f >= n4) f -= n4; }
+            quantize_piece<NP, G, SUMS>(v[b], f, fa < n4_all, lane, xq0 + (size_t)vec * vec_bytes, in_dim);
+        }
+    }
+    return ok;
+}
+
+// The same pass for one vector whose elements come from {value, tag} slots: the loads of a batch are issued together
+// (one round trip instead of one per piece), then the tags are checked and only a piece whose tag is not there yet is
+// polled (bounded; *ok false on expiry).  rot as above.
+template <int NP, int G, bool SUMS>
+__device__ __forceinline__ bool quantize_slots_to_smem(const uint2 *slots, unsigned int tag, uint32_t in_dim, uint8_t *xq, uint32_t tid,
+                                                       uint32_t nthreads, long long limit, const int *status, uint32_t rot,
+                                                       unsigned long long *stamps = nullptr)
+{
+    bool ok = true;
+    constexpr int BATCH = 4;
+    const uint32_t n4 = in_dim / 4, lane = tid & 31u;
+    for (uint32_t base = tid - lane; base < n4; base += nthreads * BATCH) {
+        uint4 lo[BATCH], hi[BATCH];
+        if (stamps && base == tid) stamps[0] = global_ns();
 #pragma unroll
-            for (int o = 1; o < G / 4; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-            const float inv = amax > 0.0f ? QMAX / amax : 0.0f;
-            int X[4];
-            X[0] = __float2int_rn(v[b].x * inv); X[1] = __float2int_rn(v[b].y * inv);
-            X[2] = __float2int_rn(v[b].z * inv); X[3] = __float2int_rn(v[b].w * inv);
+        for (int b = 0; b < BATCH; ++b) {
+            const uint32_t fa = base + b * nthreads + lane;
+            uint32_t fl = fa + rot;
+            if (fl >= n4) fl -= n4;
+            lo[b] = hi[b] = make_uint4(0u, tag, 0u, tag);
+            if (fa < n4) { lo[b] = ld_slots2(slots + 4 * (size_t)fl); hi[b] = ld_slots2(slots + 4 * (size_t)fl + 2); }
+        }
 #pragma unroll
-            for (int j = 0; j < 4; ++j) X[j] = max(-(int)QMAX, min((int)QMAX, X[j]));
-            float sum = 0.0f;
-            if constexpr (SUMS) {
-                sum = (v[b].x + v[b].y) + (v[b].z + v[b].w);
-#pragma unroll
-                for (int o = 1; o < 8; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-            }
-            if (fa < n4_all) {
-#pragma unroll
-                for (int p = 0; p < NP; ++p) {
-                    const uint32_t sel = (uint32_t)p | ((uint32_t)(4 + p) << 4);
-                    const uint32_t lo = __byte_perm((uint32_t)X[0], (uint32_t)X[1], sel);
-                    const uint32_t hi = __byte_perm((uint32_t)X[2], (uint32_t)X[3], sel);
-                    planes[(size_t)p * n4 + 4 * plane_swz(f >> 2) + (f & 3u)] = __byte_perm(lo, hi, 0x5410);
-                }
-                if ((lane & (G / 4 - 1)) == 0) scales[f / (G / 4)] = amax / QMAX;
-                if constexpr (SUMS)
-                    if ((lane & 7u) == 0) sums[f / 8] = sum;
-            }
+        for (int b = 0; b < BATCH; ++b) {
+            const uint32_t fb = base + b * nthreads;       // warp-uniform
+            if (fb >= n4) break;
+            const uint32_t fa = fb + lane;
+            uint32_t f = fa + rot;
+            if (f >= n4) f -= n4;
+            float4 v = make_float4(__uint_as_float(lo[b].x), __uint_as_float(lo[b].z), __uint_as_float(hi[b].x), __uint_as_float(hi[b].z));
+            if (lo[b].y != tag || lo[b].w != tag || hi[b].y != tag || hi[b].w != tag) v = ld_gathered4(slots + 4 * (size_t)f, tag, &ok, limit, status);
+            if (stamps && b == 0 && base == tid) stamps[1] = global_ns();
+            quantize_piece<NP, G, SUMS>(v, f, fa < n4, lane, xq, in_dim);
         }
     }
     return ok;
@@ -782,7 +860,8 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
         const uint2 *slots = EXT ? a.x_ll : nullptr;
         const unsigned int want = EXT && a.x_ll ? *reinterpret_cast<const volatile unsigned int *>(a.wait_gen) : 0u;
         if (!quantize_x_to_smem<NP, SlotT::GROUP, SlotT::SUMS>(a.x, a.in_dim, COMBINE ? (uint32_t)a.nseg : 1u, a.x_stride, xq, a.xq_vec_bytes, tid, C,
-                                                               slots, want)) {
+                                                               slots, want, a.wait_cycles, a.status,
+                                                               COMBINE ? 0u : (uint32_t)((uint64_t)blockIdx.x * (a.in_dim / 4) / gridDim.x) & ~31u)) {
             s_abort = 1;
             atomicExch(a.status, 3);
         }

@@ -2,9 +2,7 @@
 // B200 quantized dequant-matvec path.  The host logic here is the counterpart
 // of the reference's format layer (inference/src/format.m:224-337): validate the
 // TensorRef, pick the kernel from its format/variant, size the launch.
-#include "../../include/orome_cuda.h"
-
-#include <cuda_runtime.h>
+#include "ctx.h"
 
 #include <algorithm>
 #include <cstdarg>
@@ -23,57 +21,9 @@
 
 using namespace orome;
 
-struct MapKey {
-    const uint8_t *w;
-    uint32_t unit, units, rows, kb;
-    bool operator<(const MapKey &o) const { return std::tie(w, unit, units, rows, kb) < std::tie(o.w, o.unit, o.units, o.rows, o.kb); }
-};
-
-struct orome_cuda_ctx {
-    std::map<MapKey, CUtensorMap> maps;   // tensor maps of the mma kernel's tensors
-    int device = 0;
-    int sm_count = 0;
-    int smem_optin = 0;
-    int *status_dev = nullptr;
-    uint64_t launches = 0;
-    // options
-    int x_bits = 24;
-    int force_generic = 0;
-    int stage_kb = 0;        // 0 = automatic
-    int ctas_per_sm = 1;     // CTAs an SM is sized to hold (1 or 2); measured best with one large CTA
-    int grid_per_sm = 1;     // CTAs per SM a launch creates; 1 with ctas_per_sm 2 leaves room for the next kernel's CTA
-    int pdl = 1;
-    int prefetch_mb = 24;    // at most this many MiB of the next tensor are pulled into L2 by the current launch
-    const uint8_t *hint_ptr = nullptr;   // set by orome_cuda_hint_next, consumed by the next pipelined launch
-    uint64_t hint_bytes = 0;
-    // multi-GPU gather state (orome_cuda_gather_setup)
-    int g_rank = 0, g_world = 1, g_nflags = 0;
-    uint8_t *g_arena[8] = {nullptr};          // every rank's arena as mapped in this process
-    size_t g_data_bytes = 0;
-    unsigned int *g_local = nullptr;          // [n_flags] generation of each gathered vector, then the publish arrival counter
-    int g_wait = -1, g_publish = -1;          // request for the next pipelined launch
-    unsigned long long *trace_dev = nullptr;   // diagnostics buffer [trace_cap][sm_count][8]
-    int trace_cap = 0, trace_next = 0;
-    // staging for the host-buffer entry point
-    float *stage_x_host = nullptr, *stage_y_host = nullptr, *stage_x_dev = nullptr, *stage_y_dev = nullptr;
-    size_t stage_x_cap = 0, stage_y_cap = 0;
-    cudaStream_t own_stream = nullptr;
-    // scratch for routing logits when the caller passes none
-    float *logits_dev = nullptr;
-    size_t logits_cap = 0;
-    // scratch for the unfused gate/up fallback
-    float *gu_dev = nullptr;
-    size_t gu_cap = 0;
-    // scratch of the tensor-core batched form: packed fp16 X and split-K partial sums
-    float *tc_xp = nullptr, *tc_part = nullptr;
-    size_t tc_xp_cap = 0, tc_part_cap = 0;
-    int tc_min_batch = 4;    // batches from this size on use the tensor-core kernel (smaller ones: one decode launch per vector)
-    int kquant_mma = 1;      // Q4_K / Q5_K batch-1 products on the mma.sync kernel (0: dp4a kernel)
-};
-
 static thread_local std::string g_err;
 
-static int fail(int code, const char *fmt, ...)
+int orome_fail(int code, const char *fmt, ...)
 {
     char buf[512];
     va_list ap;
@@ -83,12 +33,7 @@ static int fail(int code, const char *fmt, ...)
     g_err = buf;
     return code;
 }
-
-#define CU(call)                                                                                         \
-    do {                                                                                                 \
-        cudaError_t e_ = (call);                                                                         \
-        if (e_ != cudaSuccess) return fail(OROME_ECUDA, "%s: %s", #call, cudaGetErrorString(e_));        \
-    } while (0)
+#define fail orome_fail
 
 extern "C" const char *orome_cuda_last_error(void) { return g_err.c_str(); }
 
@@ -106,8 +51,9 @@ extern "C" int orome_cuda_ctx_create(int device, orome_cuda_ctx **out)
     c->device = device;
     c->sm_count = prop.multiProcessorCount;
     c->smem_optin = (int)prop.sharedMemPerBlockOptin;
-    CU(cudaMalloc(&c->status_dev, sizeof(int)));
-    CU(cudaMemset(c->status_dev, 0, sizeof(int)));
+    CU(cudaMalloc(&c->status_dev, 256));          // the status word, and (64 bytes on) the tag generation shared by the context's chains
+    CU(cudaMemset(c->status_dev, 0, 256));
+    c->chain_gen_dev = reinterpret_cast<unsigned int *>(c->status_dev) + 16;
     CU(cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking));
     *out = c;
     return OROME_OK;
@@ -117,6 +63,7 @@ extern "C" void orome_cuda_ctx_destroy(orome_cuda_ctx *c)
 {
     if (!c) return;
     cudaSetDevice(c->device);
+    if (c->rec) orome_chain_abandon(c);
     cudaFree(c->status_dev);
     cudaFree(c->stage_x_dev);
     cudaFree(c->stage_y_dev);
@@ -138,6 +85,7 @@ extern "C" int orome_cuda_status(orome_cuda_ctx *c, int *status_out)
     CU(cudaSetDevice(c->device));
     CU(cudaDeviceSynchronize());
     CU(cudaMemcpy(status_out, c->status_dev, sizeof(int), cudaMemcpyDeviceToHost));
+    if (*status_out) CU(cudaMemset(c->status_dev, 0, sizeof(int)));      // reported once; later launches wait again
     return *status_out ? fail(OROME_ETIMEOUT, "a kernel's bounded wait expired (status %d)", *status_out) : OROME_OK;
 }
 
@@ -210,6 +158,12 @@ extern "C" int orome_cuda_set_option(orome_cuda_ctx *c, int key, int value)
     case OROME_OPT_PREFETCH_MB:
         if (value < 0 || value > 96) return fail(OROME_EINVAL, "PREFETCH_MB must be 0..96");
         c->prefetch_mb = value; return OROME_OK;
+    case OROME_OPT_WAIT_US:
+        if (value < 0 || value > 10000000) return fail(OROME_EINVAL, "WAIT_US must be 0..10000000");
+        c->wait_us = value; return OROME_OK;
+    case OROME_OPT_CHAIN_INFLIGHT:
+        if (value < 0 || value > PIPE_MAX_STAGES) return fail(OROME_EINVAL, "CHAIN_INFLIGHT must be 0..%d", PIPE_MAX_STAGES);
+        c->chain_inflight = value; return OROME_OK;
     }
     return fail(OROME_EINVAL, "set_option: unknown key %d", key);
 }
@@ -227,10 +181,14 @@ extern "C" int orome_cuda_get_option(orome_cuda_ctx *c, int key, int *value)
     case OROME_OPT_PREFETCH_MB: *value = c->prefetch_mb; return OROME_OK;
     case OROME_OPT_TC_MIN_BATCH: *value = c->tc_min_batch; return OROME_OK;
     case OROME_OPT_KQUANT_MMA: *value = c->kquant_mma; return OROME_OK;
+    case OROME_OPT_WAIT_US: *value = c->wait_us; return OROME_OK;
+    case OROME_OPT_CHAIN_INFLIGHT: *value = c->chain_inflight; return OROME_OK;
     }
     return fail(OROME_EINVAL, "get_option: unknown key %d", key);
 }
 
+#ifdef OROME_DIAGNOSTICS
+// Per-CTA timeline stamps of the pipelined kernels; compiled only into diagnostics builds (-DOROME_DIAGNOSTICS).
 extern "C" int orome_cuda_trace_begin(orome_cuda_ctx *c, int launches)
 {
     if (!c || launches < 0) return fail(OROME_EINVAL, "trace_begin: bad argument");
@@ -256,12 +214,14 @@ extern "C" int orome_cuda_trace_read(orome_cuda_ctx *c, unsigned long long *out,
     return OROME_OK;
 }
 
+#endif
+
 extern "C" uint64_t orome_cuda_launch_count(orome_cuda_ctx *c) { return c ? c->launches : 0; }
 
 // ---------------------------------------------------------------------------
 // validation shared by the entry points
 // ---------------------------------------------------------------------------
-static int check_ref(const char *who, const OromeTensorRef *r, const uint8_t **data)
+int orome_check_ref(const char *who, const OromeTensorRef *r, const uint8_t **data)
 {
     if (!r) return fail(OROME_EINVAL, "%s: NULL TensorRef", who);
     int fmt = (int)r->format;
@@ -275,6 +235,9 @@ static int check_ref(const char *who, const OromeTensorRef *r, const uint8_t **d
     *data = p;
     return OROME_OK;
 }
+
+// Bound of one device-side wait in SM cycles (the SM clock is about 2 GHz).
+long long orome_wait_cycles(const orome_cuda_ctx *c) { return c->wait_us > 0 ? (long long)c->wait_us * 2000ll : PIPE_WAIT_CYCLES; }
 
 static int post_launch(orome_cuda_ctx *c, const char *what)
 {
@@ -371,17 +334,17 @@ struct PipePlan {
     size_t smem;
 };
 
-static uint32_t pipe_group_threads(int fmt, uint32_t in_dim)
+uint32_t orome_pipe_group_threads(int fmt, uint32_t in_dim)
 {
     const uint32_t slots = fmt == FMT_Q8_0 ? in_dim / 64 : in_dim / 256 * 4;
     return (slots + 31) / 32 * 32;
 }
 
-static bool pipe_supported(int fmt, uint32_t in_dim)
+bool orome_pipe_supported(int fmt, uint32_t in_dim)
 {
-    if (fmt == FMT_Q8_0) return in_dim % 64 == 0 && pipe_group_threads(fmt, in_dim) <= PIPE_MAX_CONSUMERS;
+    if (fmt == FMT_Q8_0) return in_dim % 64 == 0 && orome_pipe_group_threads(fmt, in_dim) <= PIPE_MAX_CONSUMERS;
     if (fmt == FMT_Q4_K || fmt == FMT_Q5_K || fmt == FMT_Q6_K)
-        return in_dim % 256 == 0 && pipe_group_threads(fmt, in_dim) <= PIPE_MAX_CONSUMERS;
+        return in_dim % 256 == 0 && orome_pipe_group_threads(fmt, in_dim) <= PIPE_MAX_CONSUMERS;
     return false;
 }
 
@@ -427,7 +390,7 @@ static int plan_pipe(orome_cuda_ctx *c, int fmt, uint32_t in_dim, uint32_t total
     a.in_dim = in_dim;
     a.row_bytes = (uint32_t)row_bytes_of(fmt, in_dim);
     a.units = fmt == FMT_Q8_0 ? in_dim / 64 : in_dim / 256;
-    a.group_threads = pipe_group_threads(fmt, in_dim);
+    a.group_threads = orome_pipe_group_threads(fmt, in_dim);
     a.total_rows = total_rows;
     p.minb = c->ctas_per_sm >= 2 && a.group_threads <= PIPE_CONSUMERS_2CTA && !combine ? 2 : 1;
     if (fmt == FMT_Q6_K && c->x_bits == 24 && swiglu) p.minb = 1;   // needs more than the 96 registers of the two-CTA build
@@ -480,6 +443,7 @@ static int plan_pipe(orome_cuda_ctx *c, int fmt, uint32_t in_dim, uint32_t total
     }
     p.smem = a.stage_base + (size_t)a.stage_stride * a.nstages;
     a.status = c->status_dev;
+    a.wait_cycles = orome_wait_cycles(c);
     a.trace = nullptr;
     if (c->trace_dev && c->trace_next < c->trace_cap) a.trace = c->trace_dev + (size_t)(c->trace_next++) * c->sm_count * 8;
     {
@@ -620,7 +584,7 @@ static int plan_mma(orome_cuda_ctx *c, int fmt, uint32_t in_dim, uint32_t total_
     a.nstages = (uint32_t)std::min<size_t>(std::min<size_t>(PIPE_MAX_STAGES, tiles), (budget - a.stage_base) / a.stage_stride);
     p.smem = a.stage_base + (size_t)a.stage_stride * a.nstages;
 #ifdef OROME_MMA_TILE_TRACE
-    a.dbg_tile = getenv("OROME_DBG_TILE") ? (uint32_t)atoi(getenv("OROME_DBG_TILE")) : 0u;
+    a.dbg_tile = OROME_MMA_TILE_TRACE;      // diagnostics build: first row tile whose per-warp timeline is recorded
 #endif
     a.status = c->status_dev;
     a.trace = nullptr;
@@ -809,7 +773,7 @@ extern "C" int orome_cuda_gather_setup(orome_cuda_ctx *c, int rank, int world, v
 extern "C" int orome_cuda_gather_next(orome_cuda_ctx *c, int wait_flag, int publish_flag)
 {
     if (!c) return fail(OROME_EINVAL, "gather_next: NULL ctx");
-    if (c->g_world < 2) { c->g_wait = c->g_publish = -1; return OROME_OK; }   // single GPU: nothing to wait for or publish
+    if (c->g_world < 2 || c->rec) { c->g_wait = c->g_publish = -1; return OROME_OK; }   // single GPU, or a chain (which orders its products by their addresses)
     if (wait_flag >= c->g_nflags || publish_flag >= c->g_nflags) return fail(OROME_EINVAL, "gather_next: flag out of range (%d flags)", c->g_nflags);
     c->g_wait = wait_flag < 0 ? -1 : wait_flag;
     c->g_publish = publish_flag < 0 ? -1 : publish_flag;
@@ -818,14 +782,16 @@ extern "C" int orome_cuda_gather_next(orome_cuda_ctx *c, int wait_flag, int publ
 
 // Copies a gathered vector from its {value, tag} slots to its plain place in the arena, polling every element
 // (bounded) for the generation this rank published last under the flag.
-__global__ void __launch_bounds__(256) gather_unpack_kernel(const uint2 *slots, float *dst, uint32_t n4, const unsigned int *gen, int *status)
+__global__ void __launch_bounds__(256) gather_unpack_kernel(const uint2 *slots, float *dst, uint32_t n4, const unsigned int *gen, int *status,
+                                                            long long wait_cycles)
 {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const unsigned int tag = *reinterpret_cast<const volatile unsigned int *>(gen);
-    bool ok = true;
+    bool ok = *reinterpret_cast<const volatile int *>(status) == 0;      // an earlier expiry: copy what is there, wait for nothing
+    const bool was_ok = ok;
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += gridDim.x * blockDim.x)
-        reinterpret_cast<float4 *>(dst)[i] = ld_gathered4(slots + 4 * (size_t)i, tag, &ok);
-    if (!ok) atomicExch(status, 3);
+        reinterpret_cast<float4 *>(dst)[i] = ld_gathered4(slots + 4 * (size_t)i, tag, &ok, wait_cycles, status);
+    if (!ok && was_ok) atomicExch(status, 3);
 }
 
 extern "C" int orome_cuda_gather_wait(orome_cuda_ctx *c, int flag, float *vec_dev, uint32_t n, void *stream)
@@ -836,11 +802,12 @@ extern "C" int orome_cuda_gather_wait(orome_cuda_ctx *c, int flag, float *vec_de
     uint8_t *mine = c->g_arena[c->g_rank], *v = reinterpret_cast<uint8_t *>(vec_dev);
     if (!vec_dev || n % 4 || v < mine || v + (size_t)n * 4 > mine + c->g_data_bytes || ((v - mine) & 15))
         return fail(OROME_EINVAL, "gather_wait: the vector must lie in the gather arena, 16-byte aligned, a multiple of 4 long");
+    if (c->rec) return orome_chain_record_unpack(c, vec_dev, n);
     CU(cudaSetDevice(c->device));
     const uint2 *slots = reinterpret_cast<const uint2 *>(mine + c->g_data_bytes + 2 * (size_t)(v - mine));
     const unsigned blocks = std::max(1u, std::min((n / 4 + 255) / 256, (unsigned)c->sm_count));
     return launch_pdl(c, "gather_unpack", gather_unpack_kernel, dim3(blocks), dim3(256), static_cast<cudaStream_t>(stream), slots, vec_dev,
-                      n / 4, (const unsigned int *)(c->g_local + flag), c->status_dev);
+                      n / 4, (const unsigned int *)(c->g_local + flag), c->status_dev, orome_wait_cycles(c));
 }
 
 // ---------------------------------------------------------------------------
@@ -856,7 +823,7 @@ extern "C" int orome_cuda_matvec_group(orome_cuda_ctx *c, const OromeTensorRef *
     const uint8_t *data[PIPE_MAX_SEG];
     for (int i = 0; i < n_refs; ++i) {
         if (!refs[i].buffer) return fail(OROME_EINVAL, "matvec_group: tensor %d is absent", i);
-        int rc = check_ref("matvec_group", &refs[i], &data[i]);
+        int rc = orome_check_ref("matvec_group", &refs[i], &data[i]);
         if (rc) return rc;
         if (refs[i].format != refs[0].format || refs[i].variant != refs[0].variant || refs[i].in_dim != refs[0].in_dim)
             return fail(OROME_EINVAL, "matvec_group: tensors must share format, variant and in_dim");
@@ -871,7 +838,8 @@ extern "C" int orome_cuda_matvec_group(orome_cuda_ctx *c, const OromeTensorRef *
             if (y0 < lo || y0 + (size_t)refs[i].out_dim * 4 > hi) { c->g_wait = c->g_publish = -1; return fail(OROME_EINVAL, "matvec_group: a published y must lie inside the gather arena"); }
         }
     }
-    if (c->force_generic || !pipe_supported(fmt, refs[0].in_dim)) {
+    if (c->rec) return orome_chain_record_group(c, refs, n_refs, x_dev, y_dev);
+    if (c->force_generic || !orome_pipe_supported(fmt, refs[0].in_dim)) {
         if (c->g_world > 1 && (c->g_publish >= 0 || c->g_wait >= 0)) { c->g_wait = c->g_publish = -1; return fail(OROME_ENOTSUP, "matvec_group: this shape has no multi-GPU form"); }
         for (int i = 0; i < n_refs; ++i) {
             int rc = launch_generic(c, fmt, data[i], refs[i].out_dim, refs[i].in_dim, layout, x_dev, 1, 0, y_dev[i], 0, st);
@@ -1029,10 +997,17 @@ extern "C" int orome_cuda_matvec(orome_cuda_ctx *c, const OromeTensorRef *ref, c
         float *ys[1] = {y_dev};
         return orome_cuda_matvec_group(c, ref, 1, x_dev, ys, stream);
     }
+    if (c->rec) return fail(OROME_ENOTSUP, "matvec: only batch-1 products of quantized tensors can be recorded into a chain");
     if (batch > 1 && (ldx < (int)ref->in_dim || ldy < (int)ref->out_dim))
         return fail(OROME_EINVAL, "matvec: ldx/ldy smaller than the row length");
+    // A gather request armed for this call cannot be honoured on the paths below (no publish / wait form): drop it
+    // and say so, rather than leave it armed for an unrelated later launch.
+    if (c->g_world > 1 && (c->g_wait >= 0 || c->g_publish >= 0)) {
+        c->g_wait = c->g_publish = -1;
+        return fail(OROME_ENOTSUP, "matvec: this batch / format has no multi-GPU form (the gather request was dropped)");
+    }
     const uint8_t *data;
-    int rc = check_ref("matvec", ref, &data);
+    int rc = orome_check_ref("matvec", ref, &data);
     if (rc) return rc;
     CU(cudaSetDevice(c->device));
     const bool x_ok = ldx % 4 == 0 && !(reinterpret_cast<uintptr_t>(x_dev) & 15);
@@ -1043,7 +1018,7 @@ extern "C" int orome_cuda_matvec(orome_cuda_ctx *c, const OromeTensorRef *ref, c
     // weights are read once per vector, but the decode kernels run near the memory rate while the shape-agnostic
     // kernel below needs ~190 us per vector for a 12288 x 4096 tensor (measured: batch 8 in 1.5 ms).
     if (!c->force_generic && x_ok && (int)ref->format <= FMT_Q8_0 && c->g_world == 1 &&
-        (pipe_supported((int)ref->format, ref->in_dim) || mma_supported(c, (int)ref->format, ref->in_dim, false))) {
+        (orome_pipe_supported((int)ref->format, ref->in_dim) || mma_supported(c, (int)ref->format, ref->in_dim, false))) {
         for (int b = 0; b < batch; ++b) {
             float *ys[1] = {y_dev + (size_t)b * ldy};
             rc = orome_cuda_matvec_group(c, ref, 1, x_dev + (size_t)b * ldx, ys, stream);
@@ -1086,9 +1061,9 @@ extern "C" int orome_cuda_gate_up_swiglu(orome_cuda_ctx *c, const OromeTensorRef
     if (!gate->buffer || !up->buffer) return OROME_OK;
     if (batch < 1 || !x_dev || !out_dev) return fail(OROME_EINVAL, "gate_up_swiglu: bad x/out/batch");
     const uint8_t *gd, *ud;
-    int rc = check_ref("gate_up_swiglu(gate)", gate, &gd);
+    int rc = orome_check_ref("gate_up_swiglu(gate)", gate, &gd);
     if (rc) return rc;
-    rc = check_ref("gate_up_swiglu(up)", up, &ud);
+    rc = orome_check_ref("gate_up_swiglu(up)", up, &ud);
     if (rc) return rc;
     if (gate->format != up->format || gate->variant != up->variant || gate->out_dim != up->out_dim || gate->in_dim != up->in_dim)
         return fail(OROME_EINVAL, "gate_up_swiglu: gate and up must have the same shape, format and variant");
@@ -1099,11 +1074,15 @@ extern "C" int orome_cuda_gate_up_swiglu(orome_cuda_ctx *c, const OromeTensorRef
         const uint8_t *lo = c->g_arena[c->g_rank], *hi = lo + c->g_data_bytes, *y0 = reinterpret_cast<const uint8_t *>(out_dev);
         if (y0 < lo || y0 + (size_t)gate->out_dim * 4 > hi) { c->g_wait = c->g_publish = -1; return fail(OROME_EINVAL, "gate_up_swiglu: a published output must lie inside the gather arena"); }
     }
-    if (c->g_world > 1 && (c->g_publish >= 0 || c->g_wait >= 0) && !(batch == 1 && !c->force_generic && pipe_supported(fmt, gate->in_dim))) {
+    if (c->rec) {
+        if (batch != 1) return fail(OROME_ENOTSUP, "gate_up_swiglu: only batch-1 products can be recorded into a chain");
+        return orome_chain_record_gate_up(c, gate, up, x_dev, out_dev);
+    }
+    if (c->g_world > 1 && (c->g_publish >= 0 || c->g_wait >= 0) && !(batch == 1 && !c->force_generic && orome_pipe_supported(fmt, gate->in_dim))) {
         c->g_wait = c->g_publish = -1;
         return fail(OROME_ENOTSUP, "gate_up_swiglu: this shape has no multi-GPU form");
     }
-    if (batch == 1 && !c->force_generic && pipe_supported(fmt, gate->in_dim)) {
+    if (batch == 1 && !c->force_generic && orome_pipe_supported(fmt, gate->in_dim)) {
         if (reinterpret_cast<uintptr_t>(x_dev) & 15) return fail(OROME_EINVAL, "gate_up_swiglu: x must be 16-byte aligned");
         if (!((reinterpret_cast<uintptr_t>(gd) | reinterpret_cast<uintptr_t>(ud)) & 15) && mma_supported(c, fmt, gate->in_dim, true)) {
             MmaPlan m;
@@ -1148,7 +1127,7 @@ extern "C" int orome_cuda_dequant_rows(orome_cuda_ctx *c, const OromeTensorRef *
     if (!c || !ref || !out_dev) return fail(OROME_EINVAL, "dequant_rows: NULL argument");
     if (!ref->buffer) return fail(OROME_EINVAL, "dequant_rows: tensor is absent");   // the reference returns false (format.m:177)
     const uint8_t *data;
-    int rc = check_ref("dequant_rows", ref, &data);
+    int rc = orome_check_ref("dequant_rows", ref, &data);
     if (rc) return rc;
     if (row0 >= ref->out_dim || nrows > ref->out_dim - row0) return fail(OROME_EINVAL, "dequant_rows: rows [%u, %u) of %u", row0, row0 + nrows, ref->out_dim);
     if (nrows == 0) return OROME_OK;
@@ -1174,6 +1153,17 @@ extern "C" int orome_cuda_dequant_rows(orome_cuda_ctx *c, const OromeTensorRef *
     return post_launch(c, "dequant_rows");
 }
 
+extern "C" int orome_cuda_argmax(orome_cuda_ctx *c, const float *data_dev, uint32_t count, uint32_t *result_dev, void *stream)
+{
+    if (!c || !data_dev || !result_dev || count == 0) return fail(OROME_EINVAL, "argmax: NULL or empty argument");
+    if (c->rec) return orome_chain_record_argmax(c, data_dev, count, result_dev);
+    CU(cudaSetDevice(c->device));
+    const unsigned blocks = std::max(1u, std::min((count + 1023) / 1024, (unsigned)c->sm_count));
+    // reduction state: two 64-bit words of the context's status block (128 bytes in), left zero by every call
+    unsigned long long *state = reinterpret_cast<unsigned long long *>(c->status_dev) + 16;
+    return launch_pdl(c, "argmax", argmax_kernel, dim3(blocks), dim3(256), static_cast<cudaStream_t>(stream), data_dev, count, result_dev, state);
+}
+
 // ---------------------------------------------------------------------------
 // MoE
 // ---------------------------------------------------------------------------
@@ -1183,7 +1173,7 @@ extern "C" int orome_cuda_moe_route(orome_cuda_ctx *c, const OromeTensorRef *rou
     if (!c || !router || !x_dev || !idx_dev || !w_dev) return fail(OROME_EINVAL, "moe_route: NULL argument");
     if (!router->buffer) return fail(OROME_EINVAL, "moe_route: router tensor is absent");
     const uint8_t *data;
-    int rc = check_ref("moe_route", router, &data);
+    int rc = orome_check_ref("moe_route", router, &data);
     if (rc) return rc;
     if (router->format != OROME_QFMT_F32) return fail(OROME_ENOTSUP, "moe_route: the router must be an F32 tensor");
     if (router->out_dim > 256) return fail(OROME_EINVAL, "moe_route: %u experts (the routing kernel takes at most 256)", router->out_dim);
@@ -1216,7 +1206,7 @@ extern "C" int orome_cuda_moe_route_static(orome_cuda_ctx *c, const OromeTensorR
     if (!c || !router || !x_dev || !idx_dev || !w_dev) return fail(OROME_EINVAL, "moe_route_static: NULL argument");
     if (!router->buffer) return fail(OROME_EINVAL, "moe_route_static: router tensor is absent");
     const uint8_t *data;
-    int rc = check_ref("moe_route_static", router, &data);
+    int rc = orome_check_ref("moe_route_static", router, &data);
     if (rc) return rc;
     if (router->format != OROME_QFMT_F32) return fail(OROME_ENOTSUP, "moe_route_static: the router must be an F32 tensor");
     if (router->out_dim > 256) return fail(OROME_EINVAL, "moe_route_static: %u experts (the routing kernel takes at most 256)", router->out_dim);
@@ -1260,7 +1250,7 @@ extern "C" int orome_cuda_moe_ffn(orome_cuda_ctx *c, const OromeExpertLayerRef *
     CU(cudaSetDevice(c->device));
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const size_t grb = row_bytes_of(gfmt, hidden), drb = row_bytes_of(dfmt, inter);
-    if (!c->force_generic && pipe_supported(gfmt, hidden) && pipe_supported(dfmt, inter) && K <= (uint32_t)PIPE_MAX_SEG &&
+    if (!c->force_generic && orome_pipe_supported(gfmt, hidden) && orome_pipe_supported(dfmt, inter) && K <= (uint32_t)PIPE_MAX_SEG &&
         !((reinterpret_cast<uintptr_t>(x_dev) | reinterpret_cast<uintptr_t>(act_dev)) & 15) && (ldx % 4 == 0 || n_tokens == 1) && inter % 4 == 0) {
         // Per token: one fused gate/up launch over the K selected experts (device-side expert indices), then one
         // down launch that gives every expert its own input vector and adds the K results with the routing weights.

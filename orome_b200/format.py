@@ -15,7 +15,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "liborome_cuda.so")
 
 VARIANT_DEFAULT, VARIANT_LLAMA = 0, 1
-OPT_X_BITS, OPT_FORCE_GENERIC, OPT_STAGE_KB, OPT_CTAS_PER_SM, OPT_PDL, OPT_GRID_PER_SM, OPT_PREFETCH_MB, OPT_TC_MIN_BATCH, OPT_KQUANT_MMA = 1, 2, 3, 4, 5, 6, 7, 8, 9
+OPT_X_BITS, OPT_FORCE_GENERIC, OPT_STAGE_KB, OPT_CTAS_PER_SM, OPT_PDL, OPT_GRID_PER_SM, OPT_PREFETCH_MB, OPT_TC_MIN_BATCH, OPT_KQUANT_MMA, OPT_WAIT_US, OPT_CHAIN_INFLIGHT = 1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11
 
 OK, EINVAL, ENOTSUP, ENOMEM, ECUDA, ETIMEOUT = 0, -22, -95, -12, -5, -110
 ROUTE_STATIC_MAX_LOGITS = 64 * 256
@@ -47,7 +47,8 @@ EXPORTS = [
     "orome_cuda_matvec", "orome_cuda_matvec_group", "orome_cuda_gate_up_swiglu", "orome_cuda_dequant_rows",
     "orome_cuda_moe_route", "orome_cuda_moe_route_static", "orome_cuda_moe_ffn", "orome_cuda_moe_ffn_shard", "orome_cuda_matvec_host", "orome_cuda_set_option",
     "orome_cuda_get_option", "orome_cuda_launch_count", "orome_cuda_hint_next", "orome_cuda_peer_alloc", "orome_cuda_peer_open", "orome_cuda_peer_close", "orome_cuda_gather_setup",
-    "orome_cuda_gather_arena_bytes", "orome_cuda_gather_next", "orome_cuda_gather_wait", "orome_cuda_trace_begin", "orome_cuda_trace_read",
+    "orome_cuda_gather_arena_bytes", "orome_cuda_gather_next", "orome_cuda_gather_wait", "orome_cuda_argmax", "orome_cuda_chain_begin", "orome_cuda_chain_end",
+    "orome_cuda_chain_launch", "orome_cuda_chain_destroy", "orome_cuda_chain_info",
 ]
 
 _lib = None
@@ -95,8 +96,13 @@ def lib():
     L.orome_cuda_gather_arena_bytes.restype = sz
     L.orome_cuda_gather_next.argtypes = [vp, i32, i32]
     L.orome_cuda_gather_wait.argtypes = [vp, i32, vp, u32, vp]
-    L.orome_cuda_trace_begin.argtypes = [vp, i32]
-    L.orome_cuda_trace_read.argtypes = [vp, vp, sz]
+    L.orome_cuda_argmax.argtypes = [vp, vp, u32, vp, vp]
+    L.orome_cuda_chain_begin.argtypes = [vp]
+    L.orome_cuda_chain_end.argtypes = [vp, C.POINTER(vp)]
+    L.orome_cuda_chain_launch.argtypes = [vp, vp, vp]
+    L.orome_cuda_chain_destroy.argtypes = [vp, vp]
+    L.orome_cuda_chain_destroy.restype = None
+    L.orome_cuda_chain_info.argtypes = [vp, C.POINTER(i32), C.POINTER(C.c_uint64), C.POINTER(i32), C.POINTER(i32)]
     L.orome_cuda_launch_count.argtypes = [vp]
     L.orome_cuda_launch_count.restype = C.c_uint64
     _lib = L
@@ -165,14 +171,19 @@ class Context:
     def launch_count(self) -> int:
         return int(lib().orome_cuda_launch_count(self._h))
 
-    def trace_begin(self, launches: int):
-        _chk(lib().orome_cuda_trace_begin(self._h, launches))
+    # -- one token step as one launch (the reference's one command buffer per token, engine.m:453-454, 1048-1050) --
+    def chain_begin(self):
+        """From here to chain_end the batch-1 entry points record their product instead of launching it."""
+        _chk(lib().orome_cuda_chain_begin(self._h))
 
-    def trace_read(self, launches: int, sm_count: int = 148):
-        import numpy as np
-        out = np.zeros((launches, sm_count, 8), np.uint64)
-        _chk(lib().orome_cuda_trace_read(self._h, out.ctypes.data_as(C.c_void_p), out.size))
-        return out
+    def chain_end(self) -> "Chain":
+        out = C.c_void_p()
+        _chk(lib().orome_cuda_chain_end(self._h, C.byref(out)))
+        return Chain(self, out)
+
+    def argmax(self, data: int, count: int, result: int, stream: int = 0):
+        """Index of the largest of `count` floats at `data` into the uint32 at `result` (shaders.metal:1249-1305)."""
+        _chk(lib().orome_cuda_argmax(self._h, data, count, result, stream))
 
     # -- multi-GPU gather ----------------------------------------------------------
     def peer_alloc(self, nbytes: int):
@@ -247,6 +258,33 @@ class Context:
         """x_host / y_host: contiguous float32 numpy arrays (host memory)."""
         _chk(lib().orome_cuda_matvec_host(self._h, C.byref(ref), x_host.ctypes.data_as(C.c_void_p),
                                           y_host.ctypes.data_as(C.c_void_p), batch))
+
+
+class Chain:
+    """A recorded sequence of products (orome_cuda_chain) that one launch runs."""
+
+    def __init__(self, ctx: Context, handle):
+        self.ctx, self._h = ctx, handle
+
+    def launch(self, stream: int = 0):
+        _chk(lib().orome_cuda_chain_launch(self.ctx._h, self._h, stream))
+        
+    def info(self) -> dict:
+        n, st, sb = C.c_int(), C.c_int(), C.c_int()
+        wb = C.c_uint64()
+        _chk(lib().orome_cuda_chain_info(self._h, C.byref(n), C.byref(wb), C.byref(st), C.byref(sb)))
+        return dict(products=n.value, weight_bytes=int(wb.value), stages=st.value, stage_bytes=sb.value)
+
+    def close(self):
+        if self._h and self.ctx._h:
+            lib().orome_cuda_chain_destroy(self.ctx._h, self._h)
+        self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 def gather_arena_bytes(data_bytes: int, n_flags: int) -> int:
