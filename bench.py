@@ -210,6 +210,7 @@ class Stepper:
         g = torch.Generator(device=dev)
         g.manual_seed(1234)
         self.x_h = torch.randn(H, device=dev, generator=g)           # the step's input vector
+        self.x_a = torch.randn(A, device=dev, generator=g)
         from orome_b200.rowsplit import padded_rows
         w = ds.world
         # output vectors (padded to equal slices per rank when sharded); local slices are written in place
@@ -249,7 +250,10 @@ class Stepper:
         hint = (lambda r: None) if recording else ctx.hint_next
         gn = ctx.gather_next if armed else (lambda w, p: None)
         layer_ids = list(range(len(self.refs))) if layers is None else list(layers)
+        # the parity check reads every vector on the host: on several GPUs complete their plain copies too
+        unpack = (lambda flag, buf, n: ctx.gather_wait(flag, buf.data_ptr(), n, stream)) if (self.fused and layers is not None) else (lambda *a: None)
         x_in, first, nprod = self.x_h, True, 0
+        indep = bool(os.environ.get("OROME_BENCH_INDEPENDENT_X")) and not self.fused      # experiment: every product reads a fixed vector
         for n, li in enumerate(layer_ids):
             rq, rk, rv, ro, rg, ru, rd = self.refs[li]
             nxt_q = self.refs[layer_ids[n + 1]][0] if n + 1 < len(layer_ids) else self.lm_ref
@@ -260,19 +264,23 @@ class Stepper:
             ctx.matvec_group([rq, rk, rv], x_in.data_ptr(), [self._slice(self.q, H).data_ptr(), self._slice(self.k, KV).data_ptr(),
                                                             self._slice(self.v, KV).data_ptr()], stream)
             self._gather(self.q, H); self._gather(self.k, KV); self._gather(self.v, KV)
+            unpack(self.FLAG_QKV, self.q, H); unpack(self.FLAG_QKV, self.k, KV); unpack(self.FLAG_QKV, self.v, KV)
             hint(rg)
             gn(self.FLAG_QKV, self.FLAG_O)
-            ctx.matvec(ro, self.q.data_ptr(), self._slice(self.o, H).data_ptr(), 1, 0, 0, stream)
+            ctx.matvec(ro, (self.x_h if indep else self.q).data_ptr(), self._slice(self.o, H).data_ptr(), 1, 0, 0, stream)
             self._gather(self.o, H)
+            unpack(self.FLAG_O, self.o, H)
             hint(rd)
             gn(self.FLAG_O, self.FLAG_ACT)
-            ctx.gate_up_swiglu(rg, ru, self.o.data_ptr(), self._slice(self.act, A).data_ptr(), 1, 0, 0, stream)
+            ctx.gate_up_swiglu(rg, ru, (self.x_h if indep else self.o).data_ptr(), self._slice(self.act, A).data_ptr(), 1, 0, 0, stream)
             self._gather(self.act, A)
+            unpack(self.FLAG_ACT, self.act, A)
             hint(nxt_q)
             gn(self.FLAG_ACT, self.FLAG_DN)
-            ctx.matvec(rd, self.act.data_ptr(), self._slice(self.dn, H).data_ptr(), 1, 0, 0, stream)
+            ctx.matvec(rd, (self.x_a if indep else self.act).data_ptr(), self._slice(self.dn, H).data_ptr(), 1, 0, 0, stream)
             self._gather(self.dn, H)
-            x_in, first, nprod = self.dn, False, nprod + 4
+            unpack(self.FLAG_DN, self.dn, H)
+            x_in, first, nprod = (self.x_h if indep else self.dn), False, nprod + 4
         hint(self.refs[layer_ids[0]][0] if layer_ids else None)            # the next token starts at the first layer again
         gn(-1 if first else self.FLAG_DN, self.FLAG_LOGITS)
         ctx.matvec(self.lm_ref, x_in.data_ptr(), self._slice(self.logits, V).data_ptr(), 1, 0, 0, stream)

@@ -198,6 +198,19 @@ int  orome_cuda_moe_route(orome_cuda_ctx *ctx, const OromeTensorRef *router,
                           uint32_t *idx_dev, float *w_dev, float *logits_dev /* optional [t][n_experts] */,
                           void *stream);
 
+/* The same routing with the shared-expert gate computed in the router launch: matvec_f32_pair
+ * (shaders.metal:1368-1392) as dispatched at engine.m:656-679 puts the logit of the [1][hidden]
+ * fp32 gate tensor after the router logits, and softmax_topk_route copies it to out_params[8]
+ * (shaders.metal:1232) for the combine kernel.  idx_dev / w_dev as above; shared_logit_dev[t]
+ * receives that raw logit (the reference keeps it in slot 8 of the same 9-float params buffer;
+ * here it is its own array so that the [t][8] weight layout of the expert kernels is
+ * unchanged).  shared_gate may be an absent tensor (buffer NULL): the logit is then 0.
+ * logits_dev (optional) must hold n_experts + 1 floats per token. */
+int  orome_cuda_moe_route_pair(orome_cuda_ctx *ctx, const OromeTensorRef *router, const OromeTensorRef *shared_gate,
+                               const float *x_dev, int n_tokens, int ldx, uint32_t K,
+                               uint32_t *idx_dev, float *w_dev, float *shared_logit_dev,
+                               float *logits_dev /* optional [t][n_experts + 1] */, void *stream);
+
 /* Routing for callers that must not allocate.  No counterpart in the reference (its
  * Metal context sizes every scratch buffer once, at start-up, metal.m:155-251).
  *
@@ -237,6 +250,24 @@ int  orome_cuda_moe_ffn(orome_cuda_ctx *ctx, const OromeExpertLayerRef *layer, u
                         const uint32_t *idx_dev, const float *w_dev, uint32_t K,
                         uint32_t hidden, uint32_t inter, float *act_dev, float *out_dev, int ldo,
                         void *stream);
+
+/* The whole MoE block of encode_experts_gguf (engine.m:158-340) after routing:
+ *   out[t] = h_mid[t] + sum_k w[t][k] FFN_{e_k}(x_t) + sigmoid(shared_logit[t]) * SharedFFN(x_t)
+ * i.e. the routed experts (as orome_cuda_moe_ffn), the shared expert (fused gate/up + SwiGLU,
+ * engine.m:263-275; its down projection, engine.m:314-316) and the value the combine kernels write
+ * to hidden_out (moe_combine_copy_sq / _k8, shaders.metal:1049-1059, 1100-1120; sigmoid written as
+ * 1 / (1 + exp(-p)) like there).  The residual copy and the sum of squares those kernels also
+ * produce belong to the normalisation that follows and are not part of this path.
+ * The three shared-expert tensors may be absent (NULL pointers or NULL buffers): no shared term.
+ * h_mid_dev may be NULL (no residual input).  scratch_dev: caller-provided,
+ * orome_cuda_moe_block_scratch_floats(...) floats, 16-byte aligned. */
+int  orome_cuda_moe_block(orome_cuda_ctx *ctx, const OromeExpertLayerRef *layer, uint32_t variant,
+                          const OromeTensorRef *shared_gate_proj, const OromeTensorRef *shared_up_proj,
+                          const OromeTensorRef *shared_down_proj, const float *x_dev, int n_tokens, int ldx,
+                          const uint32_t *idx_dev, const float *w_dev, const float *shared_logit_dev,
+                          uint32_t K, uint32_t hidden, uint32_t inter, const float *h_mid_dev, int ld_mid,
+                          float *scratch_dev, float *out_dev, int ldo, void *stream);
+size_t orome_cuda_moe_block_scratch_floats(int n_tokens, uint32_t K, uint32_t hidden, uint32_t inter, uint32_t shared_inter);
 
 /* Expert-parallel share of the same operation -- no counterpart in the reference (one GPU).  This GPU holds the
  * experts [first_expert, first_expert + n_local) of the layer, packed from index 0 in layer_local; the call adds

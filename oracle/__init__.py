@@ -193,6 +193,23 @@ def moe_ffn_f64(gate, up, down, fmts, strides, x, hidden, inter, idx, w, layout=
     return out
 
 
+def moe_block_f64(gate, up, down, fmts, strides, shared, x, hidden, inter, idx, w, shared_logit, h_mid=None, layout=LAYOUT_A) -> np.ndarray:
+    """One token through the MoE block of encode_experts_gguf (engine.m:158-340), in double:
+    h_mid + sum_k w_k FFN_k(x) + sigmoid(shared_logit) * SharedFFN(x), the value moe_combine_copy_sq writes to hidden_out
+    (shaders.metal:1049-1059; sigmoid as 1 / (1 + exp(-p)), line 1051).  shared: None or
+    ((fmt, bytes, S), (fmt, bytes, S), (fmt, bytes)) for the shared gate, up and down tensors; the shared activation is
+    rounded to fp32 before its down projection, as the buffer between the two kernels is (engine.m:263-316)."""
+    out = moe_ffn_f64(gate, up, down, fmts, strides, x, hidden, inter, idx, w, layout=layout)
+    if h_mid is not None:
+        out = out + np.asarray(h_mid, np.float64)
+    if shared is not None:
+        (gf, gb, S), (uf, ub, _), (df, db) = shared
+        act = swiglu_f64(matvec_f64(gf, gb, S, hidden, x, layout=layout), matvec_f64(uf, ub, S, hidden, x, layout=layout)).astype(np.float32)
+        sh = matvec_f64(df, db, hidden, S, act, layout=layout)
+        out = out + 1.0 / (1.0 + np.exp(-np.float64(shared_logit))) * sh
+    return out
+
+
 def argmax(data) -> int:
     """Index the reference's argmax_kernel returns for this vector (ties resolved as its 1024 threads do)."""
     d = np.ascontiguousarray(data, np.float32).reshape(-1)

@@ -395,7 +395,7 @@ extern "C" int orome_cuda_chain_end(orome_cuda_ctx *c, orome_cuda_chain **out)
             for (size_t p = 0; p < first_sync && p < n; ++p) {
                 const ChainProd &P = ch->prods[p];
                 if (P.mode == CHAIN_MODE_UNPACK || !P.publish) continue;
-                for (size_t r = (size_t)std::max(F, 0L); r < n; ++r) {
+                for (size_t r = (size_t)(F + 1); r < n; ++r) {       // a peer has finished product F: it is somewhere after it
                     const ChainProd &Q = ch->prods[r];
                     for (uint32_t i = 0; i < P.nseg; ++i)
                         if (Q.xs && overlaps(P.seg[i].y, (size_t)P.seg[i].rows * 4, Q.x, (size_t)Q.in_dim * 4))

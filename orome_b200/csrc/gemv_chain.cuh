@@ -333,16 +333,17 @@ __device__ __forceinline__ void chain_signal_done(const ChainArgs &a, const Chai
 }
 
 // A vector completed by the peers, copied from its slots to its plain place (for readers outside the chain).
+template <int C>      // consumer threads of the calling kernel
 __device__ __forceinline__ void chain_unpack(const ChainArgs &a, const ChainProd &P, uint32_t lo4, uint32_t hi4, unsigned int base,
                                              volatile int *s_abort)
 {
     bool ok = !*s_abort;
     const unsigned int want = chain_tag(base, P.x_tag);
     float4 *dst = reinterpret_cast<float4 *>(P.seg[0].y);
-    for (uint32_t i = lo4 + threadIdx.x; i < hi4; i += CHAIN_CONSUMERS) dst[i] = ld_gathered4(P.xs + 4 * (size_t)i, want, &ok, a.wait_cycles, a.status);
+    for (uint32_t i = lo4 + threadIdx.x; i < hi4; i += C) dst[i] = ld_gathered4(P.xs + 4 * (size_t)i, want, &ok, a.wait_cycles, a.status);
     if (!ok && !*s_abort) { *s_abort = 1; atomicExch(a.status, 3); }
     cp_async_wait_all();
-    named_bar_sync(PIPE_BAR_CONSUMERS, CHAIN_CONSUMERS);
+    named_bar_sync(PIPE_BAR_CONSUMERS, C);
 }
 
 // Chains that mix formats: one out-of-line instance per format, each with its own register allocation (several
@@ -498,7 +499,7 @@ gemv_chain_kernel(const __grid_constant__ ChainArgs a)
         }
         if (tid == 0) CHAIN_STAMP(a, p, 1);
         if (unpack) {
-            chain_unpack(a, P, lo, hi, base, &s_abort);
+            chain_unpack<CHAIN_CONSUMERS>(a, P, lo, hi, base, &s_abort);
             continue;
         }
         if constexpr (FMTS == (1 << FMT_Q8_0)) {

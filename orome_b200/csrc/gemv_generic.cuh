@@ -80,14 +80,16 @@ gemv_generic_kernel(const uint8_t *__restrict__ data, size_t row_bytes, uint32_t
 
 // fp32 weights (the MoE router, shaders.metal:1342-1366): one warp per row, lanes take consecutive float4s so every
 // load is coalesced; up to 4 input vectors per pass.  Waits for the previous kernel first (it may produce x).
+// With W1 set, one more output row (index out_dim) comes from that single-row tensor: the router logits and the
+// shared-expert gate logit in one launch, as matvec_f32_pair does (shaders.metal:1368-1392).
 __global__ void __launch_bounds__(256)
 gemv_f32_kernel(const float *__restrict__ W, uint32_t out_dim, uint32_t in_dim, const float *__restrict__ x, int batch, int ldx,
-                float *__restrict__ y, int ldy)
+                float *__restrict__ y, int ldy, const float *__restrict__ W1 = nullptr)
 {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (row >= out_dim) return;
-    const float4 *w4 = reinterpret_cast<const float4 *>(W + (size_t)row * in_dim);
+    if (row >= out_dim + (W1 ? 1u : 0u)) return;
+    const float4 *w4 = reinterpret_cast<const float4 *>(row < out_dim ? W + (size_t)row * in_dim : W1);
     const uint32_t n4 = in_dim / 4;
     for (int b0 = 0; b0 < batch; b0 += 4) {
         float acc[4] = {0.f, 0.f, 0.f, 0.f};

@@ -10,7 +10,7 @@ namespace orome {
 // lowest index wins ties.  Softmax over the selected logits only.
 __global__ void __launch_bounds__(256)
 route_topk_kernel(const float *__restrict__ logits, int ld_logits, uint32_t n_experts, uint32_t K,
-                  uint32_t *__restrict__ idx_out, float *__restrict__ w_out)
+                  uint32_t *__restrict__ idx_out, float *__restrict__ w_out, float *__restrict__ shared_logit_out = nullptr)
 {
     __shared__ float s_val[8];
     __shared__ uint32_t s_idx[8];
@@ -56,7 +56,28 @@ route_topk_kernel(const float *__restrict__ logits, int ld_logits, uint32_t n_ex
             io[k] = k < limit ? f_idx[k] : 0u;
             wo[k] = k < limit ? w[k] * inv : 0.0f;
         }
+        // the raw logit of the shared-expert gate, which sits after the router logits (out_params[8], shaders.metal:1232)
+        if (shared_logit_out) shared_logit_out[blockIdx.x] = lg[n_experts];
     }
+}
+
+// hidden = h_mid + moe + sigmoid(shared gate logit) * shared_out: the value the reference's combine kernels compute
+// (moe_combine_copy_sq / _k8, shaders.metal:1049-1059, 1100-1120) with the weighted expert sum already formed by the
+// down-projection launch.  sigmoid as the reference writes it, 1 / (1 + exp(-p)).  h_mid and shared_out may be NULL.
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const float *__restrict__ h_mid, int ld_mid, const float *__restrict__ moe, int ld_moe, const float *__restrict__ shared_out,
+                   int ld_shared, const float *__restrict__ shared_logit, uint32_t hidden, float *__restrict__ out, int ldo)
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint32_t t = blockIdx.y, h = blockIdx.x * blockDim.x + threadIdx.x;
+    if (h >= hidden) return;
+    float v = moe[(size_t)t * ld_moe + h];
+    if (h_mid) v = h_mid[(size_t)t * ld_mid + h] + v;
+    if (shared_out) {
+        const float gate = 1.0f / (1.0f + expf(-shared_logit[t]));
+        v += gate * shared_out[(size_t)t * ld_shared + h];
+    }
+    out[(size_t)t * ldo + h] = v;
 }
 
 // Expert-parallel form: indices of the experts [first, first + count) become local (0..count-1), all others the

@@ -280,17 +280,24 @@ static int launch_pdl_smem(orome_cuda_ctx *c, const char *what, void (*kern)(KAr
 static int launch_generic(orome_cuda_ctx *c, int fmt, const uint8_t *data, uint32_t out_dim, uint32_t in_dim, int layout,
                           const float *x, int batch, int ldx, float *y, int ldy, cudaStream_t st);
 
+// shared_gate: the single-row fp32 tensor of the shared-expert gate, or NULL.  With it the logits have ne + 1 entries per
+// token and shared_logit[t] receives the last one.
 static int launch_router(orome_cuda_ctx *c, const uint8_t *data, uint32_t ne, uint32_t in_dim, const float *x, int n_tokens, int ldx,
-                         float *logits, uint32_t K, uint32_t *idx, float *w, cudaStream_t st)
+                         float *logits, uint32_t K, uint32_t *idx, float *w, cudaStream_t st, const uint8_t *shared_gate = nullptr,
+                         float *shared_logit = nullptr)
 {
     int rc;
+    const uint32_t rows = ne + (shared_gate ? 1u : 0u);
     if (in_dim % 4 == 0 && !(reinterpret_cast<uintptr_t>(x) & 15) && (n_tokens == 1 || ldx % 4 == 0))
-        rc = launch_pdl(c, "gemv_f32", gemv_f32_kernel, dim3((ne + 3) / 4), dim3(128), st, reinterpret_cast<const float *>(data), ne, in_dim,
-                        x, n_tokens, ldx, logits, (int)ne);
-    else
-        rc = launch_generic(c, FMT_F32, data, ne, in_dim, 0, x, n_tokens, ldx, logits, (int)ne, st);
+        rc = launch_pdl(c, "gemv_f32", gemv_f32_kernel, dim3((rows + 3) / 4), dim3(128), st, reinterpret_cast<const float *>(data), ne, in_dim,
+                        x, n_tokens, ldx, logits, (int)rows, reinterpret_cast<const float *>(shared_gate));
+    else {
+        rc = launch_generic(c, FMT_F32, data, ne, in_dim, 0, x, n_tokens, ldx, logits, (int)rows, st);
+        if (!rc && shared_gate) rc = launch_generic(c, FMT_F32, shared_gate, 1, in_dim, 0, x, n_tokens, ldx, logits + ne, (int)rows, st);
+    }
     if (rc) return rc;
-    return launch_pdl(c, "route_topk", route_topk_kernel, dim3(n_tokens), dim3(256), st, (const float *)logits, (int)ne, ne, K, idx, w);
+    return launch_pdl(c, "route_topk", route_topk_kernel, dim3(n_tokens), dim3(256), st, (const float *)logits, (int)rows, ne, K, idx, w,
+                      shared_gate ? shared_logit : (float *)nullptr);
 }
 
 // ---------------------------------------------------------------------------
@@ -1190,6 +1197,39 @@ extern "C" int orome_cuda_moe_route(orome_cuda_ctx *c, const OromeTensorRef *rou
     return launch_router(c, data, ne, router->in_dim, x_dev, n_tokens, ldx, logits_dev, K, idx_dev, w_dev, st);
 }
 
+extern "C" int orome_cuda_moe_route_pair(orome_cuda_ctx *c, const OromeTensorRef *router, const OromeTensorRef *shared_gate,
+                                         const float *x_dev, int n_tokens, int ldx, uint32_t K, uint32_t *idx_dev, float *w_dev,
+                                         float *shared_logit_dev, float *logits_dev, void *stream)
+{
+    if (!c || !router || !shared_gate || !x_dev || !idx_dev || !w_dev || !shared_logit_dev) return fail(OROME_EINVAL, "moe_route_pair: NULL argument");
+    if (!router->buffer) return fail(OROME_EINVAL, "moe_route_pair: router tensor is absent");
+    const uint8_t *data, *sg = nullptr;
+    int rc = orome_check_ref("moe_route_pair", router, &data);
+    if (rc) return rc;
+    if (router->format != OROME_QFMT_F32) return fail(OROME_ENOTSUP, "moe_route_pair: the router must be an F32 tensor");
+    if (router->out_dim > 255) return fail(OROME_EINVAL, "moe_route_pair: %u experts (at most 255 beside the gate row)", router->out_dim);
+    if (n_tokens < 1 || (n_tokens > 1 && ldx < (int)router->in_dim)) return fail(OROME_EINVAL, "moe_route_pair: bad n_tokens/ldx");
+    if (K < 1) return fail(OROME_EINVAL, "moe_route_pair: K must be at least 1");
+    CU(cudaSetDevice(c->device));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const uint32_t ne = router->out_dim;
+    if (shared_gate->buffer) {
+        rc = orome_check_ref("moe_route_pair(shared gate)", shared_gate, &sg);
+        if (rc) return rc;
+        // the reference fuses the two only for this shape (engine.m:660-666); anything else is not a shared-expert gate
+        if (shared_gate->format != OROME_QFMT_F32 || shared_gate->out_dim != 1 || shared_gate->in_dim != router->in_dim)
+            return fail(OROME_EINVAL, "moe_route_pair: the shared-expert gate must be an F32 tensor [1][%u]", router->in_dim);
+    } else {
+        CU(cudaMemsetAsync(shared_logit_dev, 0, (size_t)n_tokens * sizeof(float), st));      // absent gate: logit 0
+    }
+    if (!logits_dev) {
+        rc = ensure(&c->logits_dev, &c->logits_cap, (size_t)(ne + 1) * n_tokens);
+        if (rc) return rc;
+        logits_dev = c->logits_dev;
+    }
+    return launch_router(c, data, ne, router->in_dim, x_dev, n_tokens, ldx, logits_dev, K, idx_dev, w_dev, st, sg, shared_logit_dev);
+}
+
 // ---------------------------------------------------------------------------
 // routing without any allocation
 // ---------------------------------------------------------------------------
@@ -1306,6 +1346,53 @@ extern "C" int orome_cuda_moe_ffn(orome_cuda_ctx *c, const OromeExpertLayerRef *
     }
 #undef DN
     return post_launch(c, "moe_down");
+}
+
+extern "C" int orome_cuda_moe_block(orome_cuda_ctx *c, const OromeExpertLayerRef *L, uint32_t variant, const OromeTensorRef *shared_gate_proj,
+                                    const OromeTensorRef *shared_up_proj, const OromeTensorRef *shared_down_proj, const float *x_dev,
+                                    int n_tokens, int ldx, const uint32_t *idx_dev, const float *w_dev, const float *shared_logit_dev,
+                                    uint32_t K, uint32_t hidden, uint32_t inter, const float *h_mid_dev, int ld_mid, float *scratch_dev,
+                                    float *out_dev, int ldo, void *stream)
+{
+    if (!c || !L || !x_dev || !idx_dev || !w_dev || !scratch_dev || !out_dev) return fail(OROME_EINVAL, "moe_block: NULL argument");
+    if (n_tokens < 1 || (n_tokens > 1 && (ldx < (int)hidden || ldo < (int)hidden))) return fail(OROME_EINVAL, "moe_block: bad n_tokens/ldx/ldo");
+    if (h_mid_dev && n_tokens > 1 && ld_mid < (int)hidden) return fail(OROME_EINVAL, "moe_block: bad ld_mid");
+    const bool shared = shared_gate_proj && shared_up_proj && shared_down_proj && shared_gate_proj->buffer && shared_up_proj->buffer &&
+                        shared_down_proj->buffer;
+    uint32_t S = 0;
+    if (shared) {
+        S = shared_gate_proj->out_dim;
+        if (!shared_logit_dev) return fail(OROME_EINVAL, "moe_block: a shared expert needs its gate logit (orome_cuda_moe_route_pair)");
+        if (shared_gate_proj->in_dim != hidden || shared_up_proj->in_dim != hidden || shared_up_proj->out_dim != S ||
+            shared_down_proj->in_dim != S || shared_down_proj->out_dim != hidden)
+            return fail(OROME_EINVAL, "moe_block: shared expert shapes must be [S][hidden], [S][hidden], [hidden][S]");
+    }
+    // scratch: routed activations [T][K][inter], weighted expert sum [T][hidden], shared activations [T][S], shared output [T][hidden]
+    const size_t T = (size_t)n_tokens;
+    float *act = scratch_dev, *moe = act + T * K * inter, *sact = moe + T * hidden, *sout = sact + T * S;
+    if (reinterpret_cast<uintptr_t>(scratch_dev) & 15 || (K * inter) % 4 || hidden % 4 || S % 4)
+        return fail(OROME_EINVAL, "moe_block: scratch must be 16-byte aligned and the dimensions multiples of 4");
+    int rc = orome_cuda_moe_ffn(c, L, variant, x_dev, n_tokens, ldx, idx_dev, w_dev, K, hidden, inter, act, moe, (int)hidden, stream);
+    if (rc) return rc;
+    if (!L->buffer) {       // no routed experts in this layer: their sum is zero
+        CU(cudaMemsetAsync(moe, 0, T * hidden * sizeof(float), static_cast<cudaStream_t>(stream)));
+    }
+    if (shared) {
+        // the shared expert is independent of the routing result (engine.m:261-283): fused gate/up, then its down projection
+        rc = orome_cuda_gate_up_swiglu(c, shared_gate_proj, shared_up_proj, x_dev, sact, n_tokens, ldx, (int)S, stream);
+        if (rc) return rc;
+        rc = orome_cuda_matvec(c, shared_down_proj, sact, sout, n_tokens, (int)S, (int)hidden, stream);
+        if (rc) return rc;
+    }
+    CU(cudaSetDevice(c->device));
+    return launch_pdl(c, "moe_combine", moe_combine_kernel, dim3((hidden + 255) / 256, (unsigned)n_tokens), dim3(256), static_cast<cudaStream_t>(stream),
+                      h_mid_dev, n_tokens == 1 ? (int)hidden : ld_mid, (const float *)moe, (int)hidden, shared ? (const float *)sout : (const float *)nullptr,
+                      (int)hidden, shared_logit_dev, hidden, out_dev, n_tokens == 1 ? (int)hidden : ldo);
+}
+
+extern "C" size_t orome_cuda_moe_block_scratch_floats(int n_tokens, uint32_t K, uint32_t hidden, uint32_t inter, uint32_t shared_inter)
+{
+    return (size_t)n_tokens * ((size_t)K * inter + 2 * (size_t)hidden + shared_inter);
 }
 
 extern "C" int orome_cuda_moe_ffn_shard(orome_cuda_ctx *c, const OromeExpertLayerRef *L_local, uint32_t variant, const float *x_dev,

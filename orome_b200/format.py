@@ -47,7 +47,7 @@ EXPORTS = [
     "orome_cuda_matvec", "orome_cuda_matvec_group", "orome_cuda_gate_up_swiglu", "orome_cuda_dequant_rows",
     "orome_cuda_moe_route", "orome_cuda_moe_route_static", "orome_cuda_moe_ffn", "orome_cuda_moe_ffn_shard", "orome_cuda_matvec_host", "orome_cuda_set_option",
     "orome_cuda_get_option", "orome_cuda_launch_count", "orome_cuda_hint_next", "orome_cuda_peer_alloc", "orome_cuda_peer_open", "orome_cuda_peer_close", "orome_cuda_gather_setup",
-    "orome_cuda_gather_arena_bytes", "orome_cuda_gather_next", "orome_cuda_gather_wait", "orome_cuda_argmax", "orome_cuda_chain_begin", "orome_cuda_chain_end",
+    "orome_cuda_gather_arena_bytes", "orome_cuda_gather_next", "orome_cuda_gather_wait", "orome_cuda_argmax", "orome_cuda_moe_route_pair", "orome_cuda_moe_block", "orome_cuda_moe_block_scratch_floats", "orome_cuda_chain_begin", "orome_cuda_chain_end",
     "orome_cuda_chain_launch", "orome_cuda_chain_destroy", "orome_cuda_chain_info",
 ]
 
@@ -97,6 +97,10 @@ def lib():
     L.orome_cuda_gather_next.argtypes = [vp, i32, i32]
     L.orome_cuda_gather_wait.argtypes = [vp, i32, vp, u32, vp]
     L.orome_cuda_argmax.argtypes = [vp, vp, u32, vp, vp]
+    L.orome_cuda_moe_route_pair.argtypes = [vp, TR, TR, vp, i32, i32, u32, vp, vp, vp, vp, vp]
+    L.orome_cuda_moe_block.argtypes = [vp, EL, u32, TR, TR, TR, vp, i32, i32, vp, vp, vp, u32, u32, u32, vp, i32, vp, vp, i32, vp]
+    L.orome_cuda_moe_block_scratch_floats.argtypes = [i32, u32, u32, u32, u32]
+    L.orome_cuda_moe_block_scratch_floats.restype = sz
     L.orome_cuda_chain_begin.argtypes = [vp]
     L.orome_cuda_chain_end.argtypes = [vp, C.POINTER(vp)]
     L.orome_cuda_chain_launch.argtypes = [vp, vp, vp]
@@ -247,6 +251,19 @@ class Context:
         _chk(lib().orome_cuda_moe_ffn(self._h, C.byref(layer), variant, x, n_tokens, ldx, idx, w, K, hidden, inter, act, out,
                                       ldo, stream))
 
+    def moe_route_pair(self, router: TensorRef, shared_gate: TensorRef, x: int, n_tokens: int, ldx: int, K: int, idx: int, w: int,
+                       shared_logit: int, logits: int = 0, stream: int = 0):
+        """Routing plus the shared-expert gate logit in one launch (engine.m:656-679, shaders.metal:1232)."""
+        _chk(lib().orome_cuda_moe_route_pair(self._h, C.byref(router), C.byref(shared_gate), x, n_tokens, ldx, K, idx, w, shared_logit,
+                                             logits or None, stream))
+
+    def moe_block(self, layer: ExpertLayerRef, variant: int, shared, x: int, n_tokens: int, ldx: int, idx: int, w: int, shared_logit: int,
+                  K: int, hidden: int, inter: int, h_mid: int, ld_mid: int, scratch: int, out: int, ldo: int, stream: int = 0):
+        """Routed experts + shared expert + combine (engine.m:158-340).  shared: (gate, up, down) TensorRefs or None."""
+        sg, su, sd = (C.byref(r) for r in shared) if shared else (None, None, None)
+        _chk(lib().orome_cuda_moe_block(self._h, C.byref(layer), variant, sg, su, sd, x, n_tokens, ldx, idx, w, shared_logit or None, K, hidden,
+                                        inter, h_mid or None, ld_mid, scratch, out, ldo, stream))
+
     def moe_ffn_shard(self, layer_local: ExpertLayerRef, variant: int, x: int, n_tokens: int, ldx: int, idx: int, w: int, K: int,
                       hidden: int, inter: int, first_expert: int, n_local: int, idx_local: int, act: int, out: int, ldo: int,
                       stream: int = 0):
@@ -285,6 +302,10 @@ class Chain:
             self.close()
         except Exception:
             pass
+
+
+def moe_block_scratch_floats(n_tokens: int, K: int, hidden: int, inter: int, shared_inter: int) -> int:
+    return int(lib().orome_cuda_moe_block_scratch_floats(n_tokens, K, hidden, inter, shared_inter))
 
 
 def gather_arena_bytes(data_bytes: int, n_flags: int) -> int:

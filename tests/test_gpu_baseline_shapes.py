@@ -310,3 +310,49 @@ def test_cfg5_moe_expert_parallel_shares(env, moe_layer):
     for t in range(T):
         want = oracle.moe_ffn_f64(L["gate"], L["up"], L["down"], (synth.Q4_K, synth.Q4_K, synth.Q5_K), (sg, sg, sd), x[t], H, M, idx[t], w[t])
         assert rel_l2(total[t], want) <= REL_L2_TOL
+
+
+@pytest.mark.parametrize("T", [1, 5])
+def test_cfg5_moe_block_with_shared_expert(env, moe_layer, T):
+    """Router + shared-gate logit in one launch, routed experts, shared expert (Q8_0 gate/up, Q4_K down), combine with
+    the sigmoid gate and the residual input: the whole block of engine.m:158-340 at the 128-expert shape."""
+    torch, F, ctx = env
+    L = moe_layer
+    H, M, E, K, S = L["H"], L["M"], L["E"], 8, 512
+    sgd, sud = synth.host_tensor(synth.Q8_0, S, H, seed=91), synth.host_tensor(synth.Q8_0, S, H, seed=92)
+    sdd = synth.host_tensor(synth.Q4_K, H, S, seed=93)
+    sgw = (np.random.default_rng(94).standard_normal(H) / np.sqrt(H)).astype(np.float32)          # [1][H] fp32 gate row
+    x = np.atleast_2d(synth.host_x(H, T, seed=95)) * np.float32(0.02)
+    h_mid = np.atleast_2d(synth.host_x(H, T, seed=96))
+    xt, ht = dev(torch, x), dev(torch, h_mid)
+    rt, sgt = dev(torch, L["router"].view(np.uint8).reshape(-1)), dev(torch, sgw.view(np.uint8))
+    tg, tu, td = dev(torch, sgd), dev(torch, sud), dev(torch, sdd)
+    idx = torch.zeros((T, 8), device="cuda", dtype=torch.int32)
+    w = torch.zeros((T, 8), device="cuda")
+    sl = torch.full((T,), float("nan"), device="cuda")
+    logits = torch.zeros((T, E + 1), device="cuda")
+    ctx.moe_route_pair(F.tensor_ref(rt.data_ptr(), 0, synth.F32, E, H), F.tensor_ref(sgt.data_ptr(), 0, synth.F32, 1, H), xt.data_ptr(), T, H, K,
+                       idx.data_ptr(), w.data_ptr(), sl.data_ptr(), logits.data_ptr())
+    scratch = torch.empty(F.moe_block_scratch_floats(T, K, H, M, S), device="cuda")
+    out = torch.full((T, H), float("nan"), device="cuda")
+    shared = (F.tensor_ref(tg.data_ptr(), 0, synth.Q8_0, S, H), F.tensor_ref(tu.data_ptr(), 0, synth.Q8_0, S, H), F.tensor_ref(td.data_ptr(), 0, synth.Q4_K, H, S))
+    ctx.moe_block(L["layer"], 0, shared, xt.data_ptr(), T, H, idx.data_ptr(), w.data_ptr(), sl.data_ptr(), K, H, M, ht.data_ptr(), H,
+                  scratch.data_ptr(), out.data_ptr(), H)
+    torch.cuda.synchronize()
+    lg, gi, gw, gsl, got = logits.cpu().numpy(), idx.cpu().numpy().astype(np.uint32), w.cpu().numpy(), sl.cpu().numpy(), out.cpu().numpy()
+    for t in range(T):
+        # slot 8 of the reference's params: the raw logit of the gate row, which sits after the router logits
+        assert gsl[t] == lg[t, E]
+        assert abs(gsl[t] - float(np.dot(sgw.astype(np.float64), x[t].astype(np.float64)))) <= 1e-5
+        oi, ow = oracle.route(lg[t, :E], K)
+        assert np.array_equal(gi[t], oi) and np.max(np.abs(gw[t] - ow)) <= 1e-6
+        want = oracle.moe_block_f64(L["gate"], L["up"], L["down"], (synth.Q4_K, synth.Q4_K, synth.Q5_K), (L["sg"], L["sg"], L["sd"]),
+                                    ((synth.Q8_0, sgd, S), (synth.Q8_0, sud, S), (synth.Q4_K, sdd)), x[t], H, M, gi[t], gw[t], gsl[t], h_mid=h_mid[t])
+        assert rel_l2(got[t], want) <= REL_L2_TOL, t
+    # without a shared expert and without a residual input the block is the routed sum alone
+    out2 = torch.full((T, H), float("nan"), device="cuda")
+    ctx.moe_block(L["layer"], 0, None, xt.data_ptr(), T, H, idx.data_ptr(), w.data_ptr(), 0, K, H, M, 0, 0, scratch.data_ptr(), out2.data_ptr(), H)
+    torch.cuda.synchronize()
+    for t in range(T):
+        want = oracle.moe_ffn_f64(L["gate"], L["up"], L["down"], (synth.Q4_K, synth.Q4_K, synth.Q5_K), (L["sg"], L["sg"], L["sd"]), x[t], H, M, gi[t], gw[t])
+        assert rel_l2(out2.cpu().numpy()[t], want) <= REL_L2_TOL

@@ -130,7 +130,7 @@ def test_chain_q8_0_every_vector(env, x_bits):
         st.chain = ctx.chain_end()
         info = st.chain.info()
         assert info["products"] == 3 * 4 + 1 and info["stages"] >= 2
-        tol = 1e-5 if x_bits == 24 else 2e-4         # 16-bit x: 2e-5 per product, carried through thirteen products
+        tol = 1e-5 if x_bits == 24 else 3e-4         # 16-bit x: ~3e-5 per product, carried through thirteen products
         rng = np.random.default_rng(3)
         # launch it several times with fresh inputs: tags of one launch must not satisfy the next
         for rep in range(3):

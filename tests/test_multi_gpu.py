@@ -156,3 +156,79 @@ def test_fused_gather_two_gpus(fmt):
     for p in procs:
         p.join(timeout=60)
     assert all(ok for _, ok, _ in results), results
+
+
+def _chain_worker(rank, world, port, q):
+    """A recorded chain on row-split tensors: W1 x -> fused gate/up -> W3 act, every vector completed on both GPUs by
+    the producing product's peer stores, the last one copied to its plain place inside the chain (gather_wait)."""
+    import torch.distributed as dist
+    import oracle
+    from orome_b200 import format as F
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    ok, err = False, ""
+    try:
+        ctx = F.Context(rank)
+        fmt, n, m = synth.Q8_0, 1024, 2048
+        W1 = synth.host_tensor(fmt, n, n, seed=91)
+        Wg, Wu = synth.host_tensor(fmt, m, n, seed=92), synth.host_tensor(fmt, m, n, seed=93)
+        W3 = synth.host_tensor(fmt, n, m, seed=94)
+        rbn, rbm = synth.row_bytes(fmt, n), synth.row_bytes(fmt, m)
+        lo, hi = rowsplit.shard_rows(n, rank, world)
+        lom, him = rowsplit.shard_rows(m, rank, world)
+        npad, mpad = rowsplit.padded_rows(n, world), rowsplit.padded_rows(m, world)
+        arena = rowsplit.PeerArena(ctx, dist, rank, world, 2 * (npad * 4 + 256) + (mpad * 4 + 256), 1)
+        y1, act, y3 = arena.floats(npad), arena.floats(mpad), arena.floats(npad)
+        dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+        w1, wg, wu, w3 = dev(W1[lo * rbn:hi * rbn]), dev(Wg[lom * rbn:him * rbn]), dev(Wu[lom * rbn:him * rbn]), dev(W3[lo * rbm:hi * rbm])
+        xt = torch.zeros(n, device="cuda")
+        st = torch.cuda.current_stream().cuda_stream
+        ctx.chain_begin()
+        ctx.matvec(F.tensor_ref(w1.data_ptr(), 0, fmt, hi - lo, n), xt.data_ptr(), y1[lo:hi].data_ptr())
+        ctx.gate_up_swiglu(F.tensor_ref(wg.data_ptr(), 0, fmt, him - lom, n), F.tensor_ref(wu.data_ptr(), 0, fmt, him - lom, n),
+                           y1.data_ptr(), act[lom:him].data_ptr())
+        ctx.matvec(F.tensor_ref(w3.data_ptr(), 0, fmt, hi - lo, m), act.data_ptr(), y3[lo:hi].data_ptr())
+        ctx.gather_wait(0, y3.data_ptr(), n)
+        chain = ctx.chain_end()
+        assert chain.info()["products"] == 4
+        worst = 0.0
+        for rep in range(3):                                  # tags of one launch must not satisfy the next
+            x = synth.host_x(n, seed=95 + rep) * np.float32(20.0)
+            xt.copy_(torch.from_numpy(x))
+            chain.launch(st)
+            torch.cuda.synchronize()
+            dist.barrier()
+            a1 = oracle.matvec_f64(fmt, W1, n, n, x).astype(np.float32)
+            a2 = oracle.swiglu_f64(oracle.matvec_f64(fmt, Wg, m, n, a1), oracle.matvec_f64(fmt, Wu, m, n, a1)).astype(np.float32)
+            want = oracle.matvec_f64(fmt, W3, n, m, a2)
+            got = y3[:n].cpu().numpy()
+            worst = max(worst, float(np.linalg.norm(got - want) / np.linalg.norm(want)))
+            dist.barrier()
+        ok = bool(worst <= 1e-5 and ctx.status() == 0)
+        err = f"worst={worst:.2e}"
+        chain.close()
+    except Exception as ex:   # report instead of leaving the peer waiting on a barrier
+        err = repr(ex)
+    q.put((rank, ok, err))
+    try:
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_chain_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_chain_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=240) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+    assert all(ok for _, ok, _ in results), results
