@@ -10,8 +10,11 @@ the 9B Q8_0 set).  Every product reads the output of the one before it, as in th
 engine.  Every layer has its own weights (7.2 GB for the 9B set), far above the 126 MB
 L2, so no weight byte is served from cache between or within steps.
 
-Default form (`--mode chain`): the step is recorded once through the C ABI and runs as ONE
-resident kernel per step.  `--mode launches` issues one kernel per product (CUDA graph).
+Two forms of the same step.  `--mode launches` issues one kernel per product, replayed from a
+CUDA graph; `--mode chain` records the step once through the C ABI and runs it as ONE resident
+kernel.  The default, `--mode auto`, takes the form that measures faster for the GPU count:
+launches on one GPU (the chain's hand-over between products costs more than a graph node there),
+the chain on several (one launch per step instead of a launch plus a cross-GPU wait per product).
 
 Prints ONE JSON line: metric decode_matvec_tok_s (tokens per second of the whole job),
 `roofline` (algorithmic HBM bytes per step / device time against the measured copy
@@ -210,7 +213,6 @@ class Stepper:
         g = torch.Generator(device=dev)
         g.manual_seed(1234)
         self.x_h = torch.randn(H, device=dev, generator=g)           # the step's input vector
-        self.x_a = torch.randn(A, device=dev, generator=g)
         from orome_b200.rowsplit import padded_rows
         w = ds.world
         # output vectors (padded to equal slices per rank when sharded); local slices are written in place
@@ -253,7 +255,6 @@ class Stepper:
         # the parity check reads every vector on the host: on several GPUs complete their plain copies too
         unpack = (lambda flag, buf, n: ctx.gather_wait(flag, buf.data_ptr(), n, stream)) if (self.fused and layers is not None) else (lambda *a: None)
         x_in, first, nprod = self.x_h, True, 0
-        indep = bool(os.environ.get("OROME_BENCH_INDEPENDENT_X")) and not self.fused      # experiment: every product reads a fixed vector
         for n, li in enumerate(layer_ids):
             rq, rk, rv, ro, rg, ru, rd = self.refs[li]
             nxt_q = self.refs[layer_ids[n + 1]][0] if n + 1 < len(layer_ids) else self.lm_ref
@@ -267,20 +268,20 @@ class Stepper:
             unpack(self.FLAG_QKV, self.q, H); unpack(self.FLAG_QKV, self.k, KV); unpack(self.FLAG_QKV, self.v, KV)
             hint(rg)
             gn(self.FLAG_QKV, self.FLAG_O)
-            ctx.matvec(ro, (self.x_h if indep else self.q).data_ptr(), self._slice(self.o, H).data_ptr(), 1, 0, 0, stream)
+            ctx.matvec(ro, self.q.data_ptr(), self._slice(self.o, H).data_ptr(), 1, 0, 0, stream)
             self._gather(self.o, H)
             unpack(self.FLAG_O, self.o, H)
             hint(rd)
             gn(self.FLAG_O, self.FLAG_ACT)
-            ctx.gate_up_swiglu(rg, ru, (self.x_h if indep else self.o).data_ptr(), self._slice(self.act, A).data_ptr(), 1, 0, 0, stream)
+            ctx.gate_up_swiglu(rg, ru, self.o.data_ptr(), self._slice(self.act, A).data_ptr(), 1, 0, 0, stream)
             self._gather(self.act, A)
             unpack(self.FLAG_ACT, self.act, A)
             hint(nxt_q)
             gn(self.FLAG_ACT, self.FLAG_DN)
-            ctx.matvec(rd, (self.x_a if indep else self.act).data_ptr(), self._slice(self.dn, H).data_ptr(), 1, 0, 0, stream)
+            ctx.matvec(rd, self.act.data_ptr(), self._slice(self.dn, H).data_ptr(), 1, 0, 0, stream)
             self._gather(self.dn, H)
             unpack(self.FLAG_DN, self.dn, H)
-            x_in, first, nprod = (self.x_h if indep else self.dn), False, nprod + 4
+            x_in, first, nprod = self.dn, False, nprod + 4
         hint(self.refs[layer_ids[0]][0] if layer_ids else None)            # the next token starts at the first layer again
         gn(-1 if first else self.FLAG_DN, self.FLAG_LOGITS)
         ctx.matvec(self.lm_ref, x_in.data_ptr(), self._slice(self.logits, V).data_ptr(), 1, 0, 0, stream)
@@ -526,7 +527,9 @@ def run_ours(args):
                           "peak_gbs": peak, "peak_kind": kind}), flush=True)
         return
     ds = decode_set.DecodeSet(args.workload, dev, rank=rank, world=world, layers=args.layers)
-    mode = args.mode if (world == 1 or args.gather == "fused") else "launches"      # an NCCL all-gather per product cannot be chained
+    mode = args.mode if args.mode != "auto" else ("launches" if world == 1 else "chain")
+    if world > 1 and args.gather != "fused":
+        mode = "launches"                                  # an NCCL all-gather per product cannot be chained
     st = Stepper(torch, F, ctx, ds, dist, fused=args.gather == "fused", mode=mode)
     st.build()
     torch.cuda.synchronize()
@@ -682,8 +685,8 @@ def main():
     ap.add_argument("--workload", default="9b_q8_0", choices=["9b_q8_0", "27b_q4_k_m"])
     ap.add_argument("--layers", type=int, default=None, help="override the number of layers (smaller captures for profiling)")
     ap.add_argument("--x-bits", type=int, default=0, choices=[0, 16, 24])
-    ap.add_argument("--mode", default="chain", choices=["chain", "launches"],
-                    help="chain: the step is recorded once and runs as one resident kernel; launches: one kernel per product (CUDA graph)")
+    ap.add_argument("--mode", default="auto", choices=["auto", "chain", "launches"],
+                    help="auto: launches on one GPU, chain on several; chain: the step is recorded once and runs as one resident kernel; launches: one kernel per product (CUDA graph)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--extras", action="store_true", help="also time the other benchmark configurations kernel by kernel (adds ~20 s)")
     ap.add_argument("--kernel", default="", help="run only the named --extras case(s), comma separated, --steps timing repeats, and exit")

@@ -39,7 +39,7 @@ def sources() -> list[str]:
 
 
 def _deps() -> list[str]:
-    return glob.glob(os.path.join(CSRC, "*")) + [os.path.join(HERE, "..", "include", "orome_cuda.h")]
+    return glob.glob(os.path.join(CSRC, "*")) + glob.glob(os.path.join(HERE, "..", "include", "*.h"))
 
 
 def stale() -> bool:
