@@ -519,6 +519,8 @@ def run_ours(args):
         ctx.set_option(F.OPT_X_BITS, args.x_bits)
     if args.prefetch_mb >= 0:
         ctx.set_option(F.OPT_PREFETCH_MB, args.prefetch_mb)
+    if args.stage_kb > 0:
+        ctx.set_option(F.OPT_STAGE_KB, args.stage_kb)
 
     if args.kernel:
         # one configuration alone, few launches: the process a profiler capture is taken from
@@ -692,6 +694,7 @@ def main():
     ap.add_argument("--kernel", default="", help="run only the named --extras case(s), comma separated, --steps timing repeats, and exit")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="N > 1: complete y by peer stores from the kernel epilogue (fused) or by an NCCL all-gather per product")
+    ap.add_argument("--stage-kb", type=int, default=0, help="size of one stage of the weight ring in KiB (0 = library default)")
     ap.add_argument("--prefetch-mb", type=int, default=-1, help="cap of the next-tensor L2 prefetch in MiB (0 = off, -1 = library default)")
     args = ap.parse_args()
     if args.impl == "reference":

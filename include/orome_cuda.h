@@ -289,6 +289,41 @@ int  orome_cuda_moe_ffn_shard(orome_cuda_ctx *ctx, const OromeExpertLayerRef *la
  * performance hint: results do not depend on it. */
 int  orome_cuda_hint_next(orome_cuda_ctx *ctx, const OromeTensorRef *next);
 
+/* ---- the steps either side of a product, fused into it ---------------------------------
+ *
+ * The reference runs three small kernels between the attention output projection and the FFN
+ * products (engine.m:625-653): residual_add_sum_sq (shaders.metal:86-124: out = clamp(a + b,
+ * +-65504) and one partial sum of out^2 per threadgroup), then rms_norm_apply_partial
+ * (shaders.metal:126-149: x * rsqrt(sum(parts) / dim + eps) * bf16 weight).  Here the first is
+ * the epilogue of the product that makes b, the second the prologue of every product that reads
+ * the normalised vector, so neither the un-normalised nor the normalised intermediate costs a
+ * launch of its own:
+ *
+ *   orome_cuda_fuse_next(ctx, NULL, &epi);  orome_cuda_matvec(ctx, &o_proj, attn, hidden, ...);
+ *       hidden[r] = clamp(epi.residual[r] + (W attn)[r]);  epi.sum_sq_parts = partial sums of hidden^2
+ *   orome_cuda_fuse_next(ctx, &pro, NULL);  orome_cuda_gate_up_swiglu(ctx, &gate, &up, hidden, act, ...);
+ *       the product reads hidden[c] * rsqrt(sum(pro.sum_sq_parts) / in_dim + pro.eps) * bf16(pro.weight_bf16[c])
+ *
+ * A request applies to the NEXT batch-1 launch of orome_cuda_matvec / orome_format_dispatch_matvec /
+ * orome_cuda_matvec_group (prologue; epilogue for a single tensor only) or orome_cuda_gate_up_swiglu
+ * (prologue only) and is consumed by it.  A call that cannot honour it (batch > 1, F16/BF16/F32 tensors,
+ * shapes outside the decode kernels, a chain recording, a multi-GPU gather request on the same launch)
+ * drops it and returns OROME_ENOTSUP.  residual may equal the product's y (in-place add, as the
+ * reference does with buf_moe_hidden, engine.m:629).  A partials array holds OROME_SUM_SQ_PARTS floats
+ * of device memory; the epilogue writes all of them (one per CTA, zeros behind), the prologue adds all
+ * of them up, so the array needs no clearing and the two sides need not agree on a grid size. */
+#define OROME_SUM_SQ_PARTS 512
+typedef struct {
+    const void  *weight_bf16;    /* [in_dim] bf16 norm weights, 8-byte aligned (the BF16 copies format.m:437-452 makes of F32 norm tensors) */
+    const float *sum_sq_parts;   /* [OROME_SUM_SQ_PARTS], written by an epilogue (or by the caller: total in [0], zeros behind) */
+    float        eps;
+} OromeNormPrologue;
+typedef struct {
+    const float *residual;       /* [out_dim] */
+    float       *sum_sq_parts;   /* [OROME_SUM_SQ_PARTS] */
+} OromeResidualEpilogue;
+int  orome_cuda_fuse_next(orome_cuda_ctx *ctx, const OromeNormPrologue *prologue, const OromeResidualEpilogue *epilogue);
+
 /* ---- one token step as ONE launch ---------------------------------------------------------
  *
  * The reference encodes every product of a token into one command buffer and commits it once

@@ -210,6 +210,27 @@ def moe_block_f64(gate, up, down, fmts, strides, shared, x, hidden, inter, idx, 
     return out
 
 
+def residual_add_sum_sq(a, b, tg: int = 256):
+    """residual_add_sum_sq (inference/src/shaders.metal:86-124): out = clamp(a + b, -65504, 65504) in fp32 and one
+    partial sum of out^2 per threadgroup of `tg` elements (engine.m:628-638 dispatches ceil(dim / 256) groups of 256).
+    Returns (out float32, parts float32); parity unpinned (restates the shader, no reference-held vector covers it)."""
+    out = np.clip(np.asarray(a, np.float32) + np.asarray(b, np.float32), np.float32(-65504.0), np.float32(65504.0)).astype(np.float32)
+    parts = np.array([np.sum(out[i:i + tg].astype(np.float64) ** 2) for i in range(0, out.size, tg)], np.float64)
+    return out, parts.astype(np.float32)
+
+
+def rms_norm_apply_partial(x, weight_bf16, parts, eps: float) -> np.ndarray:
+    """rms_norm_apply_partial (shaders.metal:126-149): the partial sums added up in order in fp32, then
+    x * rsqrt(total / dim + eps) * bf16 weight, fp32 products in that order.  weight_bf16: uint16 bit patterns."""
+    x = np.asarray(x, np.float32)
+    total = np.float32(0.0)
+    for p in np.asarray(parts, np.float32):
+        total = np.float32(total + p)
+    rms = np.float32(1.0) / np.sqrt(np.float32(total / np.float32(x.size) + np.float32(eps)), dtype=np.float32)
+    w = (np.asarray(weight_bf16, np.uint16).astype(np.uint32) << 16).view(np.float32)
+    return ((x * rms).astype(np.float32) * w).astype(np.float32)
+
+
 def argmax(data) -> int:
     """Index the reference's argmax_kernel returns for this vector (ties resolved as its 1024 threads do)."""
     d = np.ascontiguousarray(data, np.float32).reshape(-1)

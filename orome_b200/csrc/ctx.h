@@ -42,6 +42,12 @@ struct orome_cuda_ctx {
     size_t g_data_bytes = 0;
     unsigned int *g_local = nullptr;          // [n_flags] generation of each gathered vector, then the publish arrival counter
     int g_wait = -1, g_publish = -1;          // request for the next pipelined launch
+    // fused neighbours requested for the next batch-1 product (orome_cuda_fuse_next)
+    const void *fuse_norm_w = nullptr;
+    const float *fuse_norm_parts = nullptr;
+    float fuse_norm_eps = 0.0f;
+    const float *fuse_res_in = nullptr;
+    float *fuse_res_parts = nullptr;
     unsigned long long *trace_dev = nullptr;   // diagnostics buffer [trace_cap][sm_count][8]
     int trace_cap = 0, trace_next = 0;
     // staging for the host-buffer entry point

@@ -102,7 +102,16 @@ struct PipeArgs {
     const uint2 *x_ll;                        // slots of x, or NULL when x is a plain vector
     const unsigned int *wait_gen;             // generation x must carry
     long long wait_cycles;                    // bound of the polls of a gathered x
+    // Fused neighbours of the product (single-tensor plain form).  Prologue: x is normalised while it is read,
+    // x[c] * rsqrt(sum(norm_parts) / in_dim + norm_eps) * bf16(norm_w[c]).  Epilogue: y[r] = clamp(res_in[r] + (W x)[r])
+    // and every CTA leaves the sum of squares of its y values in res_parts[blockIdx.x] (entries past the grid are zeroed).
+    const uint16_t *norm_w;
+    const float *norm_parts;
+    float norm_eps;
+    const float *res_in;
+    float *res_parts;
 };
+constexpr int PIPE_SUM_SQ_PARTS = 512;          // length of a sum-of-squares partials array
 
 // ---- PTX wrappers ---------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -380,7 +389,8 @@ template <int NP, int G, bool SUMS>
 __device__ __forceinline__ bool quantize_x_to_smem(const float *__restrict__ x, uint32_t in_dim, uint32_t nvec, uint32_t x_stride,
                                                    uint8_t *xq0, uint32_t vec_bytes, uint32_t tid, uint32_t nthreads,
                                                    const uint2 *slots = nullptr, unsigned int tag = 0,
-                                                   long long limit = PIPE_WAIT_CYCLES, const int *status = nullptr, uint32_t rot = 0)
+                                                   long long limit = PIPE_WAIT_CYCLES, const int *status = nullptr, uint32_t rot = 0,
+                                                   const uint16_t *norm_w = nullptr, float rms = 1.0f)
 {
     // rot (single vector only; a multiple of 32 four-float pieces): this CTA walks the vector starting rot pieces in and
     // wraps around.  When every CTA of a grid reads the same vector at the same moment, different rot values keep them
@@ -398,6 +408,13 @@ __device__ __forceinline__ bool quantize_x_to_smem(const float *__restrict__ x, 
             if (nvec == 1) { fl += rot; if (fl >= n4) fl -= n4; }
             if (slots) v[b] = fa < n4_all ? ld_gathered4(slots + 4 * (size_t)fl, tag, &ok, limit, status) : make_float4(0.f, 0.f, 0.f, 0.f);
             else v[b] = fa < n4_all ? __ldcg(reinterpret_cast<const float4 *>(x + (size_t)vec * x_stride) + fl) : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (norm_w && fa < n4_all) {      // the RMS-norm scale and the bf16 norm weights, applied in the reference's order
+                const uint2 w = __ldg(reinterpret_cast<const uint2 *>(norm_w) + fl);
+                v[b].x = v[b].x * rms * __uint_as_float(w.x << 16);
+                v[b].y = v[b].y * rms * __uint_as_float(w.x & 0xffff0000u);
+                v[b].z = v[b].z * rms * __uint_as_float(w.y << 16);
+                v[b].w = v[b].w * rms * __uint_as_float(w.y & 0xffff0000u);
+            }
         }
 #pragma unroll
         for (int b = 0; b < BATCH; ++b) {
@@ -859,9 +876,17 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
         // a gathered x: every element is polled for the generation this rank gave its own slice (visible after the wait above)
         const uint2 *slots = EXT ? a.x_ll : nullptr;
         const unsigned int want = EXT && a.x_ll ? *reinterpret_cast<const volatile unsigned int *>(a.wait_gen) : 0u;
+        const uint16_t *norm_w = EXT ? a.norm_w : nullptr;
+        float rms = 1.0f;
+        if (norm_w) {                         // every warp adds up the partial sums of squares for itself
+            float t = 0.0f;
+            for (uint32_t i = lane; i < (uint32_t)PIPE_SUM_SQ_PARTS; i += 32) t += __ldcg(a.norm_parts + i);
+            rms = rsqrtf(warp_sum(t) / (float)a.in_dim + a.norm_eps);
+        }
         if (!quantize_x_to_smem<NP, SlotT::GROUP, SlotT::SUMS>(a.x, a.in_dim, COMBINE ? (uint32_t)a.nseg : 1u, a.x_stride, xq, a.xq_vec_bytes, tid, C,
                                                                slots, want, a.wait_cycles, a.status,
-                                                               COMBINE ? 0u : (uint32_t)((uint64_t)blockIdx.x * (a.in_dim / 4) / gridDim.x) & ~31u)) {
+                                                               COMBINE ? 0u : (uint32_t)((uint64_t)blockIdx.x * (a.in_dim / 4) / gridDim.x) & ~31u,
+                                                               norm_w, rms)) {
             s_abort = 1;
             atomicExch(a.status, 3);
         }
@@ -898,6 +923,7 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
     }
     uint32_t which = 0, buf_n = 0, buf_row0 = 0;
     int buf_seg = 0;
+    float sq = 0.0f;                          // this thread's share of the sum of squares of the outputs (residual epilogue)
     auto flush = [&]() {
         named_bar_sync(PIPE_BAR_CONSUMERS, (int)C);
         const float *src = pbuf + (size_t)which * PLANE * (SWIGLU ? 2 : 1);
@@ -911,7 +937,13 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
             }
             if constexpr (COMBINE) accbuf[buf_row0 - wk.lo + r] += (comb_acc ? 1.0f : a.seg_weight[buf_seg]) * g;   // one owner per row and flush
             else {
-                const float val = SWIGLU ? silu_mul(g, u) : g;
+                float val = SWIGLU ? silu_mul(g, u) : g;
+                if constexpr (EXT && MODE == 0) {
+                    if (a.res_in) {           // residual add, clamped to the fp16 range as the reference's kernel does
+                        val = fminf(fmaxf(a.res_in[buf_row0 + r] + val, -65504.0f), 65504.0f);
+                        sq = fmaf(val, val, sq);
+                    }
+                }
                 y[r] = val;
                 if constexpr (EXT) {
                     if (a.npeers > 0) {
@@ -973,19 +1005,34 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
                               : pbuf + (size_t)which * PLANE * (SWIGLU ? 2 : 1) + (size_t)buf_n * GW + wig;
         const float segw = comb_acc ? a.seg_weight[t.seg] : 0.0f;
         const uint32_t rstride = comb_acc ? SL : GW;
+        // Plain Q8_0 products keep two rows of a group in flight when a tile holds more than one row per group (this
+        // row and the one rows_par further on): two independent dot products and reductions per warp hide each
+        // other's shared-memory and shuffle latency, as the gate and up rows of the fused form do.
+        constexpr bool PAIR = MODE == 0 && FMT == FMT_Q8_0;
+        const uint32_t rstep = comb_acc ? 1u : (PAIR ? 2u * a.rows_par : a.rows_par);
 #pragma unroll 1
-        for (uint32_t r = comb_acc ? 0u : group; r < t.n; r += comb_acc ? 1u : a.rows_par) {
+        for (uint32_t r = comb_acc ? 0u : group; r < t.n; r += rstep) {
             float v = 0.0f, v2 = 0.0f;
+            const bool second = PAIR && r + a.rows_par < t.n;
             if (active) {
                 v = slot.dot(base + r * a.row_bytes, part, a.layout);
                 if constexpr (SWIGLU) v2 = slot.dot(base2 + r * a.row_bytes, part, a.layout);
+                if constexpr (PAIR) { if (second) v2 = slot.dot(base + (r + a.rows_par) * a.row_bytes, part, a.layout); }
             }
-            v = warp_sum(v);
-            if constexpr (SWIGLU) v2 = warp_sum(v2);
+            if constexpr (SWIGLU || PAIR) {
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    v += __shfl_xor_sync(0xffffffffu, v, o);
+                    v2 += __shfl_xor_sync(0xffffffffu, v2, o);
+                }
+            } else {
+                v = warp_sum(v);
+            }
             if (lane == 0) {
                 if (comb_acc) dst[r * rstride] = fmaf(segw, v, dst[r * rstride]);
                 else dst[r * GW] = v;
                 if constexpr (SWIGLU) dst[PLANE + r * GW] = v2;
+                if constexpr (PAIR) { if (second) dst[(r + a.rows_par) * GW] = v2; }
             }
         }
         __syncwarp();
@@ -1009,6 +1056,20 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
                     for (int p = 0; p < a.npeers; ++p) st_slot(reinterpret_cast<uint2 *>(slot + a.peer_delta[p]), accbuf[r], pub_tag);
                 }
             }
+        }
+    }
+    if constexpr (EXT && MODE == 0) {
+        if (a.res_parts) {
+            __shared__ float s_sq[PIPE_MAX_CONSUMERS / 32];
+            sq = warp_sum(sq);
+            if (lane == 0) s_sq[tid >> 5] = sq;
+            named_bar_sync(PIPE_BAR_CONSUMERS, (int)C);
+            if (tid == 0) {
+                float t = 0.0f;
+                for (uint32_t w = 0; w < (C >> 5); ++w) t += s_sq[w];
+                a.res_parts[blockIdx.x] = t;
+            }
+            for (uint32_t i = gridDim.x + blockIdx.x * C + tid; i < (uint32_t)PIPE_SUM_SQ_PARTS; i += gridDim.x * C) a.res_parts[i] = 0.0f;
         }
     }
     if (EXT && a.npeers > 0) {

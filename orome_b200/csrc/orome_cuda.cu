@@ -412,7 +412,8 @@ static int plan_pipe(orome_cuda_ctx *c, int fmt, uint32_t in_dim, uint32_t total
     const uint32_t share = (total_rows + p.grid - 1) / p.grid;            // rows of the busiest CTA
 
     const uint32_t per_row = a.row_bytes * (swiglu ? 2 : 1);
-    const uint32_t want = (c->stage_kb ? (uint32_t)c->stage_kb : 16u) * 1024u;
+    // plain Q8_0 products pair rows inside a tile (two rows per group in flight), which needs tiles of two rows per group
+    const uint32_t want = (c->stage_kb ? (uint32_t)c->stage_kb : (fmt == FMT_Q8_0 && mode == 0 ? 64u : 16u)) * 1024u;
     a.iters = std::max(1u, std::min((uint32_t)PIPE_MAX_ITERS, want / (per_row * a.rows_par)));
     a.iters = std::min(a.iters, (share + a.rows_par - 1) / a.rows_par);
 
@@ -461,6 +462,14 @@ static int plan_pipe(orome_cuda_ctx *c, int fmt, uint32_t in_dim, uint32_t total
     a.pf_bytes = c->hint_bytes;
     c->hint_ptr = nullptr;
     c->hint_bytes = 0;
+    // fused norm prologue / residual epilogue (the entry points have checked that this launch can take them)
+    a.norm_w = static_cast<const uint16_t *>(c->fuse_norm_w);
+    a.norm_parts = c->fuse_norm_parts;
+    a.norm_eps = c->fuse_norm_eps;
+    a.res_in = c->fuse_res_in;
+    a.res_parts = c->fuse_res_parts;
+    c->fuse_norm_w = nullptr; c->fuse_norm_parts = nullptr; c->fuse_res_in = nullptr; c->fuse_res_parts = nullptr;
+    if (a.res_parts && p.grid > PIPE_SUM_SQ_PARTS) return fail(OROME_ENOTSUP, "pipe plan: more CTAs than entries in a partials array");
     return OROME_OK;
 }
 
@@ -495,7 +504,7 @@ static int launch_pipe_ext(orome_cuda_ctx *c, const PipePlan &p, cudaStream_t st
 template <int FMT, int NP, int MODE, int MINB>
 static int launch_pipe_inst(orome_cuda_ctx *c, const PipePlan &p, cudaStream_t st)
 {
-    const bool ext = p.args.seg_expert || p.args.npeers > 0 || p.args.x_ll;
+    const bool ext = p.args.seg_expert || p.args.npeers > 0 || p.args.x_ll || p.args.norm_w || p.args.res_in;
     if constexpr (MODE == 2) return launch_pipe_ext<FMT, NP, MODE, MINB, true>(c, p, st);
     else return ext ? launch_pipe_ext<FMT, NP, MODE, MINB, true>(c, p, st) : launch_pipe_ext<FMT, NP, MODE, MINB, false>(c, p, st);
 }
@@ -818,6 +827,43 @@ extern "C" int orome_cuda_gather_wait(orome_cuda_ctx *c, int flag, float *vec_de
 }
 
 // ---------------------------------------------------------------------------
+// fused neighbours of a product
+// ---------------------------------------------------------------------------
+static_assert(OROME_SUM_SQ_PARTS == PIPE_SUM_SQ_PARTS, "the header and the kernel must agree on the partials array");
+
+static void drop_fuse(orome_cuda_ctx *c)
+{
+    c->fuse_norm_w = nullptr; c->fuse_norm_parts = nullptr; c->fuse_res_in = nullptr; c->fuse_res_parts = nullptr;
+}
+static bool fuse_pending(const orome_cuda_ctx *c) { return c->fuse_norm_w || c->fuse_res_in; }
+// A fuse request on a path without the fused form: dropped, with an error, like a gather request.
+static int refuse_fuse(orome_cuda_ctx *c, const char *who)
+{
+    drop_fuse(c);
+    c->g_wait = c->g_publish = -1;
+    return fail(OROME_ENOTSUP, "%s: this call has no fused norm / residual form (the request was dropped)", who);
+}
+
+extern "C" int orome_cuda_fuse_next(orome_cuda_ctx *c, const OromeNormPrologue *pro, const OromeResidualEpilogue *epi)
+{
+    if (!c) return fail(OROME_EINVAL, "fuse_next: NULL ctx");
+    drop_fuse(c);
+    if (pro) {
+        if (!pro->weight_bf16 || !pro->sum_sq_parts || (reinterpret_cast<uintptr_t>(pro->weight_bf16) & 7) || !(pro->eps >= 0.0f))
+            return fail(OROME_EINVAL, "fuse_next: the prologue needs 8-byte aligned bf16 weights, a partials array and eps >= 0");
+        c->fuse_norm_w = pro->weight_bf16;
+        c->fuse_norm_parts = pro->sum_sq_parts;
+        c->fuse_norm_eps = pro->eps;
+    }
+    if (epi) {
+        if (!epi->residual || !epi->sum_sq_parts) { drop_fuse(c); return fail(OROME_EINVAL, "fuse_next: the epilogue needs a residual vector and a partials array"); }
+        c->fuse_res_in = epi->residual;
+        c->fuse_res_parts = epi->sum_sq_parts;
+    }
+    return OROME_OK;
+}
+
+// ---------------------------------------------------------------------------
 // matvec entry points
 // ---------------------------------------------------------------------------
 extern "C" int orome_cuda_matvec_group(orome_cuda_ctx *c, const OromeTensorRef *refs, int n_refs, const float *x_dev,
@@ -845,6 +891,10 @@ extern "C" int orome_cuda_matvec_group(orome_cuda_ctx *c, const OromeTensorRef *
             if (y0 < lo || y0 + (size_t)refs[i].out_dim * 4 > hi) { c->g_wait = c->g_publish = -1; return fail(OROME_EINVAL, "matvec_group: a published y must lie inside the gather arena"); }
         }
     }
+    const bool fused = fuse_pending(c);
+    if (fused && (c->rec || c->force_generic || !orome_pipe_supported(fmt, refs[0].in_dim) || (c->fuse_res_in && n_refs != 1) ||
+                  (c->g_world > 1 && (c->g_publish >= 0 || c->g_wait >= 0))))
+        return refuse_fuse(c, "matvec_group");
     if (c->rec) return orome_chain_record_group(c, refs, n_refs, x_dev, y_dev);
     if (c->force_generic || !orome_pipe_supported(fmt, refs[0].in_dim)) {
         if (c->g_world > 1 && (c->g_publish >= 0 || c->g_wait >= 0)) { c->g_wait = c->g_publish = -1; return fail(OROME_ENOTSUP, "matvec_group: this shape has no multi-GPU form"); }
@@ -856,7 +906,7 @@ extern "C" int orome_cuda_matvec_group(orome_cuda_ctx *c, const OromeTensorRef *
     }
     bool aligned16 = true;
     for (int i = 0; i < n_refs; ++i) aligned16 = aligned16 && !(reinterpret_cast<uintptr_t>(data[i]) & 15);
-    if ((aligned16 || fmt == FMT_Q6_K) && mma_supported(c, fmt, refs[0].in_dim, false)) {
+    if (!fused && (aligned16 || fmt == FMT_Q6_K) && mma_supported(c, fmt, refs[0].in_dim, false)) {   // the fused forms live in the dp4a kernel
         MmaPlan m;
         memset(&m, 0, sizeof m);
         uint32_t rows = 0;
@@ -1004,6 +1054,7 @@ extern "C" int orome_cuda_matvec(orome_cuda_ctx *c, const OromeTensorRef *ref, c
         float *ys[1] = {y_dev};
         return orome_cuda_matvec_group(c, ref, 1, x_dev, ys, stream);
     }
+    if (fuse_pending(c)) return refuse_fuse(c, "matvec");
     if (c->rec) return fail(OROME_ENOTSUP, "matvec: only batch-1 products of quantized tensors can be recorded into a chain");
     if (batch > 1 && (ldx < (int)ref->in_dim || ldy < (int)ref->out_dim))
         return fail(OROME_EINVAL, "matvec: ldx/ldy smaller than the row length");
@@ -1081,6 +1132,10 @@ extern "C" int orome_cuda_gate_up_swiglu(orome_cuda_ctx *c, const OromeTensorRef
         const uint8_t *lo = c->g_arena[c->g_rank], *hi = lo + c->g_data_bytes, *y0 = reinterpret_cast<const uint8_t *>(out_dev);
         if (y0 < lo || y0 + (size_t)gate->out_dim * 4 > hi) { c->g_wait = c->g_publish = -1; return fail(OROME_EINVAL, "gate_up_swiglu: a published output must lie inside the gather arena"); }
     }
+    const bool fused = fuse_pending(c);
+    if (fused && (c->rec || c->fuse_res_in || batch != 1 || c->force_generic || !orome_pipe_supported(fmt, gate->in_dim) ||
+                  (c->g_world > 1 && (c->g_publish >= 0 || c->g_wait >= 0))))
+        return refuse_fuse(c, "gate_up_swiglu");
     if (c->rec) {
         if (batch != 1) return fail(OROME_ENOTSUP, "gate_up_swiglu: only batch-1 products can be recorded into a chain");
         return orome_chain_record_gate_up(c, gate, up, x_dev, out_dev);
@@ -1091,7 +1146,7 @@ extern "C" int orome_cuda_gate_up_swiglu(orome_cuda_ctx *c, const OromeTensorRef
     }
     if (batch == 1 && !c->force_generic && orome_pipe_supported(fmt, gate->in_dim)) {
         if (reinterpret_cast<uintptr_t>(x_dev) & 15) return fail(OROME_EINVAL, "gate_up_swiglu: x must be 16-byte aligned");
-        if (!((reinterpret_cast<uintptr_t>(gd) | reinterpret_cast<uintptr_t>(ud)) & 15) && mma_supported(c, fmt, gate->in_dim, true)) {
+        if (!fused && !((reinterpret_cast<uintptr_t>(gd) | reinterpret_cast<uintptr_t>(ud)) & 15) && mma_supported(c, fmt, gate->in_dim, true)) {
             MmaPlan m;
             memset(&m, 0, sizeof m);
             m.args.seg[0] = PipeSeg{gd, ud, out_dev, gate->out_dim, 0};
@@ -1274,6 +1329,7 @@ extern "C" int orome_cuda_moe_ffn(orome_cuda_ctx *c, const OromeExpertLayerRef *
                                   uint32_t inter, float *act_dev, float *out_dev, int ldo, void *stream)
 {
     if (!c || !L || !x_dev || !idx_dev || !w_dev || !act_dev || !out_dev) return fail(OROME_EINVAL, "moe_ffn: NULL argument");
+    if (fuse_pending(c)) return refuse_fuse(c, "moe_ffn");
     if (!L->buffer) return OROME_OK;
     if (K < 1 || K > 8) return fail(OROME_EINVAL, "moe_ffn: K = %u (1..8; the reference's routing caps K at 8)", K);
     if (variant > OROME_VARIANT_LLAMA) return fail(OROME_ENOTSUP, "moe_ffn: unknown kernel variant %u", variant);
@@ -1355,6 +1411,7 @@ extern "C" int orome_cuda_moe_block(orome_cuda_ctx *c, const OromeExpertLayerRef
                                     float *out_dev, int ldo, void *stream)
 {
     if (!c || !L || !x_dev || !idx_dev || !w_dev || !scratch_dev || !out_dev) return fail(OROME_EINVAL, "moe_block: NULL argument");
+    if (fuse_pending(c)) return refuse_fuse(c, "moe_block");
     if (n_tokens < 1 || (n_tokens > 1 && (ldx < (int)hidden || ldo < (int)hidden))) return fail(OROME_EINVAL, "moe_block: bad n_tokens/ldx/ldo");
     if (h_mid_dev && n_tokens > 1 && ld_mid < (int)hidden) return fail(OROME_EINVAL, "moe_block: bad ld_mid");
     const bool shared = shared_gate_proj && shared_up_proj && shared_down_proj && shared_gate_proj->buffer && shared_up_proj->buffer &&
@@ -1401,6 +1458,7 @@ extern "C" int orome_cuda_moe_ffn_shard(orome_cuda_ctx *c, const OromeExpertLaye
                                         float *out_dev, int ldo, void *stream)
 {
     if (!c || !idx_dev || !idx_local_dev) return fail(OROME_EINVAL, "moe_ffn_shard: NULL argument");
+    if (fuse_pending(c)) return refuse_fuse(c, "moe_ffn_shard");
     if (n_tokens < 1) return fail(OROME_EINVAL, "moe_ffn_shard: n_tokens %d", n_tokens);
     if (L_local && !L_local->buffer) {      // this GPU holds no expert of the layer: its share of the sum is zero
         CU(cudaSetDevice(c->device));

@@ -41,6 +41,19 @@ class ExpertLayerRef(C.Structure):
     _fields_ = [("buffer", C.c_void_p), ("gate", ExpertProjRef), ("up", ExpertProjRef), ("down", ExpertProjRef)]
 
 
+class NormPrologue(C.Structure):
+    """rms_norm_apply_partial (shaders.metal:126-149) applied while a product reads its input."""
+    _fields_ = [("weight_bf16", C.c_void_p), ("sum_sq_parts", C.c_void_p), ("eps", C.c_float)]
+
+
+class ResidualEpilogue(C.Structure):
+    """residual_add_sum_sq (shaders.metal:86-124) applied where a product writes its output."""
+    _fields_ = [("residual", C.c_void_p), ("sum_sq_parts", C.c_void_p)]
+
+
+SUM_SQ_PARTS = 512
+
+
 EXPORTS = [
     "orome_cuda_ctx_create", "orome_cuda_ctx_destroy", "orome_cuda_last_error", "orome_cuda_status", "orome_cuda_upload",
     "orome_cuda_free", "orome_format_from_ggml_type", "orome_format_row_bytes", "orome_format_dispatch_matvec",
@@ -48,7 +61,7 @@ EXPORTS = [
     "orome_cuda_moe_route", "orome_cuda_moe_route_static", "orome_cuda_moe_ffn", "orome_cuda_moe_ffn_shard", "orome_cuda_matvec_host", "orome_cuda_set_option",
     "orome_cuda_get_option", "orome_cuda_launch_count", "orome_cuda_hint_next", "orome_cuda_peer_alloc", "orome_cuda_peer_open", "orome_cuda_peer_close", "orome_cuda_gather_setup",
     "orome_cuda_gather_arena_bytes", "orome_cuda_gather_next", "orome_cuda_gather_wait", "orome_cuda_argmax", "orome_cuda_moe_route_pair", "orome_cuda_moe_block", "orome_cuda_moe_block_scratch_floats", "orome_cuda_chain_begin", "orome_cuda_chain_end",
-    "orome_cuda_chain_launch", "orome_cuda_chain_destroy", "orome_cuda_chain_info",
+    "orome_cuda_chain_launch", "orome_cuda_chain_destroy", "orome_cuda_chain_info", "orome_cuda_fuse_next",
 ]
 
 _lib = None
@@ -107,6 +120,7 @@ def lib():
     L.orome_cuda_chain_destroy.argtypes = [vp, vp]
     L.orome_cuda_chain_destroy.restype = None
     L.orome_cuda_chain_info.argtypes = [vp, C.POINTER(i32), C.POINTER(C.c_uint64), C.POINTER(i32), C.POINTER(i32)]
+    L.orome_cuda_fuse_next.argtypes = [vp, C.POINTER(NormPrologue), C.POINTER(ResidualEpilogue)]
     L.orome_cuda_launch_count.argtypes = [vp]
     L.orome_cuda_launch_count.restype = C.c_uint64
     _lib = L
@@ -215,6 +229,11 @@ class Context:
     def gather_wait(self, flag: int, vec_ptr: int, n: int, stream: int = 0):
         """Complete the plain copy of the gathered vector of `n` floats at `vec_ptr` (inside the arena)."""
         _chk(lib().orome_cuda_gather_wait(self._h, flag, vec_ptr, n, stream))
+
+    def fuse_next(self, prologue: NormPrologue | None = None, epilogue: ResidualEpilogue | None = None):
+        """Fuse the norm (prologue) and / or the residual add + sum of squares (epilogue) into the next batch-1 product."""
+        _chk(lib().orome_cuda_fuse_next(self._h, C.byref(prologue) if prologue is not None else None,
+                                        C.byref(epilogue) if epilogue is not None else None))
 
     def hint_next(self, ref: TensorRef | None):
         _chk(lib().orome_cuda_hint_next(self._h, C.byref(ref) if ref is not None else None))

@@ -246,3 +246,19 @@ def test_moe_ffn_matches_manual_composition():
         act = (g / (1 + np.exp(-g)) * u).astype(np.float32)
         want += float(wk) * oracle.matvec_f64(synth.Q5_K, down[e * sd:(e + 1) * sd], H, M, act)
     assert np.allclose(got, want, rtol=1e-12, atol=1e-12)
+
+
+def test_norm_restatements_known_answers():
+    # shaders.metal:86-149: clamp to the fp16 range, one partial per 256 elements, weights are bf16 bit patterns
+    a = np.full(600, 2.0, np.float32)
+    b = np.full(600, 1.0, np.float32)
+    a[3], b[3] = 65000.0, 1000.0
+    a[4], b[4] = -65000.0, -1000.0
+    out, parts = oracle.residual_add_sum_sq(a, b)
+    assert out[3] == np.float32(65504.0) and out[4] == np.float32(-65504.0) and out[5] == np.float32(3.0)
+    assert parts.size == 3 and parts[1] == np.float32(256 * 9.0) and parts[2] == np.float32(88 * 9.0)
+    x = np.full(512, 3.0, np.float32)
+    one, half = np.uint16(0x3F80), np.uint16(0x3F00)
+    w = np.where(np.arange(512) % 2 == 0, one, half).astype(np.uint16)
+    y = oracle.rms_norm_apply_partial(x, w, np.array([256 * 9.0, 256 * 9.0], np.float32), 0.0)
+    assert np.allclose(y[0::2], 1.0, rtol=1e-6) and np.allclose(y[1::2], 0.5, rtol=1e-6)
