@@ -40,6 +40,30 @@ constexpr int TC_DEQ_WARPS = 16;     // two groups of 8 warps take alternate sla
 constexpr int TC_SLAB_WARPS = 8;     // warps that fill one slab
 constexpr int TC_THREADS = (TC_DEQ_WARPS + 2) * 32;
 
+// Row-split form on several GPUs (the batched counterpart of the publish fields of PipeArgs): every Y value also
+// goes, as a {value, tag} slot, into this rank's and every peer's copy of the gather arena.
+struct TcPub {
+    int npeers;                               // 0: single GPU, nothing is published
+    long long peer_delta[PIPE_MAX_PEERS];
+    const uint8_t *arena_base;
+    uint8_t *ll_origin;
+    unsigned int *pub_gen, *pub_arrived;
+};
+__device__ __forceinline__ void tc_publish(const TcPub &g, const float *addr, float val, unsigned int tag)
+{
+    uint8_t *slot = g.ll_origin + 2 * (reinterpret_cast<const uint8_t *>(addr) - g.arena_base);
+    st_slot(reinterpret_cast<uint2 *>(slot), val, tag);
+    for (int p = 0; p < g.npeers; ++p) st_slot(reinterpret_cast<uint2 *>(slot + g.peer_delta[p]), val, tag);
+}
+// One thread per CTA, after the CTA's stores: the last CTA of the grid makes the new generation this rank's current one.
+__device__ __forceinline__ void tc_publish_done(const TcPub &g, unsigned int tag)
+{
+    if (atomicAdd(g.pub_arrived, 1u) == gridDim.x - 1) {
+        *reinterpret_cast<volatile unsigned int *>(g.pub_arrived) = 0;
+        *reinterpret_cast<volatile unsigned int *>(g.pub_gen) = tag;
+    }
+}
+
 struct TcArgs {
     alignas(64) CUtensorMap wmap;   // the tensor as a 2-D array of 32-bit words [rows][row_bytes / 4], box = 128 rows x one chunk
     const uint8_t *w;          // tensor
@@ -50,6 +74,7 @@ struct TcArgs {
     uint32_t split, chunks;       // split-K parts and 256-weight chunks per row: part p takes chunks [p*chunks/split, (p+1)*chunks/split)
     int layout;
     int *status;
+    TcPub pub;                 // split == 1 only: with split-K the reduction kernel publishes
 };
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -76,17 +101,24 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t da, uint64_
 __device__ __forceinline__ uint32_t sw128_off(uint32_t r, uint32_t c) { return (r >> 3) * 1024u + (r & 7u) * 128u + ((c ^ (r & 7u)) << 4); }
 
 // X fp32 [batch][ldx] -> fp16 tiles [k_slab][npad][64] in the same swizzled layout; rows >= batch are zero.
-__global__ void pack_x_f16_kernel(const float *__restrict__ x, int batch, int ldx, uint32_t in_dim, uint32_t npad, __half *__restrict__ xp)
+// x_ll: X is a gathered matrix in the arena, read from its slots (every element polled, bounded, for the generation
+// *wait_gen); NULL: a plain matrix.
+__global__ void pack_x_f16_kernel(const float *__restrict__ x, int batch, int ldx, uint32_t in_dim, uint32_t npad, __half *__restrict__ xp,
+                                  const uint2 *x_ll, const unsigned int *wait_gen, long long wait_cycles, int *status)
 {
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    const unsigned int want = x_ll ? *reinterpret_cast<const volatile unsigned int *>(wait_gen) : 0u;
+    bool ok = true;
     const uint32_t slabs = in_dim / TC_SLAB_K;
     const size_t total = (size_t)slabs * npad * 8;   // one thread per 16-byte piece
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const uint32_t c = (uint32_t)(i & 7), n = (uint32_t)((i >> 3) % npad), ks = (uint32_t)(i / ((size_t)npad * 8));
         __half2 h[4];
         if ((int)n < batch) {
-            const float4 *src = reinterpret_cast<const float4 *>(x + (size_t)n * ldx + (size_t)ks * TC_SLAB_K + c * 8);
-            const float4 a = src[0], b = src[1];
+            const size_t off = (size_t)n * ldx + (size_t)ks * TC_SLAB_K + c * 8;
+            const float4 *src = reinterpret_cast<const float4 *>(x + off);
+            const float4 a = x_ll ? ld_gathered4(x_ll + off, want, &ok, wait_cycles, status) : src[0];
+            const float4 b = x_ll ? ld_gathered4(x_ll + off + 4, want, &ok, wait_cycles, status) : src[1];
             h[0] = __floats2half2_rn(a.x, a.y); h[1] = __floats2half2_rn(a.z, a.w);
             h[2] = __floats2half2_rn(b.x, b.y); h[3] = __floats2half2_rn(b.z, b.w);
         } else {
@@ -95,6 +127,7 @@ __global__ void pack_x_f16_kernel(const float *__restrict__ x, int batch, int ld
         uint8_t *dst = reinterpret_cast<uint8_t *>(xp) + (size_t)ks * npad * 128 + sw128_off(n, c);
         *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(h);
     }
+    if (!ok) atomicExch(status, 3);
 }
 
 // 8 consecutive weights of one row as fp16 -> one 16-byte piece.
@@ -292,6 +325,8 @@ gemm_tc_kernel(const __grid_constant__ TcArgs a)
             const uint32_t r = warp * 32 + lane;
             float *ybase = a.split == 1 ? a.y : a.y + (size_t)sp * a.batch * a.rows;
             const uint32_t ld = a.split == 1 ? a.ldy : a.rows;
+            const bool publish = a.split == 1 && a.pub.npeers > 0;
+            const unsigned int pub_tag = publish ? *reinterpret_cast<const volatile unsigned int *>(a.pub.pub_gen) + 1u : 0u;
             for (uint32_t n0 = 0; n0 < a.npad; n0 += 16) {
                 uint32_t v[16];
                 asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
@@ -302,7 +337,11 @@ gemm_tc_kernel(const __grid_constant__ TcArgs a)
                 if (r < nrows && !s_abort) {
 #pragma unroll
                     for (uint32_t i = 0; i < 16; ++i)
-                        if (n0 + i < a.batch) ybase[(size_t)(n0 + i) * ld + row0 + r] = __uint_as_float(v[i]);
+                        if (n0 + i < a.batch) {
+                            float *dst = ybase + (size_t)(n0 + i) * ld + row0 + r;
+                            *dst = __uint_as_float(v[i]);
+                            if (publish) tc_publish(a.pub, dst, __uint_as_float(v[i]), pub_tag);
+                        }
                 }
             }
         }
@@ -313,17 +352,27 @@ gemm_tc_kernel(const __grid_constant__ TcArgs a)
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(ncols) : "memory");
     }
+    if (threadIdx.x == 0 && a.split == 1 && a.pub.npeers > 0)
+        tc_publish_done(a.pub, *reinterpret_cast<const volatile unsigned int *>(a.pub.pub_gen) + 1u);
 }
 
 // Y[b][r] = sum over splits of partial[s][b][r]
-__global__ void splitk_reduce_kernel(const float *__restrict__ part, uint32_t split, uint32_t batch, uint32_t rows, float *__restrict__ y, uint32_t ldy)
+__global__ void splitk_reduce_kernel(const float *__restrict__ part, uint32_t split, uint32_t batch, uint32_t rows, float *__restrict__ y, uint32_t ldy,
+                                     const TcPub pub)
 {
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    const unsigned int pub_tag = pub.npeers > 0 ? *reinterpret_cast<const volatile unsigned int *>(pub.pub_gen) + 1u : 0u;
     const size_t n = (size_t)batch * rows;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         float acc = 0.0f;
         for (uint32_t s = 0; s < split; ++s) acc += part[(size_t)s * n + i];
-        y[(i / rows) * ldy + (i % rows)] = acc;
+        float *dst = y + (i / rows) * ldy + (i % rows);
+        *dst = acc;
+        if (pub.npeers > 0) tc_publish(pub, dst, acc, pub_tag);
+    }
+    if (pub.npeers > 0) {
+        __syncthreads();
+        if (threadIdx.x == 0) tc_publish_done(pub, pub_tag);
     }
 }
 

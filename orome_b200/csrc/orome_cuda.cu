@@ -975,9 +975,15 @@ static EncodeTiledFn encode_tiled_fn()
 }
 
 // Y[b][r] for b < batch (<= TC_MAX_N per launch; larger batches are cut into slices that each re-read the weights).
+// pub / x_ll / wait_gen: the row-split form on several GPUs (batch <= TC_MAX_N, one launch): Y is published to every
+// rank's arena by the kernel that writes it, a gathered X is read from its slots by the packing kernel.
 static int launch_tc(orome_cuda_ctx *c, int fmt, const uint8_t *data, uint32_t out_dim, uint32_t in_dim, int layout, const float *x,
-                     int batch, int ldx, float *y, int ldy, cudaStream_t st)
+                     int batch, int ldx, float *y, int ldy, cudaStream_t st, const TcPub *pub = nullptr, const uint2 *x_ll = nullptr,
+                     const unsigned int *wait_gen = nullptr)
 {
+    TcPub no_pub;
+    memset(&no_pub, 0, sizeof no_pub);
+    if (!pub) pub = &no_pub;
     const uint32_t chunk_bytes = fmt == FMT_Q8_0 ? 272u : fmt == FMT_Q4_K ? 144u : 176u;
     const uint32_t chunks = in_dim / TC_KC, tiles = (out_dim + TC_M - 1) / TC_M;
     // Split K so that the SMs stay busy: a CTA costs about one time unit per chunk plus about five to set up (TMEM,
@@ -999,7 +1005,7 @@ static int launch_tc(orome_cuda_ctx *c, int fmt, const uint8_t *data, uint32_t o
         __half *xp = reinterpret_cast<__half *>(c->tc_xp);
         const size_t pieces = (size_t)(in_dim / TC_SLAB_K) * npad * 8;
         rc = launch_pdl(c, "pack_x_f16", pack_x_f16_kernel, dim3((unsigned)std::min<size_t>((pieces + 255) / 256, 1184)), dim3(256), st,
-                        x + (size_t)b0 * ldx, nb, ldx, in_dim, npad, xp);
+                        x + (size_t)b0 * ldx, nb, ldx, in_dim, npad, xp, x_ll, wait_gen, orome_wait_cycles(c), c->status_dev);
         if (rc) return rc;
         TcArgs a;
         memset(&a, 0, sizeof a);
@@ -1018,6 +1024,7 @@ static int launch_tc(orome_cuda_ctx *c, int fmt, const uint8_t *data, uint32_t o
         a.rows = out_dim; a.in_dim = in_dim; a.row_bytes = (uint32_t)row_bytes_of(fmt, in_dim); a.chunk_bytes = chunk_bytes;
         a.batch = (uint32_t)nb; a.npad = npad; a.ldy = (uint32_t)ldy; a.split = split; a.chunks = chunks;
         a.layout = layout; a.status = c->status_dev;
+        a.pub = *pub;
         // Shared memory: one chunk's worth of fp16 slab buffers, two X tile stages, two packed-weight stages (169 KB for
         // Q4_K at batch 64).  Measured on Q4_K 12288x4096, batch 64: deeper rings (seven slab buffers, a third X stage, up
         // to six packed-weight stages, sized at run time) made the launch slower (35-41 us against 34 us), and removing
@@ -1036,7 +1043,7 @@ static int launch_tc(orome_cuda_ctx *c, int fmt, const uint8_t *data, uint32_t o
         if (split > 1) {
             const size_t n = (size_t)nb * out_dim;
             rc = launch_pdl(c, "splitk_reduce", splitk_reduce_kernel, dim3((unsigned)std::min<size_t>((n + 255) / 256, 1184)), dim3(256), st,
-                            (const float *)c->tc_part, split, (uint32_t)nb, out_dim, y + (size_t)b0 * ldy, (uint32_t)ldy);
+                            (const float *)c->tc_part, split, (uint32_t)nb, out_dim, y + (size_t)b0 * ldy, (uint32_t)ldy, *pub);
             if (rc) return rc;
         }
     }
@@ -1058,18 +1065,47 @@ extern "C" int orome_cuda_matvec(orome_cuda_ctx *c, const OromeTensorRef *ref, c
     if (c->rec) return fail(OROME_ENOTSUP, "matvec: only batch-1 products of quantized tensors can be recorded into a chain");
     if (batch > 1 && (ldx < (int)ref->in_dim || ldy < (int)ref->out_dim))
         return fail(OROME_EINVAL, "matvec: ldx/ldy smaller than the row length");
-    // A gather request armed for this call cannot be honoured on the paths below (no publish / wait form): drop it
-    // and say so, rather than leave it armed for an unrelated later launch.
-    if (c->g_world > 1 && (c->g_wait >= 0 || c->g_publish >= 0)) {
-        c->g_wait = c->g_publish = -1;
-        return fail(OROME_ENOTSUP, "matvec: this batch / format has no multi-GPU form (the gather request was dropped)");
-    }
     const uint8_t *data;
     int rc = orome_check_ref("matvec", ref, &data);
-    if (rc) return rc;
+    if (rc) { c->g_wait = c->g_publish = -1; return rc; }
     CU(cudaSetDevice(c->device));
     const bool x_ok = ldx % 4 == 0 && !(reinterpret_cast<uintptr_t>(x_dev) & 15);
-    if (batch >= c->tc_min_batch && !c->force_generic && tc_supported((int)ref->format, ref->in_dim) && x_ok)
+    const bool tc_ok = batch >= c->tc_min_batch && !c->force_generic && tc_supported((int)ref->format, ref->in_dim) && x_ok;
+    if (c->g_world > 1 && (c->g_wait >= 0 || c->g_publish >= 0)) {
+        // Row-split batched product: only the tensor-core form has a publish / wait path, and only as one launch.  Any
+        // other call drops the request and says so, rather than leave it armed for an unrelated later launch.
+        const int wait = c->g_wait, publish = c->g_publish;
+        c->g_wait = c->g_publish = -1;
+        if (!tc_ok || batch > TC_MAX_N)
+            return fail(OROME_ENOTSUP, "matvec: this batch / format has no multi-GPU form (the gather request was dropped)");
+        uint8_t *mine = c->g_arena[c->g_rank];
+        const uint8_t *end = mine + c->g_data_bytes;
+        TcPub pub;
+        memset(&pub, 0, sizeof pub);
+        pub.arena_base = mine;
+        pub.ll_origin = mine + c->g_data_bytes;
+        const uint2 *x_ll = nullptr;
+        const unsigned int *wait_gen = nullptr;
+        if (publish >= 0) {
+            const uint8_t *y0 = reinterpret_cast<const uint8_t *>(y_dev);
+            if (y0 < mine || y0 + ((size_t)(batch - 1) * ldy + ref->out_dim) * 4 > end)
+                return fail(OROME_EINVAL, "matvec: a published Y must lie inside the gather arena");
+            for (int r = 0; r < c->g_world; ++r)
+                if (r != c->g_rank) pub.peer_delta[pub.npeers++] = (long long)(c->g_arena[r] - mine);
+            pub.pub_gen = c->g_local + publish;
+            pub.pub_arrived = c->g_local + c->g_nflags;
+        }
+        if (wait >= 0) {
+            const uint8_t *xb = reinterpret_cast<const uint8_t *>(x_dev);
+            if (xb < mine || xb + ((size_t)(batch - 1) * ldx + ref->in_dim) * 4 > end)
+                return fail(OROME_EINVAL, "matvec: a launch that waits for a gathered X must read it from the gather arena");
+            x_ll = reinterpret_cast<const uint2 *>(pub.ll_origin + 2 * (size_t)(xb - mine));
+            wait_gen = c->g_local + wait;
+        }
+        return launch_tc(c, (int)ref->format, data, ref->out_dim, ref->in_dim, (int)ref->variant, x_dev, batch, ldx, y_dev, ldy,
+                         static_cast<cudaStream_t>(stream), &pub, x_ll, wait_gen);
+    }
+    if (tc_ok)
         return launch_tc(c, (int)ref->format, data, ref->out_dim, ref->in_dim, (int)ref->variant, x_dev, batch, ldx, y_dev, ldy,
                          static_cast<cudaStream_t>(stream));
     // Small batches, and formats the tensor-core form does not take (Q6_K): one batch-1 launch per input vector.  The

@@ -110,7 +110,7 @@ def test_chain_whose_peer_never_runs_expires_once_and_stays_usable(two_rank_ctx)
 
 def test_gather_request_is_dropped_by_calls_that_cannot_honour_it(two_rank_ctx):
     torch, F, ctx, arena = two_rank_ctx
-    fmt, n = synth.Q8_0, 256
+    fmt, n = synth.Q6_K, 256                              # a format without the batched tensor-core form
     wt = dev(torch, synth.host_tensor(fmt, n, n, seed=6))
     x8 = dev(torch, synth.host_x(n, 8, seed=7))
     y8 = torch.zeros((8, n), device="cuda")

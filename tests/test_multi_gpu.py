@@ -232,3 +232,75 @@ def test_chain_two_gpus():
     for p in procs:
         p.join(timeout=60)
     assert all(ok for _, ok, _ in results), results
+
+
+def _batched_worker(rank, world, port, q):
+    """Two chained batched (prefill) products, both row-split: the tensor-core kernel publishes Y, the next one's
+    packing kernel reads the gathered X from the arena's slots."""
+    import torch.distributed as dist
+    import oracle
+    from orome_b200 import format as F
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    ok, err = False, ""
+    try:
+        ctx = F.Context(rank)
+        errs = []
+        for fmt, n, m, batch in ((synth.Q8_0, 1024, 768, 8), (synth.Q4_K, 4096, 1024, 64)):
+            W1, W2 = synth.host_tensor(fmt, m, n, seed=91), synth.host_tensor(fmt, n, m, seed=92)
+            X = synth.host_x(n, batch, seed=93)
+            rb1, rb2 = synth.row_bytes(fmt, n), synth.row_bytes(fmt, m)
+            lo1, hi1 = rowsplit.shard_rows(m, rank, world)
+            lo2, hi2 = rowsplit.shard_rows(n, rank, world)
+            mp_, np_ = rowsplit.padded_rows(m, world), rowsplit.padded_rows(n, world)
+            arena = rowsplit.PeerArena(ctx, dist, rank, world, (batch * (mp_ + np_) * 4 + 1024), 2)
+            y1, y2 = arena.floats(batch * mp_).view(batch, mp_), arena.floats(batch * np_).view(batch, np_)
+            w1 = torch.from_numpy(W1[lo1 * rb1:hi1 * rb1].copy()).cuda()
+            w2 = torch.from_numpy(W2[lo2 * rb2:hi2 * rb2].copy()).cuda()
+            xt = torch.from_numpy(np.ascontiguousarray(X)).cuda()
+            st = torch.cuda.current_stream().cuda_stream
+            for rep in range(3):
+                ctx.gather_next(-1, 0)
+                ctx.matvec(F.tensor_ref(w1.data_ptr(), 0, fmt, hi1 - lo1, n), xt.data_ptr(), y1[:, lo1:].data_ptr(), batch, n, mp_, st)
+                ctx.gather_next(0, 1)
+                ctx.matvec(F.tensor_ref(w2.data_ptr(), 0, fmt, hi2 - lo2, m), y1.data_ptr(), y2[:, lo2:].data_ptr(), batch, mp_, np_, st)
+                for b in range(batch):
+                    ctx.gather_wait(0, y1[b].data_ptr(), m, st)
+                    ctx.gather_wait(1, y2[b].data_ptr(), n, st)
+                torch.cuda.synchronize()
+                dist.barrier()
+            want1 = oracle.matvec_f64(fmt, W1, m, n, X)
+            got1 = y1[:, :m].cpu().numpy()
+            want2 = oracle.matvec_f64(fmt, W2, n, m, got1)
+            e1 = np.linalg.norm(got1 - want1) / np.linalg.norm(want1)
+            e2 = np.linalg.norm(y2[:, :n].cpu().numpy() - want2) / np.linalg.norm(want2)
+            errs.append((float(e1), float(e2)))
+            ctx.gather_setup(rank, 1, None, 0, 0)
+            dist.barrier()
+        ok = bool(all(e1 <= 5e-4 and e2 <= 5e-4 for e1, e2 in errs) and ctx.status() == 0)
+        err = repr(errs)
+    except Exception as ex:   # report instead of leaving the peer waiting on a barrier
+        err = repr(ex)
+    q.put((rank, ok, err))
+    try:
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_batched_row_split_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_batched_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=240) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+    assert all(ok for _, ok, _ in results), results
