@@ -463,7 +463,7 @@ def kernel_extras(torch, F, ctx, peak, only=None, reps=3):
     gemv("q4_k_lm_head_151936x4096_b1", synth.Q4_K, 151936, 4096, 2)
     gemv("q5_k_lm_head_151936x4096_b1", synth.Q5_K, 151936, 4096, 2)
 
-    if only and "moe_layer_top8_of_128_t1" not in only:
+    if only and not ({"moe_layer_top8_of_128_t1", "moe_layer_top8_of_128_t32"} & set(only)):
         return out
     # MoE layer, one token: fp32 router 128 x 2048, top-8, gate/up Q4_K 768 x 2048, down Q5_K 2048 x 768 (6 distinct layers)
     H, M, E, K, NL = 2048, 768, 128, 8, 6
@@ -492,6 +492,26 @@ def kernel_extras(torch, F, ctx, peak, only=None, reps=3):
     nbytes = K * (2 * sg + sd) + E * H * 4
     out["moe_layer_top8_of_128_t1"] = {"us": round(t * 1e6, 2), "gbs": round(nbytes / t / 1e9, 1),
                                        "frac_of_measured_hbm": round(nbytes / t / 1e9 / peak, 3), "bytes": nbytes, "launches": 4}
+    # the same layers with a batch of 32 tokens (BASELINE configuration 5): algorithmic bytes = every distinct expert
+    # the batch selects, read once, plus the router
+    T = 32
+    xT = torch.randn(T, H, device=dev)
+    idxT = torch.zeros(T, 8, dtype=torch.int32, device=dev)
+    wT = torch.zeros(T, 8, device=dev)
+    actT = torch.empty(T, K, M, device=dev)
+    oT = torch.empty(T, H, device=dev)
+    lgT = torch.empty(T, E, device=dev)
+
+    def moe_t():
+        for buf, rw, layer, rref in layers:
+            ctx.moe_route(rref, xT.data_ptr(), T, H, K, idxT.data_ptr(), wT.data_ptr(), lgT.data_ptr(), st)
+            ctx.moe_ffn(layer, 0, xT.data_ptr(), T, H, idxT.data_ptr(), wT.data_ptr(), K, H, M, actT.data_ptr(), oT.data_ptr(), H, st)
+    t = timed(moe_t, NL)
+    distinct = int(torch.unique(idxT[:, :K]).numel())               # of the last layer run; the layers differ little
+    nbytes = distinct * (2 * sg + sd) + E * H * 4
+    out["moe_layer_top8_of_128_t32"] = {"us": round(t * 1e6, 2), "gbs": round(nbytes / t / 1e9, 1),
+                                        "frac_of_measured_hbm": round(nbytes / t / 1e9 / peak, 3), "bytes": nbytes,
+                                        "distinct_experts": distinct, "launches": 4}
     return out
 
 

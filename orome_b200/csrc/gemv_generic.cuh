@@ -91,23 +91,31 @@ gemv_f32_kernel(const float *__restrict__ W, uint32_t out_dim, uint32_t in_dim, 
     if (row >= out_dim + (W1 ? 1u : 0u)) return;
     const float4 *w4 = reinterpret_cast<const float4 *>(row < out_dim ? W + (size_t)row * in_dim : W1);
     const uint32_t n4 = in_dim / 4;
-    for (int b0 = 0; b0 < batch; b0 += 4) {
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
-        for (uint32_t c = lane; c < n4; c += 32) {
-            const float4 w = __ldg(w4 + c);
+    // grid.y cuts the batch into groups of four vectors; a warp keeps four row pieces in flight at a time
+    const int b0 = (int)blockIdx.y * 4;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (uint32_t c0 = lane; c0 < n4; c0 += 128) {
+        float4 w[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                if (b0 + i < batch) {
-                    const float4 xv = *(reinterpret_cast<const float4 *>(x + (size_t)(b0 + i) * ldx) + c);
-                    acc[i] = fmaf(w.x, xv.x, fmaf(w.y, xv.y, fmaf(w.z, xv.z, fmaf(w.w, xv.w, acc[i]))));
+        for (int u = 0; u < 4; ++u) w[u] = c0 + 32 * u < n4 ? __ldg(w4 + c0 + 32 * u) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (b0 + i < batch) {
+                const float4 *x4 = reinterpret_cast<const float4 *>(x + (size_t)(b0 + i) * ldx);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (c0 + 32 * u < n4) {
+                        const float4 xv = x4[c0 + 32 * u];
+                        acc[i] = fmaf(w[u].x, xv.x, fmaf(w[u].y, xv.y, fmaf(w[u].z, xv.z, fmaf(w[u].w, xv.w, acc[i]))));
+                    }
                 }
             }
         }
+    }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float s = warp_sum(acc[i]);
-            if (lane == 0 && b0 + i < batch) y[(size_t)(b0 + i) * ldy + row] = s;
-        }
+    for (int i = 0; i < 4; ++i) {
+        const float s = warp_sum(acc[i]);
+        if (lane == 0 && b0 + i < batch) y[(size_t)(b0 + i) * ldy + row] = s;
     }
 }
 

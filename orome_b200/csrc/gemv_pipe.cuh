@@ -84,6 +84,10 @@ struct PipeArgs {
     uint32_t x_stride;         // floats between the segments' input vectors
     const float *seg_weight;   // [nseg]
     uint32_t acc_base;         // offset of the fp32 accumulators of the CTA's rows
+    // Token batches of the MoE forms: blockIdx.y = token.  Token t reads x + t * tok_x_stride, selects its experts and
+    // weights at seg_expert / seg_weight + t * tok_sel_stride and writes every segment's output tok_y_stride floats
+    // behind token 0's.  All zero for single-token launches.
+    uint32_t tok_x_stride, tok_y_stride, tok_sel_stride;
     uint32_t xq_vec_bytes;     // bytes of one quantized input vector in shared memory
     // Multi-GPU (row-split) forms.  A gathered vector lives in every rank's gather arena as 8-byte slots
     // {value, tag}: slot of the float at arena address A = ll_origin + 2 * (A - arena_base).  Publishing: every y
@@ -701,7 +705,7 @@ constexpr uint32_t PIPE_NO_EXPERT = 0xFFFFFFFFu;
 template <bool EXT>
 __device__ __forceinline__ bool seg_skipped(const PipeArgs &a, int s)
 {
-    if constexpr (EXT) return a.seg_expert && a.seg_expert[s] == PIPE_NO_EXPERT;
+    if constexpr (EXT) return a.seg_expert && a.seg_expert[blockIdx.y * a.tok_sel_stride + s] == PIPE_NO_EXPERT;
     else return false;
 }
 
@@ -749,14 +753,14 @@ template <bool EXT>
 __device__ __forceinline__ const uint8_t *seg_w(const PipeArgs &a, int s)
 {
     const uint8_t *p = a.seg[s].w;
-    if constexpr (EXT) { if (a.seg_expert) p += (uint64_t)a.seg_expert[s] * a.w_stride; }
+    if constexpr (EXT) { if (a.seg_expert) p += (uint64_t)a.seg_expert[blockIdx.y * a.tok_sel_stride + s] * a.w_stride; }
     return p;
 }
 template <bool EXT>
 __device__ __forceinline__ const uint8_t *seg_w2(const PipeArgs &a, int s)
 {
     const uint8_t *p = a.seg[s].w2;
-    if constexpr (EXT) { if (a.seg_expert) p += (uint64_t)a.seg_expert[s] * a.w2_stride; }
+    if constexpr (EXT) { if (a.seg_expert) p += (uint64_t)a.seg_expert[blockIdx.y * a.tok_sel_stride + s] * a.w2_stride; }
     return p;
 }
 
@@ -843,7 +847,7 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
             stamp(a.trace, 1);
             // All of this CTA's rows are requested.  Pull the head of the next launch's weights into L2 so that HBM
             // keeps streaming while this grid drains and the next one starts.
-            if (a.pf_ptr && !s_abort) {
+            if (a.pf_ptr && !s_abort && blockIdx.y == 0) {
                 const uint64_t per = (a.pf_bytes / gridDim.x) & ~(uint64_t)15;
                 const uint8_t *p = a.pf_ptr + (uint64_t)blockIdx.x * per;
                 for (uint64_t off = 0; off < per; off += 32768) {
@@ -883,7 +887,7 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
             for (uint32_t i = lane; i < (uint32_t)PIPE_SUM_SQ_PARTS; i += 32) t += __ldcg(a.norm_parts + i);
             rms = rsqrtf(warp_sum(t) / (float)a.in_dim + a.norm_eps);
         }
-        if (!quantize_x_to_smem<NP, SlotT::GROUP, SlotT::SUMS>(a.x, a.in_dim, COMBINE ? (uint32_t)a.nseg : 1u, a.x_stride, xq, a.xq_vec_bytes, tid, C,
+        if (!quantize_x_to_smem<NP, SlotT::GROUP, SlotT::SUMS>(a.x + (EXT ? (size_t)blockIdx.y * a.tok_x_stride : 0), a.in_dim, COMBINE ? (uint32_t)a.nseg : 1u, a.x_stride, xq, a.xq_vec_bytes, tid, C,
                                                                slots, want, a.wait_cycles, a.status,
                                                                COMBINE ? 0u : (uint32_t)((uint64_t)blockIdx.x * (a.in_dim / 4) / gridDim.x) & ~31u,
                                                                norm_w, rms)) {
@@ -916,7 +920,8 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
     // and the row groups split the SEGMENTS among them (group g takes segments g, g + rows_par, ...; all rows of a
     // segment's tile), each with its own slots: the eight experts of a token advance side by side.
     const uint32_t SL = COMBINE ? GW * a.rows_par : GW;                 // partial sums per row
-    const bool comb_acc = COMBINE && (wk.hi - wk.lo) * SL <= 2 * PLANE;
+    // (single-token launches only: a token batch gives every CTA hundreds of rows per segment, which all row groups share)
+    const bool comb_acc = COMBINE && gridDim.y == 1 && (wk.hi - wk.lo) * SL <= 2 * PLANE;
     if (comb_acc) {
         for (uint32_t r = tid; r < (wk.hi - wk.lo) * SL; r += C) pbuf[r] = 0.0f;
         named_bar_sync(PIPE_BAR_CONSUMERS, (int)C);
@@ -927,7 +932,7 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
     auto flush = [&]() {
         named_bar_sync(PIPE_BAR_CONSUMERS, (int)C);
         const float *src = pbuf + (size_t)which * PLANE * (SWIGLU ? 2 : 1);
-        float *y = a.seg[buf_seg].y + buf_row0;
+        float *y = a.seg[buf_seg].y + buf_row0 + (EXT ? (size_t)blockIdx.y * a.tok_y_stride : 0);
         for (uint32_t r = tid; r < buf_n; r += C) {
             float g = 0.0f, u = 0.0f;
             const uint32_t nsl = comb_acc ? SL : GW;
@@ -935,7 +940,7 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
                 g += src[r * nsl + w];
                 if constexpr (SWIGLU) u += src[PLANE + r * GW + w];
             }
-            if constexpr (COMBINE) accbuf[buf_row0 - wk.lo + r] += (comb_acc ? 1.0f : a.seg_weight[buf_seg]) * g;   // one owner per row and flush
+            if constexpr (COMBINE) accbuf[buf_row0 - wk.lo + r] += (comb_acc ? 1.0f : a.seg_weight[blockIdx.y * a.tok_sel_stride + buf_seg]) * g;   // one owner per row and flush
             else {
                 float val = SWIGLU ? silu_mul(g, u) : g;
                 if constexpr (EXT && MODE == 0) {
@@ -1003,7 +1008,7 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
         if constexpr (SWIGLU) base2 = stages_s + s * a.stage_stride + a.half_stride + unit_off + delta2;
         float *dst = comb_acc ? pbuf + (size_t)(t.row0 - wk.lo) * SL + group * GW + wig
                               : pbuf + (size_t)which * PLANE * (SWIGLU ? 2 : 1) + (size_t)buf_n * GW + wig;
-        const float segw = comb_acc ? a.seg_weight[t.seg] : 0.0f;
+        const float segw = comb_acc ? a.seg_weight[blockIdx.y * a.tok_sel_stride + t.seg] : 0.0f;
         const uint32_t rstride = comb_acc ? SL : GW;
         // Plain Q8_0 products keep two rows of a group in flight when a tile holds more than one row per group (this
         // row and the one rows_par further on): two independent dot products and reductions per warp hide each
@@ -1047,7 +1052,7 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
     if constexpr (COMBINE) {
         named_bar_sync(PIPE_BAR_CONSUMERS, (int)C);
         for (uint32_t r = tid; r < wk.hi - wk.lo; r += C) {
-            float *dst = a.seg[0].y + wk.lo + r;
+            float *dst = a.seg[0].y + wk.lo + r + (EXT ? (size_t)blockIdx.y * a.tok_y_stride : 0);
             *dst = accbuf[r];
             if constexpr (EXT) {
                 if (a.npeers > 0) {

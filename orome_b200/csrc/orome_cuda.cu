@@ -289,7 +289,7 @@ static int launch_router(orome_cuda_ctx *c, const uint8_t *data, uint32_t ne, ui
     int rc;
     const uint32_t rows = ne + (shared_gate ? 1u : 0u);
     if (in_dim % 4 == 0 && !(reinterpret_cast<uintptr_t>(x) & 15) && (n_tokens == 1 || ldx % 4 == 0))
-        rc = launch_pdl(c, "gemv_f32", gemv_f32_kernel, dim3((rows + 3) / 4), dim3(128), st, reinterpret_cast<const float *>(data), ne, in_dim,
+        rc = launch_pdl(c, "gemv_f32", gemv_f32_kernel, dim3((rows + 3) / 4, (unsigned)(n_tokens + 3) / 4), dim3(128), st, reinterpret_cast<const float *>(data), ne, in_dim,
                         x, n_tokens, ldx, logits, (int)rows, reinterpret_cast<const float *>(shared_gate));
     else {
         rc = launch_generic(c, FMT_F32, data, ne, in_dim, 0, x, n_tokens, ldx, logits, (int)rows, st);
@@ -339,6 +339,7 @@ struct PipePlan {
     int grid;
     int minb;       // CTAs per SM the kernel instance is compiled for
     size_t smem;
+    int tokens;     // token batch of the MoE forms (grid.y); 0 or 1: a single-token launch
 };
 
 uint32_t orome_pipe_group_threads(int fmt, uint32_t in_dim)
@@ -408,6 +409,8 @@ static int plan_pipe(orome_cuda_ctx *c, int fmt, uint32_t in_dim, uint32_t total
     p.threads = (int)consumers + 32;
 
     p.grid = (int)std::min<uint64_t>((uint64_t)c->sm_count * std::min(p.minb, c->grid_per_sm), (total_rows + a.rows_par - 1) / a.rows_par);
+    // a token batch spreads about two waves of CTAs over the tokens (grid.y), each token's rows over grid.x CTAs
+    if (p.tokens > 1) p.grid = std::min(p.grid, (2 * c->sm_count + p.tokens - 1) / p.tokens);
     p.grid = std::max(p.grid, 1);
     const uint32_t share = (total_rows + p.grid - 1) / p.grid;            // rows of the busiest CTA
 
@@ -487,7 +490,7 @@ static int launch_pipe_ext(orome_cuda_ctx *c, const PipePlan &p, cudaStream_t st
         configured[c->device] = (size_t)max_dyn;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(p.grid);
+    cfg.gridDim = dim3(p.grid, std::max(p.tokens, 1));
     cfg.blockDim = dim3(p.threads);
     cfg.dynamicSmemBytes = p.smem;
     cfg.stream = st;
@@ -504,7 +507,7 @@ static int launch_pipe_ext(orome_cuda_ctx *c, const PipePlan &p, cudaStream_t st
 template <int FMT, int NP, int MODE, int MINB>
 static int launch_pipe_inst(orome_cuda_ctx *c, const PipePlan &p, cudaStream_t st)
 {
-    const bool ext = p.args.seg_expert || p.args.npeers > 0 || p.args.x_ll || p.args.norm_w || p.args.res_in;
+    const bool ext = p.args.seg_expert || p.args.npeers > 0 || p.args.x_ll || p.args.norm_w || p.args.res_in || p.tokens > 1;
     if constexpr (MODE == 2) return launch_pipe_ext<FMT, NP, MODE, MINB, true>(c, p, st);
     else return ext ? launch_pipe_ext<FMT, NP, MODE, MINB, true>(c, p, st) : launch_pipe_ext<FMT, NP, MODE, MINB, false>(c, p, st);
 }
@@ -1384,39 +1387,47 @@ extern "C" int orome_cuda_moe_ffn(orome_cuda_ctx *c, const OromeExpertLayerRef *
     const size_t grb = row_bytes_of(gfmt, hidden), drb = row_bytes_of(dfmt, inter);
     if (!c->force_generic && orome_pipe_supported(gfmt, hidden) && orome_pipe_supported(dfmt, inter) && K <= (uint32_t)PIPE_MAX_SEG &&
         !((reinterpret_cast<uintptr_t>(x_dev) | reinterpret_cast<uintptr_t>(act_dev)) & 15) && (ldx % 4 == 0 || n_tokens == 1) && inter % 4 == 0) {
-        // Per token: one fused gate/up launch over the K selected experts (device-side expert indices), then one
-        // down launch that gives every expert its own input vector and adds the K results with the routing weights.
-        for (int t = 0; t < n_tokens; ++t) {
-            PipePlan p;
-            memset(&p, 0, sizeof p);
-            for (uint32_t k = 0; k < K; ++k)
-                p.args.seg[k] = PipeSeg{gate, up, act_dev + ((size_t)t * K + k) * inter, inter, k * inter};
-            p.args.nseg = (int)K;
-            p.args.x = x_dev + (size_t)t * ldx;
-            p.args.layout = (int)variant;
-            int rc = plan_pipe(c, gfmt, hidden, K * inter, 1, p);
-            if (rc) return rc;
-            p.args.seg_expert = idx_dev + (size_t)t * 8;
-            p.args.w_stride = L->gate.expert_stride;
-            p.args.w2_stride = L->up.expert_stride;
-            rc = launch_pipe(c, gfmt, p, 1, st);
-            if (rc) return rc;
+        // One fused gate/up launch over the K selected experts of every token (device-side expert indices; grid.y =
+        // token), then one down launch that gives every (token, expert) its own input vector and adds a token's K
+        // results with its routing weights.
+        const size_t out_ld = n_tokens == 1 ? hidden : (size_t)ldo;
+        if ((size_t)n_tokens * K * inter > 0xFFFFFFFFull || out_ld * (size_t)n_tokens > 0xFFFFFFFFull)
+            return fail(OROME_EINVAL, "moe_ffn: token batch too large");
+        PipePlan p;
+        memset(&p, 0, sizeof p);
+        for (uint32_t k = 0; k < K; ++k)
+            p.args.seg[k] = PipeSeg{gate, up, act_dev + (size_t)k * inter, inter, k * inter};
+        p.args.nseg = (int)K;
+        p.args.x = x_dev;
+        p.args.layout = (int)variant;
+        p.tokens = n_tokens;
+        int rc = plan_pipe(c, gfmt, hidden, K * inter, 1, p);
+        if (rc) return rc;
+        p.args.seg_expert = idx_dev;
+        p.args.w_stride = L->gate.expert_stride;
+        p.args.w2_stride = L->up.expert_stride;
+        p.args.tok_x_stride = n_tokens == 1 ? 0u : (uint32_t)ldx;
+        p.args.tok_y_stride = K * inter;
+        p.args.tok_sel_stride = 8;
+        rc = launch_pipe(c, gfmt, p, 1, st);
+        if (rc) return rc;
 
-            memset(&p, 0, sizeof p);
-            for (uint32_t k = 0; k < K; ++k) p.args.seg[k] = PipeSeg{down, nullptr, out_dev + (size_t)t * (n_tokens == 1 ? hidden : ldo), hidden, 0};
-            p.args.nseg = (int)K;
-            p.args.x = act_dev + (size_t)t * K * inter;
-            p.args.layout = (int)variant;
-            rc = plan_pipe(c, dfmt, inter, hidden, 2, p);
-            if (rc) return rc;
-            p.args.seg_expert = idx_dev + (size_t)t * 8;
-            p.args.w_stride = L->down.expert_stride;
-            p.args.x_stride = inter;
-            p.args.seg_weight = w_dev + (size_t)t * 8;
-            rc = launch_pipe(c, dfmt, p, 2, st);
-            if (rc) return rc;
-        }
-        return OROME_OK;
+        memset(&p, 0, sizeof p);
+        for (uint32_t k = 0; k < K; ++k) p.args.seg[k] = PipeSeg{down, nullptr, out_dev, hidden, 0};
+        p.args.nseg = (int)K;
+        p.args.x = act_dev;
+        p.args.layout = (int)variant;
+        p.tokens = n_tokens;
+        rc = plan_pipe(c, dfmt, inter, hidden, 2, p);
+        if (rc) return rc;
+        p.args.seg_expert = idx_dev;
+        p.args.w_stride = L->down.expert_stride;
+        p.args.x_stride = inter;
+        p.args.seg_weight = w_dev;
+        p.args.tok_x_stride = K * inter;
+        p.args.tok_y_stride = (uint32_t)out_ld;
+        p.args.tok_sel_stride = 8;
+        return launch_pipe(c, dfmt, p, 2, st);
     }
     dim3 g1((inter + 7) / 8, (unsigned)n_tokens * K), g2((hidden + 7) / 8, (unsigned)n_tokens);
 #define GU(F) moe_gate_up_kernel<F><<<g1, 256, 0, st>>>(gate, L->gate.expert_stride, up, L->up.expert_stride, grb, inter, hidden, (int)variant, x_dev, ldx, idx_dev, K, act_dev)

@@ -61,3 +61,17 @@ def test_no_device_is_an_error_not_a_fallback():
         pytest.skip("a GPU is present")
     with pytest.raises(F.OromeError):
         F.Context(0)
+
+
+def test_integration_stub_compiles_as_c(tmp_path):
+    """The reference-side stub shown in INTEGRATION.md is real C against the shipped headers."""
+    import subprocess
+    text = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+    block = re.search(r"```c\n(/\* format_cuda\.c.*?)```", text, flags=re.S).group(1)
+    src = tmp_path / "format_cuda.c"
+    src.write_text(block)
+    subprocess.check_call(["gcc", "-std=c11", "-Wall", "-Werror", "-fsyntax-only", "-I", os.path.join(ROOT, "include"), str(src)])
+    # and the headers alone are C-clean
+    hdr = tmp_path / "hdr.c"
+    hdr.write_text('#include "orome_cuda.h"\n#include "orome_gguf.h"\nint main(void) { return (int)sizeof(OromeLayerTensorCache) == 0; }\n')
+    subprocess.check_call(["gcc", "-std=c99", "-pedantic", "-Wall", "-Werror", "-fsyntax-only", "-I", os.path.join(ROOT, "include"), str(hdr)])

@@ -12,7 +12,7 @@ from orome_b200 import synth
 pytestmark = pytest.mark.gpu
 
 REL_L2_TOL = 1e-4          # the tolerance the path states for fp32 accumulation
-TC_REL_L2_TOL = 1e-3       # tensor-core batched form: weights and x rounded to fp16 (the reference stages x as fp16 too)
+TC_REL_L2_TOL = 5e-4       # tensor-core batched form: weights and x rounded to fp16 (the reference stages x as fp16 too); measured 2-3e-4
 GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "decode_golden.npz"))
 FMTS = {"Q8_0": synth.Q8_0, "Q4_K": synth.Q4_K, "Q5_K": synth.Q5_K, "Q6_K": synth.Q6_K}
 QUANT = list(FMTS.values())

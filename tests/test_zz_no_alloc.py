@@ -54,3 +54,35 @@ def test_static_routing_matches_regular_entry_point_twice():
         assert ctx.status() == 0
     finally:
         ctx.close()
+
+
+def test_static_routing_allocates_no_device_memory():
+    """Free device memory (cudaMemGetInfo) is the same before and after a run of static routing calls: every buffer
+    the calls touch was there beforehand, the library adds none.  The regular entry point without a logits buffer
+    is the contrast: its first call grows the context's scratch."""
+    import torch
+    from orome_b200 import format as F
+
+    ctx = F.Context(0)
+    try:
+        n_experts, hidden, K, T = 128, 2048, 8, 32
+        wt = torch.from_numpy(synth.host_router(n_experts, hidden, seed=43).view(np.uint8).reshape(-1).copy()).cuda()
+        router = F.tensor_ref(wt.data_ptr(), 0, synth.F32, n_experts, hidden)
+        x = torch.from_numpy(np.atleast_2d(synth.host_x(hidden, T, seed=60))).cuda()
+        idx = torch.zeros((T, 8), device="cuda", dtype=torch.int32)
+        w = torch.zeros((T, 8), device="cuda")
+        stream = torch.cuda.current_stream().cuda_stream
+        ctx.moe_route_static(router, x.data_ptr(), T, hidden, K, idx.data_ptr(), w.data_ptr(), stream)    # loads the kernels
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info(0)[0]
+        for n in (T, 5, 1, T):
+            ctx.moe_route_static(router, x.data_ptr(), n, hidden, K, idx.data_ptr(), w.data_ptr(), stream)
+        torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info(0)[0] == free_before
+        assert ctx.status() == 0
+        # contrast: the regular entry point, given no logits buffer, allocates its scratch on first use
+        ctx.moe_route(router, x.data_ptr(), T, hidden, K, idx.data_ptr(), w.data_ptr(), 0, stream)
+        torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info(0)[0] <= free_before
+    finally:
+        ctx.close()
