@@ -426,6 +426,7 @@ int  orome_cuda_matvec_host(orome_cuda_ctx *ctx, const OromeTensorRef *ref,
 #define OROME_OPT_TC_MIN_BATCH    8   /* batches from this size on use the tensor-core kernel (default 4); smaller ones run one decode launch per vector */
 #define OROME_OPT_KQUANT_MMA      9   /* 1 (default): Q4_K / Q5_K batch-1 products run on the mma.sync kernel; 0: on the dp4a kernel */
 #define OROME_OPT_CHAIN_INFLIGHT 11   /* stages a chain's weight stream keeps outstanding at most (0, default: the whole ring); read at chain_end */
+#define OROME_OPT_TC_SLABS       12   /* batched tensor-core form: 0 (default) keeps the dequantized weights in tensor memory, 1 stages them in shared memory */
 #define OROME_OPT_WAIT_US        10   /* bound of one device-side wait (peer data, chain inputs, chain stages) in microseconds; 0 (default): about a second */
 int  orome_cuda_set_option(orome_cuda_ctx *ctx, int key, int value);
 int  orome_cuda_get_option(orome_cuda_ctx *ctx, int key, int *value);

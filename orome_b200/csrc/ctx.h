@@ -64,6 +64,7 @@ struct orome_cuda_ctx {
     float *tc_xp = nullptr, *tc_part = nullptr;
     size_t tc_xp_cap = 0, tc_part_cap = 0;
     int tc_min_batch = 4;    // batches from this size on use the tensor-core kernel (smaller ones: one decode launch per vector)
+    int tc_slabs = 0;        // batched form: 1 = dequantized weights staged in shared memory (the earlier form), 0 = in tensor memory
     int kquant_mma = 1;      // Q4_K / Q5_K batch-1 products on the mma.sync kernel (0: dp4a kernel)
     int chain_inflight = 0;  // stages a chain's producer keeps outstanding at most (0: the whole ring)
     int wait_us = 0;         // bound of every device-side wait in microseconds of SM clock (0: about one second)

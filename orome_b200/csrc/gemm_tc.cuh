@@ -30,15 +30,25 @@ constexpr int TC_M = 128;            // rows per CTA tile
 constexpr int TC_KC = 256;           // weights per packed chunk (8 Q8_0 blocks / one K-quant superblock)
 constexpr int TC_SLAB_K = 64;        // k per A slab = one 128-byte swizzle row of fp16
 constexpr int TC_SLABS = 4;          // fp16 slabs per 256-weight chunk
-constexpr int TC_MAX_RING = TC_SLABS; // slab buffers = one chunk's worth (six made no difference and do not fit next to Q8_0 stages)
-constexpr int TC_PK_STAGES = 2;      // packed-weight stages
-constexpr int TC_PK_MAX_STAGES = TC_PK_STAGES;
+#ifndef OROME_TC_RING
+#define OROME_TC_RING 4
+#endif
+#ifndef OROME_TC_PK
+#define OROME_TC_PK 2
+#endif
+#ifndef OROME_TC_BS
+#define OROME_TC_BS 2
+#endif
+constexpr int TC_MAX_RING = OROME_TC_RING;   // fp16 slab buffers
+constexpr int TC_PK_MAX_STAGES = 8;
+// packed-weight stages in flight: what hides the latency of the weight stream (a Q8_0 stage is 34 KB, a Q4_K one 18 KB)
+constexpr int tc_pk_stages(int fmt) { return fmt == FMT_Q8_0 ? (OROME_TC_PK < 3 ? OROME_TC_PK : 3) : OROME_TC_PK; }
 constexpr int TC_MAX_N = 64;         // input vectors per launch (padded to a multiple of 16)
-constexpr int TC_B_STAGES = 2;       // X tile stages (one chunk each)
-constexpr int TC_B_MAX_STAGES = TC_B_STAGES;
+constexpr int TC_B_STAGES = OROME_TC_BS;     // X tile stages (one chunk each)
+constexpr int TC_B_MAX_STAGES = 4;
 constexpr int TC_DEQ_WARPS = 16;     // two groups of 8 warps take alternate slabs
 constexpr int TC_SLAB_WARPS = 8;     // warps that fill one slab
-constexpr int TC_THREADS = (TC_DEQ_WARPS + 2) * 32;
+constexpr int TC_THREADS = (TC_DEQ_WARPS + 3) * 32;     // + weight producer, MMA issuer, X producer
 
 // Row-split form on several GPUs (the batched counterpart of the publish fields of PipeArgs): every Y value also
 // goes, as a {value, tag} slot, into this rank's and every peer's copy of the gather arena.
@@ -63,6 +73,14 @@ __device__ __forceinline__ void tc_publish_done(const TcPub &g, unsigned int tag
         *reinterpret_cast<volatile unsigned int *>(g.pub_gen) = tag;
     }
 }
+
+// Diagnostics builds only: SM-cycle stamps of CTA 0's pipeline (kind, index), read back by a test-bench helper.
+#ifdef OROME_DIAGNOSTICS
+__device__ long long g_tc_trace[8][80];
+#define TC_STAMP(kind, idx) do { if (blockIdx.x == 0 && (idx) < 80) g_tc_trace[kind][idx] = clock64(); } while (0)
+#else
+#define TC_STAMP(kind, idx) do { } while (0)
+#endif
 
 struct TcArgs {
     alignas(64) CUtensorMap wmap;   // the tensor as a 2-D array of 32-bit words [rows][row_bytes / 4], box = 128 rows x one chunk
@@ -208,7 +226,7 @@ gemm_tc_kernel(const __grid_constant__ TcArgs a)
     const uint32_t pk_stage_bytes = (TC_M * a.chunk_bytes + 127u) & ~127u;
     constexpr uint32_t BS = TC_B_STAGES;
     uint8_t *pk = b_tiles + BS * b_tile_bytes;
-    constexpr uint32_t PKS = TC_PK_STAGES;
+    constexpr uint32_t PKS = tc_pk_stages(FMT);
     uint64_t *bars = reinterpret_cast<uint64_t *>(pk + PKS * pk_stage_bytes);
     uint64_t *pk_full = bars, *pk_empty = bars + TC_PK_MAX_STAGES, *b_full = pk_empty + TC_PK_MAX_STAGES, *b_empty = b_full + TC_B_MAX_STAGES;
     uint64_t *a_full = b_empty + TC_B_MAX_STAGES, *a_empty = a_full + TC_MAX_RING, *acc_done = a_empty + TC_MAX_RING;
@@ -221,6 +239,10 @@ gemm_tc_kernel(const __grid_constant__ TcArgs a)
     const uint32_t chunk0 = sp * a.chunks / a.split, nchunks = (sp + 1) * a.chunks / a.split - chunk0;
     uint32_t ncols = 32;
     while (ncols < a.npad) ncols <<= 1;
+    // Every CTA walks its chunks of K from a different starting point (and wraps): at any one time the CTAs then read
+    // different tiles of the packed X, instead of all of them fetching the same 32 KB from the same few L2 slices at
+    // the same moment (measured: 3700 cycles for one X tile in lockstep).  The sum over K does not care about order.
+    const uint32_t rot = (tile * 5u + sp * 3u) % nchunks;
 
     if (tid == 0) {
         s_abort = 0;
@@ -246,7 +268,7 @@ gemm_tc_kernel(const __grid_constant__ TcArgs a)
     };
 
     if (warp == TC_DEQ_WARPS) {
-        // ---- producer: packed weights (independent of the previous kernel) and X tiles (after it) ----
+        // ---- weight producer: packed stages, independent of the previous kernel ----
         if (lane == 0) {
             const uint32_t words = a.chunk_bytes / 4;
             for (uint32_t c = 0; c < nchunks && !s_abort; ++c) {
@@ -255,14 +277,23 @@ gemm_tc_kernel(const __grid_constant__ TcArgs a)
                 mbar_expect_tx(smem_u32(pk_full + s), TC_M * a.chunk_bytes);   // the box is always full: out-of-range rows arrive as zeros
                 // x coordinate in 32-bit words: (chunk index) * chunk_bytes / 4, a multiple of 16 bytes for every format
                 asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                             ::"r"(smem_u32(pk + (size_t)s * pk_stage_bytes)), "l"(&a.wmap), "r"((chunk0 + c) * words), "r"(row0),
+                             ::"r"(smem_u32(pk + (size_t)s * pk_stage_bytes)), "l"(&a.wmap), "r"((chunk0 + (c + rot < nchunks ? c + rot : c + rot - nchunks)) * words), "r"(row0),
                                "r"(smem_u32(pk_full + s)) : "memory");
-                if (c == 0) pdl_wait();   // the packed X is the previous kernel's output
+                TC_STAMP(0, c);
+            }
+        }
+    } else if (warp == TC_DEQ_WARPS + 2) {
+        // ---- X producer: the matching pre-packed fp16 tiles (the previous kernel's output) ----
+        if (lane == 0) {
+            pdl_wait();
+            for (uint32_t c = 0; c < nchunks && !s_abort; ++c) {
                 const uint32_t sb = c % BS, kb = c / BS;
                 if (kb > 0) { wait(b_empty + sb, (kb - 1) & 1u); asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
                 mbar_expect_tx(smem_u32(b_full + sb), b_tile_bytes);
                 bulk_g2s(smem_u32(b_tiles + (size_t)sb * b_tile_bytes),
-                         reinterpret_cast<const uint8_t *>(a.xp) + (size_t)(chunk0 + c) * b_tile_bytes, b_tile_bytes, smem_u32(b_full + sb));
+                         reinterpret_cast<const uint8_t *>(a.xp) + (size_t)(chunk0 + (c + rot < nchunks ? c + rot : c + rot - nchunks)) * b_tile_bytes,
+                         b_tile_bytes, smem_u32(b_full + sb));
+                TC_STAMP(6, c);
             }
         }
     } else if (warp == TC_DEQ_WARPS + 1) {
@@ -273,15 +304,18 @@ gemm_tc_kernel(const __grid_constant__ TcArgs a)
             for (uint32_t c = 0; c < nchunks && !s_abort; ++c) {
                 const uint32_t sb = c % BS;
                 wait(b_full + sb, (c / BS) & 1u);
+                TC_STAMP(7, c);
                 for (uint32_t j = 0; j < TC_SLABS; ++j, ++slab_i) {
                     const uint32_t sa = slab_i % RING;
                     wait(a_full + sa, (slab_i / RING) & 1u);
+                    TC_STAMP(4, slab_i);
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(a_slabs + sa * 16384), b_addr = smem_u32(b_tiles + (size_t)sb * b_tile_bytes + (size_t)j * a.npad * 128);
 #pragma unroll
                     for (uint32_t k16 = 0; k16 < 4; ++k16)
                         tc_mma_f16(tmem_acc, tc_desc_sw128(a_addr + k16 * 32), tc_desc_sw128(b_addr + k16 * 32), idesc, (slab_i | k16) ? 1u : 0u);
                     tc_commit(smem_u32(a_empty + sa));     // slab free once these MMAs have read it
+                    TC_STAMP(5, slab_i);
                 }
                 tc_commit(smem_u32(b_empty + sb));
             }
@@ -296,11 +330,13 @@ gemm_tc_kernel(const __grid_constant__ TcArgs a)
         for (uint32_t c = 0; c < nchunks; ++c) {
             const uint32_t s = c % PKS;
             wait(pk_full + s, (c / PKS) & 1u);
+            if (tid == 0) TC_STAMP(1, c);
             const uint8_t *stage = pk + (size_t)s * pk_stage_bytes;
             for (uint32_t j = 0; j < TC_SLABS; ++j, ++slab_i) {
                 if ((slab_i & 1u) != grp) continue;
                 const uint32_t sa = slab_i % RING, ka = slab_i / RING;
                 if (ka > 0) wait(a_empty + sa, (ka - 1) & 1u);
+                if ((tid & 255u) == 0) TC_STAMP(2, slab_i);
                 tc_fence_after();
                 uint8_t *slab = a_slabs + sa * 16384;
                 // a slab is 128 rows x two 32-weight groups: one (row, group) per thread, four 16-byte pieces each
@@ -314,6 +350,7 @@ gemm_tc_kernel(const __grid_constant__ TcArgs a)
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> visible to the tensor core
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(a_full + sa));
+                if ((tid & 255u) == 0) TC_STAMP(3, slab_i);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(pk_empty + s));
@@ -351,6 +388,204 @@ gemm_tc_kernel(const __grid_constant__ TcArgs a)
     if (warp == 0) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(ncols) : "memory");
+    }
+    if (threadIdx.x == 0 && a.split == 1 && a.pub.npeers > 0)
+        tc_publish_done(a.pub, *reinterpret_cast<const volatile unsigned int *>(a.pub.pub_gen) + 1u);
+}
+
+
+// ---- the same product with the dequantized weights in TENSOR MEMORY --------------------------------------------------
+// In the form above a 256-weight chunk of a 128-row tile costs 64 KB of shared-memory stores (the fp16 slabs) and
+// 64 KB of operand reads by the tensor core, next to 18 KB of packed weights: measured, the kernel moves about 230 KB
+// through shared memory per chunk and its MMAs take ~100 cycles each instead of ~34.  Here the dequant warps write the
+// fp16 weights straight into tensor memory (tcgen05.st: lane = row, two weights per 32-bit column) and the MMA takes
+// its A operand from there; shared memory carries only the packed weights and the X tiles.
+//   tensor memory (512 columns): A stages of 128 columns (one chunk: 128 rows x 256 fp16) at 0, 128, 256; the fp32
+//   accumulator (npad <= 64 columns) at 384.
+//   dequant warp w: rows 32 * (w % 4) + lane (the lanes of tensor memory a warp may touch), weights
+//   64 * (w / 4) .. + 63 of the chunk; every warp works on every chunk.
+constexpr int TCA_A_STAGES = 3;
+constexpr uint32_t TCA_ACC_COL = 384;
+constexpr int TCA_B_STAGES = 3;
+// A packed stage holds KB consecutive chunks of the 128 rows (one tensor copy).  The copy engine works row by row: a
+// 128-row box of 144-byte rows took it about as long as a box of 288-byte rows (measured: ~2000 cycles per box, which
+// was the kernel's period per chunk), so K-quant tensors load two chunks per box where the K split allows it.
+constexpr int tca_pk_stages(int fmt, int kb) { return fmt == FMT_Q8_0 ? 3 : fmt == FMT_Q4_K ? (kb == 2 ? 3 : 5) : (kb == 2 ? 2 : 4); }
+
+__device__ __forceinline__ void tc_mma_f16_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n}\n"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint4 (&v)[4])
+{
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                 ::"r"(taddr), "r"(v[0].x), "r"(v[0].y), "r"(v[0].z), "r"(v[0].w), "r"(v[1].x), "r"(v[1].y), "r"(v[1].z), "r"(v[1].w),
+                   "r"(v[2].x), "r"(v[2].y), "r"(v[2].z), "r"(v[2].w), "r"(v[3].x), "r"(v[3].y), "r"(v[3].z), "r"(v[3].w) : "memory");
+}
+
+template <int FMT, int KB>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tca_kernel(const __grid_constant__ TcArgs a)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    // layout: [X tiles BS x npad*512][packed stages PKS x 128*chunk_bytes][barriers]
+    constexpr uint32_t AS = TCA_A_STAGES, BS = TCA_B_STAGES, PKS = tca_pk_stages(FMT, KB);
+    const uint32_t b_tile_bytes = a.npad * 128u * TC_SLABS;
+    uint8_t *b_tiles = smem;
+    const uint32_t pk_row_bytes = KB * a.chunk_bytes, pk_stage_bytes = (TC_M * pk_row_bytes + 127u) & ~127u;
+    uint8_t *pk = b_tiles + BS * b_tile_bytes;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(pk + PKS * pk_stage_bytes);
+    uint64_t *pk_full = bars, *pk_empty = pk_full + PKS, *b_full = pk_empty + PKS, *b_empty = b_full + BS;
+    uint64_t *a_full = b_empty + BS, *a_empty = a_full + AS, *acc_done = a_empty + AS;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_done + 1);
+    __shared__ volatile int s_abort;
+
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    const uint32_t tile = blockIdx.x / a.split, sp = blockIdx.x % a.split;
+    const uint32_t row0 = tile * TC_M, nrows = min((uint32_t)TC_M, a.rows - row0);
+    const uint32_t chunk0 = sp * a.chunks / a.split, nchunks = (sp + 1) * a.chunks / a.split - chunk0;
+    // CTAs start their walk over K at different chunks (a multiple of KB; the host gives KB = 2 only parts of even length)
+    const uint32_t rot = ((tile * 5u + sp * 3u) % nchunks) / KB * KB;
+
+    if (tid == 0) {
+        s_abort = 0;
+        for (uint32_t s = 0; s < PKS; ++s) { mbar_init(smem_u32(pk_full + s), 1); mbar_init(smem_u32(pk_empty + s), TC_DEQ_WARPS); }
+        for (uint32_t s = 0; s < BS; ++s) { mbar_init(smem_u32(b_full + s), 1); mbar_init(smem_u32(b_empty + s), 1); }
+        for (uint32_t s = 0; s < AS; ++s) { mbar_init(smem_u32(a_full + s), TC_DEQ_WARPS); mbar_init(smem_u32(a_empty + s), 1); }
+        mbar_init(smem_u32(acc_done), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 0) {   // all 512 columns: one CTA per SM (its shared memory sees to that)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
+    const uint32_t tmem_acc = tmem_base + TCA_ACC_COL;
+    pdl_launch_dependents();
+
+    auto wait = [&](uint64_t *bar, uint32_t parity) {
+        if (!s_abort && !mbar_wait_bounded(smem_u32(bar), parity)) { s_abort = 1; atomicExch(a.status, 4); }
+    };
+    auto chunk_of = [&](uint32_t c) { return chunk0 + (c + rot < nchunks ? c + rot : c + rot - nchunks); };
+
+    if (warp == TC_DEQ_WARPS) {
+        // ---- weight producer: packed stages, independent of the previous kernel ----
+        if (lane == 0) {
+            const uint32_t words = a.chunk_bytes / 4;
+            for (uint32_t c = 0, i = 0; c < nchunks && !s_abort; c += KB, ++i) {
+                const uint32_t s = i % PKS, k = i / PKS;
+                if (k > 0) { wait(pk_empty + s, (k - 1) & 1u); asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+                mbar_expect_tx(smem_u32(pk_full + s), TC_M * pk_row_bytes);    // the box is always full: out-of-range rows arrive as zeros
+                asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                             ::"r"(smem_u32(pk + (size_t)s * pk_stage_bytes)), "l"(&a.wmap), "r"(chunk_of(c) * words), "r"(row0),
+                               "r"(smem_u32(pk_full + s)) : "memory");
+                TC_STAMP(0, c);
+            }
+        }
+    } else if (warp == TC_DEQ_WARPS + 2) {
+        // ---- X producer: the matching pre-packed fp16 tiles (the previous kernel's output) ----
+        if (lane == 0) {
+            pdl_wait();
+            for (uint32_t c = 0; c < nchunks && !s_abort; ++c) {
+                const uint32_t sb = c % BS, kb = c / BS;
+                if (kb > 0) { wait(b_empty + sb, (kb - 1) & 1u); asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+                mbar_expect_tx(smem_u32(b_full + sb), b_tile_bytes);
+                bulk_g2s(smem_u32(b_tiles + (size_t)sb * b_tile_bytes), reinterpret_cast<const uint8_t *>(a.xp) + (size_t)chunk_of(c) * b_tile_bytes,
+                         b_tile_bytes, smem_u32(b_full + sb));
+                TC_STAMP(6, c);
+            }
+        }
+    } else if (warp == TC_DEQ_WARPS + 1) {
+        // ---- MMA issue: one thread; 16 x (M128 x N x K16) per chunk, A from tensor memory, B = the X tile ----
+        if (lane == 0) {
+            const uint32_t idesc = (1u << 4) | ((a.npad >> 3) << 17) | ((uint32_t)(TC_M >> 4) << 24);   // fp32 accumulate, fp16 x fp16, K-major both
+            for (uint32_t c = 0; c < nchunks && !s_abort; ++c) {
+                const uint32_t sb = c % BS, sa = c % AS;
+                wait(b_full + sb, (c / BS) & 1u);
+                TC_STAMP(7, c);
+                wait(a_full + sa, (c / AS) & 1u);
+                TC_STAMP(4, c);
+                tc_fence_after();
+                const uint32_t a_col = tmem_base + sa * 128u;
+                const uint32_t b_addr = smem_u32(b_tiles + (size_t)sb * b_tile_bytes);
+#pragma unroll
+                for (uint32_t k16 = 0; k16 < 16; ++k16)
+                    tc_mma_f16_ta(tmem_acc, a_col + k16 * 8u, tc_desc_sw128(b_addr + (k16 >> 2) * a.npad * 128u + (k16 & 3u) * 32u), idesc,
+                                  (c | k16) ? 1u : 0u);
+                tc_commit(smem_u32(a_empty + sa));     // the A stage and the X tile are free once these MMAs have read them
+                tc_commit(smem_u32(b_empty + sb));
+                TC_STAMP(5, c);
+            }
+            tc_commit(smem_u32(acc_done));
+        }
+    } else {
+        // ---- dequant warps: packed stage -> fp16 weights in tensor memory ----
+        const uint32_t quad = warp & 3u, kq = warp >> 2, r = quad * 32u + lane;
+        const uint32_t lane_addr = (quad * 32u) << 16;
+        for (uint32_t c = 0; c < nchunks; ++c) {
+            const uint32_t i = c / KB, sub = c % KB, s = i % PKS, sa = c % AS, ka = c / AS;
+            if (sub == 0) wait(pk_full + s, (i / PKS) & 1u);
+            if (tid == 0) TC_STAMP(1, c);
+            if (ka > 0) wait(a_empty + sa, (ka - 1) & 1u);
+            if (tid == 0) TC_STAMP(2, c);
+            tc_fence_after();
+            const uint8_t *row = pk + (size_t)s * pk_stage_bytes + (size_t)r * pk_row_bytes + sub * a.chunk_bytes;
+#pragma unroll
+            for (uint32_t h = 0; h < 2; ++h) {
+                uint4 v[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+                if (r < nrows) dequant_group32<FMT>(row, kq * 2u + h, a.layout, v);
+                tc_st16(tmem_base + lane_addr + sa * 128u + kq * 32u + h * 16u, v);
+            }
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(smem_u32(a_full + sa));
+                if (sub == KB - 1) mbar_arrive(smem_u32(pk_empty + s));
+                if (tid == 0) TC_STAMP(3, c);
+            }
+        }
+        // ---- epilogue: warps 0-3, lane = row ----
+        if (warp < 4) {
+            wait(acc_done, 0);
+            tc_fence_after();
+            const uint32_t rr = warp * 32 + lane;
+            float *ybase = a.split == 1 ? a.y : a.y + (size_t)sp * a.batch * a.rows;
+            const uint32_t ld = a.split == 1 ? a.ldy : a.rows;
+            const bool publish = a.split == 1 && a.pub.npeers > 0;
+            const unsigned int pub_tag = publish ? *reinterpret_cast<const volatile unsigned int *>(a.pub.pub_gen) + 1u : 0u;
+            for (uint32_t n0 = 0; n0 < a.npad; n0 += 16) {
+                uint32_t v[16];
+                asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                             : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+                               "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                             : "r"(tmem_acc + ((warp * 32u) << 16) + n0));
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (rr < nrows && !s_abort) {
+#pragma unroll
+                    for (uint32_t i = 0; i < 16; ++i)
+                        if (n0 + i < a.batch) {
+                            float *dst = ybase + (size_t)(n0 + i) * ld + row0 + rr;
+                            *dst = __uint_as_float(v[i]);
+                            if (publish) tc_publish(a.pub, dst, __uint_as_float(v[i]), pub_tag);
+                        }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
     }
     if (threadIdx.x == 0 && a.split == 1 && a.pub.npeers > 0)
         tc_publish_done(a.pub, *reinterpret_cast<const volatile unsigned int *>(a.pub.pub_gen) + 1u);

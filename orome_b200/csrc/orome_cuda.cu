@@ -148,6 +148,7 @@ extern "C" int orome_cuda_set_option(orome_cuda_ctx *c, int key, int value)
         if (value < 1 || value > 4) return fail(OROME_EINVAL, "CTAS_PER_SM must be 1..4");
         c->ctas_per_sm = value; return OROME_OK;
     case OROME_OPT_PDL: c->pdl = value != 0; return OROME_OK;
+    case OROME_OPT_TC_SLABS: c->tc_slabs = value != 0; return OROME_OK;
     case OROME_OPT_GRID_PER_SM:
         if (value < 1 || value > 2) return fail(OROME_EINVAL, "GRID_PER_SM must be 1 or 2");
         c->grid_per_sm = value; return OROME_OK;
@@ -175,6 +176,7 @@ extern "C" int orome_cuda_get_option(orome_cuda_ctx *c, int key, int *value)
     case OROME_OPT_X_BITS: *value = c->x_bits; return OROME_OK;
     case OROME_OPT_FORCE_GENERIC: *value = c->force_generic; return OROME_OK;
     case OROME_OPT_STAGE_KB: *value = c->stage_kb; return OROME_OK;
+    case OROME_OPT_TC_SLABS: *value = c->tc_slabs; return OROME_OK;
     case OROME_OPT_CTAS_PER_SM: *value = c->ctas_per_sm; return OROME_OK;
     case OROME_OPT_PDL: *value = c->pdl; return OROME_OK;
     case OROME_OPT_GRID_PER_SM: *value = c->grid_per_sm; return OROME_OK;
@@ -829,6 +831,16 @@ extern "C" int orome_cuda_gather_wait(orome_cuda_ctx *c, int flag, float *vec_de
                       n / 4, (const unsigned int *)(c->g_local + flag), c->status_dev, orome_wait_cycles(c));
 }
 
+#ifdef OROME_DIAGNOSTICS
+// Diagnostics builds only: the SM-cycle stamps CTA 0 of the last tensor-core launch left (8 kinds x 80 entries).
+extern "C" int orome_cuda_tc_trace_read(long long *host)
+{
+    CU(cudaDeviceSynchronize());
+    CU(cudaMemcpyFromSymbol(host, g_tc_trace, sizeof(long long) * 8 * 80));
+    return OROME_OK;
+}
+#endif
+
 // ---------------------------------------------------------------------------
 // fused neighbours of a product
 // ---------------------------------------------------------------------------
@@ -948,6 +960,20 @@ extern "C" int orome_cuda_matvec_group(orome_cuda_ctx *c, const OromeTensorRef *
 // ---------------------------------------------------------------------------
 static bool tc_supported(int fmt, uint32_t in_dim) { return (fmt == FMT_Q8_0 || fmt == FMT_Q4_K || fmt == FMT_Q5_K) && in_dim % TC_KC == 0; }
 
+template <int FMT, int KB>
+static int launch_tca_fmt(orome_cuda_ctx *c, const TcArgs &a, int grid, size_t smem, cudaStream_t st)
+{
+    auto kern = gemm_tca_kernel<FMT, KB>;
+    static bool configured[64] = {false};
+    if (!configured[c->device]) {
+        cudaFuncAttributes fa;
+        CU(cudaFuncGetAttributes(&fa, kern));
+        CU(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, c->smem_optin - (int)fa.sharedSizeBytes));
+        configured[c->device] = true;
+    }
+    return launch_pdl_smem(c, "gemm_tca", kern, dim3(grid), dim3(TC_THREADS), smem, st, a);
+}
+
 template <int FMT>
 static int launch_tc_fmt(orome_cuda_ctx *c, const TcArgs &a, int grid, size_t smem, cudaStream_t st)
 {
@@ -999,6 +1025,8 @@ static int launch_tc(orome_cuda_ctx *c, int fmt, const uint8_t *data, uint32_t o
         const double cost = (double)waves * ((double)((chunks + s - 1) / s) + 5.0) + (s > 1 ? 1.0 + 0.25 * s : 0.0);
         if (cost < best) { best = cost; split = s; }
     }
+    // chunks per packed stage of the tensor-memory form: two for the K-quants when every K part has an even length
+    const uint32_t kb = (!c->tc_slabs && fmt != FMT_Q8_0 && chunks % (2 * split) == 0) ? 2u : 1u;
     for (int b0 = 0; b0 < batch; b0 += TC_MAX_N) {
         const int nb = std::min(batch - b0, TC_MAX_N);
         const uint32_t npad = (uint32_t)(nb + 15) / 16 * 16;
@@ -1017,7 +1045,7 @@ static int launch_tc(orome_cuda_ctx *c, int fmt, const uint8_t *data, uint32_t o
             if (!enc) return fail(OROME_ECUDA, "gemm_tc: cuTensorMapEncodeTiled is not available");
             const cuuint64_t dims[2] = {(cuuint64_t)row_bytes_of(fmt, in_dim) / 4, out_dim};
             const cuuint64_t strides[1] = {(cuuint64_t)row_bytes_of(fmt, in_dim)};
-            const cuuint32_t box[2] = {chunk_bytes / 4, (cuuint32_t)TC_M}, estr[2] = {1, 1};
+            const cuuint32_t box[2] = {chunk_bytes / 4 * kb, (cuuint32_t)TC_M}, estr[2] = {1, 1};
             CUresult r = enc(&a.wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint8_t *>(data), dims, strides, box, estr,
                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -1034,13 +1062,27 @@ static int launch_tc(orome_cuda_ctx *c, int fmt, const uint8_t *data, uint32_t o
         // the dequant arithmetic altogether only brings it to 31 us: ring depth is not what bounds this kernel, and
         // run-time ring sizes put integer divisions on the hand-off path of every slab.
         const size_t pk_stage = (TC_M * chunk_bytes + 127) & ~127u, b_tile = (size_t)npad * 128 * TC_SLABS;
-        const size_t smem = 1024 + (size_t)TC_MAX_RING * 16384 + (size_t)TC_B_STAGES * b_tile + 512 + (size_t)TC_PK_STAGES * pk_stage;
-        if (smem > (size_t)c->smem_optin - 1024) return fail(OROME_ENOTSUP, "gemm_tc: batch %d does not fit shared memory", nb);
         const int grid = (int)(tiles * split);
-        switch (fmt) {
-        case FMT_Q8_0: rc = launch_tc_fmt<FMT_Q8_0>(c, a, grid, smem, st); break;
-        case FMT_Q4_K: rc = launch_tc_fmt<FMT_Q4_K>(c, a, grid, smem, st); break;
-        default: rc = launch_tc_fmt<FMT_Q5_K>(c, a, grid, smem, st); break;
+        if (!c->tc_slabs) {
+            // dequantized weights in tensor memory: shared memory holds X tiles and packed stages only; at least half an
+            // SM's worth is requested so that two CTAs (each wants all 512 columns of tensor memory) never share an SM
+            const size_t pk_stage_kb = (TC_M * chunk_bytes * kb + 127) & ~127u;
+            size_t smem = 1024 + (size_t)TCA_B_STAGES * b_tile + 512 + (size_t)tca_pk_stages(fmt, (int)kb) * pk_stage_kb;
+            smem = std::max<size_t>(smem, 120 * 1024);
+            if (smem > (size_t)c->smem_optin - 1024) return fail(OROME_ENOTSUP, "gemm_tca: batch %d does not fit shared memory", nb);
+            switch (fmt) {
+            case FMT_Q8_0: rc = launch_tca_fmt<FMT_Q8_0, 1>(c, a, grid, smem, st); break;
+            case FMT_Q4_K: rc = kb == 2 ? launch_tca_fmt<FMT_Q4_K, 2>(c, a, grid, smem, st) : launch_tca_fmt<FMT_Q4_K, 1>(c, a, grid, smem, st); break;
+            default: rc = kb == 2 ? launch_tca_fmt<FMT_Q5_K, 2>(c, a, grid, smem, st) : launch_tca_fmt<FMT_Q5_K, 1>(c, a, grid, smem, st); break;
+            }
+        } else {
+            const size_t smem = 1024 + (size_t)TC_MAX_RING * 16384 + (size_t)TC_B_STAGES * b_tile + 512 + (size_t)tc_pk_stages(fmt) * pk_stage;
+            if (smem > (size_t)c->smem_optin - 1024) return fail(OROME_ENOTSUP, "gemm_tc: batch %d does not fit shared memory", nb);
+            switch (fmt) {
+            case FMT_Q8_0: rc = launch_tc_fmt<FMT_Q8_0>(c, a, grid, smem, st); break;
+            case FMT_Q4_K: rc = launch_tc_fmt<FMT_Q4_K>(c, a, grid, smem, st); break;
+            default: rc = launch_tc_fmt<FMT_Q5_K>(c, a, grid, smem, st); break;
+            }
         }
         if (rc) return rc;
         if (split > 1) {

@@ -216,6 +216,27 @@ def test_matvec_x_edge_cases(env):
     assert rel_l2(gpu_matvec(env, fmt, data, out_dim, in_dim, x), want) <= REL_L2_TOL
 
 
+@pytest.mark.parametrize("fmt", [synth.Q8_0, synth.Q4_K, synth.Q5_K])
+@pytest.mark.parametrize("shape", [(300, 4096, 64), (200, 768, 20), (128, 2048, 7)])
+def test_both_forms_of_the_tensor_core_product_agree(env, fmt, shape):
+    """Dequantized weights in tensor memory (default) and staged in shared memory (OROME_OPT_TC_SLABS): the same fp16
+    operands and fp32 accumulation, so the two results differ only by the order of the sum over K."""
+    torch, F, ctx = env
+    out_dim, in_dim, batch = shape
+    data = synth.host_tensor(fmt, out_dim, in_dim, seed=synth.seed_for("forms", fmt, *shape))
+    x = synth.host_x(in_dim, batch, seed=19)
+    want = oracle.matvec_f64(fmt, data, out_dim, in_dim, x)
+    got = {}
+    for slabs in (0, 1):
+        ctx.set_option(F.OPT_TC_SLABS, slabs)
+        try:
+            got[slabs] = gpu_matvec(env, fmt, data, out_dim, in_dim, x)
+        finally:
+            ctx.set_option(F.OPT_TC_SLABS, 0)
+        assert rel_l2(got[slabs], want) <= TC_REL_L2_TOL, (slabs, rel_l2(got[slabs], want))
+    assert rel_l2(got[0], got[1]) <= 1e-6
+
+
 @pytest.mark.parametrize("fmt", QUANT + [synth.F32])
 @pytest.mark.parametrize("batch", [2, 8, 13])
 def test_batched_matvec(env, fmt, batch):
