@@ -427,6 +427,8 @@ int  orome_cuda_matvec_host(orome_cuda_ctx *ctx, const OromeTensorRef *ref,
 #define OROME_OPT_KQUANT_MMA      9   /* 1 (default): Q4_K / Q5_K batch-1 products run on the mma.sync kernel; 0: on the dp4a kernel */
 #define OROME_OPT_CHAIN_INFLIGHT 11   /* stages a chain's weight stream keeps outstanding at most (0, default: the whole ring); read at chain_end */
 #define OROME_OPT_TC_SLABS       12   /* batched tensor-core form: 0 (default) keeps the dequantized weights in tensor memory, 1 stages them in shared memory */
+#define OROME_OPT_TC_SPLIT       13   /* batched tensor-core form: K parts per row tile, 1..12; 0 (default): chosen by a cost model */
+#define OROME_OPT_TC_TILES       14   /* batched tensor-core form (tensor-memory variant): row tiles a CTA works on side by side, 1, 2 or 4; 0 (default): cost model */
 #define OROME_OPT_WAIT_US        10   /* bound of one device-side wait (peer data, chain inputs, chain stages) in microseconds; 0 (default): about a second */
 int  orome_cuda_set_option(orome_cuda_ctx *ctx, int key, int value);
 int  orome_cuda_get_option(orome_cuda_ctx *ctx, int key, int *value);

@@ -65,6 +65,8 @@ struct orome_cuda_ctx {
     size_t tc_xp_cap = 0, tc_part_cap = 0;
     int tc_min_batch = 4;    // batches from this size on use the tensor-core kernel (smaller ones: one decode launch per vector)
     int tc_slabs = 0;        // batched form: 1 = dequantized weights staged in shared memory (the earlier form), 0 = in tensor memory
+    int tc_tiles = 0;        // batched form in tensor memory: row tiles per CTA (0: chosen by the cost model)
+    int tc_split = 0;        // batched form: K parts per row tile (0: chosen by the cost model)
     int kquant_mma = 1;      // Q4_K / Q5_K batch-1 products on the mma.sync kernel (0: dp4a kernel)
     int chain_inflight = 0;  // stages a chain's producer keeps outstanding at most (0: the whole ring)
     int wait_us = 0;         // bound of every device-side wait in microseconds of SM clock (0: about one second)

@@ -90,6 +90,7 @@ struct TcArgs {
     uint32_t rows, in_dim, row_bytes, chunk_bytes;   // chunk_bytes = packed bytes of 256 weights of one row
     uint32_t batch, npad, ldy;
     uint32_t split, chunks;       // split-K parts and 256-weight chunks per row: part p takes chunks [p*chunks/split, (p+1)*chunks/split)
+    uint32_t tiles_per_cta;       // tensor-memory form: row tiles a CTA works on side by side (1, 2 or 4)
     int layout;
     int *status;
     TcPub pub;                 // split == 1 only: with split-K the reduction kernel publishes
@@ -395,22 +396,25 @@ gemm_tc_kernel(const __grid_constant__ TcArgs a)
 
 
 // ---- the same product with the dequantized weights in TENSOR MEMORY --------------------------------------------------
-// In the form above a 256-weight chunk of a 128-row tile costs 64 KB of shared-memory stores (the fp16 slabs) and
-// 64 KB of operand reads by the tensor core, next to 18 KB of packed weights: measured, the kernel moves about 230 KB
-// through shared memory per chunk and its MMAs take ~100 cycles each instead of ~34.  Here the dequant warps write the
-// fp16 weights straight into tensor memory (tcgen05.st: lane = row, two weights per 32-bit column) and the MMA takes
-// its A operand from there; shared memory carries only the packed weights and the X tiles.
-//   tensor memory (512 columns): A stages of 128 columns (one chunk: 128 rows x 256 fp16) at 0, 128, 256; the fp32
-//   accumulator (npad <= 64 columns) at 384.
+// Two findings from cycle-stamping the form above drive this one.
+// (1) A 256-weight chunk of a 128-row tile costs 64 KB of shared-memory stores (the fp16 slabs) and 64 KB of operand
+//     reads by the tensor core next to 18 KB of packed weights; its MMAs took ~100 cycles each instead of ~34.  Here
+//     the dequant warps write the fp16 weights straight into tensor memory (tcgen05.st: lane = row, two weights per
+//     32-bit column) and the MMA takes its A operand from there.
+// (2) The copy engine, not memory, set the pace after that: a tensor copy of 128 rows x 144 bytes took ~2100 cycles
+//     whether the tensor sat in HBM or in L2, and everything else queued behind it (an X tile: 4000-8000 cycles).
+//     Here the dequant threads read their packed weights with plain 16-byte loads straight into registers, one unit
+//     ahead of the one they convert; the copy engine carries only the X tiles.
+// A CTA works on `tiles_per_cta` (TT) row tiles side by side: every X tile is fetched once and multiplied with the
+// chunk of each of its row tiles, each with its own accumulator; K is split over more CTAs (args.split) instead.
+//   tensor memory (512 columns): A stages of 128 columns (one chunk of one row tile: 128 rows x 256 fp16) from column
+//   0; TT accumulators of 64 columns at the top (TT = 1, 2: three A stages; TT = 4: two).
 //   dequant warp w: rows 32 * (w % 4) + lane (the lanes of tensor memory a warp may touch), weights
-//   64 * (w / 4) .. + 63 of the chunk; every warp works on every chunk.
-constexpr int TCA_A_STAGES = 3;
-constexpr uint32_t TCA_ACC_COL = 384;
-constexpr int TCA_B_STAGES = 3;
-// A packed stage holds KB consecutive chunks of the 128 rows (one tensor copy).  The copy engine works row by row: a
-// 128-row box of 144-byte rows took it about as long as a box of 288-byte rows (measured: ~2000 cycles per box, which
-// was the kernel's period per chunk), so K-quant tensors load two chunks per box where the K split allows it.
-constexpr int tca_pk_stages(int fmt, int kb) { return fmt == FMT_Q8_0 ? 3 : fmt == FMT_Q4_K ? (kb == 2 ? 3 : 5) : (kb == 2 ? 2 : 4); }
+//   64 * (w / 4) .. + 63 of the chunk; every warp works on every (chunk, tile) unit.
+constexpr int TCA_B_STAGES = 4;
+constexpr int TCA_MAX_TT = 4;
+constexpr int TCA_THREADS = (TC_DEQ_WARPS + 2) * 32;     // + MMA issuer, X producer
+constexpr uint32_t tca_a_stages(uint32_t tt) { return (512u - 64u * tt) / 128u; }
 
 __device__ __forceinline__ void tc_mma_f16_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate)
 {
@@ -426,41 +430,135 @@ __device__ __forceinline__ void tc_st16(uint32_t taddr, const uint4 (&v)[4])
                    "r"(v[2].x), "r"(v[2].y), "r"(v[2].z), "r"(v[2].w), "r"(v[3].x), "r"(v[3].y), "r"(v[3].z), "r"(v[3].w) : "memory");
 }
 
-template <int FMT, int KB>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+// The packed bytes one dequant thread needs for its 64 weights (sub-blocks 2kq, 2kq+1 of a K-quant superblock, blocks
+// 2kq, 2kq+1 of a Q8_0 chunk) of one row, as 16-byte pieces.
+//   Q4_K: header (d, dmin, 12 scale bytes), 32 quant bytes (low nibbles = sub-block 2kq, high = 2kq+1).
+//   Q5_K: the same plus the 32 bytes of fifth bits (all eight sub-blocks share them).
+//   Q8_0: the 80 bytes from the 16-byte boundary at or below byte 68*kq of the chunk; the thread's 68 bytes start kq words in.
+template <int FMT> struct TcPacked { uint4 p[FMT == FMT_Q4_K ? 3 : 5]; };
+
+template <int FMT>
+__device__ __forceinline__ void tc_load_packed(const uint8_t *chunk, uint32_t kq, bool live, TcPacked<FMT> &d)
+{
+    constexpr int N = FMT == FMT_Q4_K ? 3 : 5;
+    if (!live) {
+#pragma unroll
+        for (int i = 0; i < N; ++i) d.p[i] = make_uint4(0, 0, 0, 0);
+        return;
+    }
+    if constexpr (FMT == FMT_Q8_0) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(chunk + ((kq * 68u) & ~15u));
+#pragma unroll
+        for (int i = 0; i < 5; ++i) d.p[i] = __ldg(src + i);
+    } else {
+        d.p[0] = __ldg(reinterpret_cast<const uint4 *>(chunk));
+        constexpr uint32_t QOFF = FMT == FMT_Q4_K ? 16u : 48u;
+        const uint4 *q = reinterpret_cast<const uint4 *>(chunk + QOFF + 32u * kq);
+        d.p[1] = __ldg(q);
+        d.p[2] = __ldg(q + 1);
+        if constexpr (FMT == FMT_Q5_K) {
+            d.p[3] = __ldg(reinterpret_cast<const uint4 *>(chunk + 16));
+            d.p[4] = __ldg(reinterpret_cast<const uint4 *>(chunk + 32));
+        }
+    }
+}
+
+// 32 weights (half h of the thread's 64) from the packed pieces -> four 16-byte fp16 pieces, element order.
+template <int FMT, int KQ>
+__device__ __forceinline__ void tc_dequant_half(const TcPacked<FMT> &d, uint32_t h, int layout, uint4 (&out)[4])
+{
+    uint32_t w[8];
+    __half2 scale, bias, addend;
+    if constexpr (FMT == FMT_Q8_0) {
+        // words KQ .. KQ+16 of the 20 loaded: block A = fp16 scale in the low half of word KQ, quants from its upper half
+        // on; block B = scale in the upper half of word KQ+8, quants = words KQ+9 .. KQ+16
+        const uint32_t v[20] = {d.p[0].x, d.p[0].y, d.p[0].z, d.p[0].w, d.p[1].x, d.p[1].y, d.p[1].z, d.p[1].w, d.p[2].x, d.p[2].y,
+                                d.p[2].z, d.p[2].w, d.p[3].x, d.p[3].y, d.p[3].z, d.p[3].w, d.p[4].x, d.p[4].y, d.p[4].z, d.p[4].w};
+        uint32_t dbits;
+        if (h == 0) {
+            dbits = v[KQ] & 0xffffu;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) w[i] = __byte_perm(v[KQ + i], v[KQ + i + 1], 0x5432u) ^ 0x80808080u;
+        } else {
+            dbits = v[KQ + 8] >> 16;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) w[i] = v[KQ + 9 + i] ^ 0x80808080u;
+        }
+        const float dd = __half2float(__ushort_as_half((unsigned short)dbits));
+        scale = __float2half2_rn(dd); bias = __float2half2_rn(1152.0f); addend = __float2half2_rn(0.0f);   // bytes are q + 128
+    } else {
+        const uint4 hd = d.p[0];
+        uint32_t scA, scB, mnA, mnB;
+        pair_scales(hd.y, hd.z, hd.w, layout, KQ, scA, scB, mnA, mnB);
+        const uint32_t sc = h ? scB : scA, mn = h ? mnB : mnA;
+        const float dd = __half2float(__ushort_as_half((unsigned short)(hd.x & 0xffffu)));
+        const float dmin = __half2float(__ushort_as_half((unsigned short)(hd.x >> 16)));
+        w[0] = d.p[1].x; w[1] = d.p[1].y; w[2] = d.p[1].z; w[3] = d.p[1].w; w[4] = d.p[2].x; w[5] = d.p[2].y; w[6] = d.p[2].z; w[7] = d.p[2].w;
+        const uint32_t shift = h * 4u;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) w[i] = (w[i] >> shift) & 0x0F0F0F0Fu;
+        if constexpr (FMT == FMT_Q5_K) {
+            const uint32_t hb[8] = {d.p[3].x, d.p[3].y, d.p[3].z, d.p[3].w, d.p[4].x, d.p[4].y, d.p[4].z, d.p[4].w};
+            const uint32_t g32 = 2u * KQ + h;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) w[i] |= ((hb[i] >> g32) & 0x01010101u) << 4;
+        }
+        scale = __float2half2_rn(dd * (float)sc); bias = __float2half2_rn(1024.0f); addend = __float2half2_rn(-(dmin * (float)mn));
+    }
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+        out[p].x = h2_bits(two_weights(w[2 * p], 0x5140u, bias, scale, addend));
+        out[p].y = h2_bits(two_weights(w[2 * p], 0x7362u, bias, scale, addend));
+        out[p].z = h2_bits(two_weights(w[2 * p + 1], 0x5140u, bias, scale, addend));
+        out[p].w = h2_bits(two_weights(w[2 * p + 1], 0x7362u, bias, scale, addend));
+    }
+}
+
+template <int FMT, int KQ>
+__device__ __forceinline__ void tc_convert_unit(const TcPacked<FMT> &d, int layout, uint32_t taddr)
+{
+#pragma unroll
+    for (uint32_t h = 0; h < 2; ++h) {
+        uint4 v[4];
+        tc_dequant_half<FMT, KQ>(d, h, layout, v);
+        tc_st16(taddr + h * 16u, v);
+    }
+}
+
+template <int FMT>
+__global__ void __launch_bounds__(TCA_THREADS, 1)
 gemm_tca_kernel(const __grid_constant__ TcArgs a)
 {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    // layout: [X tiles BS x npad*512][packed stages PKS x 128*chunk_bytes][barriers]
-    constexpr uint32_t AS = TCA_A_STAGES, BS = TCA_B_STAGES, PKS = tca_pk_stages(FMT, KB);
+    // layout: [X tiles BS x npad*512][barriers]
+    constexpr uint32_t BS = TCA_B_STAGES, MAX_AS = 3;
+    const uint32_t TT = a.tiles_per_cta, AS = tca_a_stages(TT);
     const uint32_t b_tile_bytes = a.npad * 128u * TC_SLABS;
     uint8_t *b_tiles = smem;
-    const uint32_t pk_row_bytes = KB * a.chunk_bytes, pk_stage_bytes = (TC_M * pk_row_bytes + 127u) & ~127u;
-    uint8_t *pk = b_tiles + BS * b_tile_bytes;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(pk + PKS * pk_stage_bytes);
-    uint64_t *pk_full = bars, *pk_empty = pk_full + PKS, *b_full = pk_empty + PKS, *b_empty = b_full + BS;
-    uint64_t *a_full = b_empty + BS, *a_empty = a_full + AS, *acc_done = a_empty + AS;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(b_tiles + BS * b_tile_bytes);
+    uint64_t *b_full = bars, *b_empty = b_full + BS;
+    uint64_t *a_full = b_empty + BS, *a_empty = a_full + MAX_AS, *acc_done = a_empty + MAX_AS;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_done + 1);
     __shared__ volatile int s_abort;
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
-    const uint32_t tile = blockIdx.x / a.split, sp = blockIdx.x % a.split;
-    const uint32_t row0 = tile * TC_M, nrows = min((uint32_t)TC_M, a.rows - row0);
+    const uint32_t tgroup = blockIdx.x / a.split, sp = blockIdx.x % a.split;
+    const uint32_t tile0 = tgroup * TT;                          // this CTA's row tiles: tile0 .. tile0 + TT - 1 (those inside the tensor)
     const uint32_t chunk0 = sp * a.chunks / a.split, nchunks = (sp + 1) * a.chunks / a.split - chunk0;
-    // CTAs start their walk over K at different chunks (a multiple of KB; the host gives KB = 2 only parts of even length)
-    const uint32_t rot = ((tile * 5u + sp * 3u) % nchunks) / KB * KB;
+    const uint32_t rot = (tgroup * 5u + sp * 3u) % nchunks;      // CTAs start their walk over K at different chunks
+    const uint32_t nunits = nchunks * TT;                        // unit u = (chunk u / TT, tile u % TT)
+    const uint32_t acc_col0 = 512u - 64u * TT;
 
     if (tid == 0) {
         s_abort = 0;
-        for (uint32_t s = 0; s < PKS; ++s) { mbar_init(smem_u32(pk_full + s), 1); mbar_init(smem_u32(pk_empty + s), TC_DEQ_WARPS); }
         for (uint32_t s = 0; s < BS; ++s) { mbar_init(smem_u32(b_full + s), 1); mbar_init(smem_u32(b_empty + s), 1); }
-        for (uint32_t s = 0; s < AS; ++s) { mbar_init(smem_u32(a_full + s), TC_DEQ_WARPS); mbar_init(smem_u32(a_empty + s), 1); }
+        for (uint32_t s = 0; s < MAX_AS; ++s) { mbar_init(smem_u32(a_full + s), TC_DEQ_WARPS); mbar_init(smem_u32(a_empty + s), 1); }
         mbar_init(smem_u32(acc_done), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (warp == 0) {   // all 512 columns: one CTA per SM (its shared memory sees to that)
+    if (warp == 0) {   // all 512 columns: one CTA per SM (its shared memory request sees to that)
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -468,7 +566,6 @@ gemm_tca_kernel(const __grid_constant__ TcArgs a)
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
-    const uint32_t tmem_acc = tmem_base + TCA_ACC_COL;
     pdl_launch_dependents();
 
     auto wait = [&](uint64_t *bar, uint32_t parity) {
@@ -476,22 +573,8 @@ gemm_tca_kernel(const __grid_constant__ TcArgs a)
     };
     auto chunk_of = [&](uint32_t c) { return chunk0 + (c + rot < nchunks ? c + rot : c + rot - nchunks); };
 
-    if (warp == TC_DEQ_WARPS) {
-        // ---- weight producer: packed stages, independent of the previous kernel ----
-        if (lane == 0) {
-            const uint32_t words = a.chunk_bytes / 4;
-            for (uint32_t c = 0, i = 0; c < nchunks && !s_abort; c += KB, ++i) {
-                const uint32_t s = i % PKS, k = i / PKS;
-                if (k > 0) { wait(pk_empty + s, (k - 1) & 1u); asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-                mbar_expect_tx(smem_u32(pk_full + s), TC_M * pk_row_bytes);    // the box is always full: out-of-range rows arrive as zeros
-                asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                             ::"r"(smem_u32(pk + (size_t)s * pk_stage_bytes)), "l"(&a.wmap), "r"(chunk_of(c) * words), "r"(row0),
-                               "r"(smem_u32(pk_full + s)) : "memory");
-                TC_STAMP(0, c);
-            }
-        }
-    } else if (warp == TC_DEQ_WARPS + 2) {
-        // ---- X producer: the matching pre-packed fp16 tiles (the previous kernel's output) ----
+    if (warp == TC_DEQ_WARPS + 1) {
+        // ---- X producer: the pre-packed fp16 tiles (the previous kernel's output), one per chunk ----
         if (lane == 0) {
             pdl_wait();
             for (uint32_t c = 0; c < nchunks && !s_abort; ++c) {
@@ -503,80 +586,105 @@ gemm_tca_kernel(const __grid_constant__ TcArgs a)
                 TC_STAMP(6, c);
             }
         }
-    } else if (warp == TC_DEQ_WARPS + 1) {
-        // ---- MMA issue: one thread; 16 x (M128 x N x K16) per chunk, A from tensor memory, B = the X tile ----
+    } else if (warp == TC_DEQ_WARPS) {
+        // ---- MMA issue: one thread; 16 x (M128 x N x K16) per unit, A from tensor memory, B = the chunk's X tile ----
         if (lane == 0) {
             const uint32_t idesc = (1u << 4) | ((a.npad >> 3) << 17) | ((uint32_t)(TC_M >> 4) << 24);   // fp32 accumulate, fp16 x fp16, K-major both
+            uint32_t sa = 0, ka = 0, u = 0;
             for (uint32_t c = 0; c < nchunks && !s_abort; ++c) {
-                const uint32_t sb = c % BS, sa = c % AS;
+                const uint32_t sb = c % BS;
                 wait(b_full + sb, (c / BS) & 1u);
                 TC_STAMP(7, c);
-                wait(a_full + sa, (c / AS) & 1u);
-                TC_STAMP(4, c);
-                tc_fence_after();
-                const uint32_t a_col = tmem_base + sa * 128u;
                 const uint32_t b_addr = smem_u32(b_tiles + (size_t)sb * b_tile_bytes);
+                for (uint32_t t = 0; t < TT; ++t, ++u) {
+                    wait(a_full + sa, ka & 1u);
+                    TC_STAMP(4, u);
+                    tc_fence_after();
+                    const uint32_t a_col = tmem_base + sa * 128u, d_col = tmem_base + acc_col0 + t * 64u;
 #pragma unroll
-                for (uint32_t k16 = 0; k16 < 16; ++k16)
-                    tc_mma_f16_ta(tmem_acc, a_col + k16 * 8u, tc_desc_sw128(b_addr + (k16 >> 2) * a.npad * 128u + (k16 & 3u) * 32u), idesc,
-                                  (c | k16) ? 1u : 0u);
-                tc_commit(smem_u32(a_empty + sa));     // the A stage and the X tile are free once these MMAs have read them
-                tc_commit(smem_u32(b_empty + sb));
-                TC_STAMP(5, c);
+                    for (uint32_t k16 = 0; k16 < 16; ++k16)
+                        tc_mma_f16_ta(d_col, a_col + k16 * 8u, tc_desc_sw128(b_addr + (k16 >> 2) * a.npad * 128u + (k16 & 3u) * 32u), idesc,
+                                      (c | k16) ? 1u : 0u);
+                    tc_commit(smem_u32(a_empty + sa));     // the A stage is free once these MMAs have read it
+                    TC_STAMP(5, u);
+                    if (++sa == AS) { sa = 0; ++ka; }
+                }
+                tc_commit(smem_u32(b_empty + sb));         // and the X tile after the chunk's last row tile
             }
             tc_commit(smem_u32(acc_done));
         }
     } else {
-        // ---- dequant warps: packed stage -> fp16 weights in tensor memory ----
+        // ---- dequant warps: packed weights (global -> registers, one unit ahead) -> fp16 weights in tensor memory ----
         const uint32_t quad = warp & 3u, kq = warp >> 2, r = quad * 32u + lane;
         const uint32_t lane_addr = (quad * 32u) << 16;
-        for (uint32_t c = 0; c < nchunks; ++c) {
-            const uint32_t i = c / KB, sub = c % KB, s = i % PKS, sa = c % AS, ka = c / AS;
-            if (sub == 0) wait(pk_full + s, (i / PKS) & 1u);
-            if (tid == 0) TC_STAMP(1, c);
+        uint32_t sa = 0, ka = 0, t = 0, c = 0;
+        auto unit_ptr = [&](uint32_t cc, uint32_t tt, bool &live) {
+            const uint32_t grow = (tile0 + tt) * TC_M + r;
+            live = grow < a.rows;
+            return a.w + (size_t)grow * a.row_bytes + (size_t)chunk_of(cc) * a.chunk_bytes;
+        };
+        TcPacked<FMT> cur, nxt;
+        {
+            bool live;
+            const uint8_t *p = unit_ptr(0, 0, live);
+            tc_load_packed<FMT>(p, kq, live, cur);
+        }
+        for (uint32_t u = 0; u < nunits; ++u) {
+            uint32_t tn = t + 1, cn = c;
+            if (tn == TT) { tn = 0; ++cn; }
+            if (u + 1 < nunits) {                 // the next unit's bytes are on their way while this one is converted
+                bool live;
+                const uint8_t *p = unit_ptr(cn, tn, live);
+                tc_load_packed<FMT>(p, kq, live, nxt);
+            }
+            if (tid == 0) TC_STAMP(1, u);
             if (ka > 0) wait(a_empty + sa, (ka - 1) & 1u);
-            if (tid == 0) TC_STAMP(2, c);
+            if (tid == 0) TC_STAMP(2, u);
             tc_fence_after();
-            const uint8_t *row = pk + (size_t)s * pk_stage_bytes + (size_t)r * pk_row_bytes + sub * a.chunk_bytes;
-#pragma unroll
-            for (uint32_t h = 0; h < 2; ++h) {
-                uint4 v[4] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
-                if (r < nrows) dequant_group32<FMT>(row, kq * 2u + h, a.layout, v);
-                tc_st16(tmem_base + lane_addr + sa * 128u + kq * 32u + h * 16u, v);
+            const uint32_t taddr = tmem_base + lane_addr + sa * 128u + kq * 32u;
+            switch (kq) {                         // warp-uniform; the sub-block index is a compile-time constant inside
+            case 0: tc_convert_unit<FMT, 0>(cur, a.layout, taddr); break;
+            case 1: tc_convert_unit<FMT, 1>(cur, a.layout, taddr); break;
+            case 2: tc_convert_unit<FMT, 2>(cur, a.layout, taddr); break;
+            default: tc_convert_unit<FMT, 3>(cur, a.layout, taddr); break;
             }
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             tc_fence_before();
             __syncwarp();
             if (lane == 0) {
                 mbar_arrive(smem_u32(a_full + sa));
-                if (sub == KB - 1) mbar_arrive(smem_u32(pk_empty + s));
-                if (tid == 0) TC_STAMP(3, c);
+                if (tid == 0) TC_STAMP(3, u);
             }
+            cur = nxt;
+            if (++sa == AS) { sa = 0; ++ka; }
+            t = tn; c = cn;
         }
-        // ---- epilogue: warps 0-3, lane = row ----
+        // ---- epilogue: warps 0-3, lane = row, one accumulator per row tile ----
         if (warp < 4) {
             wait(acc_done, 0);
             tc_fence_after();
-            const uint32_t rr = warp * 32 + lane;
             float *ybase = a.split == 1 ? a.y : a.y + (size_t)sp * a.batch * a.rows;
             const uint32_t ld = a.split == 1 ? a.ldy : a.rows;
             const bool publish = a.split == 1 && a.pub.npeers > 0;
             const unsigned int pub_tag = publish ? *reinterpret_cast<const volatile unsigned int *>(a.pub.pub_gen) + 1u : 0u;
-            for (uint32_t n0 = 0; n0 < a.npad; n0 += 16) {
-                uint32_t v[16];
-                asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                             : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-                               "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-                             : "r"(tmem_acc + ((warp * 32u) << 16) + n0));
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (rr < nrows && !s_abort) {
+            for (uint32_t tt = 0; tt < TT; ++tt) {
+                const uint32_t grow = (tile0 + tt) * TC_M + warp * 32 + lane;
+                for (uint32_t n0 = 0; n0 < a.npad; n0 += 16) {
+                    uint32_t v[16];
+                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+                                   "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                                 : "r"(tmem_base + ((warp * 32u) << 16) + acc_col0 + tt * 64u + n0));
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (grow < a.rows && !s_abort) {
 #pragma unroll
-                    for (uint32_t i = 0; i < 16; ++i)
-                        if (n0 + i < a.batch) {
-                            float *dst = ybase + (size_t)(n0 + i) * ld + row0 + rr;
-                            *dst = __uint_as_float(v[i]);
-                            if (publish) tc_publish(a.pub, dst, __uint_as_float(v[i]), pub_tag);
-                        }
+                        for (uint32_t i = 0; i < 16; ++i)
+                            if (n0 + i < a.batch) {
+                                float *dst = ybase + (size_t)(n0 + i) * ld + grow;
+                                *dst = __uint_as_float(v[i]);
+                                if (publish) tc_publish(a.pub, dst, __uint_as_float(v[i]), pub_tag);
+                            }
+                    }
                 }
             }
         }

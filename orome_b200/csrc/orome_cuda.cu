@@ -149,6 +149,12 @@ extern "C" int orome_cuda_set_option(orome_cuda_ctx *c, int key, int value)
         c->ctas_per_sm = value; return OROME_OK;
     case OROME_OPT_PDL: c->pdl = value != 0; return OROME_OK;
     case OROME_OPT_TC_SLABS: c->tc_slabs = value != 0; return OROME_OK;
+    case OROME_OPT_TC_SPLIT:
+        if (value < 0 || value > 12) return fail(OROME_EINVAL, "TC_SPLIT must be 0 (automatic) .. 12");
+        c->tc_split = value; return OROME_OK;
+    case OROME_OPT_TC_TILES:
+        if (value != 0 && value != 1 && value != 2 && value != 4) return fail(OROME_EINVAL, "TC_TILES must be 0 (automatic), 1, 2 or 4");
+        c->tc_tiles = value; return OROME_OK;
     case OROME_OPT_GRID_PER_SM:
         if (value < 1 || value > 2) return fail(OROME_EINVAL, "GRID_PER_SM must be 1 or 2");
         c->grid_per_sm = value; return OROME_OK;
@@ -177,6 +183,8 @@ extern "C" int orome_cuda_get_option(orome_cuda_ctx *c, int key, int *value)
     case OROME_OPT_FORCE_GENERIC: *value = c->force_generic; return OROME_OK;
     case OROME_OPT_STAGE_KB: *value = c->stage_kb; return OROME_OK;
     case OROME_OPT_TC_SLABS: *value = c->tc_slabs; return OROME_OK;
+    case OROME_OPT_TC_SPLIT: *value = c->tc_split; return OROME_OK;
+    case OROME_OPT_TC_TILES: *value = c->tc_tiles; return OROME_OK;
     case OROME_OPT_CTAS_PER_SM: *value = c->ctas_per_sm; return OROME_OK;
     case OROME_OPT_PDL: *value = c->pdl; return OROME_OK;
     case OROME_OPT_GRID_PER_SM: *value = c->grid_per_sm; return OROME_OK;
@@ -960,10 +968,10 @@ extern "C" int orome_cuda_matvec_group(orome_cuda_ctx *c, const OromeTensorRef *
 // ---------------------------------------------------------------------------
 static bool tc_supported(int fmt, uint32_t in_dim) { return (fmt == FMT_Q8_0 || fmt == FMT_Q4_K || fmt == FMT_Q5_K) && in_dim % TC_KC == 0; }
 
-template <int FMT, int KB>
+template <int FMT>
 static int launch_tca_fmt(orome_cuda_ctx *c, const TcArgs &a, int grid, size_t smem, cudaStream_t st)
 {
-    auto kern = gemm_tca_kernel<FMT, KB>;
+    auto kern = gemm_tca_kernel<FMT>;
     static bool configured[64] = {false};
     if (!configured[c->device]) {
         cudaFuncAttributes fa;
@@ -971,7 +979,7 @@ static int launch_tca_fmt(orome_cuda_ctx *c, const TcArgs &a, int grid, size_t s
         CU(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, c->smem_optin - (int)fa.sharedSizeBytes));
         configured[c->device] = true;
     }
-    return launch_pdl_smem(c, "gemm_tca", kern, dim3(grid), dim3(TC_THREADS), smem, st, a);
+    return launch_pdl_smem(c, "gemm_tca", kern, dim3(grid), dim3(TCA_THREADS), smem, st, a);
 }
 
 template <int FMT>
@@ -1018,15 +1026,20 @@ static int launch_tc(orome_cuda_ctx *c, int fmt, const uint8_t *data, uint32_t o
     // Split K so that the SMs stay busy: a CTA costs about one time unit per chunk plus about five to set up (TMEM,
     // barriers, pipeline fill -- measured: three parts in two waves were slower than one part on 96 of 148 SMs), the
     // grid runs in waves of sm_count CTAs, a split adds a reduction pass.  Parts may be uneven.
+    // Split K so that the SMs stay busy: a CTA costs about one time unit per chunk plus about five to set up (TMEM,
+    // barriers, pipeline fill -- measured: three parts in two waves were slower than one part on 96 of 148 SMs), the
+    // grid runs in waves of sm_count CTAs, a split adds a reduction pass.  Parts may be uneven.
+    // Row tiles per CTA (tensor-memory form): one.  Two or four tiles sharing each X tile were measured slower at every
+    // split (12288 x 4096, batch 64: 29 us with one tile, 37-48 us with two): the MMA issue, not the X traffic, is what a
+    // CTA waits for.  OROME_OPT_TC_TILES keeps the choice open for experiments.
     uint32_t split = 1;
+    const uint32_t tt = c->tc_slabs ? 1u : (c->tc_tiles ? std::min<uint32_t>((uint32_t)c->tc_tiles, tiles) : 1u);
     double best = 1e30;
-    for (uint32_t s = 1; s <= 12 && s <= chunks; ++s) {
-        const uint32_t ctas = tiles * s, waves = (ctas + c->sm_count - 1) / c->sm_count;
-        const double cost = (double)waves * ((double)((chunks + s - 1) / s) + 5.0) + (s > 1 ? 1.0 + 0.25 * s : 0.0);
+    for (uint32_t s = c->tc_split ? (uint32_t)c->tc_split : 1u; s <= (c->tc_split ? (uint32_t)c->tc_split : 12u) && s <= chunks; ++s) {
+        const uint32_t ctas = (tiles + tt - 1) / tt * s, waves = (ctas + c->sm_count - 1) / c->sm_count;
+        const double cost = (double)waves * ((double)((chunks + s - 1) / s) * tt + 5.0) + (s > 1 ? 1.0 + 0.25 * s : 0.0);
         if (cost < best) { best = cost; split = s; }
     }
-    // chunks per packed stage of the tensor-memory form: two for the K-quants when every K part has an even length
-    const uint32_t kb = (!c->tc_slabs && fmt != FMT_Q8_0 && chunks % (2 * split) == 0) ? 2u : 1u;
     for (int b0 = 0; b0 < batch; b0 += TC_MAX_N) {
         const int nb = std::min(batch - b0, TC_MAX_N);
         const uint32_t npad = (uint32_t)(nb + 15) / 16 * 16;
@@ -1045,7 +1058,7 @@ static int launch_tc(orome_cuda_ctx *c, int fmt, const uint8_t *data, uint32_t o
             if (!enc) return fail(OROME_ECUDA, "gemm_tc: cuTensorMapEncodeTiled is not available");
             const cuuint64_t dims[2] = {(cuuint64_t)row_bytes_of(fmt, in_dim) / 4, out_dim};
             const cuuint64_t strides[1] = {(cuuint64_t)row_bytes_of(fmt, in_dim)};
-            const cuuint32_t box[2] = {chunk_bytes / 4 * kb, (cuuint32_t)TC_M}, estr[2] = {1, 1};
+            const cuuint32_t box[2] = {chunk_bytes / 4, (cuuint32_t)TC_M}, estr[2] = {1, 1};
             CUresult r = enc(&a.wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint8_t *>(data), dims, strides, box, estr,
                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -1053,7 +1066,7 @@ static int launch_tc(orome_cuda_ctx *c, int fmt, const uint8_t *data, uint32_t o
         }
         a.w = data; a.xp = xp; a.y = split == 1 ? y + (size_t)b0 * ldy : c->tc_part;
         a.rows = out_dim; a.in_dim = in_dim; a.row_bytes = (uint32_t)row_bytes_of(fmt, in_dim); a.chunk_bytes = chunk_bytes;
-        a.batch = (uint32_t)nb; a.npad = npad; a.ldy = (uint32_t)ldy; a.split = split; a.chunks = chunks;
+        a.batch = (uint32_t)nb; a.npad = npad; a.ldy = (uint32_t)ldy; a.split = split; a.chunks = chunks; a.tiles_per_cta = tt;
         a.layout = layout; a.status = c->status_dev;
         a.pub = *pub;
         // Shared memory: one chunk's worth of fp16 slab buffers, two X tile stages, two packed-weight stages (169 KB for
@@ -1062,18 +1075,17 @@ static int launch_tc(orome_cuda_ctx *c, int fmt, const uint8_t *data, uint32_t o
         // the dequant arithmetic altogether only brings it to 31 us: ring depth is not what bounds this kernel, and
         // run-time ring sizes put integer divisions on the hand-off path of every slab.
         const size_t pk_stage = (TC_M * chunk_bytes + 127) & ~127u, b_tile = (size_t)npad * 128 * TC_SLABS;
-        const int grid = (int)(tiles * split);
+        const int grid = (int)((tiles + tt - 1) / tt * split);
         if (!c->tc_slabs) {
             // dequantized weights in tensor memory: shared memory holds X tiles and packed stages only; at least half an
             // SM's worth is requested so that two CTAs (each wants all 512 columns of tensor memory) never share an SM
-            const size_t pk_stage_kb = (TC_M * chunk_bytes * kb + 127) & ~127u;
-            size_t smem = 1024 + (size_t)TCA_B_STAGES * b_tile + 512 + (size_t)tca_pk_stages(fmt, (int)kb) * pk_stage_kb;
+            size_t smem = 1024 + (size_t)TCA_B_STAGES * b_tile + 512;
             smem = std::max<size_t>(smem, 120 * 1024);
             if (smem > (size_t)c->smem_optin - 1024) return fail(OROME_ENOTSUP, "gemm_tca: batch %d does not fit shared memory", nb);
             switch (fmt) {
-            case FMT_Q8_0: rc = launch_tca_fmt<FMT_Q8_0, 1>(c, a, grid, smem, st); break;
-            case FMT_Q4_K: rc = kb == 2 ? launch_tca_fmt<FMT_Q4_K, 2>(c, a, grid, smem, st) : launch_tca_fmt<FMT_Q4_K, 1>(c, a, grid, smem, st); break;
-            default: rc = kb == 2 ? launch_tca_fmt<FMT_Q5_K, 2>(c, a, grid, smem, st) : launch_tca_fmt<FMT_Q5_K, 1>(c, a, grid, smem, st); break;
+            case FMT_Q8_0: rc = launch_tca_fmt<FMT_Q8_0>(c, a, grid, smem, st); break;
+            case FMT_Q4_K: rc = launch_tca_fmt<FMT_Q4_K>(c, a, grid, smem, st); break;
+            default: rc = launch_tca_fmt<FMT_Q5_K>(c, a, grid, smem, st); break;
             }
         } else {
             const size_t smem = 1024 + (size_t)TC_MAX_RING * 16384 + (size_t)TC_B_STAGES * b_tile + 512 + (size_t)tc_pk_stages(fmt) * pk_stage;

@@ -15,7 +15,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "liborome_cuda.so")
 
 VARIANT_DEFAULT, VARIANT_LLAMA = 0, 1
-OPT_X_BITS, OPT_FORCE_GENERIC, OPT_STAGE_KB, OPT_CTAS_PER_SM, OPT_PDL, OPT_GRID_PER_SM, OPT_PREFETCH_MB, OPT_TC_MIN_BATCH, OPT_KQUANT_MMA, OPT_WAIT_US, OPT_CHAIN_INFLIGHT, OPT_TC_SLABS = 1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12
+OPT_X_BITS, OPT_FORCE_GENERIC, OPT_STAGE_KB, OPT_CTAS_PER_SM, OPT_PDL, OPT_GRID_PER_SM, OPT_PREFETCH_MB, OPT_TC_MIN_BATCH, OPT_KQUANT_MMA, OPT_WAIT_US, OPT_CHAIN_INFLIGHT, OPT_TC_SLABS, OPT_TC_SPLIT, OPT_TC_TILES = 1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12, 13, 14
 
 OK, EINVAL, ENOTSUP, ENOMEM, ECUDA, ETIMEOUT = 0, -22, -95, -12, -5, -110
 ROUTE_STATIC_MAX_LOGITS = 64 * 256
