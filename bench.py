@@ -186,7 +186,9 @@ def run_reference_arm(args):
         "impl": "reference", "metric": "decode_matvec_tok_s", "value": tok_s, "unit": "tok/s", "n_gpus": args.gpus,
         "steps": len(times), "warmup": max(1, args.warmup), "ms_per_step": step_s * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": name, "batch": 1, "inputs": "seeded synthetic GGUF blocks"},
+        "config": {"workload": name, "batch": 1, "layers": cpu.cfg["layers"], "weight_bytes": cpu.step_bytes,
+                   "l2": "inputs larger than L2: every layer has its own weights"},
+        "form": "CPU: the reference's row decode + fp32 dot for every product of the step, all host threads",
         "cpu_baseline": {"value": tok_s, "unit": "tok/s", "cores": cpu.cores, "kind": cpu.kind, "sample": cpu.sample_text(len(times)),
                          "cpu_gbs": cpu.step_bytes / step_s / 1e9},
         "e2e": {"value": tok_s, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -543,6 +545,10 @@ def run_ours(args):
         ctx.set_option(F.OPT_PREFETCH_MB, args.prefetch_mb)
     if args.stage_kb > 0:
         ctx.set_option(F.OPT_STAGE_KB, args.stage_kb)
+    if args.ctas_per_sm > 0:
+        ctx.set_option(F.OPT_CTAS_PER_SM, args.ctas_per_sm)
+    if args.grid_per_sm > 0:
+        ctx.set_option(F.OPT_GRID_PER_SM, args.grid_per_sm)
 
     if args.kernel:
         # one configuration alone, few launches: the process a profiler capture is taken from
@@ -551,7 +557,9 @@ def run_ours(args):
                           "peak_gbs": peak, "peak_kind": kind}), flush=True)
         return
     ds = decode_set.DecodeSet(args.workload, dev, rank=rank, world=world, layers=args.layers)
-    mode = args.mode if args.mode != "auto" else ("launches" if world == 1 else "chain")
+    # auto: the chain where it measures faster (several GPUs, one weight format: 715 vs 616 tok/s at N = 2 on the Q8_0 set);
+    # chains that mix formats run far slower than launches (the 27B set: 58 vs 217 tok/s on one GPU) and stay on launches
+    mode = args.mode if args.mode != "auto" else ("chain" if world > 1 and args.workload == "9b_q8_0" else "launches")
     if world > 1 and args.gather != "fused":
         mode = "launches"                                  # an NCCL all-gather per product cannot be chained
     st = Stepper(torch, F, ctx, ds, dist, fused=args.gather == "fused", mode=mode)
@@ -675,13 +683,14 @@ def run_ours(args):
         "vs_baseline": None, "dtype": "int8 dot products on 24-bit fixed-point x, fp32 accumulate" if ctx.get_option(F.OPT_X_BITS) == 24
         else "int8 dot products on 16-bit fixed-point x, fp32 accumulate",
         "data": "synthetic",
+        # `config` names the workload only and is the same for both arms; how this arm runs it is in `form` / `parallelism`
         "config": {"workload": args.workload, "batch": 1, "layers": ds.layers, "weight_bytes": w_bytes,
-                   "l2": "inputs larger than L2: every layer has its own weights",
-                   "form": ("one resident kernel per token step (recorded chain), every product reads its predecessor's output" if mode == "chain"
-                            else "one launch per product" + (", CUDA graph" if st.graph is not None else "")),
-                   "parallelism": "single GPU" if world == 1 else
-                   (f"row-split x{world}, y completed by tagged peer stores from the kernel epilogue (NVLink), consumers poll the data" if st.fused
-                    else f"row-split x{world} + all-gather (NCCL)")},
+                   "l2": "inputs larger than L2: every layer has its own weights"},
+        "form": ("one resident kernel per token step (recorded chain), every product reads its predecessor's output" if mode == "chain"
+                 else "one launch per product" + (", CUDA graph" if st.graph is not None else "")),
+        "parallelism": "single GPU" if world == 1 else
+        (f"row-split x{world}, y completed by tagged peer stores from the kernel epilogue (NVLink), consumers poll the data" if st.fused
+         else f"row-split x{world} + all-gather (NCCL)"),
         "roofline": roofline,
         "e2e": {"value": e2e_tok_s, "unit": "tok/s", "h2d_bytes_per_step": ds.hidden * 4, "d2h_bytes_per_step": 4,
                 "wall_tok_s": args.steps / wall},
@@ -719,6 +728,8 @@ def main():
     ap.add_argument("--kernel", default="", help="run only the named --extras case(s), comma separated, --steps timing repeats, and exit")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="N > 1: complete y by peer stores from the kernel epilogue (fused) or by an NCCL all-gather per product")
+    ap.add_argument("--ctas-per-sm", type=int, default=0, help="CTAs an SM is sized to hold in the decode kernels (0 = library default, 1)")
+    ap.add_argument("--grid-per-sm", type=int, default=0, help="CTAs per SM a decode launch creates (0 = library default, 1)")
     ap.add_argument("--stage-kb", type=int, default=0, help="size of one stage of the weight ring in KiB (0 = library default)")
     ap.add_argument("--prefetch-mb", type=int, default=-1, help="cap of the next-tensor L2 prefetch in MiB (0 = off, -1 = library default)")
     args = ap.parse_args()
