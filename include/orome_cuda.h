@@ -152,8 +152,15 @@ int  orome_format_dispatch_matvec(orome_cuda_ctx *ctx, const OromeTensorRef *ref
  * against an exact evaluation, the class of rounding the reference's own kernels apply to x
  * (shaders.metal:1470).  The first such call allocates scratch inside the context: make it
  * before any stream capture.  Smaller batches keep fp32 activations (rel-L2 <= 1e-4).
- * With a multi-GPU gather request armed (orome_cuda_gather_next), only the batch-1 quantized
- * form is available: other calls drop the request and return OROME_ENOTSUP. */
+ * Range of the fp16 operands: a weight is formed as (q - bias) * half(d * sc) + half(-dmin * mn),
+ * so |d * sc| and |dmin * mn| (Q8_0: |d|) must stay below 65504 and lose precision below 6e-5;
+ * GGUF scales of real models are orders of magnitude inside that range, and x is expected within
+ * the fp16 range as in the reference (shaders.metal:1470).  Tensors outside it: set
+ * OROME_OPT_TC_MIN_BATCH above the batch and use the fp32-activation kernels.
+ * With a multi-GPU gather request armed (orome_cuda_gather_next) the batch-1 quantized form and
+ * this tensor-core form (4 <= batch <= 64, one launch) are available: Y goes to every rank's
+ * arena from the kernel that writes it, a gathered X is read from its slots.  Any other call
+ * drops the request and returns OROME_ENOTSUP. */
 int  orome_cuda_matvec(orome_cuda_ctx *ctx, const OromeTensorRef *ref,
                        const float *x_dev, float *y_dev, int batch, int ldx, int ldy, void *stream);
 
