@@ -565,6 +565,34 @@ def run_ours(args):
     st = Stepper(torch, F, ctx, ds, dist, fused=args.gather == "fused", mode=mode)
     st.build()
     torch.cuda.synchronize()
+    fallback = None
+    if world > 1 and args.mode == "auto" and mode == "chain":
+        # Pre-flight of the automatically chosen form: two steps and the parity check on every rank.  If any rank sees an
+        # expired wait or a wrong result, every rank switches to the launch-per-product form (and the line says so).
+        ok = True
+        try:
+            for _ in range(2):
+                st.step()
+            torch.cuda.synchronize()
+            ok = ctx.status() == 0
+            if ok:
+                p = st.parity_check()
+                ok = ctx.status() == 0 and p["rel_l2"] <= 1e-4 and p["token_matches_reference_argmax"] and p["finite"]
+        except Exception as ex:                      # an expired wait surfaces as an error of ctx.status()
+            print(f"bench.py: rank {rank}: chain pre-flight failed: {ex!r}", file=sys.stderr, flush=True)
+            ok = False
+        flag = torch.tensor([1 if ok else 0], device=dev, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            try:
+                ctx.status()
+            except Exception:
+                pass
+            fallback = "the chain form failed its pre-flight check on this box; the launch-per-product form was timed instead"
+            mode = "launches"
+            st = Stepper(torch, F, ctx, ds, dist, fused=args.gather == "fused", mode=mode)
+            st.build()
+            torch.cuda.synchronize()
 
     def barrier():
         if dist is not None:
@@ -694,7 +722,7 @@ def run_ours(args):
         "roofline": roofline,
         "e2e": {"value": e2e_tok_s, "unit": "tok/s", "h2d_bytes_per_step": ds.hidden * 4, "d2h_bytes_per_step": 4,
                 "wall_tok_s": args.steps / wall},
-        "parity_check": parity,
+        "parity_check": parity, **({"fallback": fallback} if fallback else {}),
         "gpu_launches": int(launches),
         "clocks": clocks,
         "step_ms_min_med_max": [min(per) * 1e3, statistics.median(per) * 1e3, max(per) * 1e3],
