@@ -1,4 +1,4 @@
-"""Row-split products with the fused peer all-gather on two GPUs: two chained matvecs whose
+"""Row-split products with the fused peer all-gather on two and four GPUs (one process per GPU): two chained matvecs whose
 intermediate vector only exists once both ranks have stored their slices into each other's arena."""
 import os
 import socket
@@ -17,6 +17,21 @@ def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         return s.getsockname()[1]
+
+
+def _run_ranks(target, world, extra=()):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=target, args=(r, world, port, *extra, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+    assert all(ok for _, ok, _ in results), results
 
 
 def _worker(rank, world, port, fmt, n, q):
@@ -125,37 +140,15 @@ def _ep_worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
-def test_expert_parallel_moe_two_gpus():
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
-    world = 2
-    ctx = mp.get_context("spawn")
-    q = ctx.Queue()
-    port = _free_port()
-    procs = [ctx.Process(target=_ep_worker, args=(r, world, port, q)) for r in range(world)]
-    for p in procs:
-        p.start()
-    results = [q.get(timeout=240) for _ in range(world)]
-    for p in procs:
-        p.join(timeout=60)
-    assert all(ok for _, ok, _ in results), results
+@pytest.mark.parametrize("world", [2, 4])
+def test_expert_parallel_moe(world):
+    _run_ranks(_ep_worker, world)
 
 
+@pytest.mark.parametrize("world", [2, 4])
 @pytest.mark.parametrize("fmt", [synth.Q8_0, synth.Q4_K])
-def test_fused_gather_two_gpus(fmt):
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
-    world, n = 2, 1024
-    ctx = mp.get_context("spawn")
-    q = ctx.Queue()
-    port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, fmt, n, q)) for r in range(world)]
-    for p in procs:
-        p.start()
-    results = [q.get(timeout=240) for _ in range(world)]
-    for p in procs:
-        p.join(timeout=60)
-    assert all(ok for _, ok, _ in results), results
+def test_fused_gather(fmt, world):
+    _run_ranks(_worker, world, (fmt, 1024))
 
 
 def _chain_worker(rank, world, port, q):
@@ -218,20 +211,9 @@ def _chain_worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
-def test_chain_two_gpus():
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
-    world = 2
-    ctx = mp.get_context("spawn")
-    q = ctx.Queue()
-    port = _free_port()
-    procs = [ctx.Process(target=_chain_worker, args=(r, world, port, q)) for r in range(world)]
-    for p in procs:
-        p.start()
-    results = [q.get(timeout=240) for _ in range(world)]
-    for p in procs:
-        p.join(timeout=60)
-    assert all(ok for _, ok, _ in results), results
+@pytest.mark.parametrize("world", [2, 4])
+def test_chain(world):
+    _run_ranks(_chain_worker, world)
 
 
 def _batched_worker(rank, world, port, q):
@@ -290,17 +272,6 @@ def _batched_worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
-def test_batched_row_split_two_gpus():
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
-    world = 2
-    ctx = mp.get_context("spawn")
-    q = ctx.Queue()
-    port = _free_port()
-    procs = [ctx.Process(target=_batched_worker, args=(r, world, port, q)) for r in range(world)]
-    for p in procs:
-        p.start()
-    results = [q.get(timeout=240) for _ in range(world)]
-    for p in procs:
-        p.join(timeout=60)
-    assert all(ok for _, ok, _ in results), results
+@pytest.mark.parametrize("world", [2, 4])
+def test_batched_row_split(world):
+    _run_ranks(_batched_worker, world)
