@@ -5,6 +5,10 @@ module: it exists so that tests, the smoke check and the benchmark's CPU-baselin
 leg can check or time the CUDA path against a CPU statement of the reference's
 algorithm.  ``ref()`` additionally exposes the reference's own decode when it was
 compiled from the reference tree (``oracle/_ref``).
+
+Pinned against the reference's own code or vectors: the row decoders and fp16 conversion.
+Parity unpinned (restated from the shader source, no reference-held vector): scale layout B,
+routing, expert FFN / MoE block, arg-max tie order, residual / norm kernels.
 """
 from __future__ import annotations
 

@@ -16,9 +16,9 @@
  * Parity pin: decode functions are checked bit-for-bit against the reference's
  * own format.m decode (compiled from the reference tree into oracle/_ref) and
  * against the closed-form vectors of tests/test_q8_0.m, tests/test_q4k.m and
- * tests/test_f32.m.  Layout-B scales, the routing kernel and the expert FFN
- * have no reference test; they follow the shader source only (parity unpinned
- * beyond the source itself).
+ * tests/test_f32.m.  Layout-B scales, the routing kernel, the expert FFN and
+ * MoE block, and the arg-max kernel's tie order have no reference test; they
+ * follow the shader source only (parity unpinned beyond the source itself).
  */
 #include <math.h>
 #include <stdint.h>
