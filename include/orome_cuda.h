@@ -124,6 +124,11 @@ int  orome_cuda_status(orome_cuda_ctx *ctx, int *status_out);
 int  orome_cuda_upload(orome_cuda_ctx *ctx, const void *host, size_t bytes, void **dev_base);
 int  orome_cuda_free(orome_cuda_ctx *ctx, void *dev_base);
 
+/* Copy `bytes` bytes of device memory to the host after everything queued on the device has finished.  The
+ * reference reads results straight out of its shared (unified-memory) buffers, e.g. the arg-max token at
+ * engine.m:1057; on a discrete GPU that read is this call. */
+int  orome_cuda_download(orome_cuda_ctx *ctx, const void *dev, void *host, size_t bytes);
+
 /* ---- format helpers ------------------------------------------------------ */
 
 /* format_from_ggml_type, format.m:326-337 (unknown ids map to Q4_K, line 335). */

@@ -103,6 +103,15 @@ extern "C" int orome_cuda_upload(orome_cuda_ctx *c, const void *host, size_t byt
     return OROME_OK;
 }
 
+extern "C" int orome_cuda_download(orome_cuda_ctx *c, const void *dev, void *host, size_t bytes)
+{
+    if (!c || (bytes && (!dev || !host))) return fail(OROME_EINVAL, "download: NULL argument");
+    CU(cudaSetDevice(c->device));
+    CU(cudaDeviceSynchronize());
+    if (bytes) CU(cudaMemcpy(host, dev, bytes, cudaMemcpyDeviceToHost));
+    return OROME_OK;
+}
+
 extern "C" int orome_cuda_free(orome_cuda_ctx *c, void *dev_base)
 {
     if (!c) return fail(OROME_EINVAL, "free: NULL ctx");

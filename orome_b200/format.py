@@ -61,7 +61,7 @@ EXPORTS = [
     "orome_cuda_moe_route", "orome_cuda_moe_route_static", "orome_cuda_moe_ffn", "orome_cuda_moe_ffn_shard", "orome_cuda_matvec_host", "orome_cuda_set_option",
     "orome_cuda_get_option", "orome_cuda_launch_count", "orome_cuda_hint_next", "orome_cuda_peer_alloc", "orome_cuda_peer_open", "orome_cuda_peer_close", "orome_cuda_gather_setup",
     "orome_cuda_gather_arena_bytes", "orome_cuda_gather_next", "orome_cuda_gather_wait", "orome_cuda_argmax", "orome_cuda_moe_route_pair", "orome_cuda_moe_block", "orome_cuda_moe_block_scratch_floats", "orome_cuda_chain_begin", "orome_cuda_chain_end",
-    "orome_cuda_chain_launch", "orome_cuda_chain_destroy", "orome_cuda_chain_info", "orome_cuda_fuse_next",
+    "orome_cuda_chain_launch", "orome_cuda_chain_destroy", "orome_cuda_chain_info", "orome_cuda_fuse_next", "orome_cuda_download",
 ]
 
 _lib = None
@@ -85,6 +85,7 @@ def lib():
     L.orome_cuda_status.argtypes = [vp, C.POINTER(i32)]
     L.orome_cuda_upload.argtypes = [vp, vp, sz, C.POINTER(vp)]
     L.orome_cuda_free.argtypes = [vp, vp]
+    L.orome_cuda_download.argtypes = [vp, vp, vp, sz]
     L.orome_format_from_ggml_type.argtypes = [u32]
     L.orome_format_row_bytes.argtypes = [i32, u32]
     L.orome_format_row_bytes.restype = sz
@@ -167,6 +168,12 @@ class Context:
         out = C.c_void_p()
         _chk(lib().orome_cuda_upload(self._h, a.ctypes.data_as(C.c_void_p), a.nbytes, C.byref(out)))
         return int(out.value)
+
+    def download(self, dev: int, nbytes: int) -> bytes:
+        """Device memory as host bytes, after the device has finished (the reference reads its shared buffers directly)."""
+        buf = C.create_string_buffer(nbytes)
+        _chk(lib().orome_cuda_download(self._h, dev, buf, nbytes))
+        return buf.raw
 
     def free(self, dev_base: int):
         _chk(lib().orome_cuda_free(self._h, C.c_void_p(dev_base)))
