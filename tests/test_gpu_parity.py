@@ -504,3 +504,68 @@ def test_moe_ffn_expert_parallel_shares_add_up(env, world, T):
     for t in range(T):
         want = oracle.moe_ffn_f64(gate, up, down, (synth.Q4_K, synth.Q4_K, dfmt), (sg, sg, sd), xm[t], H, M, idx[t], w[t])
         assert rel_l2(total[t], want) <= REL_L2_TOL
+
+
+def test_seeded_random_shapes_every_entry_point(env):
+    """Sixty seeded random cases over formats, shapes (ragged row counts, narrow to wide rows), layouts, x widths,
+    batches, tensor offsets inside a larger buffer and the three dense entry points, each against the fp64 oracle."""
+    torch, F, ctx = env
+    rng = np.random.default_rng(20240607)
+    widths = {synth.Q8_0: [64, 192, 1024, 4096, 8192], synth.Q4_K: [256, 768, 2048, 5120], synth.Q5_K: [256, 1024, 4096],
+              synth.Q6_K: [256, 768, 2560]}
+    for case in range(60):
+        fmt = QUANT[case % 4]
+        in_dim = int(rng.choice(widths[fmt]))
+        out_dim = int(rng.integers(1, 700))
+        variant = int(rng.integers(0, 2)) if fmt in (synth.Q4_K, synth.Q5_K) else 0
+        bits = int(rng.choice([16, 24]))
+        kind = ["matvec", "group", "gate_up", "batched"][int(rng.integers(0, 4))]
+        pad = int(rng.integers(0, 8)) * 32                                  # the tensor starts `pad` bytes into its buffer
+        ctx.set_option(F.OPT_X_BITS, bits)
+        try:
+            tol = 1e-4
+            if kind == "batched":
+                batch = int(rng.integers(2, 20))
+                data = synth.host_tensor(fmt, out_dim, in_dim, seed=1000 + case)
+                x = synth.host_x(in_dim, batch, seed=2000 + case)
+                wt = dev_bytes(torch, np.concatenate([np.zeros(pad, np.uint8), data]))
+                xt, y = dev_bytes(torch, x), torch.full((batch, out_dim), float("nan"), device="cuda")
+                ctx.matvec(F.tensor_ref(wt.data_ptr(), pad, fmt, out_dim, in_dim, variant), xt.data_ptr(), y.data_ptr(), batch, in_dim, out_dim)
+                got, want = y, oracle.matvec_f64(fmt, data, out_dim, in_dim, x, layout=variant)
+                if batch >= 4 and fmt != synth.Q6_K and in_dim % 256 == 0:
+                    tol = TC_REL_L2_TOL
+            elif kind == "gate_up":
+                gd, ud = synth.host_tensor(fmt, out_dim, in_dim, seed=1000 + case), synth.host_tensor(fmt, out_dim, in_dim, seed=3000 + case)
+                x = synth.host_x(in_dim, seed=2000 + case)
+                gap = (-gd.size) % 32                                      # tensors start on 32-byte boundaries, as in a GGUF file
+                wt = dev_bytes(torch, np.concatenate([np.zeros(pad, np.uint8), gd, np.zeros(gap, np.uint8), ud]))
+                xt, y = dev_bytes(torch, x), torch.full((out_dim,), float("nan"), device="cuda")
+                ctx.gate_up_swiglu(F.tensor_ref(wt.data_ptr(), pad, fmt, out_dim, in_dim, variant),
+                                   F.tensor_ref(wt.data_ptr(), pad + gd.size + gap, fmt, out_dim, in_dim, variant), xt.data_ptr(), y.data_ptr())
+                got = y
+                want = oracle.swiglu_f64(oracle.matvec_f64(fmt, gd, out_dim, in_dim, x, layout=variant),
+                                         oracle.matvec_f64(fmt, ud, out_dim, in_dim, x, layout=variant))
+            else:
+                n_t = 1 if kind == "matvec" else int(rng.integers(2, 5))
+                rows = [out_dim] + [int(rng.integers(1, 300)) for _ in range(n_t - 1)]
+                datas = [synth.host_tensor(fmt, r, in_dim, seed=1000 + 10 * case + i) for i, r in enumerate(rows)]
+                x = synth.host_x(in_dim, seed=2000 + case)
+                datas_al = [np.concatenate([d, np.zeros((-d.size) % 32, np.uint8)]) for d in datas]      # 32-byte aligned starts
+                wt = dev_bytes(torch, np.concatenate([np.zeros(pad, np.uint8)] + datas_al))
+                xt = dev_bytes(torch, x)
+                ys = [torch.full((r,), float("nan"), device="cuda") for r in rows]
+                offs = np.cumsum([pad] + [d.size for d in datas_al[:-1]])
+                refs = [F.tensor_ref(wt.data_ptr(), int(o), fmt, r, in_dim, variant) for o, r in zip(offs, rows)]
+                if kind == "matvec":
+                    ctx.matvec(refs[0], xt.data_ptr(), ys[0].data_ptr())
+                else:
+                    ctx.matvec_group(refs, xt.data_ptr(), [y.data_ptr() for y in ys])
+                got = torch.cat(ys)
+                want = np.concatenate([oracle.matvec_f64(fmt, d, r, in_dim, x, layout=variant) for d, r in zip(datas, rows)])
+            torch.cuda.synchronize()
+            err = rel_l2(got.cpu().numpy(), want)
+            if bits == 16 and kind == "gate_up":
+                tol = 3e-4                     # the product of two 16-bit-x results: the option's documented bound
+            assert err <= tol, (case, kind, fmt, out_dim, in_dim, variant, bits, pad, err)
+        finally:
+            ctx.set_option(F.OPT_X_BITS, 24)
