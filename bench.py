@@ -537,6 +537,9 @@ def run_ours(args):
         dist = dist_mod
     dev = torch.device("cuda", local)
     ctx = F.Context(local)
+    if args.x_bits < 0:
+        chained = args.mode == "chain" or (args.mode == "auto" and world > 1)
+        args.x_bits = 24 if chained else 16
     if args.x_bits:
         ctx.set_option(F.OPT_X_BITS, args.x_bits)
     if args.prefetch_mb >= 0:
@@ -707,7 +710,8 @@ def run_ours(args):
         "metric": "decode_matvec_tok_s", "value": tok_s, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
         "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "int8 dot products on 24-bit fixed-point x, fp32 accumulate" if ctx.get_option(F.OPT_X_BITS) == 24
-        else "int8 dot products on 16-bit fixed-point x, fp32 accumulate",
+        else ("int8 dot products on 16-bit fixed-point x, fp32 accumulate" if mode == "chain" else
+              "int8 dot products on fixed-point x (16-bit for plain products, 24-bit for the fused gate/up), fp32 accumulate"),
         "data": "synthetic",
         # `config` names the workload only and is the same for both arms; how this arm runs it is in `form` / `parallelism`
         "config": {"workload": args.workload, "batch": 1, "layers": ds.layers, "weight_bytes": w_bytes,
@@ -743,10 +747,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="9b_q8_0", choices=["9b_q8_0", "27b_q4_k_m"])
     ap.add_argument("--layers", type=int, default=None, help="override the number of layers (smaller captures for profiling)")
-    ap.add_argument("--x-bits", type=int, default=24, choices=[0, 16, 24],
-                    help="width of the per-group fixed-point form of x inside the kernels: 24 (default, the library's default: products "
-                         "within 2e-7 of the oracle), 16 (about 3 %% faster; products within about 3e-5, the fused gate/up output up to "
-                         "1e-4 on small row samples, which leaves the parity check of this bench too little margin), 0 = leave the library's default")
+    ap.add_argument("--x-bits", type=int, default=-1, choices=[-1, 0, 16, 24],
+                    help="width of the per-group fixed-point form of x inside the kernels: 24 (the library's default: products within 2e-7 "
+                         "of the oracle), 16 (plain products within about 3e-5, finer than the fp16 x of the reference's kernels; the fused "
+                         "gate/up form stays at 24 bits), 0 = leave the library's default; -1 (default): 16 for the launch-per-product form "
+                         "on one GPU, where the consumers' speed counts, 24 for chains (one width for all products, fused ones included)")
     ap.add_argument("--mode", default="auto", choices=["auto", "chain", "launches"],
                     help="auto: launches on one GPU, chain on several; chain: the step is recorded once and runs as one resident kernel; launches: one kernel per product (CUDA graph)")
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -427,10 +427,12 @@ int  orome_cuda_matvec_host(orome_cuda_ctx *ctx, const OromeTensorRef *ref,
 /* Integer options; unknown keys return OROME_EINVAL.
  *   OROME_OPT_X_BITS      16 or 24: fixed-point width used for x inside the
  *                         quantized matvec kernels (default 24: products within 2e-6 of an
- *                         exact evaluation).  16 is about 3 % faster on Q8_0; a product is
- *                         then within about 3e-5, which is inside the path's 1e-4, but the
- *                         fused gate/up output (a product of two such results) can reach
- *                         1e-4 on small row sets.
+ *                         exact evaluation).  16 makes plain products about 3 % faster on
+ *                         Q8_0 at about 3e-5 (finer than the fp16 x of the reference's kernels,
+ *                         inside the path's 1e-4).  The fused gate/up form reads x at 24 bits
+ *                         whatever the option says: its output is a product of two results
+ *                         and reached 1e-4 at 16 bits.  A recorded chain uses one width for all
+ *                         of its products: the option's.
  *   OROME_OPT_FORCE_GENERIC  1 = always use the plain (non-pipelined) kernels. */
 #define OROME_OPT_X_BITS         1
 #define OROME_OPT_FORCE_GENERIC  2

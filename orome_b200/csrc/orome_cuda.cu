@@ -420,7 +420,7 @@ static int plan_pipe(orome_cuda_ctx *c, int fmt, uint32_t in_dim, uint32_t total
     a.group_threads = orome_pipe_group_threads(fmt, in_dim);
     a.total_rows = total_rows;
     p.minb = c->ctas_per_sm >= 2 && a.group_threads <= PIPE_CONSUMERS_2CTA && !combine ? 2 : 1;
-    if (fmt == FMT_Q6_K && c->x_bits == 24 && swiglu) p.minb = 1;   // needs more than the 96 registers of the two-CTA build
+    if (fmt == FMT_Q6_K && swiglu) p.minb = 1;   // the fused form reads x at 24 bits: more than the 96 registers of the two-CTA build
     const uint32_t max_consumers = p.minb == 2 ? PIPE_CONSUMERS_2CTA : PIPE_MAX_CONSUMERS;
     a.rows_par = std::max(1u, std::min((uint32_t)PIPE_MAX_ROWS_PAR, max_consumers / a.group_threads));
     a.rows_par = std::min(a.rows_par, std::max(1u, total_rows));
@@ -452,7 +452,9 @@ static int plan_pipe(orome_cuda_ctx *c, int fmt, uint32_t in_dim, uint32_t total
     const size_t red_bytes = (size_t)2 * a.red_rows * gw * (swiglu ? 2 : 1) * sizeof(float);
     a.xs_base = (uint32_t)((a.red_base + red_bytes + 127) / 128 * 128);
     // quantized x: one byte plane per 8 bits of x, a scale per group (16 for Q6_K, else 32), a sum per 32 elements
-    const size_t np = c->x_bits == 24 ? 3 : 2;
+    // the fused gate/up form always reads x at 24 bits: its output is a product of two results, which at 16 bits can
+    // leave the 1e-4 bound (measured: 5e-5 typical, 1.1e-4 on small row sets); plain products follow the option
+    const size_t np = (c->x_bits == 24 || swiglu) ? 3 : 2;
     const size_t xq_vec = (np * in_dim + (size_t)in_dim / (fmt == FMT_Q6_K ? 16 : 32) * 4 + (size_t)in_dim / 32 * 4 + 15) / 16 * 16;
     a.xq_vec_bytes = (uint32_t)xq_vec;
     const size_t xq_bytes = xq_vec * (combine ? std::max(a.nseg, 1) : 1);
@@ -543,7 +545,7 @@ static int launch_pipe_np(orome_cuda_ctx *c, const PipePlan &p, int mode, cudaSt
 template <int FMT>
 static int launch_pipe_fmt(orome_cuda_ctx *c, const PipePlan &p, int mode, cudaStream_t st)
 {
-    return c->x_bits == 24 ? launch_pipe_np<FMT, 3>(c, p, mode, st) : launch_pipe_np<FMT, 2>(c, p, mode, st);
+    return (c->x_bits == 24 || mode == 1) ? launch_pipe_np<FMT, 3>(c, p, mode, st) : launch_pipe_np<FMT, 2>(c, p, mode, st);
 }
 
 static int launch_pipe(orome_cuda_ctx *c, int fmt, const PipePlan &p, int mode, cudaStream_t st)
@@ -711,12 +713,13 @@ static int launch_mma(orome_cuda_ctx *c, int fmt, MmaPlan &p, bool swiglu, cudaS
     int rc = mma_encode_maps(c, fmt, p, swiglu);
     if (rc) return rc;
     const bool b24 = c->x_bits == 24;
+    // the fused form always reads x at 24 bits (see plan_pipe)
     if (fmt == FMT_Q4_K) {
-        if (swiglu) return b24 ? launch_mma_inst<FMT_Q4_K, 3, true>(c, p, st) : launch_mma_inst<FMT_Q4_K, 2, true>(c, p, st);
+        if (swiglu) return launch_mma_inst<FMT_Q4_K, 3, true>(c, p, st);
         return b24 ? launch_mma_inst<FMT_Q4_K, 3, false>(c, p, st) : launch_mma_inst<FMT_Q4_K, 2, false>(c, p, st);
     }
     if (fmt == FMT_Q6_K) return b24 ? launch_mma_inst<FMT_Q6_K, 3, false>(c, p, st) : launch_mma_inst<FMT_Q6_K, 2, false>(c, p, st);
-    if (swiglu) return b24 ? launch_mma_inst<FMT_Q5_K, 3, true>(c, p, st) : launch_mma_inst<FMT_Q5_K, 2, true>(c, p, st);
+    if (swiglu) return launch_mma_inst<FMT_Q5_K, 3, true>(c, p, st);
     return b24 ? launch_mma_inst<FMT_Q5_K, 3, false>(c, p, st) : launch_mma_inst<FMT_Q5_K, 2, false>(c, p, st);
 }
 
