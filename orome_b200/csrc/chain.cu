@@ -430,8 +430,6 @@ extern "C" int orome_cuda_chain_end(orome_cuda_ctx *c, orome_cuda_chain **out)
             if (r != c->g_rank) a.peer_delta[np++] = (long long)(c->g_arena[r] - arena);
         a.npeers = np;
         a.rank = c->g_rank;
-        // the last 256 bytes of every arena: one progress word per rank
-        a.progress = reinterpret_cast<unsigned int *>(const_cast<uint8_t *>(arena) + 3 * c->g_data_bytes);
     }
     *out = ch;
     return OROME_OK;

@@ -19,10 +19,13 @@
 //     row, rows side by side) is per product and comes from the table.
 //   * Polling every element from every thread would flood L2 (71 000 threads re-reading the same 32 KB while the
 //     weight stream needs that bandwidth), so completion is also COUNTED: a CTA that has stored its rows of a
-//     product bumps that product's counter, the CTA that completes the count stores the product's tag into a
-//     progress word of every GPU, and consumers have one lane per warp watch the counter (and the peers' progress
-//     words) before anyone touches the slots.  Counters and progress words are hints without memory ordering: the
-//     tags stay the guarantee, a slot that is not visible yet when the hint is just gets polled.
+//     product bumps that product's counter, and consumers have one lane per warp watch the counter before anyone
+//     touches the slots.  The counter is a hint without memory ordering: the tags stay the guarantee, a slot that
+//     is not visible yet when the hint is just gets polled.  The counter covers THIS GPU's rows only; the peers'
+//     slices are simply polled for (their stores are on their way while this GPU finishes its own rows).  A second
+//     hint for them -- a progress word that the CTA completing a count stored into every peer, watched with
+//     system-scope loads -- was measured and removed: it put a second NVLink hop behind the data it announced
+//     (N = 4: 728 -> 956 tok/s on the 9B Q8_0 set, N = 2: 695 -> 745).
 //   * Every wait is bounded (wait_cycles); expiry sets the status word, is sticky for the rest of the launch, and
 //     a launch that finds the status word set does not wait at all.
 //
@@ -55,7 +58,7 @@ struct alignas(16) ChainProd {
     uint8_t nseg, mode, layout, fmt;
     uint8_t publish;            // outputs also go to the peers' slots
     uint8_t argmax;             // the launch also reduces this product's outputs to the index of their maximum
-    uint8_t dep_peers;          // the product that writes the input is row-split over the GPUs: the peers' progress counts too
+    uint8_t dep_peers;          // the product that writes the input is row-split over the GPUs (kept for diagnostics)
     uint8_t iters;              // rows per group and tile
     uint32_t in_dim, row_bytes, units, group_threads;
     uint32_t rows_par, half_stride, total_rows, red_rows;
@@ -77,7 +80,6 @@ struct ChainArgs {
     unsigned int *arrived;      // CTAs that finished the launch
     unsigned int *epoch;        // launches of this chain so far
     unsigned int *done;         // [nprods] CTAs that finished each product, counted over all launches: (epoch + 1) * grid when complete
-    unsigned int *progress;     // [world] in this GPU's arena: tag of the last published product each rank completed (peers write theirs)
     int rank;
     long long wait_cycles;
     unsigned long long *argmax_part;   // [grid] per-CTA candidates of the arg-max epilogue
@@ -299,37 +301,24 @@ __device__ __forceinline__ unsigned int ld_hint_sys(const unsigned int *p)
     return v;
 }
 
-// One lane per warp waits until every CTA here (and, for a row-split vector, every peer) reports the product that
-// writes this product's input as complete.  Returns false when the wait ran out.
-__device__ __forceinline__ bool chain_wait_input(const ChainArgs &a, const ChainProd &P, unsigned int base, unsigned int target)
+// One lane per warp waits until every CTA of this GPU reports the product that writes this product's input as
+// complete.  Returns false when the wait ran out.
+__device__ __forceinline__ bool chain_wait_input(const ChainArgs &a, const ChainProd &P, unsigned int target)
 {
     const unsigned int *cnt = a.done + (P.x_tag - 1u);
-    const unsigned int want = chain_tag(base, P.x_tag);
     const long long t0 = clock64();
     for (uint32_t it = 0;; ++it) {
-        bool ready = (int)(ld_hint(cnt) - target) >= 0;
-        if (ready && P.dep_peers)
-            for (int r = 0; r <= a.npeers; ++r)
-                if (r != a.rank && (int)((ld_hint_sys(a.progress + r) - want) << 1) < 0) ready = false;
-        if (ready) return true;
+        if ((int)(ld_hint(cnt) - target) >= 0) return true;
         if (clock64() - t0 > a.wait_cycles) return false;
         if ((it & 63u) == 63u && *reinterpret_cast<const volatile int *>(a.status) != 0) return false;
         __nanosleep(32);
     }
 }
 
-// A CTA is done with product p (its rows are stored, or it had none): count it; the CTA that completes the count
-// tells every GPU.
-__device__ __forceinline__ void chain_signal_done(const ChainArgs &a, const ChainProd &P, uint32_t p, unsigned int base, unsigned int target)
+// A CTA is done with product p (its rows are stored, or it had none): count it.
+__device__ __forceinline__ void chain_signal_done(const ChainArgs &a, uint32_t p)
 {
-    const unsigned int before = atomicAdd(a.done + p, 1u);
-    if (P.publish && before + 1u == target) {
-        const unsigned int tag = chain_tag(base, P.y_tag);
-        unsigned int *mine = a.progress + a.rank;
-        *reinterpret_cast<volatile unsigned int *>(mine) = tag;
-        for (int q = 0; q < a.npeers; ++q)
-            *reinterpret_cast<volatile unsigned int *>(reinterpret_cast<uint8_t *>(mine) + a.peer_delta[q]) = tag;
-    }
+    atomicAdd(a.done + p, 1u);
 }
 
 // A vector completed by the peers, copied from its slots to its plain place (for readers outside the chain).
@@ -487,13 +476,13 @@ gemv_chain_kernel(const __grid_constant__ ChainArgs a)
         if (lo >= hi) {          // no row of this product here: nothing to wait for, nothing to write
             cp_async_wait_all();
             named_bar_sync(PIPE_BAR_CONSUMERS, CHAIN_CONSUMERS);
-            if (tid == 0 && !unpack) chain_signal_done(a, P, p, base, target);
+            if (tid == 0 && !unpack) chain_signal_done(a, p);
             continue;
         }
         if (tid == 0) CHAIN_STAMP(a, p, 0);
         if (P.xs && !s_abort) {  // the input comes out of the chain: one lane per warp watches for its completion
             int ok = 1;
-            if (lane == 0) ok = chain_wait_input(a, P, base, target);
+            if (lane == 0) ok = chain_wait_input(a, P, target);
             ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok && !s_abort) { s_abort = 1; atomicExch(a.status, 3); }
         }
@@ -508,7 +497,7 @@ gemv_chain_kernel(const __grid_constant__ ChainArgs a)
             chain_dispatch<NP>(a, P, smem, full, empty, lo, hi, s, parity, base, &s_abort, best, p);
         }
         named_bar_sync(PIPE_BAR_CONSUMERS, CHAIN_CONSUMERS);      // every thread has issued its stores of this product
-        if (tid == 0) { chain_signal_done(a, P, p, base, target); CHAIN_STAMP(a, p, 5); }
+        if (tid == 0) { chain_signal_done(a, p); CHAIN_STAMP(a, p, 5); }
     }
 
     // ---- arg-max epilogue: the CTA's best candidate, then the last CTA to arrive reduces all of them
