@@ -409,15 +409,13 @@ extern "C" int orome_cuda_chain_end(orome_cuda_ctx *c, orome_cuda_chain **out)
     // ---- device copies ---------------------------------------------------------------------------------------------
     CU(cudaMalloc(&ch->prods_dev, n * sizeof(ChainProd)));
     CU(cudaMemcpy(ch->prods_dev, ch->prods.data(), n * sizeof(ChainProd), cudaMemcpyHostToDevice));
-    CU(cudaMalloc(&ch->words_dev, (16 + n) * sizeof(unsigned int)));       // [0] arrivals of a launch, [1] launches so far, [16..] per-product counts
-    CU(cudaMemset(ch->words_dev, 0, (16 + n) * sizeof(unsigned int)));
+    CU(cudaMalloc(&ch->words_dev, 16 * sizeof(unsigned int)));       // [0] arrivals of a launch
+    CU(cudaMemset(ch->words_dev, 0, 16 * sizeof(unsigned int)));
     a.prods = ch->prods_dev;
     a.nprods = (uint32_t)n;
     a.status = c->status_dev;
     a.gen = c->chain_gen_dev;
     a.arrived = ch->words_dev;
-    a.epoch = ch->words_dev + 1;
-    a.done = ch->words_dev + 16;
     a.rank = 0;
     if (argmax_out) {
         CU(cudaMalloc(&ch->argmax_part, (size_t)ch->grid * sizeof(unsigned long long)));

@@ -17,15 +17,11 @@
 //   * Consumers (15 warps) are the pipelined kernel's: x as per-group fixed point in byte planes, dp4a against
 //     the packed weights as they lie, per-row partial sums flushed in batches.  The thread mapping (threads per
 //     row, rows side by side) is per product and comes from the table.
-//   * Polling every element from every thread would flood L2 (71 000 threads re-reading the same 32 KB while the
-//     weight stream needs that bandwidth), so completion is also COUNTED: a CTA that has stored its rows of a
-//     product bumps that product's counter, and consumers have one lane per warp watch the counter before anyone
-//     touches the slots.  The counter is a hint without memory ordering: the tags stay the guarantee, a slot that
-//     is not visible yet when the hint is just gets polled.  The counter covers THIS GPU's rows only; the peers'
-//     slices are simply polled for (their stores are on their way while this GPU finishes its own rows).  A second
-//     hint for them -- a progress word that the CTA completing a count stored into every peer, watched with
-//     system-scope loads -- was measured and removed: it put a second NVLink hop behind the data it announced
-//     (N = 4: 728 -> 956 tok/s on the 9B Q8_0 set, N = 2: 695 -> 745).
+//   * Nothing announces a finished product: a reader goes straight to the slots, takes what carries the tag and polls
+//     (bounded) for what does not yet.  Completion counters per product, watched by one lane per warp before anyone
+//     touched the slots, and progress words stored into the peers, were built to keep 71 000 threads from re-reading
+//     the same 32 KB; measured, they only delayed the readers (9B Q8_0 set: N = 1 552 -> 604 tok/s without them,
+//     N = 2 695 -> 768, N = 4 728 -> 982) and were removed.
 //   * Every wait is bounded (wait_cycles); expiry sets the status word, is sticky for the rest of the launch, and
 //     a launch that finds the status word set does not wait at all.
 //
@@ -78,8 +74,6 @@ struct ChainArgs {
     int *status;
     unsigned int *gen;          // generation base of the chain's tags, advanced by nprods when a launch ends
     unsigned int *arrived;      // CTAs that finished the launch
-    unsigned int *epoch;        // launches of this chain so far
-    unsigned int *done;         // [nprods] CTAs that finished each product, counted over all launches: (epoch + 1) * grid when complete
     int rank;
     long long wait_cycles;
     unsigned long long *argmax_part;   // [grid] per-CTA candidates of the arg-max epilogue
@@ -288,38 +282,6 @@ __device__ __forceinline__ void chain_product(const ChainArgs &a, const ChainPro
     if (tid == 0) CHAIN_STAMP(a, p, 4);
 }
 
-__device__ __forceinline__ unsigned int ld_hint(const unsigned int *p)
-{
-    unsigned int v;
-    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ unsigned int ld_hint_sys(const unsigned int *p)
-{
-    unsigned int v;
-    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-
-// One lane per warp waits until every CTA of this GPU reports the product that writes this product's input as
-// complete.  Returns false when the wait ran out.
-__device__ __forceinline__ bool chain_wait_input(const ChainArgs &a, const ChainProd &P, unsigned int target)
-{
-    const unsigned int *cnt = a.done + (P.x_tag - 1u);
-    const long long t0 = clock64();
-    for (uint32_t it = 0;; ++it) {
-        if ((int)(ld_hint(cnt) - target) >= 0) return true;
-        if (clock64() - t0 > a.wait_cycles) return false;
-        if ((it & 63u) == 63u && *reinterpret_cast<const volatile int *>(a.status) != 0) return false;
-        __nanosleep(32);
-    }
-}
-
-// A CTA is done with product p (its rows are stored, or it had none): count it.
-__device__ __forceinline__ void chain_signal_done(const ChainArgs &a, uint32_t p)
-{
-    atomicAdd(a.done + p, 1u);
-}
 
 // A vector completed by the peers, copied from its slots to its plain place (for readers outside the chain).
 template <int C>      // consumer threads of the calling kernel
@@ -466,7 +428,6 @@ gemv_chain_kernel(const __grid_constant__ ChainArgs a)
     uint32_t s = 0, parity = 0;
     unsigned long long *best = s_best + (tid >> 5);
     if (lane == 0) *best = 0ull;
-    const unsigned int target = (*reinterpret_cast<const volatile unsigned int *>(a.epoch) + 1u) * G;     // count of a complete product
     for (uint32_t p = 0; p < a.nprods; ++p) {
         const ChainProd &P = desc[p % 3];
         // the next product's descriptor goes into the buffer that held product p - 2, which every thread has left
@@ -476,16 +437,9 @@ gemv_chain_kernel(const __grid_constant__ ChainArgs a)
         if (lo >= hi) {          // no row of this product here: nothing to wait for, nothing to write
             cp_async_wait_all();
             named_bar_sync(PIPE_BAR_CONSUMERS, CHAIN_CONSUMERS);
-            if (tid == 0 && !unpack) chain_signal_done(a, p);
             continue;
         }
         if (tid == 0) CHAIN_STAMP(a, p, 0);
-        if (P.xs && !s_abort) {  // the input comes out of the chain: one lane per warp watches for its completion
-            int ok = 1;
-            if (lane == 0) ok = chain_wait_input(a, P, target);
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok && !s_abort) { s_abort = 1; atomicExch(a.status, 3); }
-        }
         if (tid == 0) CHAIN_STAMP(a, p, 1);
         if (unpack) {
             chain_unpack<CHAIN_CONSUMERS>(a, P, lo, hi, base, &s_abort);
@@ -497,7 +451,7 @@ gemv_chain_kernel(const __grid_constant__ ChainArgs a)
             chain_dispatch<NP>(a, P, smem, full, empty, lo, hi, s, parity, base, &s_abort, best, p);
         }
         named_bar_sync(PIPE_BAR_CONSUMERS, CHAIN_CONSUMERS);      // every thread has issued its stores of this product
-        if (tid == 0) { chain_signal_done(a, p); CHAIN_STAMP(a, p, 5); }
+        if (tid == 0) CHAIN_STAMP(a, p, 5);
     }
 
     // ---- arg-max epilogue: the CTA's best candidate, then the last CTA to arrive reduces all of them
@@ -527,7 +481,6 @@ gemv_chain_kernel(const __grid_constant__ ChainArgs a)
             }
             *reinterpret_cast<volatile unsigned int *>(a.arrived) = 0;
             *reinterpret_cast<volatile unsigned int *>(a.gen) = base + a.nprods;
-            *reinterpret_cast<volatile unsigned int *>(a.epoch) = *reinterpret_cast<volatile unsigned int *>(a.epoch) + 1u;
         }
     }
 }
