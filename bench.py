@@ -455,7 +455,8 @@ def kernel_extras(torch, F, ctx, peak, only=None, reps=3):
     gemv("q4_k_12288x4096_b1", synth.Q4_K, 12288, 4096, 12)
     gemv("q4_k_4096x12288_b1", synth.Q4_K, 4096, 12288, 12)
     gemv("q8_0_12288x4096_b8_tcgen05", synth.Q8_0, 12288, 4096, 6, batch=8)
-    gemv("q6_k_5120x17408_b8_per_vector", synth.Q6_K, 5120, 17408, 3, batch=8)
+    gemv("q6_k_5120x17408_b8_tcgen05", synth.Q6_K, 5120, 17408, 3, batch=8)
+    gemv("q6_k_5120x17408_b64_tcgen05", synth.Q6_K, 5120, 17408, 3, batch=64)
     gemv("q4_k_12288x4096_b64_tcgen05", synth.Q4_K, 12288, 4096, 6, batch=64)
     gemv("q4_k_4096x12288_b64_tcgen05", synth.Q4_K, 4096, 12288, 6, batch=64)
     gemv("q5_k_12288x4096_b1", synth.Q5_K, 12288, 4096, 10)

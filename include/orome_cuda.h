@@ -152,13 +152,13 @@ int  orome_format_dispatch_matvec(orome_cuda_ctx *ctx, const OromeTensorRef *ref
  * b < batch, x row stride ldx, y row stride ldy (in floats).  batch == 1 is the
  * decode matvec; larger batches are the prefill form, which the reference runs
  * as one matvec per token (main.m:745-747).  Batches of OROME_OPT_TC_MIN_BATCH (default 4)
- * and more on Q8_0 / Q4_K / Q5_K tensors whose in_dim is a multiple of 256 run on the tensor
+ * and more on Q8_0 / Q4_K / Q5_K / Q6_K tensors whose in_dim is a multiple of 256 run on the tensor
  * cores (tcgen05) with weights and x rounded to fp16 and fp32 accumulation: rel-L2 <= 5e-4
  * against an exact evaluation, the class of rounding the reference's own kernels apply to x
  * (shaders.metal:1470).  The first such call allocates scratch inside the context: make it
  * before any stream capture.  Smaller batches keep fp32 activations (rel-L2 <= 1e-4).
  * Range of the fp16 operands: a weight is formed as (q - bias) * half(d * sc) + half(-dmin * mn),
- * so |d * sc| and |dmin * mn| (Q8_0: |d|) must stay below 65504 and lose precision below 6e-5;
+ * so |d * sc| and |dmin * mn| (Q8_0: |d|; Q6_K: |d * sc| only) must stay below 65504 and lose precision below 6e-5;
  * GGUF scales of real models are orders of magnitude inside that range, and x is expected within
  * the fp16 range as in the reference (shaders.metal:1470).  Tensors outside it: set
  * OROME_OPT_TC_MIN_BATCH above the batch and use the fp32-activation kernels.

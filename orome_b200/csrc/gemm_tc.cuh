@@ -435,11 +435,48 @@ __device__ __forceinline__ void tc_st16(uint32_t taddr, const uint4 (&v)[4])
 //   Q4_K: header (d, dmin, 12 scale bytes), 32 quant bytes (low nibbles = sub-block 2kq, high = 2kq+1).
 //   Q5_K: the same plus the 32 bytes of fifth bits (all eight sub-blocks share them).
 //   Q8_0: the 80 bytes from the 16-byte boundary at or below byte 68*kq of the chunk; the thread's 68 bytes start kq words in.
+//   Q6_K (210-byte superblocks, 2-byte aligned): thread kq takes half n = kq / 2 of the superblock and the elements
+//   l = 16 (kq % 2) .. + 15 of that half's four 32-groups (weights 128 n + 32 j + l, j = 0..3): 16 bytes of ql[l],
+//   16 of ql[32 + l], 16 of qh[l], the half's eight scale bytes and d.  (Taking 64 consecutive weights instead would
+//   need all 64 ql bytes for one of their nibbles each.)
 template <int FMT> struct TcPacked { uint4 p[FMT == FMT_Q4_K ? 3 : 5]; };
+template <> struct TcPacked<FMT_Q6_K> { uint32_t qa[4], qb[4], qh[4], sc[2], d; };
+
+// N consecutive 32-bit words from a 2-byte aligned address: aligned word loads, one more and a funnel shift when the
+// address is 2 (mod 4).  Reads at most two bytes before p and never a whole word past p + 4 N.
+template <int N>
+__device__ __forceinline__ void ldg_words_a2(const uint8_t *p, uint32_t (&out)[N])
+{
+    const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+    const uint32_t *q = reinterpret_cast<const uint32_t *>(a & ~(uintptr_t)3);
+    const bool odd = (a & 2u) != 0;
+    uint32_t w[N + 1];
+#pragma unroll
+    for (int i = 0; i < N; ++i) w[i] = __ldg(q + i);
+    w[N] = odd ? __ldg(q + N) : 0u;
+    const uint32_t sh = odd ? 16u : 0u;
+#pragma unroll
+    for (int i = 0; i < N; ++i) out[i] = __funnelshift_r(w[i], w[i + 1], sh);
+}
 
 template <int FMT>
 __device__ __forceinline__ void tc_load_packed(const uint8_t *chunk, uint32_t kq, bool live, TcPacked<FMT> &d)
 {
+    if constexpr (FMT == FMT_Q6_K) {
+        if (!live) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) d.qa[i] = d.qb[i] = d.qh[i] = 0u;
+            d.sc[0] = d.sc[1] = d.d = 0u;
+            return;
+        }
+        const uint32_t n = kq >> 1, l0 = 16u * (kq & 1u);
+        ldg_words_a2<4>(chunk + 64u * n + l0, d.qa);
+        ldg_words_a2<4>(chunk + 64u * n + 32u + l0, d.qb);
+        ldg_words_a2<4>(chunk + 128u + 32u * n + l0, d.qh);
+        ldg_words_a2<2>(chunk + 192u + 8u * n, d.sc);
+        d.d = __ldg(reinterpret_cast<const unsigned short *>(chunk + 208));
+        return;
+    } else {
     constexpr int N = FMT == FMT_Q4_K ? 3 : 5;
     if (!live) {
 #pragma unroll
@@ -460,6 +497,7 @@ __device__ __forceinline__ void tc_load_packed(const uint8_t *chunk, uint32_t kq
             d.p[3] = __ldg(reinterpret_cast<const uint4 *>(chunk + 16));
             d.p[4] = __ldg(reinterpret_cast<const uint4 *>(chunk + 32));
         }
+    }
     }
 }
 
@@ -514,14 +552,50 @@ __device__ __forceinline__ void tc_dequant_half(const TcPacked<FMT> &d, uint32_t
     }
 }
 
+__device__ __forceinline__ void tc_st8(uint32_t taddr, const uint32_t (&v)[8])
+{
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                 ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]) : "memory");
+}
+
+// Q6_K, 32-group J of the thread's half: its 16 weights (q - 32) * d * scale as fp16, two per word (format.m:131-174:
+// ql nibble | two qh bits << 4, scale 8 n + 2 J + l / 16).
+template <int KQ, int J>
+__device__ __forceinline__ void tc_dequant_q6_group(const TcPacked<FMT_Q6_K> &d, uint32_t (&out)[8])
+{
+    constexpr int SI = (KQ & 1) + 2 * J;             // scale byte inside the half's eight
+    const int sc = (int)(signed char)((d.sc[SI >> 2] >> (8 * (SI & 3))) & 0xffu);
+    const float dd = __half2float(__ushort_as_half((unsigned short)d.d));
+    const __half2 scale = __float2half2_rn(dd * (float)sc), bias = __float2half2_rn(1056.0f), addend = __float2half2_rn(0.0f);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t ql = (J & 1) ? d.qb[i] : d.qa[i];
+        const uint32_t lo = (J < 2 ? ql : ql >> 4) & 0x0F0F0F0Fu;
+        const uint32_t w = lo | (((d.qh[i] >> (2 * J)) & 0x03030303u) << 4);
+        out[2 * i] = h2_bits(two_weights(w, 0x5140u, bias, scale, addend));
+        out[2 * i + 1] = h2_bits(two_weights(w, 0x7362u, bias, scale, addend));
+    }
+}
+
+// taddr: the thread's lane and the stage's column 32 * KQ (two weights per column).
 template <int FMT, int KQ>
 __device__ __forceinline__ void tc_convert_unit(const TcPacked<FMT> &d, int layout, uint32_t taddr)
 {
+    if constexpr (FMT == FMT_Q6_K) {
+        // group J, elements 16 (KQ % 2) ..: weights 128 (KQ / 2) + 32 J + 16 (KQ % 2) .., i.e. column 64 (KQ / 2) + 16 J + 8 (KQ % 2)
+        const uint32_t col = taddr - 24u * (KQ & 1);
+        uint32_t v[8];
+        tc_dequant_q6_group<KQ, 0>(d, v); tc_st8(col, v);
+        tc_dequant_q6_group<KQ, 1>(d, v); tc_st8(col + 16u, v);
+        tc_dequant_q6_group<KQ, 2>(d, v); tc_st8(col + 32u, v);
+        tc_dequant_q6_group<KQ, 3>(d, v); tc_st8(col + 48u, v);
+    } else {
 #pragma unroll
-    for (uint32_t h = 0; h < 2; ++h) {
-        uint4 v[4];
-        tc_dequant_half<FMT, KQ>(d, h, layout, v);
-        tc_st16(taddr + h * 16u, v);
+        for (uint32_t h = 0; h < 2; ++h) {
+            uint4 v[4];
+            tc_dequant_half<FMT, KQ>(d, h, layout, v);
+            tc_st16(taddr + h * 16u, v);
+        }
     }
 }
 

@@ -979,7 +979,12 @@ extern "C" int orome_cuda_matvec_group(orome_cuda_ctx *c, const OromeTensorRef *
 // ---------------------------------------------------------------------------
 // batched form on the tensor cores
 // ---------------------------------------------------------------------------
-static bool tc_supported(int fmt, uint32_t in_dim) { return (fmt == FMT_Q8_0 || fmt == FMT_Q4_K || fmt == FMT_Q5_K) && in_dim % TC_KC == 0; }
+// Q6_K (rows only 2-byte aligned, no tensor map possible) exists in the tensor-memory form only.
+static bool tc_supported(const orome_cuda_ctx *c, int fmt, uint32_t in_dim)
+{
+    if (in_dim % TC_KC != 0) return false;
+    return fmt == FMT_Q8_0 || fmt == FMT_Q4_K || fmt == FMT_Q5_K || (fmt == FMT_Q6_K && !c->tc_slabs);
+}
 
 template <int FMT>
 static int launch_tca_fmt(orome_cuda_ctx *c, const TcArgs &a, int grid, size_t smem, cudaStream_t st)
@@ -1034,7 +1039,7 @@ static int launch_tc(orome_cuda_ctx *c, int fmt, const uint8_t *data, uint32_t o
     TcPub no_pub;
     memset(&no_pub, 0, sizeof no_pub);
     if (!pub) pub = &no_pub;
-    const uint32_t chunk_bytes = fmt == FMT_Q8_0 ? 272u : fmt == FMT_Q4_K ? 144u : 176u;
+    const uint32_t chunk_bytes = fmt == FMT_Q8_0 ? 272u : fmt == FMT_Q4_K ? 144u : fmt == FMT_Q5_K ? 176u : 210u;
     const uint32_t chunks = in_dim / TC_KC, tiles = (out_dim + TC_M - 1) / TC_M;
     // Split K so that the SMs stay busy: a CTA costs about one time unit per chunk plus about five to set up (TMEM,
     // barriers, pipeline fill -- measured: three parts in two waves were slower than one part on 96 of 148 SMs), the
@@ -1066,7 +1071,7 @@ static int launch_tc(orome_cuda_ctx *c, int fmt, const uint8_t *data, uint32_t o
         if (rc) return rc;
         TcArgs a;
         memset(&a, 0, sizeof a);
-        {
+        if (c->tc_slabs) {      // the staged form fetches its packed weights with tensor copies
             EncodeTiledFn enc = encode_tiled_fn();
             if (!enc) return fail(OROME_ECUDA, "gemm_tc: cuTensorMapEncodeTiled is not available");
             const cuuint64_t dims[2] = {(cuuint64_t)row_bytes_of(fmt, in_dim) / 4, out_dim};
@@ -1098,7 +1103,8 @@ static int launch_tc(orome_cuda_ctx *c, int fmt, const uint8_t *data, uint32_t o
             switch (fmt) {
             case FMT_Q8_0: rc = launch_tca_fmt<FMT_Q8_0>(c, a, grid, smem, st); break;
             case FMT_Q4_K: rc = launch_tca_fmt<FMT_Q4_K>(c, a, grid, smem, st); break;
-            default: rc = launch_tca_fmt<FMT_Q5_K>(c, a, grid, smem, st); break;
+            case FMT_Q5_K: rc = launch_tca_fmt<FMT_Q5_K>(c, a, grid, smem, st); break;
+            default: rc = launch_tca_fmt<FMT_Q6_K>(c, a, grid, smem, st); break;
             }
         } else {
             const size_t smem = 1024 + (size_t)TC_MAX_RING * 16384 + (size_t)TC_B_STAGES * b_tile + 512 + (size_t)tc_pk_stages(fmt) * pk_stage;
@@ -1140,7 +1146,7 @@ extern "C" int orome_cuda_matvec(orome_cuda_ctx *c, const OromeTensorRef *ref, c
     if (rc) { c->g_wait = c->g_publish = -1; return rc; }
     CU(cudaSetDevice(c->device));
     const bool x_ok = ldx % 4 == 0 && !(reinterpret_cast<uintptr_t>(x_dev) & 15);
-    const bool tc_ok = batch >= c->tc_min_batch && !c->force_generic && tc_supported((int)ref->format, ref->in_dim) && x_ok;
+    const bool tc_ok = batch >= c->tc_min_batch && !c->force_generic && tc_supported(c, (int)ref->format, ref->in_dim) && x_ok;
     if (c->g_world > 1 && (c->g_wait >= 0 || c->g_publish >= 0)) {
         // Row-split batched product: only the tensor-core form has a publish / wait path, and only as one launch.  Any
         // other call drops the request and says so, rather than leave it armed for an unrelated later launch.

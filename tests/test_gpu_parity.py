@@ -245,22 +245,23 @@ def test_batched_matvec(env, fmt, batch):
     x = synth.host_x(in_dim, batch, seed=3)
     y = gpu_matvec(env, fmt, data, out_dim, in_dim, x)
     want = oracle.matvec_f64(fmt, data, out_dim, in_dim, x)
-    on_tensor_cores = batch >= 4 and fmt in (synth.Q8_0, synth.Q4_K, synth.Q5_K)
+    on_tensor_cores = batch >= 4 and fmt in QUANT
     assert y.shape == want.shape and rel_l2(y, want) <= (TC_REL_L2_TOL if on_tensor_cores else REL_L2_TOL)
 
 
-@pytest.mark.parametrize("fmt", [synth.Q8_0, synth.Q4_K, synth.Q5_K])
-@pytest.mark.parametrize("shape", [(300, 4096, 64), (128, 1024, 33), (1000, 2048, 16), (257, 12288, 48), (96, 512, 100)])
+@pytest.mark.parametrize("fmt", QUANT)
+@pytest.mark.parametrize("shape", [(300, 4096, 64), (128, 1024, 33), (1000, 2048, 16), (257, 12288, 48), (96, 512, 100), (131, 1280, 9)])
 def test_prefill_gemm_on_tensor_cores(env, fmt, shape):
-    """Ragged row tiles, split-K, padded and multi-slice batches; both scale layouts for the K-quants."""
+    """Ragged row tiles, split-K, padded and multi-slice batches; both scale layouts for Q4_K / Q5_K.  Q6_K rows are
+    only 2-byte aligned (1280 weights: 1050 bytes a row, so rows start at every residue of 2 mod 16)."""
     torch, F, ctx = env
     out_dim, in_dim, batch = shape
     data = synth.host_tensor(fmt, out_dim, in_dim, seed=synth.seed_for("tc", fmt, *shape))
     x = synth.host_x(in_dim, batch, seed=17)
-    for variant in ((0, 1) if fmt != synth.Q8_0 else (0,)):
+    for variant in ((0, 1) if fmt in (synth.Q4_K, synth.Q5_K) else (0,)):
         before = ctx.launch_count
         y = gpu_matvec(env, fmt, data, out_dim, in_dim, x, variant)
-        assert ctx.launch_count - before >= 2                       # pack + tensor-core kernel (+ split-K reduction)
+        assert 2 <= ctx.launch_count - before <= 3 * ((batch + 63) // 64)                      # pack + tensor-core kernel (+ split-K reduction)
         want = oracle.matvec_f64(fmt, data, out_dim, in_dim, x, layout=variant)
         err = rel_l2(y, want)
         assert err <= TC_REL_L2_TOL, (fmt, shape, variant, err)
@@ -532,7 +533,7 @@ def test_seeded_random_shapes_every_entry_point(env):
                 xt, y = dev_bytes(torch, x), torch.full((batch, out_dim), float("nan"), device="cuda")
                 ctx.matvec(F.tensor_ref(wt.data_ptr(), pad, fmt, out_dim, in_dim, variant), xt.data_ptr(), y.data_ptr(), batch, in_dim, out_dim)
                 got, want = y, oracle.matvec_f64(fmt, data, out_dim, in_dim, x, layout=variant)
-                if batch >= 4 and fmt != synth.Q6_K and in_dim % 256 == 0:
+                if batch >= 4 and in_dim % 256 == 0:
                     tol = TC_REL_L2_TOL
             elif kind == "gate_up":
                 gd, ud = synth.host_tensor(fmt, out_dim, in_dim, seed=1000 + case), synth.host_tensor(fmt, out_dim, in_dim, seed=3000 + case)
