@@ -65,6 +65,17 @@ struct MmaArgs {
     unsigned int *pub_gen, *pub_arrived;
     const uint2 *x_ll;
     const unsigned int *wait_gen;
+    // MoE forms (template parameter MOE): the experts of a projection are one stacked tensor (expert e = rows
+    // e * expert_rows .. of the tensor that map[0] describes), the chosen experts are read on the device.
+    //   MOE 1, fused gate/up: segment s = expert seg_expert[s], all segments share x.
+    //   MOE 2, down + combine: y[r] = sum_s seg_weight[s] * (W_{seg_expert[s]}[r] . x_s); the x_s lie one behind the
+    //          other (units = nchunks * kc superblocks), chunk s of a row tile is expert s, the weight is folded
+    //          into the scales of x_s.
+    // blockIdx.y = token: x, y, indices and weights advance by their strides.
+    const uint32_t *seg_expert;
+    const float *seg_weight;
+    uint32_t expert_rows;
+    uint32_t tok_x_stride, tok_y_stride, tok_sel_stride;
 };
 
 template <int OFF>
@@ -454,10 +465,14 @@ __device__ __forceinline__ bool mma_next_tile(const MmaArgs &a, uint32_t &cur, u
     return true;
 }
 
-template <int FMT, int NP, bool SWIGLU, bool EXT>
+template <int FMT, int NP, bool SWIGLU, bool EXT, int MOE = 0>
 __global__ void __launch_bounds__(MMA_MAX_THREADS, 1)
 gemv_mma_kernel(const __grid_constant__ MmaArgs a)
 {
+    static_assert(MOE == 0 || (FMT != FMT_Q6_K && !EXT), "the MoE forms are built for Q4_K / Q5_K on one GPU");
+    static_assert(MOE != 1 || SWIGLU, "MOE 1 is the fused gate/up form");
+    static_assert(MOE != 2 || !SWIGLU, "MOE 2 is the down + combine form");
+    __shared__ uint32_t s_expert[PIPE_MAX_SEG];
     constexpr uint32_t UNIT = FMT == FMT_Q4_K ? 144 : FMT == FMT_Q5_K ? 176 : 210;
     constexpr bool Q6 = FMT == FMT_Q6_K;
     static_assert(!(Q6 && SWIGLU), "the fused gate/up form is built for Q4_K and Q5_K only");
@@ -488,13 +503,22 @@ gemv_mma_kernel(const __grid_constant__ MmaArgs a)
     pdl_launch_dependents();
     if (tid == 0) stamp(a.trace, 0);
 
-    const uint32_t lo = (uint32_t)((uint64_t)blockIdx.x * a.total_rows / gridDim.x);
-    const uint32_t hi = (uint32_t)((uint64_t)(blockIdx.x + 1) * a.total_rows / gridDim.x);
+    // MoE forms: whole row tiles per CTA (row counts are multiples of 16 there), so that no box reaches past the rows
+    // of the last expert of the stack
+    const uint32_t split_units = MOE != 0 ? a.total_rows / MMA_TILE_ROWS : a.total_rows, split_mul = MOE != 0 ? MMA_TILE_ROWS : 1u;
+    const uint32_t lo = (uint32_t)((uint64_t)blockIdx.x * split_units / gridDim.x) * split_mul;
+    const uint32_t hi = (uint32_t)((uint64_t)(blockIdx.x + 1) * split_units / gridDim.x) * split_mul;
 
     if (producer) {
         // The weight copies do not depend on the previous kernel: no griddepcontrol.wait on this path.
         // With two producer warps, warp p issues the stages i with i % 2 == p.
         const uint32_t pw = warp - CW;
+        if constexpr (MOE != 0) {      // the expert indices are the previous kernel's output
+            pdl_wait();
+            const uint32_t nsel = MOE == 1 ? (uint32_t)a.nseg : a.nchunks;
+            if (lane < (uint32_t)PIPE_MAX_SEG) s_expert[lane] = lane < nsel ? a.seg_expert[blockIdx.y * a.tok_sel_stride + lane] : 0u;
+            __syncwarp();
+        }
         uint32_t cur = lo, s = 0, k = 0, issued = 0, used_mask = 0, par_mask = 0;
         int seg = 0;
         bool ok = true;
@@ -546,8 +570,12 @@ gemv_mma_kernel(const __grid_constant__ MmaArgs a)
                 } else if (lane == 0) {
                     const uint32_t dst = smem_u32(stages + (size_t)sc * a.stage_stride);
                     mbar_expect_tx(bar, a.box_bytes * (SWIGLU ? 2u : 1u));   // a box is always whole: what lies outside the tensor arrives as zeros
-                    tma_box(dst, &a.map[t.seg][0], c * a.kc, t.row0, bar);
-                    if constexpr (SWIGLU) tma_box(dst + a.half_stride, &a.map[t.seg][1], c * a.kc, t.row0, bar);
+                    const int ms = MOE == 0 ? t.seg : 0;
+                    uint32_t sb0 = c * a.kc, row0 = t.row0;
+                    if constexpr (MOE == 1) row0 += s_expert[t.seg] * a.expert_rows;
+                    if constexpr (MOE == 2) { row0 += s_expert[c] * a.expert_rows; sb0 = 0; }
+                    tma_box(dst, &a.map[ms][0], sb0, row0, bar);
+                    if constexpr (SWIGLU) tma_box(dst + a.half_stride, &a.map[ms][1], sb0, row0, bar);
                 }
             }
         }
@@ -576,7 +604,7 @@ gemv_mma_kernel(const __grid_constant__ MmaArgs a)
     {
         const uint2 *slots = EXT ? a.x_ll : nullptr;
         const unsigned int want = EXT && a.x_ll ? *reinterpret_cast<const volatile unsigned int *>(a.wait_gen) : 0u;
-        if (!quantize_x_mma<NP, Q6>(a.x, U, xq, warp, lane, CW, slots, want)) {
+        if (!quantize_x_mma<NP, Q6>(a.x + (MOE != 0 ? (size_t)blockIdx.y * a.tok_x_stride : 0), U, xq, warp, lane, CW, slots, want)) {
             s_abort = 1;
             atomicExch(a.status, 3);
         }
@@ -586,6 +614,15 @@ gemv_mma_kernel(const __grid_constant__ MmaArgs a)
         for (uint32_t z = tid; z < 768 / 4; z += C) reinterpret_cast<uint32_t *>(xq + (size_t)U * MMA_XQ_SB + 8 * U)[z] = 0u;
     }
     named_bar_sync(PIPE_BAR_CONSUMERS, (int)C);
+    if constexpr (MOE == 2) {      // the routing weight of an expert goes into the scales of its input vector
+        float *xsf = reinterpret_cast<float *>(xq + (size_t)U * MMA_XQ_SB);
+        for (uint32_t u = tid; u < U; u += C) {
+            const float wgt = a.seg_weight[blockIdx.y * a.tok_sel_stride + u / a.kc];
+            xsf[u] *= wgt;
+            xsf[U + u] *= wgt;
+        }
+        named_bar_sync(PIPE_BAR_CONSUMERS, (int)C);
+    }
     if (tid == 0) stamp(a.trace, 3);
     const uint32_t xs_s = smem_u32(xq) + U * MMA_XQ_SB;                // xs[U], then sxs[U]
     const uint32_t plane = g < (uint32_t)NP ? g : 0u;                  // columns past the planes repeat plane 0 and are weighted 0
@@ -608,7 +645,7 @@ gemv_mma_kernel(const __grid_constant__ MmaArgs a)
     auto flush = [&]() {
         named_bar_sync(PIPE_BAR_CONSUMERS, (int)C);
         const float *src = red + (size_t)which * PLANE * (SWIGLU ? 2 : 1);
-        float *y = a.seg[buf_seg].y + buf_row0;
+        float *y = a.seg[buf_seg].y + buf_row0 + (MOE != 0 ? (size_t)blockIdx.y * a.tok_y_stride : 0);
         for (uint32_t r = tid; r < buf_n; r += C) {
             float gsum = 0.0f, usum = 0.0f;
             for (uint32_t w = 0; w < SLOTS; ++w) {

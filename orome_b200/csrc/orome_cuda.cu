@@ -570,6 +570,7 @@ static EncodeTiledFn encode_tiled_fn();
 struct MmaPlan {
     MmaArgs args;
     int threads, grid;
+    int tokens;        // MoE forms: grid rows (one per token)
     size_t smem;
 };
 
@@ -581,22 +582,37 @@ static bool mma_supported(const orome_cuda_ctx *c, int fmt, uint32_t in_dim, boo
     return c->kquant_mma && !c->force_generic && fmt_ok && in_dim % 256 == 0 && in_dim >= 256;
 }
 
-static int plan_mma(orome_cuda_ctx *c, int fmt, uint32_t in_dim, uint32_t total_rows, bool swiglu, MmaPlan &p)
+// nvec > 1: the combine form of the MoE down projection -- a row is the sum over nvec experts of a product with that
+// expert's own input vector (in_dim wide each, one behind the other); a stage then holds one expert's whole rows.
+// grid_cap > 0 (MoE forms): at most that many CTAs, each with the same whole number of row tiles where that divides.
+static int plan_mma(orome_cuda_ctx *c, int fmt, uint32_t in_dim, uint32_t total_rows, bool swiglu, MmaPlan &p, uint32_t nvec = 0, uint32_t grid_cap = 0)
 {
     MmaArgs &a = p.args;
     const uint32_t unit = fmt == FMT_Q4_K ? 144u : fmt == FMT_Q5_K ? 176u : 210u;
+    const uint32_t units_row = in_dim / 256;
     a.in_dim = in_dim;
-    a.units = in_dim / 256;
-    a.row_bytes = a.units * unit;
+    a.units = units_row * std::max(1u, nvec);
+    a.row_bytes = units_row * unit;
     a.total_rows = total_rows;
     // a stage of about stage_kb (default 40) KiB: 16 rows (x2 in the fused form) of kc superblocks
     const uint32_t want = (c->stage_kb ? (uint32_t)c->stage_kb : 40u) * 1024u;
-    const uint32_t kc_max = std::max(1u, std::min(a.units, want / (MMA_TILE_ROWS * unit * (swiglu ? 2u : 1u))));
-    a.nchunks = (a.units + kc_max - 1) / kc_max;
-    a.kc = (a.units + a.nchunks - 1) / a.nchunks;
+    const uint32_t kc_max = std::max(1u, std::min(units_row, want / (MMA_TILE_ROWS * unit * (swiglu ? 2u : 1u))));
+    if (nvec > 0) {
+        if (units_row > kc_max) return fail(OROME_ENOTSUP, "mma plan: combine form with rows of %u superblocks", units_row);
+        a.nchunks = nvec;
+        a.kc = units_row;
+    } else {
+        a.nchunks = (a.units + kc_max - 1) / kc_max;
+        a.kc = (a.units + a.nchunks - 1) / a.nchunks;
+    }
     const uint32_t rounds = (a.kc + MMA_MAX_WARPS - 1) / MMA_MAX_WARPS;
     a.nwarps = (a.kc + rounds - 1) / rounds;
     p.grid = (int)std::max<uint64_t>(1, std::min<uint64_t>((uint64_t)c->sm_count, (total_rows + MMA_TILE_ROWS - 1) / MMA_TILE_ROWS));
+    if (grid_cap) {
+        const uint32_t tiles = (total_rows + MMA_TILE_ROWS - 1) / MMA_TILE_ROWS, cap = std::max(1u, std::min(grid_cap, tiles));
+        const uint32_t per = (tiles + cap - 1) / cap;
+        p.grid = (int)((tiles + per - 1) / per);
+    }
     const uint32_t share = (total_rows + p.grid - 1) / p.grid;
     // stages (row tiles x chunks) go round the groups: as many groups as the warp budget and the CTA's stage count allow
     const uint32_t cta_stages = (share + MMA_TILE_ROWS - 1) / MMA_TILE_ROWS * a.nchunks;
@@ -674,10 +690,10 @@ static int mma_encode_maps(orome_cuda_ctx *c, int fmt, MmaPlan &p, bool swiglu)
     return OROME_OK;
 }
 
-template <int FMT, int NP, bool SWIGLU, bool EXT>
+template <int FMT, int NP, bool SWIGLU, bool EXT, int MOE = 0>
 static int launch_mma_ext(orome_cuda_ctx *c, const MmaPlan &p, cudaStream_t st)
 {
-    auto kern = gemv_mma_kernel<FMT, NP, SWIGLU, EXT>;
+    auto kern = gemv_mma_kernel<FMT, NP, SWIGLU, EXT, MOE>;
     static size_t configured[64] = {0};   // per device: dynamic shared memory opted in so far
     if (configured[c->device] < p.smem) {
         cudaFuncAttributes fa;
@@ -688,7 +704,7 @@ static int launch_mma_ext(orome_cuda_ctx *c, const MmaPlan &p, cudaStream_t st)
         configured[c->device] = (size_t)max_dyn;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(p.grid);
+    cfg.gridDim = dim3(p.grid, MOE != 0 ? p.tokens : 1);
     cfg.blockDim = dim3(p.threads);
     cfg.dynamicSmemBytes = p.smem;
     cfg.stream = st;
@@ -700,6 +716,16 @@ static int launch_mma_ext(orome_cuda_ctx *c, const MmaPlan &p, cudaStream_t st)
     CU(cudaLaunchKernelEx(&cfg, kern, p.args));
     ++c->launches;
     return OROME_OK;
+}
+
+// The MoE forms of the mma kernel (Q4_K / Q5_K): fused gate/up over device-chosen experts, down + weighted combine.
+static int launch_mma_moe(orome_cuda_ctx *c, int fmt, MmaPlan &p, bool gate_up, cudaStream_t st)
+{
+    const bool b24 = c->x_bits == 24;
+    if (gate_up)      // the fused form always reads x at 24 bits
+        return fmt == FMT_Q4_K ? launch_mma_ext<FMT_Q4_K, 3, true, false, 1>(c, p, st) : launch_mma_ext<FMT_Q5_K, 3, true, false, 1>(c, p, st);
+    if (fmt == FMT_Q4_K) return b24 ? launch_mma_ext<FMT_Q4_K, 3, false, false, 2>(c, p, st) : launch_mma_ext<FMT_Q4_K, 2, false, false, 2>(c, p, st);
+    return b24 ? launch_mma_ext<FMT_Q5_K, 3, false, false, 2>(c, p, st) : launch_mma_ext<FMT_Q5_K, 2, false, false, 2>(c, p, st);
 }
 
 template <int FMT, int NP, bool SWIGLU>
@@ -1436,6 +1462,13 @@ extern "C" int orome_cuda_moe_route_static(orome_cuda_ctx *c, const OromeTensorR
     return launch_router(c, data, ne, router->in_dim, x_dev, n_tokens, ldx, logits, K, idx_dev, w_dev, st);
 }
 
+// Set by orome_cuda_moe_ffn_shard around its call: the index list may hold "no expert here" entries, which only the
+// dp4a kernel steps over.
+static thread_local bool g_moe_may_skip = false;
+// Row extent given to the tensor map of an expert stack (the number of experts is not part of an ExpertLayerRef; row
+// tiles never leave an expert's rows, so the extent only has to cover every expert).
+constexpr uint32_t MOE_STACK_ROWS = 1u << 24;
+
 extern "C" int orome_cuda_moe_ffn(orome_cuda_ctx *c, const OromeExpertLayerRef *L, uint32_t variant, const float *x_dev,
                                   int n_tokens, int ldx, const uint32_t *idx_dev, const float *w_dev, uint32_t K, uint32_t hidden,
                                   uint32_t inter, float *act_dev, float *out_dev, int ldo, void *stream)
@@ -1458,6 +1491,66 @@ extern "C" int orome_cuda_moe_ffn(orome_cuda_ctx *c, const OromeExpertLayerRef *
     CU(cudaSetDevice(c->device));
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const size_t grb = row_bytes_of(gfmt, hidden), drb = row_bytes_of(dfmt, inter);
+    // Q4_K / Q5_K experts stacked without gaps: the mma kernel's MoE forms (the indices must all be real experts).
+    auto mma_moe_ok = [&](int fmt, uint32_t in_dim, uint32_t rows, size_t stride, size_t rb) {
+        return c->kquant_mma && !c->force_generic && !g_moe_may_skip && (fmt == FMT_Q4_K || fmt == FMT_Q5_K) && in_dim % 256 == 0 &&
+               rows % MMA_TILE_ROWS == 0 && stride == (size_t)rows * rb;
+    };
+    const uint32_t moe_grid_cap = n_tokens == 1 ? (uint32_t)c->sm_count : std::max(1u, 2u * (uint32_t)c->sm_count / (uint32_t)n_tokens);
+    const bool x_ok16 = !((reinterpret_cast<uintptr_t>(x_dev) | reinterpret_cast<uintptr_t>(act_dev)) & 15) && (ldx % 4 == 0 || n_tokens == 1);
+    const size_t out_ld_m = n_tokens == 1 ? hidden : (size_t)ldo;
+    const bool sizes_ok = (size_t)n_tokens * K * inter <= 0xFFFFFFFFull && out_ld_m * (size_t)n_tokens <= 0xFFFFFFFFull;
+    bool gate_up_done = false;
+    if (x_ok16 && sizes_ok && mma_moe_ok(gfmt, hidden, inter, L->gate.expert_stride, grb) && L->up.expert_stride == L->gate.expert_stride) {
+        MmaPlan m;
+        memset(&m, 0, sizeof m);
+        for (uint32_t k = 0; k < K; ++k) m.args.seg[k] = PipeSeg{gate, up, act_dev + (size_t)k * inter, inter, k * inter};
+        m.args.nseg = (int)K;
+        m.args.x = x_dev;
+        m.args.layout = (int)variant;
+        int rc = plan_mma(c, gfmt, hidden, K * inter, true, m, 0, moe_grid_cap);
+        if (rc == OROME_OK) {
+            const uint32_t unit = gfmt == FMT_Q4_K ? 144u : 176u, kb = m.args.pitch / unit;
+            rc = mma_tensor_map(c, gate, unit, hidden / 256, MOE_STACK_ROWS, kb, &m.args.map[0][0]);
+            if (rc == OROME_OK) rc = mma_tensor_map(c, up, unit, hidden / 256, MOE_STACK_ROWS, kb, &m.args.map[0][1]);
+            if (rc) return rc;
+            m.args.seg_expert = idx_dev;
+            m.args.expert_rows = inter;
+            m.args.tok_x_stride = n_tokens == 1 ? 0u : (uint32_t)ldx;
+            m.args.tok_y_stride = K * inter;
+            m.args.tok_sel_stride = 8;
+            m.tokens = n_tokens;
+            rc = launch_mma_moe(c, gfmt, m, true, st);
+            if (rc) return rc;
+            gate_up_done = true;
+        } else if (rc != OROME_ENOTSUP) return rc;
+    }
+    auto down_mma = [&]() -> int {      // OROME_ENOTSUP: not this form
+        if (!(x_ok16 && sizes_ok && mma_moe_ok(dfmt, inter, hidden, L->down.expert_stride, drb))) return OROME_ENOTSUP;
+        MmaPlan m;
+        memset(&m, 0, sizeof m);
+        m.args.seg[0] = PipeSeg{down, nullptr, out_dev, hidden, 0};
+        m.args.nseg = 1;
+        m.args.x = act_dev;
+        m.args.layout = (int)variant;
+        int rc = plan_mma(c, dfmt, inter, hidden, false, m, K, moe_grid_cap);
+        if (rc) return rc;
+        const uint32_t unit = dfmt == FMT_Q4_K ? 144u : 176u, kb = m.args.pitch / unit;
+        rc = mma_tensor_map(c, down, unit, inter / 256, MOE_STACK_ROWS, kb, &m.args.map[0][0]);
+        if (rc) return rc;
+        m.args.seg_expert = idx_dev;
+        m.args.seg_weight = w_dev;
+        m.args.expert_rows = hidden;
+        m.args.tok_x_stride = K * inter;
+        m.args.tok_y_stride = (uint32_t)out_ld_m;
+        m.args.tok_sel_stride = 8;
+        m.tokens = n_tokens;
+        return launch_mma_moe(c, dfmt, m, false, st);
+    };
+    if (gate_up_done) {
+        const int rc = down_mma();
+        if (rc != OROME_ENOTSUP) return rc;
+    }
     if (!c->force_generic && orome_pipe_supported(gfmt, hidden) && orome_pipe_supported(dfmt, inter) && K <= (uint32_t)PIPE_MAX_SEG &&
         !((reinterpret_cast<uintptr_t>(x_dev) | reinterpret_cast<uintptr_t>(act_dev)) & 15) && (ldx % 4 == 0 || n_tokens == 1) && inter % 4 == 0) {
         // One fused gate/up launch over the K selected experts of every token (device-side expert indices; grid.y =
@@ -1467,23 +1560,28 @@ extern "C" int orome_cuda_moe_ffn(orome_cuda_ctx *c, const OromeExpertLayerRef *
         if ((size_t)n_tokens * K * inter > 0xFFFFFFFFull || out_ld * (size_t)n_tokens > 0xFFFFFFFFull)
             return fail(OROME_EINVAL, "moe_ffn: token batch too large");
         PipePlan p;
-        memset(&p, 0, sizeof p);
-        for (uint32_t k = 0; k < K; ++k)
-            p.args.seg[k] = PipeSeg{gate, up, act_dev + (size_t)k * inter, inter, k * inter};
-        p.args.nseg = (int)K;
-        p.args.x = x_dev;
-        p.args.layout = (int)variant;
-        p.tokens = n_tokens;
-        int rc = plan_pipe(c, gfmt, hidden, K * inter, 1, p);
-        if (rc) return rc;
-        p.args.seg_expert = idx_dev;
-        p.args.w_stride = L->gate.expert_stride;
-        p.args.w2_stride = L->up.expert_stride;
-        p.args.tok_x_stride = n_tokens == 1 ? 0u : (uint32_t)ldx;
-        p.args.tok_y_stride = K * inter;
-        p.args.tok_sel_stride = 8;
-        rc = launch_pipe(c, gfmt, p, 1, st);
-        if (rc) return rc;
+        int rc;
+        if (!gate_up_done) {
+            memset(&p, 0, sizeof p);
+            for (uint32_t k = 0; k < K; ++k)
+                p.args.seg[k] = PipeSeg{gate, up, act_dev + (size_t)k * inter, inter, k * inter};
+            p.args.nseg = (int)K;
+            p.args.x = x_dev;
+            p.args.layout = (int)variant;
+            p.tokens = n_tokens;
+            rc = plan_pipe(c, gfmt, hidden, K * inter, 1, p);
+            if (rc) return rc;
+            p.args.seg_expert = idx_dev;
+            p.args.w_stride = L->gate.expert_stride;
+            p.args.w2_stride = L->up.expert_stride;
+            p.args.tok_x_stride = n_tokens == 1 ? 0u : (uint32_t)ldx;
+            p.args.tok_y_stride = K * inter;
+            p.args.tok_sel_stride = 8;
+            rc = launch_pipe(c, gfmt, p, 1, st);
+            if (rc) return rc;
+            rc = down_mma();
+            if (rc != OROME_ENOTSUP) return rc;
+        }
 
         memset(&p, 0, sizeof p);
         for (uint32_t k = 0; k < K; ++k) p.args.seg[k] = PipeSeg{down, nullptr, out_dev, hidden, 0};
@@ -1591,7 +1689,10 @@ extern "C" int orome_cuda_moe_ffn_shard(orome_cuda_ctx *c, const OromeExpertLaye
     int rc = launch_pdl(c, "moe_localize", moe_localize_kernel, dim3((n + 127) / 128), dim3(128), static_cast<cudaStream_t>(stream), idx_dev, n,
                         first_expert, n_local, idx_local_dev);
     if (rc) return rc;
-    return orome_cuda_moe_ffn(c, L_local, variant, x_dev, n_tokens, ldx, idx_local_dev, w_dev, K, hidden, inter, act_dev, out_dev, ldo, stream);
+    g_moe_may_skip = true;
+    rc = orome_cuda_moe_ffn(c, L_local, variant, x_dev, n_tokens, ldx, idx_local_dev, w_dev, K, hidden, inter, act_dev, out_dev, ldo, stream);
+    g_moe_may_skip = false;
+    return rc;
 }
 
 // ---------------------------------------------------------------------------

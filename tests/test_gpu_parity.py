@@ -436,11 +436,23 @@ def test_route_matches_oracle_including_ties(env):
         assert np.max(np.abs(w[0].cpu().numpy() - ow)) <= 1e-6
 
 
+@pytest.mark.parametrize("kquant_mma", [1, 0])
 @pytest.mark.parametrize("T", [1, 5])
-@pytest.mark.parametrize("down_fmt", [synth.Q5_K, synth.Q4_K])
-def test_moe_ffn_matches_oracle(env, T, down_fmt):
+@pytest.mark.parametrize("down_fmt", [synth.Q5_K, synth.Q4_K, synth.Q6_K])
+def test_moe_ffn_matches_oracle(env, T, down_fmt, kquant_mma):
+    """Both kernels behind the entry point: the mma kernel's MoE forms (Q4_K / Q5_K; a Q6_K down projection then runs
+    on the dp4a kernel after an mma gate/up) and, with OROME_OPT_KQUANT_MMA = 0, the dp4a kernel for both phases."""
     torch, F, ctx = env
     H, M, E, K = 512, 256, 16, 8
+    ctx.set_option(F.OPT_KQUANT_MMA, kquant_mma)
+    try:
+        _moe_ffn_case(env, T, down_fmt, H, M, E, K)
+    finally:
+        ctx.set_option(F.OPT_KQUANT_MMA, 1)
+
+
+def _moe_ffn_case(env, T, down_fmt, H, M, E, K):
+    torch, F, ctx = env
     gate = synth.host_tensor(synth.Q4_K, E * M, H, seed=21)
     up = synth.host_tensor(synth.Q4_K, E * M, H, seed=22)
     down = synth.host_tensor(down_fmt, E * H, M, seed=23)
