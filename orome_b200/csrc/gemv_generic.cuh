@@ -82,41 +82,46 @@ gemv_generic_kernel(const uint8_t *__restrict__ data, size_t row_bytes, uint32_t
 // load is coalesced; up to 4 input vectors per pass.  Waits for the previous kernel first (it may produce x).
 // With W1 set, one more output row (index out_dim) comes from that single-row tensor: the router logits and the
 // shared-expert gate logit in one launch, as matvec_f32_pair does (shaders.metal:1368-1392).
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
 gemv_f32_kernel(const float *__restrict__ W, uint32_t out_dim, uint32_t in_dim, const float *__restrict__ x, int batch, int ldx,
                 float *__restrict__ y, int ldy, const float *__restrict__ W1 = nullptr)
 {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the next kernel may set itself up; it waits for this one's results itself
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const uint32_t row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (row >= out_dim + (W1 ? 1u : 0u)) return;
+    // One CTA of four warps per row: a 2048-wide row is then one round of four 16-byte loads per thread, all in flight
+    // together (a warp per row needed four dependent rounds, and a 128-row router matrix kept only 33 CTAs busy).
+    const uint32_t row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const float4 *w4 = reinterpret_cast<const float4 *>(row < out_dim ? W + (size_t)row * in_dim : W1);
     const uint32_t n4 = in_dim / 4;
-    // grid.y cuts the batch into groups of four vectors; a warp keeps four row pieces in flight at a time
+    // grid.y cuts the batch into groups of four vectors
     const int b0 = (int)blockIdx.y * 4;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    for (uint32_t c0 = lane; c0 < n4; c0 += 128) {
+    for (uint32_t c0 = tid; c0 < n4; c0 += 512) {
         float4 w[4];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) w[u] = c0 + 32 * u < n4 ? __ldg(w4 + c0 + 32 * u) : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int u = 0; u < 4; ++u) w[u] = c0 + 128 * u < n4 ? __ldg(w4 + c0 + 128 * u) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             if (b0 + i < batch) {
                 const float4 *x4 = reinterpret_cast<const float4 *>(x + (size_t)(b0 + i) * ldx);
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
-                    if (c0 + 32 * u < n4) {
-                        const float4 xv = x4[c0 + 32 * u];
+                    if (c0 + 128 * u < n4) {
+                        const float4 xv = x4[c0 + 128 * u];
                         acc[i] = fmaf(w[u].x, xv.x, fmaf(w[u].y, xv.y, fmaf(w[u].z, xv.z, fmaf(w[u].w, xv.w, acc[i]))));
                     }
                 }
             }
         }
     }
+    __shared__ float red[4][4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const float s = warp_sum(acc[i]);
-        if (lane == 0 && b0 + i < batch) y[(size_t)(b0 + i) * ldy + row] = s;
+        if (lane == 0) red[warp][i] = s;
     }
+    __syncthreads();
+    if (tid < 4 && b0 + (int)tid < batch) y[(size_t)(b0 + tid) * ldy + row] = (red[0][tid] + red[1][tid]) + (red[2][tid] + red[3][tid]);
 }
 
 // out = silu(gate) * up, elementwise (shaders.metal:1018-1030); used after two

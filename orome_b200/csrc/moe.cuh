@@ -12,16 +12,22 @@ __global__ void __launch_bounds__(256)
 route_topk_kernel(const float *__restrict__ logits, int ld_logits, uint32_t n_experts, uint32_t K,
                   uint32_t *__restrict__ idx_out, float *__restrict__ w_out, float *__restrict__ shared_logit_out = nullptr)
 {
-    __shared__ float s_val[8];
-    __shared__ uint32_t s_idx[8];
+    // Per round one barrier: the warps' candidates go to one of two buffers in turn, and EVERY warp then reduces the eight
+    // candidates for itself (same operations in the same order, so the same winner), which saves the second barrier
+    // and the trip of the winner through shared memory.  Lanes 8..31 of that second reduction hold -inf, so its
+    // steps 16 and 8 can never change lanes 0..7 and are left out.
+    __shared__ float s_val[2][8];
+    __shared__ uint32_t s_idx[2][8];
     __shared__ float f_val[8];
     __shared__ uint32_t f_idx[8];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the next kernel may set itself up; it waits for this one's results itself
     asm volatile("griddepcontrol.wait;" ::: "memory");   // the logits are the previous kernel's output
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const float *lg = logits + (size_t)blockIdx.x * ld_logits;
     float my = tid < n_experts ? lg[tid] : -INFINITY;
     const uint32_t limit = K < 8 ? K : 8;
     for (uint32_t round = 0; round < limit; ++round) {
+        const uint32_t buf = round & 1u;
         float v = my;
         uint32_t id = tid;
 #pragma unroll
@@ -30,21 +36,20 @@ route_topk_kernel(const float *__restrict__ logits, int ld_logits, uint32_t n_ex
             uint32_t oi = __shfl_down_sync(0xffffffffu, id, o);
             if (ov > v) { v = ov; id = oi; }
         }
-        if (lane == 0) { s_val[warp] = v; s_idx[warp] = id; }
+        if (lane == 0) { s_val[buf][warp] = v; s_idx[buf][warp] = id; }
         __syncthreads();
-        if (warp == 0) {
-            float v2 = lane < 8 ? s_val[lane] : -INFINITY;
-            uint32_t i2 = lane < 8 ? s_idx[lane] : 0u;
+        float v2 = lane < 8 ? s_val[buf][lane] : -INFINITY;
+        uint32_t i2 = lane < 8 ? s_idx[buf][lane] : 0u;
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                float ov = __shfl_down_sync(0xffffffffu, v2, o);
-                uint32_t oi = __shfl_down_sync(0xffffffffu, i2, o);
-                if (ov > v2) { v2 = ov; i2 = oi; }
-            }
-            if (lane == 0) { f_val[round] = v2; f_idx[round] = i2; }
+        for (int o = 4; o > 0; o >>= 1) {
+            float ov = __shfl_down_sync(0xffffffffu, v2, o);
+            uint32_t oi = __shfl_down_sync(0xffffffffu, i2, o);
+            if (ov > v2) { v2 = ov; i2 = oi; }
         }
-        __syncthreads();
-        if (tid == f_idx[round]) my = -INFINITY;
+        v2 = __shfl_sync(0xffffffffu, v2, 0);
+        i2 = __shfl_sync(0xffffffffu, i2, 0);
+        if (tid == 0) { f_val[round] = v2; f_idx[round] = i2; }
+        if (tid == i2) my = -INFINITY;
     }
     if (tid == 0) {
         float w[8], sum = 0.0f, mx = limit ? f_val[0] : 0.0f;

@@ -308,7 +308,7 @@ static int launch_router(orome_cuda_ctx *c, const uint8_t *data, uint32_t ne, ui
     int rc;
     const uint32_t rows = ne + (shared_gate ? 1u : 0u);
     if (in_dim % 4 == 0 && !(reinterpret_cast<uintptr_t>(x) & 15) && (n_tokens == 1 || ldx % 4 == 0))
-        rc = launch_pdl(c, "gemv_f32", gemv_f32_kernel, dim3((rows + 3) / 4, (unsigned)(n_tokens + 3) / 4), dim3(128), st, reinterpret_cast<const float *>(data), ne, in_dim,
+        rc = launch_pdl(c, "gemv_f32", gemv_f32_kernel, dim3(rows, (unsigned)(n_tokens + 3) / 4), dim3(128), st, reinterpret_cast<const float *>(data), ne, in_dim,
                         x, n_tokens, ldx, logits, (int)rows, reinterpret_cast<const float *>(shared_gate));
     else {
         rc = launch_generic(c, FMT_F32, data, ne, in_dim, 0, x, n_tokens, ldx, logits, (int)rows, st);
