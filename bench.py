@@ -411,7 +411,8 @@ class Stepper:
 
 def kernel_extras(torch, F, ctx, peak, only=None, reps=3):
     """Short per-kernel passes on the other benchmark configurations (rank 0, one GPU): absolute GB/s of the
-    algorithmic bytes and the fraction of the measured HBM peak, back-to-back launches over distinct weight copies.
+    algorithmic bytes and the fraction of the measured HBM peak, back-to-back launches over distinct weight copies,
+    replayed as a CUDA graph.
     `only` restricts the run to the named cases (a small, short process for a profiler capture)."""
     from orome_b200 import synth
     dev = torch.device("cuda", ctx.device)
@@ -428,6 +429,20 @@ def kernel_extras(torch, F, ctx, peak, only=None, reps=3):
             best = min(best, e0.elapsed_time(e1) / n)
         return best * 1e-3
 
+    def graphed(fn):
+        """The layers as one CUDA graph (the reference commits one command buffer per token, engine.m:1048-1050): issued
+        call by call from Python, four launches of a few microseconds each are bounded by the host, not by the GPU."""
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            fn(side.cuda_stream)
+            torch.cuda.synchronize()
+            with torch.cuda.graph(g, stream=side):
+                fn(torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        return g
+
     def gemv(name, fmt, od, idim, copies, batch=1, variant=0):
         if only and name not in only:
             return
@@ -439,12 +454,13 @@ def kernel_extras(torch, F, ctx, peak, only=None, reps=3):
         y = torch.empty(batch, od, device=dev)
         refs = [F.tensor_ref(buf.data_ptr(), i * tb, fmt, od, idim, variant) for i in range(copies)]
 
-        def go():
+        def go(stream):
             for i, r in enumerate(refs):
                 if batch == 1:
                     ctx.hint_next(refs[(i + 1) % copies])
-                ctx.matvec(r, x.data_ptr(), y.data_ptr(), batch, idim, od, st)
-        t = timed(go, copies)
+                ctx.matvec(r, x.data_ptr(), y.data_ptr(), batch, idim, od, stream)
+        g = graphed(go)
+        t = timed(g.replay, copies)
         nbytes = synth.tensor_bytes(fmt, od, idim) + 4 * batch * (idim + od)
         out[name] = {"us": round(t * 1e6, 2), "gbs": round(nbytes / t / 1e9, 1), "frac_of_measured_hbm": round(nbytes / t / 1e9 / peak, 3),
                      "bytes": nbytes}
@@ -487,14 +503,16 @@ def kernel_extras(torch, F, ctx, peak, only=None, reps=3):
     o = torch.empty(H, device=dev)
     lg = torch.empty(E, device=dev)
 
-    def moe():
+    def moe(stream):
         for buf, rw, layer, rref in layers:
-            ctx.moe_route(rref, x.data_ptr(), 1, H, K, idx.data_ptr(), w.data_ptr(), lg.data_ptr(), st)
-            ctx.moe_ffn(layer, 0, x.data_ptr(), 1, H, idx.data_ptr(), w.data_ptr(), K, H, M, act.data_ptr(), o.data_ptr(), H, st)
-    t = timed(moe, NL)
+            ctx.moe_route(rref, x.data_ptr(), 1, H, K, idx.data_ptr(), w.data_ptr(), lg.data_ptr(), stream)
+            ctx.moe_ffn(layer, 0, x.data_ptr(), 1, H, idx.data_ptr(), w.data_ptr(), K, H, M, act.data_ptr(), o.data_ptr(), H, stream)
+    g1 = graphed(moe)
+    t = timed(g1.replay, NL)
     nbytes = K * (2 * sg + sd) + E * H * 4
     out["moe_layer_top8_of_128_t1"] = {"us": round(t * 1e6, 2), "gbs": round(nbytes / t / 1e9, 1),
-                                       "frac_of_measured_hbm": round(nbytes / t / 1e9 / peak, 3), "bytes": nbytes, "launches": 4}
+                                       "frac_of_measured_hbm": round(nbytes / t / 1e9 / peak, 3), "bytes": nbytes, "launches": 4,
+                                       "form": "cuda graph of 6 layers"}
     # the same layers with a batch of 32 tokens (BASELINE configuration 5): algorithmic bytes = every distinct expert
     # the batch selects, read once, plus the router
     T = 32
@@ -505,16 +523,17 @@ def kernel_extras(torch, F, ctx, peak, only=None, reps=3):
     oT = torch.empty(T, H, device=dev)
     lgT = torch.empty(T, E, device=dev)
 
-    def moe_t():
+    def moe_t(stream):
         for buf, rw, layer, rref in layers:
-            ctx.moe_route(rref, xT.data_ptr(), T, H, K, idxT.data_ptr(), wT.data_ptr(), lgT.data_ptr(), st)
-            ctx.moe_ffn(layer, 0, xT.data_ptr(), T, H, idxT.data_ptr(), wT.data_ptr(), K, H, M, actT.data_ptr(), oT.data_ptr(), H, st)
-    t = timed(moe_t, NL)
+            ctx.moe_route(rref, xT.data_ptr(), T, H, K, idxT.data_ptr(), wT.data_ptr(), lgT.data_ptr(), stream)
+            ctx.moe_ffn(layer, 0, xT.data_ptr(), T, H, idxT.data_ptr(), wT.data_ptr(), K, H, M, actT.data_ptr(), oT.data_ptr(), H, stream)
+    gT = graphed(moe_t)
+    t = timed(gT.replay, NL)
     distinct = int(torch.unique(idxT[:, :K]).numel())               # of the last layer run; the layers differ little
     nbytes = distinct * (2 * sg + sd) + E * H * 4
     out["moe_layer_top8_of_128_t32"] = {"us": round(t * 1e6, 2), "gbs": round(nbytes / t / 1e9, 1),
                                         "frac_of_measured_hbm": round(nbytes / t / 1e9 / peak, 3), "bytes": nbytes,
-                                        "distinct_experts": distinct, "launches": 4}
+                                        "distinct_experts": distinct, "launches": 4, "form": "cuda graph of 6 layers"}
     return out
 
 
