@@ -29,7 +29,7 @@ namespace orome {
 
 constexpr int MMA_TILE_ROWS = 16;
 constexpr int MMA_MAX_WARPS = 8;                  // consumer warps of a group
-constexpr int MMA_MAX_GROUPS = 3;
+constexpr int MMA_MAX_GROUPS = 5;
 constexpr int MMA_MAX_CONSUMER_WARPS = 16;        // groups * warps per group
 constexpr int MMA_MAX_PRODUCERS = 2;              // producer warps (two where every row is its own copy)
 constexpr int MMA_MAX_THREADS = (MMA_MAX_CONSUMER_WARPS + MMA_MAX_PRODUCERS) * 32;
@@ -601,6 +601,8 @@ gemv_mma_kernel(const __grid_constant__ MmaArgs a)
     pdl_wait();   // x is the previous kernel's output
     if (tid == 0) stamp(a.trace, 2);
     uint8_t *xq = smem + a.xs_base;
+    float moe_wgt = 1.0f;      // MoE form 2: the routing weight of the expert whose input this thread's superblock belongs to
+    if constexpr (MOE == 2) { if (tid < U) moe_wgt = a.seg_weight[blockIdx.y * a.tok_sel_stride + tid / a.kc]; }
     {
         const uint2 *slots = EXT ? a.x_ll : nullptr;
         const unsigned int want = EXT && a.x_ll ? *reinterpret_cast<const volatile unsigned int *>(a.wait_gen) : 0u;
@@ -617,7 +619,7 @@ gemv_mma_kernel(const __grid_constant__ MmaArgs a)
     if constexpr (MOE == 2) {      // the routing weight of an expert goes into the scales of its input vector
         float *xsf = reinterpret_cast<float *>(xq + (size_t)U * MMA_XQ_SB);
         for (uint32_t u = tid; u < U; u += C) {
-            const float wgt = a.seg_weight[blockIdx.y * a.tok_sel_stride + u / a.kc];
+            const float wgt = u == tid ? moe_wgt : a.seg_weight[blockIdx.y * a.tok_sel_stride + u / a.kc];   // loaded before the quantization above
             xsf[u] *= wgt;
             xsf[U + u] *= wgt;
         }
