@@ -110,14 +110,14 @@ def test_chain_whose_peer_never_runs_expires_once_and_stays_usable(two_rank_ctx)
 
 def test_gather_request_is_dropped_by_calls_that_cannot_honour_it(two_rank_ctx):
     torch, F, ctx, arena = two_rank_ctx
-    fmt, n = synth.Q6_K, 256                              # a format without the batched tensor-core form
+    fmt, n = synth.Q6_K, 256
     wt = dev(torch, synth.host_tensor(fmt, n, n, seed=6))
     x8 = dev(torch, synth.host_x(n, 8, seed=7))
     y8 = torch.zeros((8, n), device="cuda")
     ref = F.tensor_ref(wt.data_ptr(), 0, fmt, n, n)
     ctx.gather_next(-1, 1)
     with pytest.raises(F.OromeError) as e:
-        ctx.matvec(ref, x8.data_ptr(), y8.data_ptr(), 8, n, n)       # the batched form has no publish path
+        ctx.matvec(ref, x8.data_ptr(), y8.data_ptr(), 3, n, n)       # batches 2-3 (one decode launch per vector) have no publish path
     assert e.value.code == F.ENOTSUP
     # the request is gone: the next batch-1 launch is a plain local one (y outside the arena would be refused if it published)
     y = torch.zeros(n, device="cuda")
