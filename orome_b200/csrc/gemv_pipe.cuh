@@ -394,8 +394,10 @@ __device__ __forceinline__ bool quantize_x_to_smem(const float *__restrict__ x, 
                                                    uint8_t *xq0, uint32_t vec_bytes, uint32_t tid, uint32_t nthreads,
                                                    const uint2 *slots = nullptr, unsigned int tag = 0,
                                                    long long limit = PIPE_WAIT_CYCLES, const int *status = nullptr, uint32_t rot = 0,
-                                                   const uint16_t *norm_w = nullptr, float rms = 1.0f)
+                                                   const uint16_t *norm_w = nullptr, float rms = 1.0f, uint32_t issued_bar = 0)
 {
+    // issued_bar: shared address of an mbarrier on which every warp arrives once the loads of its first batch are on
+    // their way (0: none).  The weight producer holds its copies back until then, see the kernel.
     // rot (single vector only; a multiple of 32 four-float pieces): this CTA walks the vector starting rot pieces in and
     // wraps around.  When every CTA of a grid reads the same vector at the same moment, different rot values keep them
     // on different cache lines (L2 slices) at any one time instead of all queueing on the same line.
@@ -420,6 +422,10 @@ __device__ __forceinline__ bool quantize_x_to_smem(const float *__restrict__ x, 
                 v[b].w = v[b].w * rms * __uint_as_float(w.y & 0xffff0000u);
             }
         }
+        if (issued_bar && base == tid - lane) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(issued_bar);
+        }
 #pragma unroll
         for (int b = 0; b < BATCH; ++b) {
             const uint32_t fb = base + b * nthreads;       // warp-uniform
@@ -430,6 +436,10 @@ __device__ __forceinline__ bool quantize_x_to_smem(const float *__restrict__ x, 
             if (nvec == 1) { f += rot; if (f >= n4) f -= n4; }
             quantize_piece<NP, G, SUMS>(v[b], f, fa < n4_all, lane, xq0 + (size_t)vec * vec_bytes, in_dim);
         }
+    }
+    if (issued_bar && tid - lane >= n4_all) {      // a warp without a piece of x arrives all the same
+        __syncwarp();
+        if (lane == 0) mbar_arrive(issued_bar);
     }
     return ok;
 }
@@ -802,6 +812,11 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
     float *red = reinterpret_cast<float *>(smem + a.red_base);
     uint8_t *stages = smem + a.stage_base;
     __shared__ volatile int s_abort;
+    // x before weights: when this kernel's weights already sit in L2 (the previous launch prefetched them), a full ring
+    // of copies requested at entry keeps the SM's inbound path busy for microseconds, and the loads of x -- which the
+    // consumers can only issue once the previous kernel has finished -- queue behind all of it.  So the producer
+    // requests its first tile at once and the rest only after every consumer warp has its loads of x on their way.
+    __shared__ uint64_t s_x_issued;
 
     using SlotT = Slot<FMT, NP>;
     constexpr int P = SlotT::PARTS;
@@ -817,6 +832,7 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
             mbar_init(smem_u32(full + s), 1);
             mbar_init(smem_u32(empty + s), C >> 5);
         }
+        mbar_init(smem_u32(&s_x_issued), C >> 5);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -843,6 +859,7 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
                 issue_tile<SWIGLU, EXT>(a, t, stages + (size_t)s * a.stage_stride, smem_u32(full + s));
                 ++i;
                 if (++s == a.nstages) { s = 0; ++k; }
+                if (i == 1) mbar_wait_bounded(smem_u32(&s_x_issued), 0);      // x first (see above); an expired wait only loses the ordering
             }
             stamp(a.trace, 1);
             // All of this CTA's rows are requested.  Pull the head of the next launch's weights into L2 so that HBM
@@ -890,7 +907,7 @@ gemv_pipe_kernel(const __grid_constant__ PipeArgs a)
         if (!quantize_x_to_smem<NP, SlotT::GROUP, SlotT::SUMS>(a.x + (EXT ? (size_t)blockIdx.y * a.tok_x_stride : 0), a.in_dim, COMBINE ? (uint32_t)a.nseg : 1u, a.x_stride, xq, a.xq_vec_bytes, tid, C,
                                                                slots, want, a.wait_cycles, a.status,
                                                                COMBINE ? 0u : (uint32_t)((uint64_t)blockIdx.x * (a.in_dim / 4) / gridDim.x) & ~31u,
-                                                               norm_w, rms)) {
+                                                               norm_w, rms, smem_u32(&s_x_issued))) {
             s_abort = 1;
             atomicExch(a.status, 3);
         }
