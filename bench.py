@@ -570,6 +570,9 @@ def run_ours(args):
         ctx.set_option(F.OPT_CTAS_PER_SM, args.ctas_per_sm)
     if args.grid_per_sm > 0:
         ctx.set_option(F.OPT_GRID_PER_SM, args.grid_per_sm)
+    for kv in args.opt:                       # any other OROME_OPT_* by number, for experiments: --opt 15=2
+        k, v = kv.split("=")
+        ctx.set_option(int(k), int(v))
 
     if args.kernel:
         # one configuration alone, few launches: the process a profiler capture is taken from
@@ -781,6 +784,7 @@ def main():
                     help="N > 1: complete y by peer stores from the kernel epilogue (fused) or by an NCCL all-gather per product")
     ap.add_argument("--ctas-per-sm", type=int, default=0, help="CTAs an SM is sized to hold in the decode kernels (0 = library default, 1)")
     ap.add_argument("--grid-per-sm", type=int, default=0, help="CTAs per SM a decode launch creates (0 = library default, 1)")
+    ap.add_argument("--opt", action="append", default=[], metavar="KEY=VALUE", help="set a library option by its number (OROME_OPT_*), for experiments")
     ap.add_argument("--stage-kb", type=int, default=0, help="size of one stage of the weight ring in KiB (0 = library default)")
     ap.add_argument("--prefetch-mb", type=int, default=-1, help="cap of the next-tensor L2 prefetch in MiB (0 = off, -1 = library default)")
     args = ap.parse_args()
