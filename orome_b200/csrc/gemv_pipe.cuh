@@ -404,6 +404,11 @@ __device__ __forceinline__ bool quantize_x_to_smem(const float *__restrict__ x, 
     bool ok = true;
     constexpr int BATCH = 8;
     const uint32_t n4 = in_dim / 4, n4_all = n4 * nvec, lane = tid & 31u;
+    if (issued_bar && slots) {      // a gathered x is polled until the peers have written it: nothing to order the copies behind
+        __syncwarp();
+        if (lane == 0) mbar_arrive(issued_bar);
+        issued_bar = 0;
+    }
     for (uint32_t base = tid - lane; base < n4_all; base += nthreads * BATCH) {
         float4 v[BATCH];
 #pragma unroll
