@@ -446,9 +446,19 @@ def test_moe_ffn_matches_oracle(env, T, down_fmt, kquant_mma):
     H, M, E, K = 512, 256, 16, 8
     ctx.set_option(F.OPT_KQUANT_MMA, kquant_mma)
     try:
-        _moe_ffn_case(env, T, down_fmt, H, M, E, K)
+        for bits in (24, 16):                     # the down projection follows the option, the fused gate/up always reads 24 bits
+            ctx.set_option(F.OPT_X_BITS, bits)
+            _moe_ffn_case(env, T, down_fmt, H, M, E, K)
     finally:
         ctx.set_option(F.OPT_KQUANT_MMA, 1)
+        ctx.set_option(F.OPT_X_BITS, 24)
+
+
+@pytest.mark.parametrize("shape", [(768, 256, 6, 3, 1), (256, 512, 9, 8, 37), (1024, 768, 40, 5, 2)])
+def test_moe_ffn_other_shapes(env, shape):
+    """Fewer than eight experts per token, a token batch larger than the grid cap, rows of one to four superblocks."""
+    H, M, E, K, T = shape
+    _moe_ffn_case(env, T, synth.Q5_K, H, M, E, K)
 
 
 def _moe_ffn_case(env, T, down_fmt, H, M, E, K):
@@ -462,8 +472,11 @@ def _moe_ffn_case(env, T, down_fmt, H, M, E, K):
     x = synth.host_x(H, T, seed=24)
     xm = np.atleast_2d(x)
     rng = np.random.default_rng(25)
-    idx = np.stack([rng.permutation(E)[:8] for _ in range(T)]).astype(np.uint32)
-    w = rng.random((T, 8)).astype(np.float32)
+    idx = np.zeros((T, 8), np.uint32)                # eight slots per token, the first K in use
+    w = np.zeros((T, 8), np.float32)
+    for t in range(T):
+        idx[t, :K] = rng.permutation(E)[:K]
+        w[t, :K] = rng.random(K)
     w /= w.sum(1, keepdims=True)
     layer = F.ExpertLayerRef(wt.data_ptr(), F.ExpertProjRef(0, sg, synth.Q4_K), F.ExpertProjRef(gate.size, sg, synth.Q4_K),
                              F.ExpertProjRef(gate.size + up.size, sd, down_fmt))
@@ -474,8 +487,8 @@ def _moe_ffn_case(env, T, down_fmt, H, M, E, K):
     torch.cuda.synchronize()
     got = out.cpu().numpy()
     for t in range(T):
-        want = oracle.moe_ffn_f64(gate, up, down, (synth.Q4_K, synth.Q4_K, down_fmt), (sg, sg, sd), xm[t], H, M, idx[t], w[t])
-        assert rel_l2(got[t], want) <= REL_L2_TOL
+        want = oracle.moe_ffn_f64(gate, up, down, (synth.Q4_K, synth.Q4_K, down_fmt), (sg, sg, sd), xm[t], H, M, idx[t, :K], w[t, :K])
+        assert rel_l2(got[t], want) <= REL_L2_TOL, (t, rel_l2(got[t], want))
 
 
 @pytest.mark.parametrize("world", [2, 4])
