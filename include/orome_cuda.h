@@ -443,7 +443,7 @@ int  orome_cuda_matvec_host(orome_cuda_ctx *ctx, const OromeTensorRef *ref,
 #define OROME_OPT_PREFETCH_MB     7   /* cap on the L2 prefetch of orome_cuda_hint_next, MiB (0 = off) */
 #define OROME_OPT_TC_MIN_BATCH    8   /* batches from this size on use the tensor-core kernel (default 4); smaller ones run one decode launch per vector */
 #define OROME_OPT_KQUANT_MMA      9   /* 1 (default): Q4_K / Q5_K batch-1 products run on the mma.sync kernel; 0: on the dp4a kernel */
-#define OROME_OPT_CHAIN_INFLIGHT 11   /* stages a chain's weight stream keeps outstanding at most (0, default: the whole ring); read at chain_end */
+#define OROME_OPT_CHAIN_INFLIGHT 11   /* stages a chain's weight stream keeps outstanding at most (0, default: what fits 136 KiB, two at least; at most the ring); read at chain_end */
 #define OROME_OPT_TC_SLABS       12   /* batched tensor-core form: 0 (default) keeps the dequantized weights in tensor memory, 1 stages them in shared memory */
 #define OROME_OPT_TC_SPLIT       13   /* batched tensor-core form: K parts per row tile, 1..12; 0 (default): chosen by a cost model */
 #define OROME_OPT_TC_TILES       14   /* batched tensor-core form (tensor-memory variant): row tiles a CTA works on side by side, 1, 2 or 4; 0 (default): cost model */

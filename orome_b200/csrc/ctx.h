@@ -68,7 +68,7 @@ struct orome_cuda_ctx {
     int tc_tiles = 0;        // batched form in tensor memory: row tiles per CTA (0: chosen by the cost model)
     int tc_split = 0;        // batched form: K parts per row tile (0: chosen by the cost model)
     int kquant_mma = 1;      // Q4_K / Q5_K batch-1 products on the mma.sync kernel (0: dp4a kernel)
-    int chain_inflight = 0;  // stages a chain's producer keeps outstanding at most (0: the whole ring)
+    int chain_inflight = 0;  // stages a chain's producer keeps outstanding at most (0: what fits 136 KiB, two at least)
     int wait_us = 0;         // bound of every device-side wait in microseconds of SM clock (0: about one second)
     // chain recording (orome_cuda_chain_begin .. _end): while set, the batch-1 entry points record instead of launching
     struct ChainRecording *rec = nullptr;
