@@ -470,6 +470,8 @@ def kernel_extras(torch, F, ctx, peak, only=None, reps=3):
     gemv("q8_0_4096x4096_b1", synth.Q8_0, 4096, 4096, 24)
     gemv("q4_k_12288x4096_b1", synth.Q4_K, 12288, 4096, 12)
     gemv("q4_k_4096x12288_b1", synth.Q4_K, 4096, 12288, 12)
+    gemv("q4_k_12288x4096_b2_two_vectors_per_launch", synth.Q4_K, 12288, 4096, 12, batch=2)
+    gemv("q4_k_12288x4096_b3", synth.Q4_K, 12288, 4096, 12, batch=3)
     gemv("q8_0_12288x4096_b8_tcgen05", synth.Q8_0, 12288, 4096, 6, batch=8)
     gemv("q6_k_5120x17408_b8_tcgen05", synth.Q6_K, 5120, 17408, 3, batch=8)
     gemv("q6_k_5120x17408_b64_tcgen05", synth.Q6_K, 5120, 17408, 3, batch=64)

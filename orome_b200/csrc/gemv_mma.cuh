@@ -34,6 +34,16 @@ constexpr int MMA_MAX_CONSUMER_WARPS = 16;        // groups * warps per group
 constexpr int MMA_MAX_PRODUCERS = 2;              // producer warps (two where every row is its own copy)
 constexpr int MMA_MAX_THREADS = (MMA_MAX_CONSUMER_WARPS + MMA_MAX_PRODUCERS) * 32;
 constexpr uint32_t MMA_XQ_SB = 864;               // quantized x per superblock: 8 groups x 3 planes x 32 B, then the sums (<= 96 B)
+// Two input vectors at once (NTOK = 2; Q4_K / Q5_K plain products): the mma's B operand has eight columns of which one
+// vector's byte planes fill two or three, so the planes of a second vector ride in the next columns and both products come
+// out of the same instructions -- the weights are read, unpacked and multiplied once for the two.  Column c = vector c / NP,
+// plane c % NP.  Quantized x per superblock: [sub-block][column][32 B], then [column][8 sum bytes]; two scales per vector.
+template <int NP, int NTOK> __host__ __device__ constexpr uint32_t mma_xq_js() { return NTOK == 1 ? 96u : (uint32_t)(NTOK * NP) * 32u; }
+template <int NP, int NTOK> __host__ __device__ constexpr uint32_t mma_xq_sums() { return NTOK == 1 ? 768u : 8u * mma_xq_js<NP, NTOK>(); }
+template <int NP, int NTOK> __host__ __device__ constexpr uint32_t mma_xq_sb()
+{
+    return NTOK == 1 ? MMA_XQ_SB : (mma_xq_sums<NP, NTOK>() + (uint32_t)(NTOK * NP) * 8u + 15u) / 16u * 16u;
+}
 
 struct MmaArgs {
     alignas(64) CUtensorMap map[PIPE_MAX_SEG][2];   // per segment: its tensor (and the up tensor in the fused form)
@@ -157,6 +167,59 @@ __device__ __forceinline__ void mma_pair(uint2 w0, uint2 w1, const uint2 (&B)[8]
     } else {
         acc[0] += sb0 * ch[0]; acc[1] += sb0 * ch[1]; acc[2] += sb1 * ch[2]; acc[3] += sb1 * ch[3];
     }
+}
+
+// The integer part of one superblock of rows g, g+8: f[0..1] / f[2..3] = the scaled dot products of row g / g+8 in this thread's
+// two columns, m[..] the same for the mins term; hx0 / hx1 = the rows' (d, dmin) words.
+template <int FMT>
+__device__ __forceinline__ void mma_superblock_core(uint32_t h0, uint32_t h1, uint32_t t, const uint2 (&B)[8], uint32_t bsx, int layout,
+                                                    float (&f)[4], int (&m)[4], uint32_t &hx0, uint32_t &hx1)
+{
+    constexpr int QOFF = FMT == FMT_Q4_K ? 16 : 48;
+    const uint32_t s0 = h0 + 8u * t, s1 = h1 + 8u * t;
+    const uint4 hd0 = lds128<0>(h0), hd1 = lds128<0>(h1);
+    const uint2 wa0 = lds64<QOFF>(s0), wa1 = lds64<QOFF>(s1), wb0 = lds64<QOFF + 32>(s0), wb1 = lds64<QOFF + 32>(s1);
+    const uint2 wc0 = lds64<QOFF + 64>(s0), wc1 = lds64<QOFF + 64>(s1), wd0 = lds64<QOFF + 96>(s0), wd1 = lds64<QOFF + 96>(s1);
+    uint2 qh0 = make_uint2(0u, 0u), qh1 = make_uint2(0u, 0u);
+    if constexpr (FMT == FMT_Q5_K) { qh0 = lds64<16>(s0); qh1 = lds64<16>(s1); }
+    const uint32_t bs = lds32<0>(bsx);
+    uint32_t scl0, sch0, mnl0, mnh0, scl1, sch1, mnl1, mnh1;
+    unpack_scales4(hd0.y, hd0.z, hd0.w, layout, scl0, sch0, mnl0, mnh0);
+    unpack_scales4(hd1.y, hd1.z, hd1.w, layout, scl1, sch1, mnl1, mnh1);
+    int acc[4] = {0, 0, 0, 0}, accH[4] = {0, 0, 0, 0};
+    mma_pair<FMT, 0>(wa0, wa1, B, qh0, qh1, scl0, sch0, scl1, sch1, acc, accH);
+    mma_pair<FMT, 1>(wb0, wb1, B, qh0, qh1, scl0, sch0, scl1, sch1, acc, accH);
+    mma_pair<FMT, 2>(wc0, wc1, B, qh0, qh1, scl0, sch0, scl1, sch1, acc, accH);
+    mma_pair<FMT, 3>(wd0, wd1, B, qh0, qh1, scl0, sch0, scl1, sch1, acc, accH);
+    mma_u8s8_k16(m, t == 0 ? mnl0 : (t == 1 ? mnh0 : 0u), t == 0 ? mnl1 : (t == 1 ? mnh1 : 0u), bs);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) f[i] = FMT == FMT_Q4_K ? fmaf((float)accH[i], 0.0625f, (float)acc[i]) : (float)acc[i];
+    hx0 = hd0.x;
+    hx1 = hd1.x;
+}
+
+// Two input vectors (A, B): this thread's two columns belong to A and / or B with the weights cwA*, cwB* (0 where a column is
+// not the vector's).
+template <int FMT>
+__device__ __forceinline__ void mma_superblock2(uint32_t h0, uint32_t h1, uint32_t t, const uint2 (&B)[8], uint32_t bsx, float xsA, float sxsA,
+                                                float xsB, float sxsB, float cwA0, float cwA1, float cwB0, float cwB1, int layout,
+                                                float &yA0, float &yA1, float &yB0, float &yB1)
+{
+    float f[4];
+    int m[4];
+    uint32_t hx0, hx1;
+    mma_superblock_core<FMT>(h0, h1, t, B, bsx, layout, f, m, hx0, hx1);
+    const float d0 = __half2float(__ushort_as_half((unsigned short)(hx0 & 0xffffu))), d1 = __half2float(__ushort_as_half((unsigned short)(hx1 & 0xffffu)));
+    const float n0 = __half2float(__ushort_as_half((unsigned short)(hx0 >> 16))), n1 = __half2float(__ushort_as_half((unsigned short)(hx1 >> 16)));
+    const float m0 = (float)m[0], m1 = (float)m[1], m2 = (float)m[2], m3 = (float)m[3];
+    yA0 = fmaf(d0 * xsA, fmaf(cwA1, f[1], cwA0 * f[0]), yA0);
+    yA0 = fmaf(-n0 * sxsA, fmaf(cwA1, m1, cwA0 * m0), yA0);
+    yB0 = fmaf(d0 * xsB, fmaf(cwB1, f[1], cwB0 * f[0]), yB0);
+    yB0 = fmaf(-n0 * sxsB, fmaf(cwB1, m1, cwB0 * m0), yB0);
+    yA1 = fmaf(d1 * xsA, fmaf(cwA1, f[3], cwA0 * f[2]), yA1);
+    yA1 = fmaf(-n1 * sxsA, fmaf(cwA1, m3, cwA0 * m2), yA1);
+    yB1 = fmaf(d1 * xsB, fmaf(cwB1, f[3], cwB0 * f[2]), yB1);
+    yB1 = fmaf(-n1 * sxsB, fmaf(cwB1, m3, cwB0 * m2), yB1);
 }
 
 template <int FMT>
@@ -342,15 +405,19 @@ __device__ __forceinline__ uint32_t plane_word(uint32_t u0, uint32_t u1, uint32_
 // Q6 form: instead of the float sums, the sums of the signed digits over every 16 elements, as two balanced bytes:
 // at +768 [plane p][low / high byte][16 groups].
 // With `slots` set x is a gathered vector read from its {value, tag} slots (polled for `tag`); false = a poll expired.
-template <int NP, bool Q6>
+// NTOK = 2: vector `b` (0 or 1) of two, into its columns of the wider layout (see mma_xq_sb).
+template <int NP, bool Q6, int NTOK = 1>
 __device__ __forceinline__ bool quantize_x_mma(const float *__restrict__ x, uint32_t units, uint8_t *xq, uint32_t warp, uint32_t lane,
-                                               uint32_t nwarps, const uint2 *slots = nullptr, unsigned int tag = 0)
+                                               uint32_t nwarps, const uint2 *slots = nullptr, unsigned int tag = 0, uint32_t b_tok = 0)
 {
+    static_assert(NTOK == 1 || !Q6, "two vectors at once: Q4_K / Q5_K only");
+    constexpr uint32_t XQSB = mma_xq_sb<NP, NTOK>(), JS = mma_xq_js<NP, NTOK>(), SUMS = mma_xq_sums<NP, NTOK>();
+    const uint32_t col0 = NTOK == 1 ? 0u : b_tok * NP;
     bool ok = true;
     constexpr int QMAXI = NP == 3 ? 127 * 65536 + 127 * 256 + 127 : 127 * 256 + 127;
     constexpr float QMAX = (float)QMAXI;
     constexpr int XB = 4;
-    float *xs = reinterpret_cast<float *>(xq + (size_t)units * MMA_XQ_SB), *sxs = xs + units;
+    float *xs = reinterpret_cast<float *>(xq + (size_t)units * XQSB), *sxs = xs + units * NTOK;
     for (uint32_t ub = warp; ub < units; ub += nwarps * XB) {
         float4 v0[XB], v1[XB];
 #pragma unroll
@@ -400,11 +467,11 @@ __device__ __forceinline__ bool quantize_x_mma(const float *__restrict__ x, uint
             uint32_t uq[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) uq[i] = (uint32_t)max(-QMAXI, min(QMAXI, __float2int_rn(v[i] * inv))) + digit_bias<NP>();
-            uint8_t *sb = xq + (size_t)u * MMA_XQ_SB;
+            uint8_t *sb = xq + (size_t)u * XQSB;
 #pragma unroll
             for (int p = 0; p < NP; ++p) {
                 const uint2 pw = make_uint2(plane_word(uq[0], uq[1], uq[2], uq[3], p), plane_word(uq[4], uq[5], uq[6], uq[7], p));
-                *reinterpret_cast<uint2 *>(sb + (lane >> 2) * 96 + p * 32 + (lane & 3u) * 8) = pw;
+                *reinterpret_cast<uint2 *>(sb + (lane >> 2) * JS + (col0 + p) * 32 + (lane & 3u) * 8) = pw;
                 if constexpr (Q6) {
                     int sd = __dp4a((int)pw.x, 0x01010101, __dp4a((int)pw.y, 0x01010101, 0));
                     sd += __shfl_xor_sync(0xffffffffu, sd, 1);                    // 16 elements = two lanes
@@ -419,10 +486,10 @@ __device__ __forceinline__ bool quantize_x_mma(const float *__restrict__ x, uint
                 const uint32_t us = (uint32_t)max(-QMAXI, min(QMAXI, __float2int_rn(sum[b] * sinv))) + digit_bias<NP>();
                 if ((lane & 3u) == 0) {
 #pragma unroll
-                    for (int p = 0; p < NP; ++p) sb[768 + p * 8 + (lane >> 2)] = (uint8_t)(((us >> (8 * p)) & 255u) ^ 0x80u);
+                    for (int p = 0; p < NP; ++p) sb[SUMS + (col0 + p) * 8 + (lane >> 2)] = (uint8_t)(((us >> (8 * p)) & 255u) ^ 0x80u);
                 }
             }
-            if (lane == 0) { xs[u] = amax[b] / QMAX; sxs[u] = smax[b] / QMAX; }
+            if (lane == 0) { xs[u * NTOK + (NTOK == 1 ? 0u : b_tok)] = amax[b] / QMAX; sxs[u * NTOK + (NTOK == 1 ? 0u : b_tok)] = smax[b] / QMAX; }
         }
     }
     return ok;
@@ -465,11 +532,14 @@ __device__ __forceinline__ bool mma_next_tile(const MmaArgs &a, uint32_t &cur, u
     return true;
 }
 
-template <int FMT, int NP, bool SWIGLU, bool EXT, int MOE = 0>
+template <int FMT, int NP, bool SWIGLU, bool EXT, int MOE = 0, int NTOK = 1>
 __global__ void __launch_bounds__(MMA_MAX_THREADS, 1)
 gemv_mma_kernel(const __grid_constant__ MmaArgs a)
 {
     static_assert(MOE == 0 || (FMT != FMT_Q6_K && !EXT), "the MoE forms are built for Q4_K / Q5_K on one GPU");
+    static_assert(NTOK == 1 || (NTOK == 2 && FMT != FMT_Q6_K && !SWIGLU && !EXT && MOE == 0), "two vectors at once: plain Q4_K / Q5_K products on one GPU");
+    constexpr bool TWO = NTOK == 2;
+    constexpr uint32_t XQSB = mma_xq_sb<NP, NTOK>(), XJS = mma_xq_js<NP, NTOK>(), XSUMS = mma_xq_sums<NP, NTOK>();
     static_assert(MOE != 1 || SWIGLU, "MOE 1 is the fused gate/up form");
     static_assert(MOE != 2 || !SWIGLU, "MOE 2 is the down + combine form");
     __shared__ uint32_t s_expert[PIPE_MAX_SEG];
@@ -606,10 +676,11 @@ gemv_mma_kernel(const __grid_constant__ MmaArgs a)
     {
         const uint2 *slots = EXT ? a.x_ll : nullptr;
         const unsigned int want = EXT && a.x_ll ? *reinterpret_cast<const volatile unsigned int *>(a.wait_gen) : 0u;
-        if (!quantize_x_mma<NP, Q6>(a.x + (MOE != 0 ? (size_t)blockIdx.y * a.tok_x_stride : 0), U, xq, warp, lane, CW, slots, want)) {
+        if (!quantize_x_mma<NP, Q6, NTOK>(a.x + (MOE != 0 ? (size_t)blockIdx.y * a.tok_x_stride : 0), U, xq, warp, lane, CW, slots, want, 0u)) {
             s_abort = 1;
             atomicExch(a.status, 3);
         }
+        if constexpr (TWO) quantize_x_mma<NP, Q6, NTOK>(a.x + a.tok_x_stride, U, xq, warp, lane, CW, nullptr, 0u, 1u);
     }
     const unsigned int pub_tag = EXT && a.npeers > 0 ? *reinterpret_cast<const volatile unsigned int *>(a.pub_gen) + 1u : 0u;
     if constexpr (Q6) {   // a block of zeros for lanes whose product column is empty
@@ -626,12 +697,19 @@ gemv_mma_kernel(const __grid_constant__ MmaArgs a)
         named_bar_sync(PIPE_BAR_CONSUMERS, (int)C);
     }
     if (tid == 0) stamp(a.trace, 3);
-    const uint32_t xs_s = smem_u32(xq) + U * MMA_XQ_SB;                // xs[U], then sxs[U]
-    const uint32_t plane = g < (uint32_t)NP ? g : 0u;                  // columns past the planes repeat plane 0 and are weighted 0
+    const uint32_t xs_s = smem_u32(xq) + U * XQSB;                     // xs[U * NTOK], then sxs[U * NTOK]
+    const uint32_t plane = g < (uint32_t)(NP * NTOK) ? g : 0u;         // columns past the planes repeat column 0 and are weighted 0
     const uint32_t xq_s = smem_u32(xq) + plane * 32u + t4 * 8u;       // this thread's x bytes of sub-block 0, superblock 0
-    const uint32_t sx_s = smem_u32(xq) + 768u + plane * 8u + (t4 & 1u) * 4u;
+    const uint32_t sx_s = smem_u32(xq) + XSUMS + plane * 8u + (t4 & 1u) * 4u;
     // columns 2t, 2t+1 of the products are byte planes 2t, 2t+1
     const float cw0 = t4 == 0 ? 1.0f : (t4 == 1 && NP == 3 ? 65536.0f : 0.0f), cw1 = t4 == 0 ? 256.0f : 0.0f;
+    // two vectors: column c is plane c % NP of vector c / NP; this thread's columns 2t, 2t+1 count for vector A and / or B
+    auto col_w = [](uint32_t c, uint32_t vec) {
+        const uint32_t pl = c % NP;
+        const float w = pl == 0 ? 1.0f : (pl == 1 ? 256.0f : 65536.0f);
+        return c < (uint32_t)(2 * NP) && c / NP == vec ? w : 0.0f;
+    };
+    const float cwA0 = col_w(2 * t4, 0), cwA1 = col_w(2 * t4 + 1, 0), cwB0 = col_w(2 * t4, 1), cwB1 = col_w(2 * t4 + 1, 1);
 
     // Q6_K: column g = (first / second 16 elements of a group, plane g % 3); lanes of unused columns read a block of zeros
     const uint32_t q6_plane = g % 3u;
@@ -646,16 +724,17 @@ gemv_mma_kernel(const __grid_constant__ MmaArgs a)
     int buf_seg = 0;
     auto flush = [&]() {
         named_bar_sync(PIPE_BAR_CONSUMERS, (int)C);
-        const float *src = red + (size_t)which * PLANE * (SWIGLU ? 2 : 1);
+        const float *src = red + (size_t)which * PLANE * (SWIGLU || TWO ? 2 : 1);
         float *y = a.seg[buf_seg].y + buf_row0 + (MOE != 0 ? (size_t)blockIdx.y * a.tok_y_stride : 0);
         for (uint32_t r = tid; r < buf_n; r += C) {
             float gsum = 0.0f, usum = 0.0f;
             for (uint32_t w = 0; w < SLOTS; ++w) {
                 gsum += src[r * SLOTS + w];
-                if constexpr (SWIGLU) usum += src[PLANE + r * SLOTS + w];
+                if constexpr (SWIGLU || TWO) usum += src[PLANE + r * SLOTS + w];
             }
             const float val = SWIGLU ? silu_mul(gsum, usum) : gsum;
             y[r] = val;
+            if constexpr (TWO) y[a.tok_y_stride + r] = usum;      // the second vector's product
             if constexpr (EXT) {
                 if (a.npeers > 0) {
                     uint8_t *slot = a.ll_origin + 2 * (reinterpret_cast<const uint8_t *>(y + r) - a.arena_base);
@@ -711,14 +790,20 @@ gemv_mma_kernel(const __grid_constant__ MmaArgs a)
                 for (uint32_t u = wig; u < kn; u += NW) {
                     const uint32_t ug = u0 + u;
                     uint2 B[8];
-                    const uint32_t xa = xq_s + ug * MMA_XQ_SB;
-                    B[0] = lds64<0>(xa);   B[1] = lds64<96>(xa);  B[2] = lds64<192>(xa); B[3] = lds64<288>(xa);
-                    B[4] = lds64<384>(xa); B[5] = lds64<480>(xa); B[6] = lds64<576>(xa); B[7] = lds64<672>(xa);
-                    const float xsu = __uint_as_float(lds32<0>(xs_s + 4u * ug)), sxsu = __uint_as_float(lds32<0>(xs_s + 4u * (U + ug)));
+                    const uint32_t xa = xq_s + ug * XQSB;
+                    B[0] = lds64<0>(xa);       B[1] = lds64<XJS>(xa);     B[2] = lds64<2 * XJS>(xa); B[3] = lds64<3 * XJS>(xa);
+                    B[4] = lds64<4 * XJS>(xa); B[5] = lds64<5 * XJS>(xa); B[6] = lds64<6 * XJS>(xa); B[7] = lds64<7 * XJS>(xa);
                     const uint32_t h0 = row_s + u * UNIT, h1 = h0 + 8u * a.pitch;
-                    mma_superblock<FMT>(h0, h1, t4, B, sx_s + ug * MMA_XQ_SB, xsu, sxsu, cw0, cw1, a.layout, yg0, yg1);
-                    if constexpr (SWIGLU)
-                        mma_superblock<FMT>(h0 + a.half_stride, h1 + a.half_stride, t4, B, sx_s + ug * MMA_XQ_SB, xsu, sxsu, cw0, cw1, a.layout, yu0, yu1);
+                    if constexpr (TWO) {
+                        const float xsA = __uint_as_float(lds32<0>(xs_s + 8u * ug)), xsB = __uint_as_float(lds32<4>(xs_s + 8u * ug));
+                        const float sxsA = __uint_as_float(lds32<0>(xs_s + 8u * (U + ug))), sxsB = __uint_as_float(lds32<4>(xs_s + 8u * (U + ug)));
+                        mma_superblock2<FMT>(h0, h1, t4, B, sx_s + ug * XQSB, xsA, sxsA, xsB, sxsB, cwA0, cwA1, cwB0, cwB1, a.layout, yg0, yg1, yu0, yu1);
+                    } else {
+                        const float xsu = __uint_as_float(lds32<0>(xs_s + 4u * ug)), sxsu = __uint_as_float(lds32<0>(xs_s + 4u * (U + ug)));
+                        mma_superblock<FMT>(h0, h1, t4, B, sx_s + ug * XQSB, xsu, sxsu, cw0, cw1, a.layout, yg0, yg1);
+                        if constexpr (SWIGLU)
+                            mma_superblock<FMT>(h0 + a.half_stride, h1 + a.half_stride, t4, B, sx_s + ug * XQSB, xsu, sxsu, cw0, cw1, a.layout, yu0, yu1);
+                    }
                 }
             }
             __syncwarp();
@@ -729,14 +814,14 @@ gemv_mma_kernel(const __grid_constant__ MmaArgs a)
         // add the byte planes (quad) and leave this warp's share of rows g, g+8 for the flush
         yg0 += __shfl_xor_sync(0xffffffffu, yg0, 1); yg1 += __shfl_xor_sync(0xffffffffu, yg1, 1);
         yg0 += __shfl_xor_sync(0xffffffffu, yg0, 2); yg1 += __shfl_xor_sync(0xffffffffu, yg1, 2);
-        if constexpr (SWIGLU) {
+        if constexpr (SWIGLU || TWO) {
             yu0 += __shfl_xor_sync(0xffffffffu, yu0, 1); yu1 += __shfl_xor_sync(0xffffffffu, yu1, 1);
             yu0 += __shfl_xor_sync(0xffffffffu, yu0, 2); yu1 += __shfl_xor_sync(0xffffffffu, yu1, 2);
         }
         if (t4 == 0) {
-            float *dst = red + (size_t)which * PLANE * (SWIGLU ? 2 : 1) + (size_t)buf_n * SLOTS + warp;
-            if (g < t.n) { dst[g * SLOTS] = yg0; if constexpr (SWIGLU) dst[PLANE + g * SLOTS] = yu0; }
-            if (g + 8 < t.n) { dst[(g + 8) * SLOTS] = yg1; if constexpr (SWIGLU) dst[PLANE + (g + 8) * SLOTS] = yu1; }
+            float *dst = red + (size_t)which * PLANE * (SWIGLU || TWO ? 2 : 1) + (size_t)buf_n * SLOTS + warp;
+            if (g < t.n) { dst[g * SLOTS] = yg0; if constexpr (SWIGLU || TWO) dst[PLANE + g * SLOTS] = yu0; }
+            if (g + 8 < t.n) { dst[(g + 8) * SLOTS] = yg1; if constexpr (SWIGLU || TWO) dst[PLANE + (g + 8) * SLOTS] = yu1; }
         }
         buf_n += t.n;
         MMA_TILE_STAMP(a, tile_no, warp, 2);

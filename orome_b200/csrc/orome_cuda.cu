@@ -585,7 +585,9 @@ static bool mma_supported(const orome_cuda_ctx *c, int fmt, uint32_t in_dim, boo
 // nvec > 1: the combine form of the MoE down projection -- a row is the sum over nvec experts of a product with that
 // expert's own input vector (in_dim wide each, one behind the other); a stage then holds one expert's whole rows.
 // grid_cap > 0 (MoE forms): at most that many CTAs, each with the same whole number of row tiles where that divides.
-static int plan_mma(orome_cuda_ctx *c, int fmt, uint32_t in_dim, uint32_t total_rows, bool swiglu, MmaPlan &p, uint32_t nvec = 0, uint32_t grid_cap = 0)
+// two: the form that multiplies two input vectors at once (plain Q4_K / Q5_K): wider quantized x, two result planes.
+static int plan_mma(orome_cuda_ctx *c, int fmt, uint32_t in_dim, uint32_t total_rows, bool swiglu, MmaPlan &p, uint32_t nvec = 0, uint32_t grid_cap = 0,
+                    bool two = false)
 {
     MmaArgs &a = p.args;
     const uint32_t unit = fmt == FMT_Q4_K ? 144u : fmt == FMT_Q5_K ? 176u : 210u;
@@ -631,9 +633,10 @@ static int plan_mma(orome_cuda_ctx *c, int fmt, uint32_t in_dim, uint32_t total_
     a.stage_stride = a.half_stride * (swiglu ? 2 : 1);
     a.red_base = 2 * 8 * PIPE_MAX_STAGES;
     a.red_rows = std::max<uint32_t>(MMA_TILE_ROWS, std::min<uint32_t>((share + MMA_TILE_ROWS - 1) / MMA_TILE_ROWS * MMA_TILE_ROWS, 128u));
-    const size_t red_bytes = (size_t)2 * a.red_rows * a.nwarps * a.ngroups * (swiglu ? 2 : 1) * sizeof(float);
+    const size_t red_bytes = (size_t)2 * a.red_rows * a.nwarps * a.ngroups * (swiglu || two ? 2 : 1) * sizeof(float);
     a.xs_base = (uint32_t)((a.red_base + red_bytes + 127) / 128 * 128);
-    const size_t xq_bytes = (size_t)a.units * MMA_XQ_SB + (size_t)a.units * 8 + 768;   // planes and sums, two scales per superblock, a block of zeros
+    const size_t xq_sb = !two ? MMA_XQ_SB : (c->x_bits == 24 ? mma_xq_sb<3, 2>() : mma_xq_sb<2, 2>());
+    const size_t xq_bytes = (size_t)a.units * xq_sb + (size_t)a.units * 8 * (two ? 2 : 1) + 768;   // planes and sums, two scales per superblock and vector, a block of zeros
     a.stage_base = (uint32_t)((a.xs_base + xq_bytes + 127) / 128 * 128);
     const size_t budget = std::min<size_t>(228 * 1024 - 1024 - 256, (size_t)c->smem_optin - 256);
     if (budget < a.stage_base + a.stage_stride) return fail(OROME_ENOTSUP, "mma plan: in_dim %u does not fit shared memory", in_dim);
@@ -690,10 +693,10 @@ static int mma_encode_maps(orome_cuda_ctx *c, int fmt, MmaPlan &p, bool swiglu)
     return OROME_OK;
 }
 
-template <int FMT, int NP, bool SWIGLU, bool EXT, int MOE = 0>
+template <int FMT, int NP, bool SWIGLU, bool EXT, int MOE = 0, int NTOK = 1>
 static int launch_mma_ext(orome_cuda_ctx *c, const MmaPlan &p, cudaStream_t st)
 {
-    auto kern = gemv_mma_kernel<FMT, NP, SWIGLU, EXT, MOE>;
+    auto kern = gemv_mma_kernel<FMT, NP, SWIGLU, EXT, MOE, NTOK>;
     static size_t configured[64] = {0};   // per device: dynamic shared memory opted in so far
     if (configured[c->device] < p.smem) {
         cudaFuncAttributes fa;
@@ -716,6 +719,16 @@ static int launch_mma_ext(orome_cuda_ctx *c, const MmaPlan &p, cudaStream_t st)
     CU(cudaLaunchKernelEx(&cfg, kern, p.args));
     ++c->launches;
     return OROME_OK;
+}
+
+// Two input vectors in one pass over the weights (plain Q4_K / Q5_K): x at the context's width.
+static int launch_mma_two(orome_cuda_ctx *c, int fmt, MmaPlan &p, cudaStream_t st)
+{
+    int rc = mma_encode_maps(c, fmt, p, false);
+    if (rc) return rc;
+    const bool b24 = c->x_bits == 24;
+    if (fmt == FMT_Q4_K) return b24 ? launch_mma_ext<FMT_Q4_K, 3, false, false, 0, 2>(c, p, st) : launch_mma_ext<FMT_Q4_K, 2, false, false, 0, 2>(c, p, st);
+    return b24 ? launch_mma_ext<FMT_Q5_K, 3, false, false, 0, 2>(c, p, st) : launch_mma_ext<FMT_Q5_K, 2, false, false, 0, 2>(c, p, st);
 }
 
 // The MoE forms of the mma kernel (Q4_K / Q5_K): fused gate/up over device-chosen experts, down + weighted combine.
@@ -1215,7 +1228,27 @@ extern "C" int orome_cuda_matvec(orome_cuda_ctx *c, const OromeTensorRef *ref, c
     // kernel below needs ~190 us per vector for a 12288 x 4096 tensor (measured: batch 8 in 1.5 ms).
     if (!c->force_generic && x_ok && (int)ref->format <= FMT_Q8_0 && c->g_world == 1 &&
         (orome_pipe_supported((int)ref->format, ref->in_dim) || mma_supported(c, (int)ref->format, ref->in_dim, false))) {
-        for (int b = 0; b < batch; ++b) {
+        // Q4_K / Q5_K: two vectors per launch in the mma kernel (the second one's byte planes ride in columns of the B
+        // operand that a single vector leaves empty), so a batch of two or three reads the weights once or twice
+        const int fmt = (int)ref->format;
+        const bool pairs = (fmt == FMT_Q4_K || fmt == FMT_Q5_K) && mma_supported(c, fmt, ref->in_dim, false) && !(reinterpret_cast<uintptr_t>(data) & 15);
+        int b = 0;
+        for (; pairs && b + 1 < batch; b += 2) {
+            MmaPlan m;
+            memset(&m, 0, sizeof m);
+            m.args.seg[0] = PipeSeg{data, nullptr, y_dev + (size_t)b * ldy, ref->out_dim, 0};
+            m.args.nseg = 1;
+            m.args.x = x_dev + (size_t)b * ldx;
+            m.args.layout = (int)ref->variant;
+            rc = plan_mma(c, fmt, ref->in_dim, ref->out_dim, false, m, 0, 0, true);
+            if (rc == OROME_ENOTSUP) break;      // too wide for the two-vector layout: one vector per launch
+            if (rc) return rc;
+            m.args.tok_x_stride = (uint32_t)ldx;
+            m.args.tok_y_stride = (uint32_t)ldy;
+            rc = launch_mma_two(c, fmt, m, static_cast<cudaStream_t>(stream));
+            if (rc) return rc;
+        }
+        for (; b < batch; ++b) {
             float *ys[1] = {y_dev + (size_t)b * ldy};
             rc = orome_cuda_matvec_group(c, ref, 1, x_dev + (size_t)b * ldx, ys, stream);
             if (rc) return rc;

@@ -249,6 +249,29 @@ def test_batched_matvec(env, fmt, batch):
     assert y.shape == want.shape and rel_l2(y, want) <= (TC_REL_L2_TOL if on_tensor_cores else REL_L2_TOL)
 
 
+@pytest.mark.parametrize("fmt", [synth.Q4_K, synth.Q5_K])
+@pytest.mark.parametrize("shape", [(300, 4096), (70, 1024), (1000, 12288), (35, 256), (2100, 5120)])
+def test_two_vectors_per_launch(env, fmt, shape):
+    """Batches of two and three on Q4_K / Q5_K: the mma kernel multiplies two input vectors in one pass over the weights
+    (one launch for two vectors, two for three), at both x widths and both scale layouts, inside the fp32-activation bound."""
+    torch, F, ctx = env
+    out_dim, in_dim = shape
+    data = synth.host_tensor(fmt, out_dim, in_dim, seed=synth.seed_for("two", fmt, *shape))
+    try:
+        for bits in (24, 16):
+            ctx.set_option(F.OPT_X_BITS, bits)
+            for batch, variant in ((2, 0), (3, 1)):
+                x = synth.host_x(in_dim, batch, seed=31 + batch)
+                before = ctx.launch_count
+                y = gpu_matvec(env, fmt, data, out_dim, in_dim, x, variant)
+                assert ctx.launch_count - before == (batch + 1) // 2
+                want = oracle.matvec_f64(fmt, data, out_dim, in_dim, x, layout=variant)
+                col = np.linalg.norm(y - want, axis=1) / np.linalg.norm(want, axis=1)
+                assert col.max() <= REL_L2_TOL, (fmt, shape, bits, batch, col)
+    finally:
+        ctx.set_option(F.OPT_X_BITS, 24)
+
+
 @pytest.mark.parametrize("fmt", QUANT)
 @pytest.mark.parametrize("shape", [(300, 4096, 64), (128, 1024, 33), (1000, 2048, 16), (257, 12288, 48), (96, 512, 100), (131, 1280, 9)])
 def test_prefill_gemm_on_tensor_cores(env, fmt, shape):
