@@ -156,7 +156,8 @@ int  orome_format_dispatch_matvec(orome_cuda_ctx *ctx, const OromeTensorRef *ref
  * cores (tcgen05) with weights and x rounded to fp16 and fp32 accumulation: rel-L2 <= 5e-4
  * against an exact evaluation, the class of rounding the reference's own kernels apply to x
  * (shaders.metal:1470).  The first such call allocates scratch inside the context: make it
- * before any stream capture.  Smaller batches keep fp32 activations (rel-L2 <= 1e-4).
+ * before any stream capture.  Smaller batches keep fp32 activations (rel-L2 <= 1e-4): one decode
+ * launch per vector, or, on Q4_K / Q5_K, one per pair of vectors (the weights are read once per pair).
  * Range of the fp16 operands: a weight is formed as (q - bias) * half(d * sc) + half(-dmin * mn),
  * so |d * sc| and |dmin * mn| (Q8_0: |d|; Q6_K: |d * sc| only) must stay below 65504 and lose precision below 6e-5;
  * GGUF scales of real models are orders of magnitude inside that range, and x is expected within
