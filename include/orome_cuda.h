@@ -180,7 +180,10 @@ int  orome_cuda_matvec_group(orome_cuda_ctx *ctx, const OromeTensorRef *refs, in
 /* Fused gate/up + SwiGLU: out[b][r] = silu(Wg x_b)[r] * (Wu x_b)[r], silu(g) = g / (1 + exp(-g)).
  * Replaces shared_gate_up_swiglu_q4k / _q8_0 and fused_gate_up_swiglu_q4k_llama
  * (shaders.metal:2316-2445, 2451-2584) as dispatched by encode_dense_ffn
- * (engine.m:342-392).  gate and up must have identical shape and format. */
+ * (engine.m:342-392).  gate and up must have identical shape and format.
+ * batch > 1 is two batched products (orome_cuda_matvec: its dispatch, scratch and precision class;
+ * from OROME_OPT_TC_MIN_BATCH vectors on that is the fp16 tensor-core form) and an elementwise pass,
+ * the reference's unfused branch (engine.m:388-404). */
 int  orome_cuda_gate_up_swiglu(orome_cuda_ctx *ctx, const OromeTensorRef *gate, const OromeTensorRef *up,
                                const float *x_dev, float *out_dev, int batch, int ldx, int ldo, void *stream);
 

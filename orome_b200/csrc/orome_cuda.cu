@@ -1345,10 +1345,18 @@ extern "C" int orome_cuda_gate_up_swiglu(orome_cuda_ctx *c, const OromeTensorRef
     rc = ensure(&c->gu_dev, &c->gu_cap, 2 * n * batch);
     if (rc) return rc;
     float *g = c->gu_dev, *u = c->gu_dev + n * batch;
-    rc = launch_generic(c, fmt, gd, gate->out_dim, gate->in_dim, layout, x_dev, batch, ldx, g, (int)n, st);
-    if (rc) return rc;
-    rc = launch_generic(c, fmt, ud, up->out_dim, up->in_dim, layout, x_dev, batch, ldx, u, (int)n, st);
-    if (rc) return rc;
+    if (batch > 1) {
+        // the batched product's own dispatch: tensor cores from OROME_OPT_TC_MIN_BATCH vectors on, decode launches below
+        rc = orome_cuda_matvec(c, gate, x_dev, g, batch, ldx, (int)n, stream);
+        if (rc) return rc;
+        rc = orome_cuda_matvec(c, up, x_dev, u, batch, ldx, (int)n, stream);
+        if (rc) return rc;
+    } else {
+        rc = launch_generic(c, fmt, gd, gate->out_dim, gate->in_dim, layout, x_dev, batch, ldx, g, (int)n, st);
+        if (rc) return rc;
+        rc = launch_generic(c, fmt, ud, up->out_dim, up->in_dim, layout, x_dev, batch, ldx, u, (int)n, st);
+        if (rc) return rc;
+    }
     size_t tot = n * batch;
     swiglu_kernel<<<(unsigned)((tot + 255) / 256), 256, 0, st>>>(g, u, out_dev, (uint32_t)n, batch, (int)n, batch == 1 ? (int)n : ldo);
     return post_launch(c, "swiglu");

@@ -381,6 +381,25 @@ def test_matvec_group_and_fused_gate_up_many_rows(env, fmt):
 
 
 @pytest.mark.parametrize("fmt", [synth.Q8_0, synth.Q4_K, synth.Q6_K])
+def test_gate_up_swiglu_prefill_batch(env, fmt):
+    """A batch of nine: the two products run on the tensor cores (fp16 operands), the output is a product of the two
+    results, so the bound is twice the tensor-core form's."""
+    torch, F, ctx = env
+    out_dim, in_dim, batch = 300, 2048, 9
+    gd = synth.host_tensor(fmt, out_dim, in_dim, seed=41)
+    ud = synth.host_tensor(fmt, out_dim, in_dim, seed=42)
+    xm = synth.host_x(in_dim, batch, seed=43)
+    gt, ut, xt = dev_bytes(torch, gd), dev_bytes(torch, ud), dev_bytes(torch, xm)
+    out = torch.full((batch, out_dim), float("nan"), device="cuda")
+    before = ctx.launch_count
+    ctx.gate_up_swiglu(make_ref(F, gt, fmt, out_dim, in_dim), make_ref(F, ut, fmt, out_dim, in_dim), xt.data_ptr(), out.data_ptr(), batch, in_dim, out_dim)
+    torch.cuda.synchronize()
+    assert ctx.launch_count - before >= 4                          # pack + tensor-core kernel, twice (the elementwise pass is not counted)
+    want = oracle.swiglu_f64(oracle.matvec_f64(fmt, gd, out_dim, in_dim, xm), oracle.matvec_f64(fmt, ud, out_dim, in_dim, xm))
+    assert rel_l2(out.cpu().numpy(), want) <= 2 * TC_REL_L2_TOL
+
+
+@pytest.mark.parametrize("fmt", [synth.Q8_0, synth.Q4_K, synth.Q6_K])
 @pytest.mark.parametrize("batch", [1, 3])
 def test_gate_up_swiglu(env, fmt, batch):
     torch, F, ctx = env
