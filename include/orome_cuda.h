@@ -444,7 +444,7 @@ int  orome_cuda_matvec_host(orome_cuda_ctx *ctx, const OromeTensorRef *ref,
 #define OROME_OPT_CTAS_PER_SM    4
 #define OROME_OPT_PDL            5
 #define OROME_OPT_GRID_PER_SM    6
-#define OROME_OPT_PREFETCH_MB     7   /* cap on the L2 prefetch of orome_cuda_hint_next, MiB (0 = off) */
+#define OROME_OPT_PREFETCH_MB     7   /* cap on the L2 prefetch of orome_cuda_hint_next, MiB (default 8; 0 = off) */
 #define OROME_OPT_TC_MIN_BATCH    8   /* batches from this size on use the tensor-core kernel (default 4); smaller ones run one decode launch per vector */
 #define OROME_OPT_KQUANT_MMA      9   /* 1 (default): Q4_K / Q5_K batch-1 products run on the mma.sync kernel; 0: on the dp4a kernel */
 #define OROME_OPT_CHAIN_INFLIGHT 11   /* stages a chain's weight stream keeps outstanding at most (0, default: what fits 136 KiB, two at least; at most the ring); read at chain_end */

@@ -33,7 +33,8 @@ struct orome_cuda_ctx {
     int ctas_per_sm = 1;     // CTAs an SM is sized to hold (1 or 2); measured best with one large CTA
     int grid_per_sm = 1;     // CTAs per SM a launch creates; 1 with ctas_per_sm 2 leaves room for the next kernel's CTA
     int pdl = 1;
-    int prefetch_mb = 24;    // at most this many MiB of the next tensor are pulled into L2 by the current launch
+    int prefetch_mb = 8;     // at most this many MiB of the next tensor are pulled into L2 by the current launch (measured on the 9B set
+                             // once x is requested before the weights: 3 MiB 655, 6 658.6, 8 656.5, 12 657, 24 649-650, 40 649 tok/s; 27B set 217.6 at 8, 213-216 at 24)
     const uint8_t *hint_ptr = nullptr;   // set by orome_cuda_hint_next, consumed by the next pipelined launch
     uint64_t hint_bytes = 0;
     // multi-GPU gather state (orome_cuda_gather_setup)
